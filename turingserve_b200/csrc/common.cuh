@@ -1,0 +1,75 @@
+// Shared helpers for the sm_100a kernels: storage types, conversions, reductions, the C ABI.
+//
+// Every entry point is `extern "C" int ts_<name>(..., void* stream)`.  It returns 0 on success,
+// a positive cudaError_t when the launch failed, or a negative code when the arguments were
+// refused (ts_last_error() then holds the reason).  Nothing here allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TS_API extern "C" __attribute__((visibility("default")))
+
+enum TsDtype : int { TS_F32 = 0, TS_BF16 = 1 };
+
+// Argument refusals (negative return codes).
+enum TsError : int {
+  TS_ERR_DTYPE = -1,
+  TS_ERR_SHAPE = -2,
+  TS_ERR_ALIGN = -3,
+  TS_ERR_UNSUPPORTED = -4,
+  TS_ERR_LIMIT = -5,
+};
+
+void ts_set_error(const char* fmt, ...);
+
+#define TS_REFUSE(code, ...)   \
+  do {                         \
+    ts_set_error(__VA_ARGS__); \
+    return (code);             \
+  } while (0)
+
+#define TS_LAUNCH_CHECK()                                          \
+  do {                                                             \
+    cudaError_t e__ = cudaGetLastError();                          \
+    if (e__ != cudaSuccess) {                                      \
+      ts_set_error("%s: %s", __func__, cudaGetErrorString(e__));   \
+      return (int)e__;                                             \
+    }                                                              \
+    return 0;                                                      \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+// Round a 32-bit value to the storage type and back (the model-dtype rounding points).
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f(from_f<T>(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `scratch` holds at least 32 floats.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -1,0 +1,213 @@
+// Row-wise and element-wise kernels: embedding gather, (residual +) RMSNorm, SiLU*mul,
+// rotary encoding fused with the key/value cache write, row gather.
+//
+// Numerics follow the reference's op twins (turingserve/ops/reference.py:13-57) with the
+// model-dtype rounding points of its Triton kernels (turingserve/ops/triton_rmsnorm.py:10-27,
+// triton_silu_mul.py:10-18, triton_rope.py:10-24, triton_kv_write.py:10-25): statistics, the
+// rotation and the activation are computed in 32-bit and rounded once.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// Embedding: out[t, :] = table[ids[t], :]   (turingserve/model/qwen2.py:41)
+template <typename T>
+__global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
+                                 const int* __restrict__ ids, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const T* src = table + (size_t)id * hidden;
+  T* dst = out + (size_t)t * hidden;
+  const int bytes = hidden * (int)sizeof(T);
+  if ((bytes & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+TS_API int ts_embedding(void* out, const void* table, const int* ids, int T, int hidden, int vocab,
+                        int dtype, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    embedding_kernel<float><<<T, 128, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab);
+  else if (dtype == TS_BF16)
+    embedding_kernel<bf16><<<T, 128, 0, s>>>((bf16*)out, (const bf16*)table, ids, hidden, vocab);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_embedding: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// Row gather: out[s, :] = x[rows[s], :]
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                   const int* __restrict__ rows, int width) {
+  const T* src = x + (size_t)rows[blockIdx.x] * width;
+  T* dst = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+TS_API int ts_gather_rows(void* out, const void* x, const int* rows, int S, int width, int dtype,
+                          void* stream) {
+  if (S <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    gather_rows_kernel<float><<<S, 256, 0, s>>>((float*)out, (const float*)x, rows, width);
+  else if (dtype == TS_BF16)
+    gather_rows_kernel<bf16><<<S, 256, 0, s>>>((bf16*)out, (const bf16*)x, rows, width);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_gather_rows: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm, optionally with the residual add in front:
+//   r = x (+ residual, rounded to T and stored back);  y = w * T(r32 * rsqrt(mean(r32^2) + eps))
+// (turingserve/ops/reference.py:13-23).  One block per row; the row is read twice, the second
+// time from cache.  WT is the scale's type: T, or float when the checkpoint stores it in 32-bit.
+template <typename T, typename WT>
+__global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* residual,
+                               const WT* __restrict__ w, float eps, int hidden) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_f(x[base + i]);
+    if (residual != nullptr) {
+      v = round_to<T>(v + to_f(residual[base + i]));
+      residual[base + i] = from_f<T>(v);
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  const T* src = residual != nullptr ? residual : x;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float y = round_to<T>(to_f(src[base + i]) * rstd);
+    out[base + i] = from_f<T>(to_f(w[i]) * y);
+  }
+}
+
+TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, float eps, int T,
+                      int hidden, int dtype, int w_dtype, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (dtype == TS_F32 && w_dtype == TS_F32)
+    rmsnorm_kernel<float, float><<<T, threads, 0, s>>>((float*)out, (const float*)x, (float*)residual,
+                                                       (const float*)w, eps, hidden);
+  else if (dtype == TS_BF16 && w_dtype == TS_BF16)
+    rmsnorm_kernel<bf16, bf16><<<T, threads, 0, s>>>((bf16*)out, (const bf16*)x, (bf16*)residual,
+                                                     (const bf16*)w, eps, hidden);
+  else if (dtype == TS_BF16 && w_dtype == TS_F32)
+    rmsnorm_kernel<bf16, float><<<T, threads, 0, s>>>((bf16*)out, (const bf16*)x, (bf16*)residual,
+                                                      (const float*)w, eps, hidden);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_rmsnorm: dtype %d with scale dtype %d", dtype, w_dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// SiLU*mul: out[t, i] = T(silu(g)) * u with gu[t] = [g(0..I) | u(0..I)]
+// (turingserve/ops/reference.py:26-28; rounding as triton_silu_mul.py:15-18).
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_f(gu[t * 2 * inter + i]);
+    const float u = to_f(gu[t * 2 * inter + inter + i]);
+    const float s = round_to<T>(g / (1.f + expf(-g)));
+    out[idx] = from_f<T>(s * u);
+  }
+}
+
+TS_API int ts_silu_mul(void* out, const void* gu, int T, int inter, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t total = (size_t)T * inter;
+  const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  if (dtype == TS_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, inter, total);
+  else if (dtype == TS_BF16)
+    silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gu, inter, total);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_silu_mul: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// Rotary encoding of q and k in place in qkv[T, (H+2KVH)*D], fused with the cache write of the
+// rotated k and of v.  Rotate-half over the first `rot` dims of each head:
+//   o[i] = x[i]*c - x[i+rot/2]*s,  o[i+rot/2] = x[i+rot/2]*c + x[i]*s,   c,s = T(table[pos, i])
+// (turingserve/ops/reference.py:31-42).  Cache layout per run: [pages, KVH, page, D]; slot < 0
+// skips the write (reference.py:50-57).  k_cache == nullptr: rotate only (a run that reads
+// another run's cache).
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                     T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     const int* __restrict__ slots, int H, int KVH, int D, int rot,
+                                     int page) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = (k_cache != nullptr) ? slots[t] : -1;
+  const int half = rot / 2;
+  T* row = qkv + (size_t)t * (H + 2 * KVH) * D;
+  size_t cache_base = 0;
+  if (slot >= 0) cache_base = ((size_t)(slot / page) * KVH * page + (size_t)(slot % page)) * D;
+  const size_t head_stride = (size_t)page * D;
+  // q and k heads: pairs (i, i+half) for i < half, untouched dims rot..D-1
+  const int pair_items = (H + KVH) * (D - half);   // per head: half pairs + (D - rot) pass-through
+  for (int idx = threadIdx.x; idx < pair_items; idx += blockDim.x) {
+    const int head = idx / (D - half);
+    const int i = idx % (D - half);
+    T* x = row + (size_t)head * D;
+    const bool is_k = head >= H;
+    T* kdst = (is_k && slot >= 0) ? k_cache + cache_base + (size_t)(head - H) * head_stride : nullptr;
+    if (i < half) {
+      const float c = round_to<T>(cos_t[(size_t)pos * half + i]);
+      const float s = round_to<T>(sin_t[(size_t)pos * half + i]);
+      const float x1 = to_f(x[i]), x2 = to_f(x[i + half]);
+      const T o1 = from_f<T>(x1 * c - x2 * s);
+      const T o2 = from_f<T>(x2 * c + x1 * s);
+      x[i] = o1;
+      x[i + half] = o2;
+      if (kdst != nullptr) {
+        kdst[i] = o1;
+        kdst[i + half] = o2;
+      }
+    } else {
+      const int d = rot + (i - half);
+      if (kdst != nullptr) kdst[d] = x[d];
+    }
+  }
+  if (slot >= 0) {
+    const T* v = row + (size_t)(H + KVH) * D;
+    for (int idx = threadIdx.x; idx < KVH * D; idx += blockDim.x) {
+      const int head = idx / D, d = idx % D;
+      v_cache[cache_base + (size_t)head * head_stride + d] = v[idx];
+    }
+  }
+}
+
+TS_API int ts_rope_kv_write(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
+                            void* k_cache, void* v_cache, const int* slots, int T, int H, int KVH,
+                            int D, int rot, int page, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > D || (rot & 1)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: rotary_dim %d for head_dim %d", rot, D);
+  if (rot > 0 && (cos_t == nullptr || sin_t == nullptr)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: tables missing");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    rope_kv_write_kernel<float><<<T, 256, 0, s>>>((float*)qkv, positions, cos_t, sin_t, (float*)k_cache,
+                                                  (float*)v_cache, slots, H, KVH, D, rot, page);
+  else if (dtype == TS_BF16)
+    rope_kv_write_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache,
+                                                 (bf16*)v_cache, slots, H, KVH, D, rot, page);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_rope_kv_write: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}

@@ -1,0 +1,19 @@
+// Last-error text of the C ABI (one buffer per host thread).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void ts_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+TS_API const char* ts_last_error() { return g_error; }
+
+// Compiled-for architecture and ABI version, so the Python side can refuse a stale library.
+TS_API int ts_abi_version() { return 3; }

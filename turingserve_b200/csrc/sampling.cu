@@ -1,0 +1,291 @@
+// Sampling on the device: logit edits (penalties, stop-token masking) and the draw
+// (greedy / temperature / top-k / top-p / exponential race), one block per logits row.
+//
+// Order and formulas follow turingserve/sampling/sampler.py:45-107 and
+// turingserve/sampling/penalties.py:20-45:
+//   bad row (non-finite logit) -> flagged; greedy -> first index of the maximum;
+//   otherwise scaled = logits / temperature; keep the top_k largest; p = softmax over the kept;
+//   walking down in value, an entry is dropped once the mass before it reaches top_p (the first is
+//   always kept); p = softmax over what remains; token = argmax(p / E), E ~ Exp(1).
+// Where the reference sorts, this kernel finds the two value thresholds by radix selection over
+// order-preserving integer keys (four 8-bit passes each), so equal values are kept or dropped
+// together.  E comes from Philox4x32-10 keyed by the request's seed, counter = (vocabulary index,
+// number of tokens the request has drawn so far).
+#include "common.cuh"
+
+namespace {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ uint32_t philox_first_word(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                      uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+// E ~ Exp(1) for vocabulary entry i of a request's `drawn`-th draw.
+__device__ __forceinline__ float exponential(uint64_t seed, uint64_t drawn, uint32_t i) {
+  const uint32_t r = philox_first_word(i, (uint32_t)drawn, (uint32_t)(drawn >> 32), 0u,
+                                       (uint32_t)seed, (uint32_t)(seed >> 32));
+  const float u = ((float)(r >> 8) + 0.5f) * (1.0f / 16777216.0f);    // (0, 1)
+  return -logf(u);
+}
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ Best block_best(Best x, Best* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = x;
+  __syncthreads();
+  Best t = scratch[lane < nw ? lane : 0];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+    t = better(t, y);
+  }
+  return t;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* __restrict__ logits,
+              const float* __restrict__ fparams, const long long* __restrict__ iparams, int V) {
+  __shared__ Best best_s[32];
+  __shared__ float red_s[32];
+  __shared__ int cnt_s[256];
+  __shared__ float mass_s[256];
+  __shared__ uint32_t sel_prefix;
+  __shared__ float sel_above;
+  __shared__ int sel_k;
+  __shared__ int any_bad;
+
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  const float temp = fparams[row * 2 + 0], top_p = fparams[row * 2 + 1];
+  const long long top_k = iparams[row * 4 + 0];
+  const uint64_t seed = (uint64_t)iparams[row * 4 + 1], drawn = (uint64_t)iparams[row * 4 + 2];
+
+  if (threadIdx.x == 0) any_bad = 0;
+  __syncthreads();
+  Best b{-INFINITY, 0x7fffffff};
+  bool bad = false;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = x[i];
+    if (!isfinite(v)) bad = true;
+    b = better(b, Best{v, i});
+  }
+  if (bad) any_bad = 1;
+  b = block_best(b, best_s);        // has __syncthreads inside: any_bad is visible after it
+  if (any_bad) {
+    if (threadIdx.x == 0) {
+      tokens[row] = 0;
+      bad_out[row] = 1;
+    }
+    return;
+  }
+  if (threadIdx.x == 0) bad_out[row] = 0;
+  if (!(temp > 0.f)) {
+    if (threadIdx.x == 0) tokens[row] = b.i;
+    return;
+  }
+  const float m = b.v / temp;
+  uint32_t keep_from = 0u;          // entries with order_key >= keep_from are kept
+
+  if (top_k > 0 && top_k < V) {     // exact key of the top_k-th largest value
+    if (threadIdx.x == 0) {
+      sel_prefix = 0u;
+      sel_k = (int)top_k;
+    }
+    uint32_t mask = 0u;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      if (threadIdx.x < 256) cnt_s[threadIdx.x] = 0;
+      __syncthreads();
+      const uint32_t prefix = sel_prefix;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const uint32_t k = order_key(x[i] / temp);
+        if ((k & mask) == prefix) atomicAdd(&cnt_s[(k >> shift) & 255u], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int k = sel_k, chosen = 0;
+        for (int bin = 255; bin >= 0; --bin) {
+          if (k <= cnt_s[bin]) {
+            chosen = bin;
+            break;
+          }
+          k -= cnt_s[bin];
+        }
+        sel_k = k;
+        sel_prefix = prefix | ((uint32_t)chosen << shift);
+      }
+      mask |= 255u << shift;
+      __syncthreads();
+    }
+    keep_from = sel_prefix;
+  }
+
+  if (top_p < 1.f) {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float s = x[i] / temp;
+      if (order_key(s) >= keep_from) z += expf(s - m);
+    }
+    z = block_sum(z, red_s);
+    const float limit = top_p * z;
+    if (threadIdx.x == 0) {
+      sel_prefix = 0u;
+      sel_above = 0.f;
+    }
+    uint32_t mask = 0u;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      if (threadIdx.x < 256) {
+        cnt_s[threadIdx.x] = 0;
+        mass_s[threadIdx.x] = 0.f;
+      }
+      __syncthreads();
+      const uint32_t prefix = sel_prefix;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float s = x[i] / temp;
+        const uint32_t k = order_key(s);
+        if (k >= keep_from && (k & mask) == prefix) {
+          atomicAdd(&cnt_s[(k >> shift) & 255u], 1);
+          atomicAdd(&mass_s[(k >> shift) & 255u], expf(s - m));
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float above = sel_above, above_chosen = sel_above;
+        int chosen = 255;
+        for (int bin = 255; bin >= 0; --bin) {
+          if (cnt_s[bin] == 0) continue;
+          if (!(above < limit)) break;
+          chosen = bin;
+          above_chosen = above;
+          above += mass_s[bin];
+        }
+        sel_above = above_chosen;
+        sel_prefix = prefix | ((uint32_t)chosen << shift);
+      }
+      mask |= 255u << shift;
+      __syncthreads();
+    }
+    keep_from = max(keep_from, sel_prefix);
+  }
+
+  float z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = x[i] / temp;
+    if (order_key(s) >= keep_from) z += expf(s - m);
+  }
+  z = block_sum(z, red_s);
+  Best w{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = x[i] / temp;
+    if (order_key(s) < keep_from) continue;
+    const float p = expf(s - m) / z;
+    w = better(w, Best{p / exponential(seed, drawn, (uint32_t)i), i});
+  }
+  w = block_best(w, best_s);
+  if (threadIdx.x == 0) tokens[row] = w.i;
+}
+
+// Logit edits.  meta[row] = {a, b, c, d}: ids[a:b] prompt tokens, ids[b:c] output tokens (both
+// empty when the row has no penalties), ids[c:d] tokens to mask to -inf.  pen[row] = {repetition,
+// presence, frequency}.  seen = prompt or output: logit > 0 ? logit / rep : logit * rep; then
+// logit -= frequency * count_in_output; then logit -= presence * (count_in_output > 0).
+__global__ void penalize_kernel(float* __restrict__ logits, const int* __restrict__ ids,
+                                const int* __restrict__ meta, const float* __restrict__ pen, int V) {
+  extern __shared__ uint32_t bits[];           // [2][ceil(V/32)]: seen, seen-in-output
+  const int words = (V + 31) / 32;
+  uint32_t* seen = bits;
+  uint32_t* seen_out = bits + words;
+  const int row = blockIdx.x;
+  float* x = logits + (size_t)row * V;
+  const int a = meta[row * 8 + 0], b = meta[row * 8 + 1], c = meta[row * 8 + 2], d = meta[row * 8 + 3];
+  const float rep = pen[row * 4 + 0], presence = pen[row * 4 + 1], frequency = pen[row * 4 + 2];
+  for (int i = threadIdx.x; i < 2 * words; i += blockDim.x) bits[i] = 0u;
+  __syncthreads();
+  for (int i = a + threadIdx.x; i < c; i += blockDim.x) {
+    const int t = ids[i];
+    if (t < 0 || t >= V) continue;
+    const uint32_t bit = 1u << (t & 31);
+    const uint32_t old = atomicOr(&seen[t >> 5], bit);
+    if (!(old & bit)) {                        // first sighting: repetition penalty, once
+      const float v = x[t];
+      x[t] = v > 0.f ? v / rep : v * rep;
+    }
+  }
+  __syncthreads();
+  for (int i = b + threadIdx.x; i < c; i += blockDim.x) {
+    const int t = ids[i];
+    if (t < 0 || t >= V) continue;
+    const uint32_t bit = 1u << (t & 31);
+    const uint32_t old = atomicOr(&seen_out[t >> 5], bit);
+    if (!(old & bit)) {
+      int count = 0;
+      for (int j = b; j < c; ++j) count += (ids[j] == t);
+      float v = x[t];
+      v = v - frequency * (float)count;
+      v = v - presence * 1.0f;
+      x[t] = v;
+    }
+  }
+  __syncthreads();
+  for (int i = c + threadIdx.x; i < d; i += blockDim.x) {
+    const int t = ids[i];
+    if (t >= 0 && t < V) x[t] = -INFINITY;
+  }
+}
+
+}  // namespace
+
+// out[0:S] tokens, out[S:2S] bad flags.
+TS_API int ts_sample(int* out, const float* logits, const float* fparams, const long long* iparams, int S,
+                     int V, void* stream) {
+  if (S <= 0) return 0;
+  if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample: vocabulary %d", V);
+  sample_kernel<<<S, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(out, out + S, logits, fparams, iparams, V);
+  TS_LAUNCH_CHECK();
+}
+
+TS_API int ts_penalize(float* logits, const int* ids, const int* meta, const float* pen, int S, int V,
+                       void* stream) {
+  if (S <= 0) return 0;
+  const size_t smem = 2 * (size_t)((V + 31) / 32) * sizeof(uint32_t);
+  if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_penalize: vocabulary %d too large", V);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(penalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_penalize: %s", cudaGetErrorString(e));
+    configured = smem;
+  }
+  penalize_kernel<<<S, 256, smem, (cudaStream_t)stream>>>(logits, ids, meta, pen, V);
+  TS_LAUNCH_CHECK();
+}

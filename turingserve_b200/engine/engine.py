@@ -1,0 +1,231 @@
+"""LLMEngine: add requests, step until they finish.
+
+One step = schedule -> one forward over the flat batch -> sample -> commit tokens -> finish and
+free (turingserve/engine/engine.py:96-184).  Finish rules in the reference's order
+(turingserve/engine/output_processor.py:26-44, turingserve/engine/stop.py:8-11): a stop token
+(``stop_token_ids``, or an end-of-sequence id unless ``ignore_eos``) -> "stop"; ``max_tokens``
+produced or ``max_model_len`` reached -> "length".  A row of non-finite logits, or a request that
+can never be scheduled, finishes with "error" (engine.py:142-146,199-208).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+
+import torch
+
+from turingserve_b200.cache.manager import CacheManager
+from turingserve_b200.config.engine_config import EngineConfig
+from turingserve_b200.engine.batch import StepEntry
+from turingserve_b200.engine.request import BatchPlan, Request, RequestOutput, Status
+from turingserve_b200.engine.runner import ModelRunner, run_needs
+from turingserve_b200.engine.scheduler import Scheduler
+from turingserve_b200.sampling.params import SamplingParams
+from turingserve_b200.sampling.sampler import Sampler, SampleRow, derive_seed
+
+
+@dataclass
+class FinalOutput:
+    request_id: str
+    token_ids: list[int]
+    finish_reason: str | None
+    prompt_tokens: int
+
+
+class StepTimer:
+    """Wall-clock seconds per phase of the last step (turingserve/utils/timing.py:9-24)."""
+
+    def __init__(self) -> None:
+        self.t: dict[str, float] = {}
+        self._t0: dict[str, float] = {}
+
+    def reset(self) -> None:
+        self.t.clear()
+
+    def start(self, name: str) -> None:
+        self._t0[name] = time.perf_counter()
+
+    def stop(self, name: str) -> None:
+        self.t[name] = self.t.get(name, 0.0) + time.perf_counter() - self._t0.pop(name)
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, runner, cache: CacheManager, scheduler: Scheduler,
+                 sampler, eos_ids: tuple[int, ...], max_model_len: int) -> None:
+        self.cfg, self.runner, self.cache = cfg, runner, cache
+        self.scheduler, self.sampler = scheduler, sampler
+        self.eos_ids = tuple(eos_ids)
+        self.max_model_len = max_model_len
+        self.requests: dict[str, Request] = {}
+        self._aborts: list[str] = []
+        self._arrivals = 0
+        self.timer = StepTimer()
+        self.step_count = 0
+
+    # -- construction ---------------------------------------------------------------------------
+    @classmethod
+    def from_config(cls, cfg: EngineConfig) -> LLMEngine:
+        """Start-up order of turingserve/engine/builder.py:29-135: config -> weights -> model ->
+        number of pages (flag, or from free memory) -> cache -> runner, scheduler, sampler."""
+        from turingserve_b200 import kernels
+        from turingserve_b200.config.registry import load_model_config
+        from turingserve_b200.weights.loader import load_model
+
+        mcfg = load_model_config(cfg.model)
+        cfg.validate(mcfg.max_position_embeddings)
+        max_len = cfg.resolve_max_model_len(mcfg.max_position_embeddings)
+        kernels.ops()                                   # build/load the CUDA library; fails loudly
+        device = torch.device("cuda", torch.cuda.current_device())
+        model, mcfg = load_model(cfg.model, cfg.torch_dtype, device, max_len)
+        needs = run_needs(model)
+        num_pages = cfg.num_blocks
+        if num_pages is None:
+            free, total = torch.cuda.mem_get_info(device)
+            per_page = max(1, CacheManager.bytes_per_page(needs, cfg.block_size, cfg.torch_dtype))
+            budget = free - (1.0 - cfg.gpu_memory_utilization) * total - (2 << 30)
+            wanted = cfg.max_num_seqs * cfg.max_blocks_per_seq(max_len) + 1
+            num_pages = int(max(2, min(budget // per_page, wanted)))
+        cache = CacheManager(needs, cfg.block_size, num_pages, cfg.max_num_seqs, cfg.torch_dtype, device)
+        runner = ModelRunner(model, cache, max(cfg.max_num_batched_tokens, cfg.max_num_seqs),
+                             cfg.max_num_seqs, max_len,
+                             cfg.graph_batch_sizes if cfg.cuda_graphs else ())
+        scheduler = Scheduler(cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, cfg.watermark)
+        return cls(cfg, runner, cache, scheduler, Sampler(device), mcfg.eos_token_ids, max_len)
+
+    # -- requests -----------------------------------------------------------------------------------
+    def add_request(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams) -> Request:
+        if request_id in self.requests:
+            raise ValueError(f"duplicate request id {request_id}")
+        if not prompt_token_ids:
+            raise ValueError("a request needs at least one prompt token")
+        seed = params.seed if params.seed is not None else derive_seed(self.cfg.seed, self._arrivals)
+        self._arrivals += 1
+        req = Request(request_id, list(prompt_token_ids), len(prompt_token_ids), params, seed=seed)
+        self.requests[request_id] = req
+        self.scheduler.add(req)
+        return req
+
+    def abort(self, request_id: str) -> None:
+        self._aborts.append(request_id)
+
+    def has_unfinished(self) -> bool:
+        return bool(self._aborts) or self.scheduler.has_unfinished()
+
+    # -- one step -----------------------------------------------------------------------------------
+    def step(self) -> list[RequestOutput]:
+        t = self.timer
+        t.reset()
+        outputs = self._process_aborts()
+        t.start("schedule")
+        plan = self.scheduler.schedule()
+        t.stop("schedule")
+        for req in plan.failed:
+            outputs.append(self._finish(req, "error", []))
+        self._finalize(outputs)
+        if not plan.items:
+            return outputs + self._fail_unschedulable()
+        outputs += self._run(plan)
+        self.step_count += 1
+        return outputs
+
+    def _run(self, plan: BatchPlan) -> list[RequestOutput]:
+        t = self.timer
+        t.start("forward")
+        entries = []
+        for it in plan.items:
+            r = it.request
+            start = r.num_computed
+            entries.append(StepEntry(r.cache, r.token_ids[start:start + it.num_tokens],
+                                     [it.num_tokens - 1] if it.samples else []))
+        logits = self.runner.step(entries)
+        t.stop("forward")
+        sampling = [it.request for it in plan.items if it.samples]
+        tokens = bad = None
+        t.start("sample")
+        if sampling:
+            rows = [SampleRow(r.params, r.seed, r.num_drawn, r.token_ids[:r.num_prompt_tokens],
+                              r.output_ids, self._stop_ids(r)) for r in sampling]
+            tokens, bad = self.sampler.sample(logits, rows)
+        t.stop("sample")
+        t.start("output")
+        outputs: list[RequestOutput] = []
+        for row, req in enumerate(sampling):
+            if bad[row]:
+                outputs.append(self._finish(req, "error", []))
+                continue
+            outputs.append(self._commit(req, int(tokens[row])))
+        self._finalize(outputs)
+        t.stop("output")
+        return outputs
+
+    def _stop_ids(self, req: Request) -> tuple[int, ...]:
+        return tuple(self.eos_ids) + tuple(req.params.stop_token_ids)
+
+    def _commit(self, req: Request, token: int) -> RequestOutput:
+        req.token_ids.append(token)
+        req.num_drawn += 1
+        p = req.params
+        if token in p.stop_token_ids or ((not p.ignore_eos) and token in self.eos_ids):
+            return self._finish(req, "stop", [token])
+        if req.num_output >= p.max_tokens or len(req.token_ids) >= self.max_model_len:
+            return self._finish(req, "length", [token])
+        return self._output(req, [token])
+
+    def _output(self, req: Request, tokens: list[int]) -> RequestOutput:
+        return RequestOutput(req.request_id, tokens, req.finished, req.finish_reason,
+                             req.num_prompt_tokens, req.num_output)
+
+    def _finish(self, req: Request, reason: str, tokens: list[int]) -> RequestOutput:
+        req.status = Status.FINISHED
+        req.finish_reason = reason
+        return self._output(req, tokens)
+
+    def _finalize(self, outputs: list[RequestOutput]) -> None:
+        for out in outputs:
+            if not out.finished:
+                continue
+            req = self.requests.pop(out.request_id, None)
+            if req is not None:
+                self.scheduler.finish(req)
+
+    def _process_aborts(self) -> list[RequestOutput]:
+        outs = []
+        ids, self._aborts = self._aborts, []
+        for rid in ids:
+            req = self.requests.get(rid)
+            if req is None or req.finished:
+                continue
+            outs.append(self._finish(req, "abort", []))
+        self._finalize(outs)
+        return outs
+
+    def _fail_unschedulable(self) -> list[RequestOutput]:
+        req = self.scheduler.unschedulable()
+        if req is None:
+            return []
+        out = self._finish(req, "error", [])
+        self._finalize([out])
+        return [out]
+
+    # -- offline helper -----------------------------------------------------------------------------
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]
+                 ) -> list[FinalOutput]:
+        """Run ``prompts`` (lists of token ids) to completion (turingserve/engine/engine.py:237-259)."""
+        plist = params if isinstance(params, list) else [params] * len(prompts)
+        if len(plist) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or a single one for all")
+        ids = [f"gen-{id(self)}-{i}-{time.monotonic_ns()}" for i in range(len(prompts))]
+        for rid, p, sp in zip(ids, prompts, plist):
+            self.add_request(rid, p, sp)
+        finals = {rid: FinalOutput(rid, [], None, len(p)) for rid, p in zip(ids, prompts)}
+        while self.has_unfinished():
+            for out in self.step():
+                f = finals.get(out.request_id)
+                if f is None:
+                    continue
+                f.token_ids += out.delta_token_ids
+                if out.finished:
+                    f.finish_reason = out.finish_reason
+        return [finals[r] for r in ids]
+

@@ -1,0 +1,139 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and return the
+logits at the wanted places.
+
+One call = one forward pass over a flat token batch that may mix portions of prompts with single
+decoded tokens (turingserve/runner/model_runner.py:20-32; design in docs/ARCHITECTURE.md:224-237 of
+the reference).  It runs only the tokens it is given; everything earlier comes from the cache.
+
+Pure-decode steps whose request count fits a captured size are replayed from a CUDA graph (the
+reference captures the decode forward per batch size, turingserve/runner/cuda_graphs.py:44-78).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from turingserve_b200.cache.manager import CacheManager, RunNeeds
+from turingserve_b200.engine.batch import StepEntry, StepInputBuilder, StepInputs
+from turingserve_b200.parts.model import DecoderModel
+
+
+def run_needs(model: DecoderModel) -> list[RunNeeds]:
+    """What each run of the model's schedule needs from the cache manager."""
+    out = []
+    for r, run in enumerate(model.cfg.schedule):
+        mixer = model.run_mixer(r)
+        out.append(RunNeeds(cache=mixer.cache_need(), state=mixer.state_need(), cache_from=run.cache_from))
+    return out
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_tokens: int, max_requests: int,
+                 max_model_len: int, graph_batch_sizes: tuple[int, ...] = ()) -> None:
+        self.model, self.cache = model, cache
+        self.max_model_len = max_model_len
+        self.max_pages = -(-max_model_len // cache.page_size)
+        self.builder = StepInputBuilder(cache, max_tokens, max_requests, self.max_pages, model.device)
+        self.views = cache.views()
+        self.graph_batch_sizes = tuple(sorted(graph_batch_sizes))
+        self._graphs: dict[int, _DecodeGraph] = {}
+
+    # -- the step ---------------------------------------------------------------------------------
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Logits [sum(len(e.want)), vocab] fp32 in the order of ``entries`` and of each ``want``
+        (None when nothing is wanted).  Grows each request's pages, runs, then advances the cache."""
+        self._check(entries)
+        for e in entries:
+            self.cache.grow(e.cache, len(e.tokens))
+        graph_size = self._graph_size(entries)
+        if graph_size is not None:
+            logits = self._replay(graph_size, entries)
+        else:
+            step = self.builder.build(entries)
+            logits = self.forward(step)
+        for e in entries:
+            self.cache.advance(e.cache, len(e.tokens))
+        return logits
+
+    def forward(self, step: StepInputs) -> torch.Tensor | None:
+        hidden = self.model.forward(step, self.views, self.cache.states)
+        if step.sample_rows.shape[0] == 0:
+            return None
+        return self.model.logits(hidden, step.sample_rows)
+
+    def _check(self, entries: list[StepEntry]) -> None:
+        seen = set()
+        vocab = self.model.cfg.vocab_size
+        for e in entries:
+            if id(e.cache) in seen:
+                raise ValueError(f"request {e.cache.request_id!r} appears twice in one step")
+            seen.add(id(e.cache))
+            if not e.tokens:
+                raise ValueError(f"request {e.cache.request_id!r} brings no tokens")
+            if e.cache.num_tokens + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"request {e.cache.request_id!r} would exceed max_model_len {self.max_model_len}")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"request {e.cache.request_id!r}: token id outside [0, {vocab})")
+
+    # -- CUDA graphs for pure-decode steps ----------------------------------------------------------
+    def _graph_size(self, entries: list[StepEntry]) -> int | None:
+        if not self.graph_batch_sizes:
+            return None
+        n = len(entries)
+        if any(len(e.tokens) != 1 or e.want != [0] for e in entries):
+            return None
+        for s in self.graph_batch_sizes:
+            if s >= n:
+                return s
+        return None
+
+    def _replay(self, size: int, entries: list[StepEntry]) -> torch.Tensor:
+        g = self._graphs.get(size)
+        if g is None:
+            g = self._graphs[size] = _DecodeGraph(self, size)
+        return g.run(entries)
+
+
+class _DecodeGraph:
+    """One captured decode step for ``size`` requests: static input arena, static logits."""
+
+    def __init__(self, runner: ModelRunner, size: int) -> None:
+        self.runner, self.size = runner, size
+        b = runner.builder
+        self.arena = torch.zeros(b.capacity, dtype=torch.int32, device=runner.model.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.order: list[int] = []
+
+    def _build(self, entries: list[StepEntry]) -> StepInputs:
+        r = self.runner
+        return r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - len(entries),
+                               arena=self.arena)
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+        step = self._build(entries)
+        if self.graph is None:
+            r = self.runner
+            # warm up outside capture (lazy module state, allocator pools), then capture
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                full = _with_all_rows(step, self.size)
+                r.forward(full)
+            torch.cuda.current_stream().wait_stream(s)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = r.forward(_with_all_rows(step, self.size))
+            self.graph = graph
+        self.graph.replay()
+        # rows are in batch order (decodes first = caller order for pure decode)
+        return self.logits[:len(entries)]
+
+
+def _with_all_rows(step: StepInputs, size: int) -> StepInputs:
+    """In a captured decode step every row is sampled: row b of the logits is request b."""
+    import dataclasses
+
+    rows = torch.arange(size, dtype=torch.int32, device=step.input_ids.device)
+    return dataclasses.replace(step, sample_rows=rows)

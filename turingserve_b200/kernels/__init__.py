@@ -1,0 +1,169 @@
+"""The CUDA kernels (sm_100a) behind one object, ``ops()``.
+
+The library is built in-tree at the first call (``kernels.build``) and loaded with ctypes; every
+function takes raw device pointers and the current CUDA stream.  There is no other backend: on a
+machine without the library and without nvcc, or without a CUDA device, ``ops()`` raises.
+
+Kernels and their reference counterparts (turingserve/ops/__init__.py:15-19 lists the op
+namespace): embedding, rmsnorm (+residual), linear, rope fused with the cache write, paged
+attention, silu*mul, sampling.  bfloat16 matrix products go to cuBLAS through ``torch.mm`` where
+the reference uses ``F.linear`` (turingserve/ops/triton_ops.py:74-76), unless a hand-written
+tensor-core kernel takes the shape; float32 products always use this library's FFMA kernel.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from turingserve_b200.kernels.build import build, library_path
+
+_OPS = None
+
+c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class CudaOps:
+    """ctypes front of ``libturingserve_b200.so``."""
+
+    ABI = 3
+
+    def __init__(self, lib_path: str) -> None:
+        self.lib_path = lib_path
+        self.lib = ctypes.CDLL(lib_path)
+        self.lib.ts_last_error.restype = ctypes.c_char_p
+        if self.lib.ts_abi_version() != self.ABI:
+            raise KernelError(f"{lib_path} has ABI {self.lib.ts_abi_version()}, this package needs {self.ABI}")
+        P, I, F = c_void_p, c_int, c_float
+        sigs = {
+            "ts_embedding": [P, P, P, I, I, I, I, P],
+            "ts_gather_rows": [P, P, P, I, I, I, P],
+            "ts_rmsnorm": [P, P, P, P, F, I, I, I, I, P],
+            "ts_silu_mul": [P, P, I, I, I, P],
+            "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+            "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
+            "ts_sample": [P, P, P, P, I, I, P],
+            "ts_penalize": [P, P, P, P, I, I, P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        self.use_library_gemm = True
+
+    # -- plumbing -----------------------------------------------------------------------------------
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            msg = self.lib.ts_last_error().decode(errors="replace")
+            raise KernelError(f"{what} failed ({rc}): {msg}")
+
+    # -- kernels ------------------------------------------------------------------------------------
+    def embedding(self, out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+        T, h = out.shape
+        self._check(self.lib.ts_embedding(_ptr(out), _ptr(table), _ptr(ids), T, h, table.shape[0],
+                                          _code(out.dtype), self._stream()), "embedding")
+
+    def gather_rows(self, out: torch.Tensor, x: torch.Tensor, rows: torch.Tensor) -> None:
+        S, w = out.shape
+        self._check(self.lib.ts_gather_rows(_ptr(out), _ptr(x), _ptr(rows), S, w, _code(x.dtype),
+                                            self._stream()), "gather_rows")
+
+    def rmsnorm(self, out, x, weight, eps: float, residual=None) -> None:
+        T, h = x.shape
+        self._check(self.lib.ts_rmsnorm(_ptr(out), _ptr(x), _ptr(residual), _ptr(weight), float(eps), T, h,
+                                        _code(x.dtype), _code(weight.dtype), self._stream()), "rmsnorm")
+
+    def silu_mul(self, out, gu) -> None:
+        T, inter = out.shape
+        self._check(self.lib.ts_silu_mul(_ptr(out), _ptr(gu), T, inter, _code(gu.dtype), self._stream()),
+                    "silu_mul")
+
+    def rope_kv_write(self, qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
+                      page_size) -> None:
+        T = qkv.shape[0]
+        self._check(self.lib.ts_rope_kv_write(
+            _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
+            T, H, KVH, D, rotary_dim, page_size, _code(qkv.dtype), self._stream()), "rope_kv_write")
+
+    def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
+                  window) -> None:
+        self._check(self.lib.ts_attention_generic(
+            _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(step.q_start),
+            _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H, KVH, D,
+            page_size, float(scale), 0 if window is None else int(window), _code(qkv.dtype),
+            self._stream()), "attention")
+
+    def linear(self, out, x, w, bias=None, rows=None) -> None:
+        """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias."""
+        M, N = out.shape
+        K = w.shape[1]
+        if x.dtype == torch.bfloat16 and self.use_library_gemm:
+            if rows is not None:
+                xg = torch.empty((M, K), dtype=x.dtype, device=x.device)
+                self.gather_rows(xg, x, rows)
+                x = xg
+            if out.dtype == torch.float32:
+                torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+                if bias is not None:
+                    out.add_(bias.float())
+            elif bias is not None:
+                torch.addmm(bias, x, w.t(), out=out)
+            else:
+                torch.mm(x, w.t(), out=out)
+            return
+        self._check(self.lib.ts_linear_simt(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows), M, N, K,
+                                            _code(x.dtype), _code(out.dtype), self._stream()), "linear")
+
+    def sample(self, out, logits, fparams, iparams) -> None:
+        S, V = logits.shape
+        self._check(self.lib.ts_sample(_ptr(out), _ptr(logits), _ptr(fparams), _ptr(iparams), S, V,
+                                       self._stream()), "sample")
+
+    def penalize(self, logits, ids, meta, pen) -> None:
+        S, V = logits.shape
+        self._check(self.lib.ts_penalize(_ptr(logits), _ptr(ids), _ptr(meta), _ptr(pen), S, V,
+                                         self._stream()), "penalize")
+
+
+def ops():
+    """The kernel object; builds and loads the CUDA library on first use.  Raises when there is
+    no CUDA device or the library cannot be built: there is no fallback."""
+    global _OPS
+    if _OPS is None:
+        if not torch.cuda.is_available():
+            raise KernelError("turingserve_b200 needs a CUDA device (sm_100a); none is available")
+        _OPS = CudaOps(build())
+    return _OPS
+
+
+def use(ops_object) -> None:
+    """Install another object behind ``ops()`` (tests drive the engine's host logic with a plain
+    torch twin of every kernel this way); ``use(None)`` goes back to the CUDA library."""
+    global _OPS
+    _OPS = ops_object
+
+
+__all__ = ["CudaOps", "KernelError", "build", "library_path", "ops", "use"]

@@ -1,0 +1,101 @@
+"""Sampler: penalties -> min_tokens -> greedy / temperature -> top-k -> top-p -> exponential-race
+draw, all in device kernels, one device-to-host copy at the end
+(turingserve/sampling/sampler.py:68-107, turingserve/sampling/penalties.py:20-45).
+
+The draw is ``argmax(probs / E)`` with E ~ Exp(1) per vocabulary entry, as the reference
+(sampler.py:95-103).  Where the reference takes E from a ``torch.Generator`` per seeded request
+and a shared one for the rest, here E comes from a counter-based generator keyed by
+(the request's seed, how many tokens it has drawn so far, the vocabulary index): a request's
+stream never depends on its batch-mates, seeded or not.  Requests without a seed get one derived
+from the engine seed and their arrival number.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from turingserve_b200 import kernels
+from turingserve_b200.sampling.params import SamplingParams
+
+_MASK64 = (1 << 64) - 1
+
+
+def derive_seed(engine_seed: int, ordinal: int) -> int:
+    """splitmix64 of (engine seed, arrival number): the seed of a request that brought none."""
+    z = (engine_seed * 0x9E3779B97F4A7C15 + ordinal + 0x632BE59BD9B4E019) & _MASK64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK64
+    return (z ^ (z >> 31)) & _MASK64
+
+
+@dataclass
+class SampleRow:
+    """What the sampler needs to know about the request behind one logits row."""
+
+    params: SamplingParams
+    seed: int                       # 64-bit seed of this request's stream
+    num_drawn: int                  # tokens this request has sampled so far (the stream position)
+    prompt_ids: list[int]
+    output_ids: list[int]
+    stop_ids: tuple[int, ...] = ()  # eos + stop_token_ids, masked while num_output < min_tokens
+
+
+class Sampler:
+    def __init__(self, device) -> None:
+        self.device = torch.device(device)
+
+    @torch.inference_mode()
+    def sample(self, logits: torch.Tensor, rows: list[SampleRow]) -> tuple[np.ndarray, np.ndarray]:
+        """logits [S, V] fp32 on the device -> (tokens[S], bad[S]) on the host.  ``bad`` marks rows
+        with a non-finite logit; their token is the argmax of zeros, as sampler.py:73-74."""
+        ops = kernels.ops()
+        S, V = logits.shape
+        assert S == len(rows)
+        dev = self.device
+        if any(r.params.uses_penalties or len(r.output_ids) < r.params.min_tokens for r in rows):
+            logits = logits.clone()
+            self._edit_logits(ops, logits, rows)
+        f = np.zeros((S, 2), dtype=np.float32)
+        i = np.zeros((S, 4), dtype=np.int64)
+        for n, r in enumerate(rows):
+            p = r.params
+            f[n, 0] = 0.0 if p.greedy else p.temperature
+            f[n, 1] = p.top_p
+            i[n, 0] = p.top_k
+            i[n, 1] = np.int64(np.uint64(r.seed & _MASK64).astype(np.int64))
+            i[n, 2] = r.num_drawn
+        fp = torch.from_numpy(f).to(dev, non_blocking=True)
+        ip = torch.from_numpy(i).to(dev, non_blocking=True)
+        out = torch.empty((2, S), dtype=torch.int32, device=dev)
+        ops.sample(out, logits, fp, ip)
+        host = out.cpu().numpy()                       # the one device-to-host copy of the step
+        return host[0].astype(np.int64), host[1].astype(bool)
+
+    def _edit_logits(self, ops, logits: torch.Tensor, rows: list[SampleRow]) -> None:
+        """Penalties (penalties.py:20-45), then stop tokens masked to -inf while fewer than
+        ``min_tokens`` were produced (sampler.py:24-28,84-86).  Token lists travel as one flat
+        int32 array with offsets."""
+        flat: list[int] = []
+        meta = np.zeros((len(rows), 8), dtype=np.int32)
+        pen = np.zeros((len(rows), 4), dtype=np.float32)
+        for n, r in enumerate(rows):
+            p = r.params
+            a = len(flat)
+            if p.uses_penalties:
+                flat += r.prompt_ids
+            b = len(flat)
+            if p.uses_penalties:
+                flat += r.output_ids
+            c = len(flat)
+            if len(r.output_ids) < p.min_tokens:
+                flat += list(r.stop_ids)
+            d = len(flat)
+            meta[n, :4] = (a, b, c, d)
+            pen[n, :3] = (p.repetition_penalty, p.presence_penalty, p.frequency_penalty)
+        dev = self.device
+        ids = torch.tensor(flat if flat else [0], dtype=torch.int32).to(dev, non_blocking=True)
+        ops.penalize(logits, ids, torch.from_numpy(meta).to(dev, non_blocking=True),
+                     torch.from_numpy(pen).to(dev, non_blocking=True))
