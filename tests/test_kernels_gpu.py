@@ -1,0 +1,238 @@
+"""Each CUDA kernel alone against its plain torch twin, at sizes other than the engine's test
+models (shape grids after the reference's tests/kernels/test_kernels.py:22-154)."""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests.twin_ops import TwinOps, paged_attention
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: dict(atol=2e-5, rtol=2e-5), torch.bfloat16: dict(atol=2e-2, rtol=2e-2)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from turingserve_b200 import kernels
+    kernels.use(None)
+    return kernels.ops()
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@dataclasses.dataclass
+class FakeStep:
+    q_start: torch.Tensor
+    seq_lens: torch.Tensor
+    num_requests: int
+    max_q_len: int
+    max_seq_len: int
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    for V, h in [(50, 64), (301, 80), (1000, 1536), (77, 30)]:
+        table = _rand((V, h), dtype, 1)
+        ids = torch.randint(0, V, (23,), dtype=torch.int32)
+        out = torch.empty((23, h), dtype=dtype, device="cuda")
+        ops.embedding(out, table.cuda(), ids.cuda())
+        assert torch.equal(out.cpu(), table[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [1, 7, 130])
+@pytest.mark.parametrize("N", [64, 224, 1000, 1536, 4100])
+def test_rmsnorm(ops, dtype, T, N):
+    twin = TwinOps()
+    x, r, w = _rand((T, N), dtype, 2), _rand((T, N), dtype, 3), (1 + 0.1 * _rand((N,), torch.float32, 4)).to(dtype)
+    for eps in (1e-6, 1e-3):
+        out = torch.empty((T, N), dtype=dtype, device="cuda")
+        ops.rmsnorm(out, x.cuda(), w.cuda(), eps)
+        ref = torch.empty_like(x)
+        twin.rmsnorm(ref, x, w, eps)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+        res = r.clone().cuda()
+        ops.rmsnorm(out, x.cuda(), w.cuda(), eps, res)
+        rref = r.clone()
+        twin.rmsnorm(ref, x, w, eps, rref)
+        assert torch.equal(res.cpu(), rref), "residual sum is a single rounding: must be exact"
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+    if dtype == torch.bfloat16:                      # a scale stored in 32-bit stays 32-bit
+        w32 = 1 + 0.1 * _rand((N,), torch.float32, 5)
+        out = torch.empty((T, N), dtype=dtype, device="cuda")
+        ops.rmsnorm(out, x.cuda(), w32.cuda(), 1e-6)
+        ref = torch.empty_like(x)
+        twin.rmsnorm(ref, x, w32, 1e-6)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    twin = TwinOps()
+    for T, inter in [(1, 128), (33, 4864), (5, 1001), (2048, 96)]:
+        gu = _rand((T, 2 * inter), dtype, 6, 3.0)
+        out = torch.empty((T, inter), dtype=dtype, device="cuda")
+        ops.silu_mul(out, gu.cuda())
+        ref = torch.empty((T, inter), dtype=dtype)
+        twin.silu_mul(ref, gu)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,D,rot", [(4, 2, 16, 16), (14, 2, 64, 64), (12, 2, 128, 128), (5, 5, 48, 48),
+                                         (6, 3, 32, 16), (2, 1, 80, 0)])
+def test_rope_kv_write(ops, dtype, H, KVH, D, rot):
+    twin = TwinOps()
+    T, page, pages = 37, 8, 12
+    qkv = _rand((T, (H + 2 * KVH) * D), dtype, 7)
+    pos = torch.randint(0, 500, (T,), dtype=torch.int32)
+    cos, sin = plain.rope_tables(max(rot, 2), 10000.0, 500)
+    perm = torch.randperm(page * (pages - 1))[:T].to(torch.int32) + page
+    slots = perm.clone()
+    slots[5] = -1
+    slots[20] = -1
+    kc = _rand((pages, KVH, page, D), dtype, 8)
+    vc = _rand((pages, KVH, page, D), dtype, 9)
+    q_d, kc_d, vc_d = qkv.clone().cuda(), kc.clone().cuda(), vc.clone().cuda()
+    ops.rope_kv_write(q_d, pos.cuda(), cos.cuda() if rot else None, sin.cuda() if rot else None, H, KVH, D, rot,
+                      kc_d, vc_d, slots.cuda(), page)
+    q_r, kc_r, vc_r = qkv.clone(), kc.clone(), vc.clone()
+    twin.rope_kv_write(q_r, pos, cos, sin, H, KVH, D, rot, kc_r, vc_r, slots, page)
+    tol = dict(atol=1e-6, rtol=1e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(q_d.cpu().float(), q_r.float(), **tol)
+    torch.testing.assert_close(kc_d.cpu().float(), kc_r.float(), **tol)
+    assert torch.equal(vc_d.cpu(), vc_r), "values are copied, not computed"
+    # rotate only (a run that reads another run's cache)
+    q_d2 = qkv.clone().cuda()
+    ops.rope_kv_write(q_d2, pos.cuda(), cos.cuda() if rot else None, sin.cuda() if rot else None, H, KVH, D, rot,
+                      None, None, slots.cuda(), page)
+    torch.testing.assert_close(q_d2.cpu().float(), q_r.float(), **tol)
+
+
+def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None):
+    """Random q/k/v for several requests, laid into a shuffled paged cache."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(q_lens)
+    seq_lens = [q + p for q, p in zip(q_lens, prefixes)]
+    n_pages = [-(-s // page) for s in seq_lens]
+    total = sum(n_pages) + 1
+    ids = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    W = max(n_pages + [1])
+    bt = torch.zeros((B, W), dtype=torch.int32)
+    kc = torch.zeros((total, KVH, page, D))
+    vc = torch.zeros((total, KVH, page, D))
+    T = sum(q_lens)
+    qkv = torch.randn((T, (H + 2 * KVH) * D), generator=g)
+    at = 0
+    for b in range(B):
+        mine = [ids.pop() for _ in range(n_pages[b])]
+        bt[b, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        k = torch.randn((seq_lens[b], KVH, D), generator=g)
+        v = torch.randn((seq_lens[b], KVH, D), generator=g)
+        if needle is not None and needle < seq_lens[b]:
+            # one far key lines up with the last query of every head: its value must come out
+            last = at + q_lens[b] - 1
+            G = H // KVH
+            for kvh in range(KVH):
+                q = qkv[last, kvh * G * D:(kvh * G + 1) * D]
+                k[needle, kvh] = 100.0 * q / q.norm()
+                for gi in range(G):
+                    qkv[last, (kvh * G + gi) * D:(kvh * G + gi + 1) * D] = q
+        for j in range(seq_lens[b]):
+            kc[mine[j // page], :, j % page] = k[j]
+            vc[mine[j // page], :, j % page] = v[j]
+        at += q_lens[b]
+    qs = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    return qkv.to(dtype), kc.to(dtype), vc.to(dtype), bt, qs, sl
+
+
+def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None):
+    qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle)
+    T = qkv.shape[0]
+    scale = D ** -0.5
+    step = FakeStep(qs.cuda(), sl.cuda(), len(q_lens), max(q_lens), int(sl.max()))
+    out = torch.full((T, H * D), float("nan"), dtype=dtype, device="cuda")
+    ops.attention(out, qkv.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, H, KVH, D, page, scale, window)
+    ref = torch.empty((T, H * D), dtype=torch.float32)
+    paged_attention(ref, qkv.float(), kc.float(), vc.float(), bt, qs, sl, H, KVH, D, page, scale, window)
+    return out.cpu().float(), ref, (qkv, kc, vc, bt, qs, sl)
+
+
+ATT_TOL = {torch.float32: dict(atol=2e-5, rtol=1e-4), torch.bfloat16: dict(atol=1e-2, rtol=1e-2)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,D,page", [(4, 2, 16, 16), (14, 2, 64, 16), (12, 2, 128, 16), (8, 8, 64, 8),
+                                          (5, 5, 48, 4), (3, 1, 256, 16), (6, 1, 80, 32)])
+def test_attention_decode(ops, dtype, H, KVH, D, page):
+    lens = [1, 2, 15, 16, 17, 100, 1000, 0, 33]
+    out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [1] * len(lens), [max(l - 1, 0) if l else -1 for l in lens], 11)
+    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+    assert torch.all(out[7] == 0), "a padding row (context 0) gives zeros"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,D,page", [(4, 2, 16, 16), (12, 2, 128, 16), (14, 2, 64, 8), (5, 5, 48, 16)])
+@pytest.mark.parametrize("case", [[(1, 0)], [(15, 16)], [(16, 37)], [(17, 1000)], [(300, 0)],
+                                  [(1, 5), (1, 99), (40, 0), (2, 31), (33, 64)]])
+def test_attention_chunks(ops, dtype, H, KVH, D, page, case):
+    out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [c[0] for c in case], [c[1] for c in case], 12)
+    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 24, 200])
+def test_attention_window(ops, dtype, window):
+    out, ref, _ = _run_attention(ops, dtype, 6, 2, 32, 8, [1, 40, 7, 1], [99, 0, 90, 3], 13, window=window)
+    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("needle", [0, 14, 15, 16, 17, 31, 32, 99, 511, 777])
+def test_attention_needle(ops, dtype, needle):
+    """One far key among hundreds carries all the weight: the output is that key's value
+    (reference tests/kernels/test_kernels.py:135-154)."""
+    H, KVH, D, page = 12, 2, 128, 16
+    out, ref, (qkv, kc, vc, bt, qs, sl) = _run_attention(ops, dtype, H, KVH, D, page, [1, 9], [899, 891], 14,
+                                                       needle=needle)
+    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+    for b in range(2):
+        last = int(qs[b + 1]) - 1
+        pg = int(bt[b, needle // page])
+        for kvh in range(KVH):
+            v = vc[pg, kvh, needle % page].float()
+            got = out[last, kvh * (H // KVH) * D:(kvh * (H // KVH) + 1) * D]
+            torch.testing.assert_close(got, v, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 300, 130), (65, 129, 257), (130, 70, 1000), (3, 1000, 48)])
+def test_linear(ops, dtype, M, N, K):
+    x, w, b = _rand((M + 5, K), dtype, 20), _rand((N, K), dtype, 21, 0.1), _rand((N,), dtype, 22)
+    rows = torch.randperm(M + 5)[:M].to(torch.int32)
+    ref = torch.nn.functional.linear(x.float(), w.float(), b.float())
+    tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=5e-2, rtol=2e-2)
+    for use_lib in ([False, True] if dtype == torch.bfloat16 else [False]):
+        ops.use_library_gemm = use_lib
+        try:
+            out = torch.empty((M + 5, N), dtype=dtype, device="cuda")
+            ops.linear(out, x.cuda(), w.cuda(), b.cuda())
+            torch.testing.assert_close(out.cpu().float(), ref, **tol)
+            out32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+            ops.linear(out32, x.cuda(), w.cuda(), None, rows.cuda())
+            ref32 = torch.nn.functional.linear(x.float()[rows.long()], w.float())
+            torch.testing.assert_close(out32.cpu(), ref32, atol=1e-4 if dtype == torch.float32 else 2e-3, rtol=1e-4)
+        finally:
+            ops.use_library_gemm = True

@@ -1,0 +1,100 @@
+"""The engine on the GPU against the plain implementation: the same requests whole, with the last
+32 tokens decoded one by one, in portions of changing size, and mixed with other requests in a
+pool so small that pages are used again; in 32-bit and in bfloat16; in-process and through
+``bin/trace_run`` as a user starts it."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests import schedules, tiny
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31]}
+# float32: the reference's own bound for logits (tests/correctness/test_vs_hf.py:40-48).
+# bfloat16: 8 bits of mantissa; logits of these models reach |2.5|; the bound is 3% of the largest
+# expected logit of the request, about eight bfloat16 roundings.
+F32_TOL = 1e-4
+BF16_REL = 3e-2
+
+
+def expected_logits(folder, reqs):
+    cfg, w = plain.read_folder(folder)
+    return {rid: plain.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+
+
+def requests_for(name, folder):
+    cfg, _ = plain.read_folder(folder)
+    return {f"r{i}": tiny.random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+def check(got, expected, dtype):
+    if dtype == "float32":
+        bad = schedules.first_bad(got, expected, F32_TOL)
+        assert bad is None, f"first wrong place (request, position, error): {bad}"
+    else:
+        for rid, rows in got.items():
+            tol = BF16_REL * float(np.abs(expected[rid]).max())
+            bad = schedules.first_bad({rid: rows}, expected, tol)
+            assert bad is None, f"first wrong place (request, position, error): {bad}, bound {tol}"
+
+
+def replay_in_process(folder, name, steps, dtype):
+    from turingserve_b200 import kernels
+    from turingserve_b200.engine.replay import Replayer
+    kernels.use(None)
+    rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name))
+    outs = {}
+    with torch.inference_mode():
+        for s in steps:
+            o = rp.step(s)
+            if o is not None:
+                outs[s["step"]] = o
+            rp.cache.check()
+    assert not rp.cache.live
+    return schedules.collect(steps, outs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed"])
+def test_schedules_match_plain(tmp_path, name, schedule, dtype):
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = getattr(schedules, schedule)(reqs)
+    got = replay_in_process(folder, name, steps, dtype)
+    assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
+    check(got, expected_logits(folder, reqs), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a subprocess: steps on stdin, `done <step>` after each, files in --out."""
+    name = "B"
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = schedules.mixed(reqs, seed=3)
+    out = tmp_path / f"out_{dtype}"
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                          "--out", str(out), "--max-tokens", str(schedules.peak_tokens(steps)),
+                          "--block-size", str(tiny.page_size(name))],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for s in steps:
+        p.stdin.write(json.dumps(s) + "\n")
+        p.stdin.flush()
+        assert p.stdout.readline().strip() == f"done {s['step']}"
+    p.stdin.close()
+    assert p.wait(timeout=120) == 0
+    V = plain.read_folder(folder)[0]["vocab_size"]
+    outs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, V) for s in steps}
+    check(schedules.collect(steps, outs), expected_logits(folder, reqs), dtype)

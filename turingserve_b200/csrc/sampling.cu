@@ -3,7 +3,7 @@
 //
 // Order and formulas follow turingserve/sampling/sampler.py:45-107 and
 // turingserve/sampling/penalties.py:20-45:
-//   bad row (non-finite logit) -> flagged; greedy -> first index of the maximum;
+//   bad row (a NaN or +inf logit; -inf marks a masked entry) -> flagged; greedy -> first index of the maximum;
 //   otherwise scaled = logits / temperature; keep the top_k largest; p = softmax over the kept;
 //   walking down in value, an entry is dropped once the mass before it reaches top_p (the first is
 //   always kept); p = softmax over what remains; token = argmax(p / E), E ~ Exp(1).
@@ -98,7 +98,7 @@ sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* 
   bool bad = false;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float v = x[i];
-    if (!isfinite(v)) bad = true;
+    if (isnan(v) || v == INFINITY) bad = true;       // -inf is a masked entry, not a fault
     b = better(b, Best{v, i});
   }
   if (bad) any_bad = 1;
