@@ -1,0 +1,168 @@
+"""The scheduler's decisions, with a model-free runner (after the reference's
+tests/unit/test_scheduler.py:13-120)."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from tests.fakes import expected_output, make_fake_engine
+from turingserve_b200.sampling import SamplingParams
+
+
+def greedy(n, **kw):
+    return SamplingParams(temperature=0.0, max_tokens=n, **kw)
+
+
+def check_invariants(eng, plan_items=None):
+    eng.cache.check()
+    s = eng.scheduler
+    assert len(s.running) <= s.max_num_seqs
+    assert all(r.cache is not None for r in s.running) and all(r.cache is None for r in s.waiting)
+
+
+def run(eng, reqs, check=True):
+    for rid, (p, sp) in reqs.items():
+        eng.add_request(rid, p, sp)
+    out = {rid: [] for rid in reqs}
+    reasons = {}
+    steps = 0
+    while eng.has_unfinished():
+        for o in eng.step():
+            out[o.request_id] += o.delta_token_ids
+            if o.finished:
+                reasons[o.request_id] = o.finish_reason
+        if check:
+            check_invariants(eng)
+        steps += 1
+        assert steps < 100000
+    return out, reasons, steps
+
+
+def test_chunked_prefill_takes_ceil_steps_and_samples_once():
+    eng = make_fake_engine(num_pages=128, budget=64)
+    prompt = list(range(1000))
+    out, reasons, steps = run(eng, {"a": (prompt, greedy(1))})
+    assert steps == 16                                             # ceil(1000 / 64)
+    sizes = [n for st in eng.runner.steps for _, n in st]
+    assert sizes == [64] * 15 + [40]
+    assert out["a"] == expected_output(prompt, 1) and reasons["a"] == "length"
+
+
+def test_decodes_first_and_budget_respected():
+    eng = make_fake_engine(num_pages=256, budget=48, max_seqs=8)
+    reqs = {f"r{i}": (list(range(i, i + 30 + 17 * i)), greedy(12)) for i in range(5)}
+    for rid, (p, sp) in reqs.items():
+        eng.add_request(rid, p, sp)
+    while eng.has_unfinished():
+        plan = eng.scheduler.schedule()
+        assert plan.num_tokens <= 48
+        kinds = [it.num_tokens == 1 and it.request.num_uncomputed == 1 for it in plan.items]
+        assert kinds == sorted(kinds, reverse=True), "decodes come first"
+        assert plan.num_decode == sum(kinds)
+        eng._run(plan)
+        eng.step_count += 1
+        check_invariants(eng)
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_match_solo_runs_and_free_everything(seed):
+    rng = random.Random(seed)
+    eng = make_fake_engine(num_pages=rng.choice([24, 40, 200]), budget=rng.choice([16, 48, 200]),
+                           max_seqs=rng.choice([2, 4, 8]), window=rng.choice([None, 40]))
+    reqs = {}
+    for i in range(12):
+        p = [rng.randrange(1000) for _ in range(rng.choice([1, 5, 17, 60, 130]))]
+        reqs[f"r{i}"] = (p, greedy(rng.choice([1, 4, 20])))
+    out, reasons, _ = run(eng, reqs)
+    for rid, (p, sp) in reqs.items():
+        if reasons[rid] == "error":
+            assert len(p) + sp.max_tokens > (eng.cache.num_pages - 1) * 16 - 16
+            continue
+        assert out[rid] == expected_output(p, sp.max_tokens), rid
+    assert not eng.cache.live and eng.cache.min_free() == eng.cache.num_pages - 1
+
+
+def test_pages_run_out_newest_is_preempted_and_outputs_do_not_change():
+    reqs = {f"r{i}": (list(range(10 * i, 10 * i + 40)), greedy(60)) for i in range(4)}
+    big, _, _ = run(make_fake_engine(num_pages=400), dict(reqs))
+    small_eng = make_fake_engine(num_pages=16)                      # 15 pages = 240 tokens < 4 x 100
+    small, reasons, _ = run(small_eng, dict(reqs))
+    assert small == big and set(reasons.values()) == {"length"}
+    assert small_eng.scheduler.num_preemptions > 0
+    # the victim was the newest running request, and it went back to the FRONT of the queue
+    eng = make_fake_engine(num_pages=9, budget=256)                 # 8 pages
+    for i in range(2):
+        eng.add_request(f"r{i}", list(range(60)), greedy(40))       # 4 pages each at admission
+    eng.step()
+    eng.step()
+    while eng.scheduler.num_preemptions == 0:
+        eng.step()
+    assert [r.request_id for r in eng.scheduler.waiting] == ["r1"]
+    assert [r.request_id for r in eng.scheduler.running] == ["r0"]
+    assert eng.requests["r1"].num_computed == 0 and eng.requests["r1"].num_output > 0
+    check_invariants(eng)
+
+
+def test_no_admission_in_a_step_that_preempted_and_watermark():
+    eng = make_fake_engine(num_pages=9, budget=256, watermark=0.3)  # keeps 2 pages free at admission
+    assert eng.scheduler.watermark_pages == 2
+    eng.add_request("a", list(range(16 * 6)), greedy(4))             # 6 pages: fits with 2 left
+    eng.add_request("b", list(range(16)), greedy(4))                 # 1 page would leave 1 < watermark
+    eng.step()
+    assert [r.request_id for r in eng.scheduler.running] == ["a"]
+    assert [r.request_id for r in eng.scheduler.waiting] == ["b"]
+
+
+def test_unschedulable_request_errors_others_go_on():
+    eng = make_fake_engine(num_pages=5, budget=32)                   # 64 tokens of cache
+    out, reasons, _ = run(eng, {"big": (list(range(100)), greedy(4)), "ok": (list(range(10)), greedy(4))})
+    assert reasons == {"big": "error", "ok": "length"}
+    assert out["ok"] == expected_output(list(range(10)), 4) and out["big"] == []
+    assert not eng.cache.live
+
+
+def test_two_prompts_that_block_each_other_are_untangled():
+    eng = make_fake_engine(num_pages=9, budget=48, max_seqs=4)       # 8 pages; each prompt needs 6
+    reqs = {"a": (list(range(90)), greedy(3)), "b": (list(range(5, 95)), greedy(3))}
+    out, reasons, _ = run(eng, reqs)
+    assert reasons == {"a": "length", "b": "length"}
+    for rid, (p, sp) in reqs.items():
+        assert out[rid] == expected_output(p, 3)
+    assert eng.scheduler.num_preemptions >= 1
+
+
+def test_abort_and_stop_rules():
+    eng = make_fake_engine()
+    eng.add_request("a", [1, 2, 3], greedy(50))
+    eng.add_request("b", [4, 5, 6], greedy(50))
+    eng.step()
+    eng.abort("a")
+    outs = eng.step()
+    assert any(o.request_id == "a" and o.finish_reason == "abort" for o in outs)
+    assert "a" not in eng.requests
+    check_invariants(eng)
+    while eng.has_unfinished():
+        eng.step()
+    assert not eng.cache.live
+    # stop tokens: eos unless ignore_eos; stop_token_ids always; max_model_len
+    first = expected_output([7, 8, 9], 3)
+    eng = make_fake_engine(eos=(first[1],))
+    out, reasons, _ = run(eng, {"x": ([7, 8, 9], greedy(10)), "y": ([7, 8, 9], greedy(10, ignore_eos=True)),
+                                "z": ([7, 8, 9], greedy(10, stop_token_ids=[first[0]]))})
+    assert out["x"] == first[:2] and reasons["x"] == "stop"
+    assert len(out["y"]) == 10 and reasons["y"] == "length"
+    assert out["z"] == first[:1] and reasons["z"] == "stop"
+    eng = make_fake_engine(max_model_len=8)
+    out, reasons, _ = run(eng, {"m": ([1, 2, 3, 4, 5], greedy(10))})
+    assert len(out["m"]) == 3 and reasons["m"] == "length"
+
+
+def test_duplicate_and_empty_requests_are_refused():
+    eng = make_fake_engine()
+    eng.add_request("a", [1], greedy(1))
+    with pytest.raises(ValueError, match="duplicate"):
+        eng.add_request("a", [1], greedy(1))
+    with pytest.raises(ValueError, match="at least one"):
+        eng.add_request("b", [], greedy(1))

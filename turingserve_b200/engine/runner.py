@@ -11,8 +11,11 @@ reference captures the decode forward per batch size, turingserve/runner/cuda_gr
 
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
+from turingserve_b200 import kernels
 from turingserve_b200.cache.manager import CacheManager, RunNeeds
 from turingserve_b200.engine.batch import StepEntry, StepInputBuilder, StepInputs
 from turingserve_b200.parts.model import DecoderModel
@@ -104,36 +107,36 @@ class _DecodeGraph:
         self.arena = torch.zeros(b.capacity, dtype=torch.int32, device=runner.model.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
-        self.order: list[int] = []
+        # in a captured decode step every row is sampled: row b of the logits is request b
+        self.rows = torch.arange(size, dtype=torch.int32, device=runner.model.device)
+        self.kernels_per_replay = 0
 
     def _build(self, entries: list[StepEntry]) -> StepInputs:
         r = self.runner
-        return r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - len(entries),
+        step = r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - len(entries),
                                arena=self.arena)
+        # launch geometry must not depend on this step's lengths: size it for the longest context
+        return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len)
 
     def run(self, entries: list[StepEntry]) -> torch.Tensor:
         step = self._build(entries)
+        ops = kernels.ops()
         if self.graph is None:
             r = self.runner
-            # warm up outside capture (lazy module state, allocator pools), then capture
+            # warm up outside capture (lazy set-up, allocator pools), then capture
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                full = _with_all_rows(step, self.size)
-                r.forward(full)
+                r.forward(step)
             torch.cuda.current_stream().wait_stream(s)
             graph = torch.cuda.CUDAGraph()
+            before = getattr(ops, "launches", 0)
             with torch.cuda.graph(graph):
-                self.logits = r.forward(_with_all_rows(step, self.size))
+                self.logits = r.forward(step)
+            self.kernels_per_replay = getattr(ops, "launches", 0) - before
             self.graph = graph
         self.graph.replay()
+        if hasattr(ops, "launches"):
+            ops.launches += self.kernels_per_replay
         # rows are in batch order (decodes first = caller order for pure decode)
         return self.logits[:len(entries)]
-
-
-def _with_all_rows(step: StepInputs, size: int) -> StepInputs:
-    """In a captured decode step every row is sampled: row b of the logits is request b."""
-    import dataclasses
-
-    rows = torch.arange(size, dtype=torch.int32, device=step.input_ids.device)
-    return dataclasses.replace(step, sample_rows=rows)

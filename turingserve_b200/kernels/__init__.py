@@ -69,6 +69,7 @@ class CudaOps:
             fn.argtypes = args
             fn.restype = c_int
         self.use_library_gemm = True
+        self.launches = 0           # kernels of this library launched (graph replays add their share)
 
     # -- plumbing -----------------------------------------------------------------------------------
     @staticmethod
@@ -76,6 +77,7 @@ class CudaOps:
         return torch.cuda.current_stream().cuda_stream
 
     def _check(self, rc: int, what: str) -> None:
+        self.launches += 1
         if rc != 0:
             msg = self.lib.ts_last_error().decode(errors="replace")
             raise KernelError(f"{what} failed ({rc}): {msg}")
