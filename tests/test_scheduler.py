@@ -92,13 +92,14 @@ def test_pages_run_out_newest_is_preempted_and_outputs_do_not_change():
     assert small == big and set(reasons.values()) == {"length"}
     assert small_eng.scheduler.num_preemptions > 0
     # the victim was the newest running request, and it went back to the FRONT of the queue
-    eng = make_fake_engine(num_pages=9, budget=256)                 # 8 pages
+    eng = make_fake_engine(num_pages=10, budget=256)                # 9 pages
     for i in range(2):
-        eng.add_request(f"r{i}", list(range(60)), greedy(40))       # 4 pages each at admission
-    eng.step()
-    eng.step()
-    while eng.scheduler.num_preemptions == 0:
+        eng.add_request(f"r{i}", list(range(60)), greedy(40))       # 4 pages each at admission, 7 at the end
+    for _ in range(200):
+        if eng.scheduler.num_preemptions:
+            break
         eng.step()
+    assert eng.scheduler.num_preemptions == 1
     assert [r.request_id for r in eng.scheduler.waiting] == ["r1"]
     assert [r.request_id for r in eng.scheduler.running] == ["r0"]
     assert eng.requests["r1"].num_computed == 0 and eng.requests["r1"].num_output > 0
@@ -124,13 +125,41 @@ def test_unschedulable_request_errors_others_go_on():
 
 
 def test_two_prompts_that_block_each_other_are_untangled():
-    eng = make_fake_engine(num_pages=9, budget=48, max_seqs=4)       # 8 pages; each prompt needs 6
-    reqs = {"a": (list(range(90)), greedy(3)), "b": (list(range(5, 95)), greedy(3))}
-    out, reasons, _ = run(eng, reqs)
+    """Both running requests are in the middle of their prompts and neither portion fits: the newest
+    gives its pages to the other (the reference would wait forever)."""
+    from turingserve_b200.engine.request import Status
+    eng = make_fake_engine(num_pages=9, budget=48, max_seqs=4)       # 8 pages = 128 tokens
+    reqs = {"a": (list(range(100)), greedy(3)), "b": (list(range(5, 105)), greedy(3))}
+    for rid, (p, sp) in reqs.items():
+        r = eng.add_request(rid, p, sp)
+        eng.scheduler.waiting.remove(r)
+        r.status = Status.RUNNING
+        r.cache = eng.cache.admit(rid)
+        eng.runner.step([type("E", (), {"cache": r.cache, "tokens": p[:60], "want": []})()])   # 4 pages each
+        eng.scheduler.running.append(r)
+    assert eng.cache.min_free() == 0
+    plan = eng.scheduler.schedule()
+    assert [it.request.request_id for it in plan.items] == ["a"] and plan.items[0].num_tokens == 40
+    assert [r.request_id for r in plan.preempted] == ["b"] and eng.scheduler.waiting[0].request_id == "b"
+    eng._run(plan)
+    out = {"a": [], "b": []}
+    reasons = {}
+    for _ in range(100):
+        for o in eng.step():
+            out[o.request_id] += o.delta_token_ids
+            if o.finished:
+                reasons[o.request_id] = o.finish_reason
+        check_invariants(eng)
     assert reasons == {"a": "length", "b": "length"}
     for rid, (p, sp) in reqs.items():
-        assert out[rid] == expected_output(p, 3)
-    assert eng.scheduler.num_preemptions >= 1
+        assert (expected_output(p, 3)[-len(out[rid]):] == out[rid]) and len(out[rid]) >= 2
+    # a lone request whose prompt can never fit is handed back as failed, not retried forever
+    eng = make_fake_engine(num_pages=5, budget=48)                   # 64 tokens of cache
+    r = eng.add_request("big", list(range(100)), greedy(2))
+    outs = []
+    for _ in range(10):
+        outs += eng.step()
+    assert [(o.request_id, o.finish_reason) for o in outs] == [("big", "error")] and not eng.cache.live
 
 
 def test_abort_and_stop_rules():
