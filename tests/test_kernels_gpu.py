@@ -38,6 +38,7 @@ class FakeStep:
     num_requests: int
     max_q_len: int
     max_seq_len: int
+    num_decode: int = 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -158,13 +159,20 @@ def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, nee
     return qkv.to(dtype), kc.to(dtype), vc.to(dtype), bt, qs, sl
 
 
-def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None):
+def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True):
     qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle)
     T = qkv.shape[0]
     scale = D ** -0.5
-    step = FakeStep(qs.cuda(), sl.cuda(), len(q_lens), max(q_lens), int(sl.max()))
+    nd = 0
+    while nd < len(q_lens) and q_lens[nd] == 1:
+        nd += 1
+    step = FakeStep(qs.cuda(), sl.cuda(), len(q_lens), max(q_lens), int(sl.max()), nd)
     out = torch.full((T, H * D), float("nan"), dtype=dtype, device="cuda")
-    ops.attention(out, qkv.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, H, KVH, D, page, scale, window)
+    ops.use_fast_attention = fast
+    try:
+        ops.attention(out, qkv.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, H, KVH, D, page, scale, window)
+    finally:
+        ops.use_fast_attention = True
     ref = torch.empty((T, H * D), dtype=torch.float32)
     paged_attention(ref, qkv.float(), kc.float(), vc.float(), bt, qs, sl, H, KVH, D, page, scale, window)
     return out.cpu().float(), ref, (qkv, kc, vc, bt, qs, sl)
@@ -177,10 +185,23 @@ ATT_TOL = {torch.float32: dict(atol=2e-5, rtol=1e-4), torch.bfloat16: dict(atol=
 @pytest.mark.parametrize("H,KVH,D,page", [(4, 2, 16, 16), (14, 2, 64, 16), (12, 2, 128, 16), (8, 8, 64, 8),
                                           (5, 5, 48, 4), (3, 1, 256, 16), (6, 1, 80, 32)])
 def test_attention_decode(ops, dtype, H, KVH, D, page):
-    lens = [1, 2, 15, 16, 17, 100, 1000, 0, 33]
-    out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [1] * len(lens), [max(l - 1, 0) if l else -1 for l in lens], 11)
-    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
-    assert torch.all(out[7] == 0), "a padding row (context 0) gives zeros"
+    lens = [1, 2, 15, 16, 17, 100, 1000, 0, 33, 64, 65, 257, 4000]
+    for fast in (True, False):
+        out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [1] * len(lens),
+                                     [max(l - 1, 0) if l else -1 for l in lens], 11, fast=fast)
+        torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+        assert torch.all(out[7] == 0), "a padding row (context 0) gives zeros"
+
+
+@pytest.mark.parametrize("B,ctx", [(1, 3000), (3, 700), (64, 90)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_split_counts(ops, B, ctx, window):
+    """Few requests with long contexts are cut into many key splits, many requests into one."""
+    H, KVH, D, page = 12, 2, 128, 16
+    lens = [max(ctx - 7 * i, 1 + i) for i in range(B)]
+    assert ops.decode_splits(1, KVH, 3000) > 4 and ops.decode_splits(256, KVH, 90) == 1
+    out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * B, [l - 1 for l in lens], 15, window=window)
+    torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -1,0 +1,348 @@
+// Paged grouped-query DECODE attention in bfloat16 (one new token per request), split over the
+// keys so that a small batch still fills the GPU.
+//
+// Counterpart of the reference's split-K flash-decoding kernels
+// (turingserve/ops/triton_decode_attention.py:101-163: partial (m, l, acc) per partition, then a
+// reduce kernel) and of its grouped kernel (:60-95: the G query heads of a kv head share every
+// key/value tile).  Semantics as turingserve/ops/reference.py:60-77,94-111 for q_len = 1.
+//
+// Work split: one block per (key split, kv head, request); 4 warps.  The block streams its share
+// of the keys in tiles of 64 through a 3-stage cp.async pipeline into XOR-swizzled shared memory;
+// warp w owns keys 16w..16w+15 of every tile.  The G query heads sit in the 16 rows of one
+// mma.sync m16n8k16 tile (rows >= G are zero), scores and the softmax state are 32-bit, the
+// probabilities are rounded to bfloat16 for the second product as the reference does
+// (triton_prefill_attention.py:58).  Warps keep independent online-softmax states over disjoint
+// keys and merge them through shared memory at the end; with more than one split the block
+// writes an unnormalised partial (m, l, acc) to scratch and `merge` finishes the job.
+#include <mma.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE = 64;        // keys per pipeline stage
+constexpr int DEC_STAGES = 3;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Byte offset of 16-byte chunk `c` of row `row` in a [rows][D] bf16 tile whose chunks are XOR-swizzled
+// within each 128-byte line.
+template <int D> __device__ __forceinline__ int swz(int row, int c) {
+  return row * (D * 2) + ((c & ~7) | ((c ^ row) & 7)) * 16;
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
+                        const int* __restrict__ q_start, const int* __restrict__ seq_lens, int table_width,
+                        int H, int KVH, int page, float scale, int window, int nsplit) {
+  constexpr int CH = D / 8;                       // 16-byte chunks per row
+  constexpr int KS = D / 16;                      // k-steps of the score product
+  constexpr int NT = D / 8;                       // n-tiles of the output
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = H / KVH;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq_len = seq_lens[b];
+  const int row_q = q_start[b];                   // the request's single query token
+  const int lo = (window > 0) ? max(0, seq_len - window) : 0;
+  const int span = max(seq_len - lo, 0);
+  int chunk = (span + nsplit - 1) / nsplit;
+  chunk = (chunk + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
+  const int k_begin = lo + split * chunk;
+  const int k_end = min(seq_len, k_begin + chunk);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + DEC_TILE - 1) / DEC_TILE : 0;
+
+  unsigned char* k_s = smem;                                       // [STAGES][TILE][D] bf16
+  unsigned char* v_s = smem + DEC_STAGES * DEC_TILE * D * 2;
+
+  // query fragments: rows 0..G-1 of the group, zero above
+  unsigned qf[KS][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
+    const bf16* qbase = qkv + (size_t)row_q * (H + 2 * KVH) * D + (size_t)kvh * G * D;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k = ks * 16 + kc;
+      qf[ks][0] = r0 < G ? *reinterpret_cast<const unsigned*>(qbase + r0 * D + k) : 0u;
+      qf[ks][1] = r1 < G ? *reinterpret_cast<const unsigned*>(qbase + r1 * D + k) : 0u;
+      qf[ks][2] = r0 < G ? *reinterpret_cast<const unsigned*>(qbase + r0 * D + k + 8) : 0u;
+      qf[ks][3] = r1 < G ? *reinterpret_cast<const unsigned*>(qbase + r1 * D + k + 8) : 0u;
+    }
+  }
+
+  auto load_tile = [&](int tile, int stage) {
+    const int j0 = k_begin + tile * DEC_TILE;
+    unsigned char* ks_ = k_s + stage * DEC_TILE * D * 2;
+    unsigned char* vs_ = v_s + stage * DEC_TILE * D * 2;
+    for (int idx = threadIdx.x; idx < DEC_TILE * CH; idx += DEC_WARPS * 32) {
+      const int key = idx / CH, c = idx % CH;
+      const int j = j0 + key;
+      const bool ok = j < k_end;
+      size_t off = 0;
+      if (ok) {
+        const int pg = block_tables[(size_t)b * table_width + j / page];
+        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j % page)) * D + c * 8;
+      }
+      cp_async_16(ks_ + swz<D>(key, c), k_cache + off, ok);
+      cp_async_16(vs_ + swz<D>(key, c), v_cache + off, ok);
+    }
+  };
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sc = scale * LOG2E;
+
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_tiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  for (int t = 0; t < n_tiles; ++t) {
+    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncthreads();
+    const unsigned char* ks_ = k_s + (t % DEC_STAGES) * DEC_TILE * D * 2;
+    const unsigned char* vs_ = v_s + (t % DEC_STAGES) * DEC_TILE * D * 2;
+    const int key0 = warp * 16;                                    // this warp's keys in the tile
+    const int j_base = k_begin + t * DEC_TILE + key0;
+    if (j_base < k_end) {                                          // warp-uniform
+      // scores S[16 x 16] = Q . K^T
+      float s_acc[2][4] = {};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+        const int mat = lane >> 3, r = lane & 7;
+        const int key = key0 + (mat >> 1) * 8 + r;
+        const int c = ks * 2 + (mat & 1);
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, ks_ + swz<D>(key, c));
+        mma_bf16(s_acc[0], qf[ks], b0, b1);
+        mma_bf16(s_acc[1], qf[ks], b2, b3);
+      }
+      // mask, online softmax (rows lane/4 and lane/4 + 8; columns (lane%4)*2 + {0,1} of each n-tile)
+      float p[2][4];
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j_base + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const float v = j < k_end ? s_acc[nt][e] * sc : -INFINITY;
+          s_acc[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);                // finite: the warp has >= 1 valid key
+        corr[r] = exp2f(m_run[r] - m_new);                         // exp2(-inf) = 0 on the first tile
+        m_run[r] = m_new;
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[nt][e] = exp2f(s_acc[nt][e] - m_run[e >> 1]);
+          rs[e >> 1] += p[nt][e];
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        l_run[r] = l_run[r] * corr[r] + rs[r];
+      }
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      // P as the A operand of the second product (16 rows x 16 keys)
+      unsigned pf[4];
+      pf[0] = pack_bf16(p[0][0], p[0][1]);
+      pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]);
+      pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+      for (int i = 0; i < NT; i += 2) {
+        // matrices: (keys 0-7, d tile i), (keys 8-15, d tile i), (keys 0-7, d tile i+1), (keys 8-15, d tile i+1)
+        const int mat = lane >> 3, r = lane & 7;
+        const int key = key0 + (mat & 1) * 8 + r;
+        const int c = i + (mat >> 1);
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + swz<D>(key, c));
+        mma_bf16(o[i], pf, b0, b1);
+        mma_bf16(o[i + 1], pf, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps' states through shared memory (the stage buffers are free now)
+  float* m_s = reinterpret_cast<float*>(smem);                     // [WARPS][16]
+  float* l_s = m_s + DEC_WARPS * 16;                               // [WARPS][16]
+  float* o_s = l_s + DEC_WARPS * 16;                               // [WARPS][16][D]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    if ((lane & 3) == 0) {
+      m_s[warp * 16 + r0] = m_run[0];
+      m_s[warp * 16 + r1] = m_run[1];
+      l_s[warp * 16 + r0] = l_run[0];
+      l_s[warp * 16 + r1] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      float* a = o_s + ((size_t)warp * 16 + r0) * D + d;
+      float* c = o_s + ((size_t)warp * 16 + r1) * D + d;
+      a[0] = o[i][0];
+      a[1] = o[i][1];
+      c[0] = o[i][2];
+      c[1] = o[i][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, m_s[w * 16 + g]);
+    float L = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float f = exp2f(m_s[w * 16 + g] - M);
+        L += l_s[w * 16 + g] * f;
+        acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+      }
+    }
+    const int h = kvh * G + g;
+    if (nsplit == 1) {
+      out[(size_t)row_q * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * H + h) * nsplit + split;
+      part_acc[pi * D + d] = acc;
+      if (d == 0) {
+        part_ml[pi * 2 + 0] = M;
+        part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// out[b, h, :] = sum_s acc_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)   (all in 32-bit)
+__global__ void attention_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
+                                              const float* __restrict__ part_ml, const int* __restrict__ q_start,
+                                              int H, int D, int nsplit) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const size_t base = ((size_t)b * H + h) * nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  const int row = q_start[b];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float L = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+      for (int s = 0; s < nsplit; ++s) {
+        const float f = exp2f(part_ml[(base + s) * 2] - M);
+        L += part_ml[(base + s) * 2 + 1] * f;
+        acc += part_acc[(base + s) * D + d] * f;
+      }
+    }
+    out[(size_t)row * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+template <int D>
+int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, const bf16* k_cache,
+                  const bf16* v_cache, const int* block_tables, const int* q_start, const int* seq_lens, int B,
+                  int table_width, int H, int KVH, int page, float scale, int window, int nsplit, cudaStream_t s) {
+  const size_t stage_bytes = (size_t)2 * DEC_STAGES * DEC_TILE * D * 2;
+  const size_t merge_bytes = sizeof(float) * ((size_t)2 * DEC_WARPS * 16 + (size_t)DEC_WARPS * 16 * D);
+  const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  attention_decode_kernel<D><<<dim3(nsplit, KVH, B), DEC_WARPS * 32, smem, s>>>(
+      out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
+      scale, window, nsplit);
+  if (nsplit > 1)
+    attention_decode_merge_kernel<<<dim3(H, B), D <= 128 ? D : 128, 0, s>>>(out, part_acc, part_ml, q_start, H, D, nsplit);
+  TS_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+// Whether this kernel takes the shape (else the caller uses the generic kernel).
+TS_API int ts_attention_decode_supported(int H, int KVH, int D, int dtype) {
+  return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && H / KVH <= 16 && (D == 64 || D == 128);
+}
+
+// Scratch needed for `nsplit` splits, in floats: acc [B, H, nsplit, D] then ml [B, H, nsplit, 2].
+TS_API long long ts_attention_decode_scratch_floats(int B, int H, int D, int nsplit) {
+  return nsplit > 1 ? (long long)B * H * nsplit * (D + 2) : 0;
+}
+
+// One query token per request (rows q_start[b]); `scratch` holds ts_attention_decode_scratch_floats()
+// floats when nsplit > 1.  window <= 0: none.
+TS_API int ts_attention_decode(void* out, void* scratch, const void* qkv, const void* k_cache, const void* v_cache,
+                               const int* block_tables, const int* q_start, const int* seq_lens, int B,
+                               int table_width, int H, int KVH, int D, int page, float scale, int window,
+                               int nsplit, void* stream) {
+  if (B <= 0) return 0;
+  if (!ts_attention_decode_supported(H, KVH, D, TS_BF16))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode: H=%d KVH=%d D=%d is not taken by this kernel", H, KVH, D);
+  if (nsplit < 1 || nsplit > 65535 || B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode: nsplit=%d B=%d", nsplit, B);
+  if (nsplit > 1 && scratch == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_attention_decode: %d splits need scratch", nsplit);
+  float* acc = (float*)scratch;
+  float* ml = acc ? acc + (size_t)B * H * nsplit * D : nullptr;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64)
+    return launch_decode<64>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+                             block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, s);
+  return launch_decode<128>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+                            block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, s);
+}

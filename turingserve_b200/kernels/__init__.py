@@ -61,6 +61,7 @@ class CudaOps:
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
+            "ts_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
             "ts_penalize": [P, P, P, P, I, I, P],
         }
@@ -68,6 +69,13 @@ class CudaOps:
             fn = getattr(self.lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
+        self.lib.ts_attention_decode_supported.restype = c_int
+        self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
+        self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        self.num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self._scratch: torch.Tensor | None = None
+        self.use_fast_attention = True
         self.use_library_gemm = True
         self.launches = 0           # kernels of this library launched (graph replays add their share)
 
@@ -110,13 +118,43 @@ class CudaOps:
             _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
             T, H, KVH, D, rotary_dim, page_size, _code(qkv.dtype), self._stream()), "rope_kv_write")
 
+    def scratch(self, floats: int, device) -> torch.Tensor:
+        """A float32 work buffer of at least ``floats`` elements, kept between calls."""
+        if self._scratch is None or self._scratch.numel() < floats or self._scratch.device != device:
+            self._scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        return self._scratch
+
+    def decode_splits(self, num_requests: int, KVH: int, max_seq_len: int) -> int:
+        """How many pieces each request's keys are cut into so that the launch fills the GPU."""
+        want = -(-2 * self.num_sms // max(1, num_requests * KVH))
+        return max(1, min(want, -(-max_seq_len // 256)))
+
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window) -> None:
+        """Rows of requests with one token (the first ``step.num_decode`` requests) go to the
+        split-key decode kernel when it takes the shape; the rest to the chunk kernels."""
+        w = 0 if window is None else int(window)
+        code = _code(qkv.dtype)
+        B, nd = step.num_requests, 0
+        width = block_tables.shape[1]
+        if self.use_fast_attention and step.num_decode > 0 and self.lib.ts_attention_decode_supported(H, KVH, D, code):
+            nd = step.num_decode
+            nsplit = self.decode_splits(nd, KVH, step.max_seq_len)
+            scratch = None
+            if nsplit > 1:
+                scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), qkv.device)
+            self._check(self.lib.ts_attention_decode(
+                _ptr(out), _ptr(scratch), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                _ptr(step.q_start), _ptr(step.seq_lens), nd, width, H, KVH, D, page_size, float(scale), w,
+                nsplit, self._stream()), "attention_decode")
+            if nsplit > 1:
+                self.launches += 1
+        if nd == B:
+            return
         self._check(self.lib.ts_attention_generic(
-            _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(step.q_start),
-            _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H, KVH, D,
-            page_size, float(scale), 0 if window is None else int(window), _code(qkv.dtype),
-            self._stream()), "attention")
+            _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), block_tables.data_ptr() + 4 * nd * width,
+            step.q_start.data_ptr() + 4 * nd, step.seq_lens.data_ptr() + 4 * nd, B - nd, width,
+            step.max_q_len, H, KVH, D, page_size, float(scale), w, code, self._stream()), "attention")
 
     def linear(self, out, x, w, bias=None, rows=None) -> None:
         """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias."""
