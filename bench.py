@@ -158,14 +158,18 @@ def run_ours(a) -> dict:
         cache.release(rc)
         return e0.elapsed_time(e1)
 
-    ptoks = rng.integers(0, V, size=a.prefill_tokens).tolist()
-    for _ in range(3):
-        prefill_once(ptoks)
-    pms = sorted(prefill_once(ptoks) for _ in range(5))[2]
-    T = a.prefill_tokens
-    pflops = 2.0 * T * nums["linear_params"] + layers * nums["attn_flops_per_layer"](T) + 2.0 * nums["head_params"]
-    prefill = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
-               "frac": round(pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflop": round(pflops / 1e12, 3)}
+    phases = set(a.phases.split(","))
+    prefill = None
+    if "prefill" in phases:
+        ptoks = rng.integers(0, V, size=a.prefill_tokens).tolist()
+        for _ in range(3):
+            prefill_once(ptoks)
+        pms = sorted(prefill_once(ptoks) for _ in range(5))[2]
+        T = a.prefill_tokens
+        pflops = 2.0 * T * nums["linear_params"] + layers * nums["attn_flops_per_layer"](T) + 2.0 * nums["head_params"]
+        prefill = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                   "frac": round(pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "tflop": round(pflops / 1e12, 3)}
 
     # ---- decode through the step function -----------------------------------------------------------
     def decode_run(batch: int, steps: int, warmup: int):
@@ -197,34 +201,39 @@ def run_ours(a) -> dict:
     step_bytes = nums["weight_bytes_decode"] + B * ctx_mid * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms / 1e3) / 1e9
     points = {}
-    for b in (1, 64):
-        pms_, _, _ = decode_run(b, min(steps, 64), 3)
-        points[f"decode_b{b}"] = round(b / (pms_ / 1e3), 1)
+    if "points" in phases:
+        for b in (1, 64):
+            pms_, _, _ = decode_run(b, min(steps, 64), 3)
+            points[f"decode_b{b}"] = round(b / (pms_ / 1e3), 1)
 
     # ---- end to end: LLMEngine.step with scheduler and sampler, host tokens in and out ----------------
-    prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(B)]
-    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + B + 8, ignore_eos=True)
-    for i, p in enumerate(prompts):
-        eng.add_request(f"e{i}", p, params)
-    while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
+    e2e = None
+    if "e2e" in phases:
+        prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(B)]
+        params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + B + 8, ignore_eos=True)
+        for i, p in enumerate(prompts):
+            eng.add_request(f"e{i}", p, params)
+        while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
+            eng.step()
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n_tok = 0
+        for _ in range(steps):
+            n_tok += sum(len(o.delta_token_ids) for o in eng.step())
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        for rid in list(eng.requests):
+            eng.abort(rid)
         eng.step()
-    for _ in range(warmup):
-        eng.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    n_tok = 0
-    for _ in range(steps):
-        n_tok += sum(len(o.delta_token_ids) for o in eng.step())
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    for rid in list(eng.requests):
-        eng.abort(rid)
-    eng.step()
-    # per step: the input arena (ids, positions, request index, starts, lengths, slots, rows, slot map,
-    # block tables) goes up; sampler parameters go up; tokens and flags come back
-    width = runner.max_pages
-    h2d = 4 * (4 * B + (B + 1) + 3 * B + B * width) + B * (2 * 4 + 4 * 8)
-    d2h = 2 * B * 4
+        # per step: the input arena (ids, positions, request index, starts, lengths, slots, rows, slot
+        # map, block tables) goes up; sampler parameters go up; tokens and flags come back
+        width = runner.max_pages
+        h2d = 4 * (4 * B + (B + 1) + 3 * B + B * width) + B * (2 * 4 + 4 * 8)
+        d2h = 2 * B * 4
+        e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": round(1e3 * e2e_s / steps, 4)}
 
     return {
         "metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts, bf16)",
@@ -239,8 +248,7 @@ def run_ours(a) -> dict:
                    "l2": "inputs larger than L2 (weights %.2f GB per step)" % (nums["weight_bytes_decode"] / 1e9),
                    "peaks": pk_src},
         "clocks": clocks.summary(),
-        "e2e": {"value": round(n_tok / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(1e3 * e2e_s / steps, 4)},
+        "e2e": e2e,
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -327,6 +335,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--phases", default="prefill,decode,points,e2e",
+                    help="which measurements to run (decode always runs); fewer for a profiler capture")
     a = ap.parse_args()
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
