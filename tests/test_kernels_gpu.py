@@ -209,15 +209,28 @@ def test_attention_decode_split_counts(ops, B, ctx, window):
 @pytest.mark.parametrize("case", [[(1, 0)], [(15, 16)], [(16, 37)], [(17, 1000)], [(300, 0)],
                                   [(1, 5), (1, 99), (40, 0), (2, 31), (33, 64)]])
 def test_attention_chunks(ops, dtype, H, KVH, D, page, case):
-    out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [c[0] for c in case], [c[1] for c in case], 12)
-    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+    for fast in (True, False):
+        out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [c[0] for c in case], [c[1] for c in case], 12,
+                                     fast=fast)
+        torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("H,KVH,D", [(12, 2, 128), (28, 4, 128), (14, 2, 64), (4, 4, 64), (40, 2, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_long_portions(ops, H, KVH, D, window):
+    """Portions of hundreds of tokens after long prefixes, several requests of different shape in
+    one launch, group sizes that are no power of two (and one above 16)."""
+    out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, 16, [1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129],
+                                 16, window=window)
+    torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 16, 24, 200])
 def test_attention_window(ops, dtype, window):
-    out, ref, _ = _run_attention(ops, dtype, 6, 2, 32, 8, [1, 40, 7, 1], [99, 0, 90, 3], 13, window=window)
-    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+    for H, KVH, D in [(6, 2, 32), (6, 2, 64)]:
+        out, ref, _ = _run_attention(ops, dtype, H, KVH, D, 8, [1, 40, 7, 1], [99, 0, 90, 3], 13, window=window)
+        torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -257,3 +270,27 @@ def test_linear(ops, dtype, M, N, K):
             torch.testing.assert_close(out32.cpu(), ref32, atol=1e-4 if dtype == torch.float32 else 2e-3, rtol=1e-4)
         finally:
             ops.use_library_gemm = True
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 128, 129, 300, 2048])
+@pytest.mark.parametrize("N,K", [(128, 64), (1536, 1536), (200, 200), (2048, 8960), (17920, 1536), (1000, 72)])
+def test_linear_tensor_core(ops, M, N, K):
+    """The tcgen05 product in both orientations, with K split or not, against float64."""
+    x, w, b = _rand((M, K), torch.bfloat16, 30, 1.0), _rand((N, K), torch.bfloat16, 31, 0.05), _rand((N,), torch.bfloat16, 32)
+    ref = (x.double() @ w.double().T + b.double()).float()
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    ops.use_tc_gemm = True
+    try:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        ops.linear(out, xd, wd, bd)
+        torch.testing.assert_close(out.cpu().float(), ref, atol=3e-2, rtol=2e-2)
+        out32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        ops.linear(out32, xd, wd, None)
+        torch.testing.assert_close(out32.cpu(), ref - b.float(), atol=2e-3, rtol=1e-3)
+        rows = torch.randperm(M)[: max(1, M // 2)].to(torch.int32)
+        outr = torch.empty((rows.shape[0], N), dtype=torch.float32, device="cuda")
+        ops.linear(outr, xd, wd, None, rows.cuda())
+        torch.testing.assert_close(outr.cpu(), (ref - b.float())[rows.long()], atol=2e-3, rtol=1e-3)
+        assert ops.tc_status() == 0, "a block of the tensor-core product gave up on a wait"
+    finally:
+        ops.use_tc_gemm = False

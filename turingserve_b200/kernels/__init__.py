@@ -62,6 +62,8 @@ class CudaOps:
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+            "ts_attention_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+            "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
             "ts_penalize": [P, P, P, P, I, I, P],
         }
@@ -71,6 +73,13 @@ class CudaOps:
             fn.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_supported.restype = c_int
+        self.lib.ts_linear_tc_supported.argtypes = [I, I, I]
+        self.lib.ts_linear_tc_supported.restype = c_int
+        self.lib.ts_linear_tc_status.argtypes = []
+        self.lib.ts_linear_tc_status.restype = c_int
+        self.use_tc_gemm = False
+        self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
+        self.lib.ts_attention_prefill_supported.restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self.num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -151,6 +160,12 @@ class CudaOps:
                 self.launches += 1
         if nd == B:
             return
+        if self.use_fast_attention and self.lib.ts_attention_prefill_supported(H, KVH, D, code):
+            self._check(self.lib.ts_attention_prefill(
+                _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), block_tables.data_ptr() + 4 * nd * width,
+                step.q_start.data_ptr() + 4 * nd, step.seq_lens.data_ptr() + 4 * nd, B - nd, width,
+                step.max_q_len, H, KVH, D, page_size, float(scale), w, self._stream()), "attention_prefill")
+            return
         self._check(self.lib.ts_attention_generic(
             _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), block_tables.data_ptr() + 4 * nd * width,
             step.q_start.data_ptr() + 4 * nd, step.seq_lens.data_ptr() + 4 * nd, B - nd, width,
@@ -160,11 +175,21 @@ class CudaOps:
         """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias."""
         M, N = out.shape
         K = w.shape[1]
+        if x.dtype == torch.bfloat16 and (self.use_tc_gemm or self.use_library_gemm) and rows is not None:
+            xg = torch.empty((M, K), dtype=x.dtype, device=x.device)
+            self.gather_rows(xg, x, rows)
+            x, rows = xg, None
+        if (x.dtype == torch.bfloat16 and self.use_tc_gemm and self.lib.ts_linear_tc_supported(M, N, K)
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            splits = self.tc_splits(M, N, K)
+            scratch = self.scratch(splits * M * N, x.device) if splits > 1 else None
+            self._check(self.lib.ts_linear_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(scratch), M, N, K,
+                                              1 if out.dtype == torch.float32 else 0, splits, self._stream()),
+                        "linear_tc")
+            if splits > 1:
+                self.launches += 1
+            return
         if x.dtype == torch.bfloat16 and self.use_library_gemm:
-            if rows is not None:
-                xg = torch.empty((M, K), dtype=x.dtype, device=x.device)
-                self.gather_rows(xg, x, rows)
-                x = xg
             if out.dtype == torch.float32:
                 torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
                 if bias is not None:
@@ -176,6 +201,20 @@ class CudaOps:
             return
         self._check(self.lib.ts_linear_simt(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows), M, N, K,
                                             _code(x.dtype), _code(out.dtype), self._stream()), "linear")
+
+    def tc_splits(self, M: int, N: int, K: int) -> int:
+        """Pieces K is cut into for a few-token product, so that about one tile lands on every SM."""
+        if M > 128:
+            return 1
+        tiles = -(-N // 128)
+        k_blocks = -(-K // 64)
+        if tiles >= self.num_sms // 2:
+            return 1
+        return max(1, min(self.num_sms // tiles, k_blocks // 2))
+
+    def tc_status(self) -> int:
+        """0 when no tensor-core GEMM block ever gave up on a wait (synchronises the device)."""
+        return int(self.lib.ts_linear_tc_status())
 
     def sample(self, out, logits, fparams, iparams) -> None:
         S, V = logits.shape
