@@ -1,0 +1,92 @@
+"""(c)'s generality: parts chosen layer by layer, a mixer with state of its own registered from
+the test, a position-free layer, partial rotary, a layer that runs twice, a run that reads another
+run's cache, two cache groups.  Runs on the CPU with the kernel twins and, marked gpu, on the GPU."""
+
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests import schedules, tiny, toy
+from tests.twin_ops import TwinOps
+from turingserve_b200 import kernels
+from turingserve_b200.engine.replay import Replayer
+from turingserve_b200.weights import write_random_model
+
+
+def _toy_folder(tmp_path):
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, toy.make(toy.TOY), seed=5, std=0.1)
+    return folder
+
+
+def _run_toy(folder, device, dtype, tol):
+    cfg_json, w = plain.read_folder(folder)
+    reqs = {f"r{i}": tiny.random_ids(n, toy.TOY["vocab"], 50 + i) for i, n in enumerate([40, 7, 61, 23, 35])}
+    expected = {rid: toy.plain_forward(toy.TOY, w, t).numpy() for rid, t in reqs.items()}
+    for sched in ("whole", "decode_tail", "portions", "mixed"):
+        steps = getattr(schedules, sched)(reqs)
+        rp = Replayer(folder, dtype, schedules.peak_tokens(steps), device, page_size=8)
+        assert len(rp.cache.groups) == 2, "full and windowed attention runs live in separate groups"
+        assert sum(s is not None for s in rp.cache.states) == 2, "the running-mean layer runs twice: two states"
+        outs = {}
+        with torch.inference_mode():
+            for s in steps:
+                o = rp.step(s)
+                if o is not None:
+                    outs[s["step"]] = o
+                rp.cache.check()
+        got = schedules.collect(steps, outs)
+        bad = schedules.first_bad(got, expected, tol)
+        assert bad is None, f"{sched}: first wrong place {bad}"
+
+
+def test_toy_architecture_on_cpu(tmp_path):
+    kernels.use(TwinOps())
+    try:
+        _run_toy(_toy_folder(tmp_path), "cpu", torch.float32, 1e-4)
+    finally:
+        kernels.use(None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 0.06)])
+def test_toy_architecture_on_gpu(tmp_path, dtype, tol):
+    kernels.use(None)
+    _run_toy(_toy_folder(tmp_path), "cuda", dtype, tol)
+
+
+def test_schedule_that_repeats_and_shares_on_qwen2(tmp_path):
+    """The run order is data: the same Qwen2 weights with a layer run twice and a shared cache."""
+    from turingserve_b200.config import LayerRun
+    from turingserve_b200.engine.batch import StepEntry
+    from turingserve_b200.engine.runner import ModelRunner, run_needs
+    from turingserve_b200.cache import CacheManager
+    from turingserve_b200.parts.model import DecoderModel
+    from turingserve_b200.weights.loader import load_into
+    kernels.use(TwinOps())
+    try:
+        folder = tiny.make_tiny_folder("B", tmp_path)
+        cfg_json, w = plain.read_folder(folder)
+        sched = [(0, None), (1, None), (1, None), (2, 1), (0, None)]
+        cfg = tiny.tiny_config("B").with_schedule([LayerRun(l, f) for l, f in sched])
+        model = DecoderModel(cfg, torch.float32, "cpu", 256)
+        load_into(model, folder)
+        cache = CacheManager(run_needs(model), 8, 40, 2, torch.float32, "cpu")
+        runner = ModelRunner(model, cache, 128, 2, 256)
+        ids = tiny.random_ids(45, cfg.vocab_size, 9)
+        rc = cache.admit("a")
+        with torch.inference_mode():
+            a = runner.step([StepEntry(rc, ids[:17], list(range(17)))])
+            b = runner.step([StepEntry(rc, ids[17:19], [0, 1])])
+            c = runner.step([StepEntry(rc, ids[19:], list(range(26)))])
+        got = torch.cat([a, b, c])
+        want = plain.forward(cfg_json, w, ids, schedule=sched)
+        assert (got - want).abs().max() < 1e-4
+        assert len(cache.groups[0].runs) == 4                       # run 3 reads run 1's cache and owns none
+    finally:
+        kernels.use(None)

@@ -1,0 +1,157 @@
+"""A toy architecture defined entirely in the test-suite: it registers a mixer with per-request state
+of its own (a running mean), a position-free attention layer, and a run schedule that names a
+layer twice and lets a run read another run's cache.  Nothing under ``turingserve_b200`` knows
+about it; it is no model of anyone's.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from turingserve_b200.config.model_config import (
+    AttentionSpec, GatedMLPSpec, LayerRun, LayerSpec, ModelConfig, RMSNormSpec, RotarySpec)
+from turingserve_b200.config.registry import Architecture, LayerTensorNames, TensorNames, register_architecture
+from turingserve_b200.parts.base import BuildContext, Mixer, ParamSpec, StateNeed, register
+
+NAME = "ToyStateLM"
+
+
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    """y_t = W . mean(x_0 .. x_t): the state is the running sum and the count."""
+
+    kind: str = "running_mean"
+
+
+class RunningMeanMixer(Mixer):
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.h = ctx.hidden_size
+        self.w = None
+
+    def parameters(self):
+        return {"proj.weight": ParamSpec((self.h, self.h))}
+
+    def load(self, t):
+        self.w = t["proj.weight"]
+
+    def state_need(self):
+        return StateNeed((self.h + 1,), torch.float32)
+
+    def forward(self, x, step, cache, state):
+        slots = step.state_slots.tolist()
+        out = torch.empty_like(x)
+        at = 0
+        for b, n in enumerate(step.q_lens):
+            if step.seq_lens is not None and n == 0:
+                continue
+            st = state[slots[b]]
+            if step.starts[b] == 0:
+                st.zero_()                                   # the first portion of a request starts clean
+            rows = x[at:at + n].float()
+            sums = rows.cumsum(0) + st[: self.h]
+            counts = st[self.h] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+            mean = (sums / counts[:, None]).to(x.dtype)
+            out[at:at + n] = F.linear(mean.float(), self.w.float()).to(x.dtype)
+            st[: self.h] = sums[-1]
+            st[self.h] = counts[-1]
+            at += n
+        return out
+
+
+register("mixer", "running_mean", RunningMeanMixer)
+
+
+def parse_config(c: dict, gen=None) -> ModelConfig:
+    h, heads, kv, d = c["width"], c["heads"], c["kv_heads"], c["head_size"]
+    norm = RMSNormSpec(eps=c["eps"])
+    ffn = GatedMLPSpec(intermediate_size=c["ffn_width"])
+    rope = RotarySpec(theta=c["theta"], rotary_dim=c.get("rotary_dim", d), max_positions=c["max_positions"])
+    layers = []
+    for kind in c["mixers"]:
+        if kind == "mean":
+            mixer = RunningMeanSpec()
+        else:
+            mixer = AttentionSpec(num_heads=heads, num_kv_heads=kv, head_dim=d, scale=c.get("scale", d ** -0.5),
+                                  qkv_bias=False, out_bias=True, position=None if kind == "nope" else rope,
+                                  window=c.get("window") if kind == "window" else None)
+        layers.append(LayerSpec(mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm))
+    schedule = tuple(LayerRun(l, f) for l, f in c.get("schedule", [(i, None) for i in range(len(layers))]))
+    return ModelConfig(architecture=NAME, hidden_size=h, vocab_size=c["vocab"], layers=tuple(layers),
+                       schedule=schedule, final_norm=norm, tie_word_embeddings=False,
+                       max_position_embeddings=c["max_positions"])
+
+
+def tensor_names(cfg: ModelConfig) -> TensorNames:
+    layers = tuple(LayerTensorNames(mixer=f"blocks.{i}.mix.", feed_forward=f"blocks.{i}.ffn.",
+                                    mixer_norm=f"blocks.{i}.norm_a.", ffn_norm=f"blocks.{i}.norm_b.")
+                   for i in range(len(cfg.layers)))
+    return TensorNames(embedding="embed.weight", lm_head="head.weight", final_norm="norm_out.", layers=layers)
+
+
+_JSON: dict[int, dict] = {}
+
+
+def to_config_json(cfg: ModelConfig) -> dict:
+    return _JSON[id(cfg)]
+
+
+def make(c: dict) -> ModelConfig:
+    c = {"architectures": [NAME], **c}
+    cfg = parse_config(c)
+    _JSON[id(cfg)] = c
+    return cfg
+
+
+register_architecture(Architecture(NAME, parse_config, tensor_names, to_config_json))
+
+
+# -- a plain whole-sequence implementation of the toy model (for the tests only) ------------------------
+def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
+    from tests import plain_qwen2 as plain
+    x_ids = torch.as_tensor(ids, dtype=torch.long)
+    T = len(ids)
+    h = w["embed.weight"][x_ids]
+    d, H, KVH = c["head_size"], c["heads"], c["kv_heads"]
+    rot = c.get("rotary_dim", d)
+    cos, sin = plain.rope_tables(rot, c["theta"], T)
+    pos = torch.arange(T)
+    kept = []
+    schedule = c.get("schedule", [(i, None) for i in range(len(c["mixers"]))])
+
+    def rope(t):
+        if rot == d:
+            return plain.apply_rope(t, pos, cos, sin)
+        return torch.cat([plain.apply_rope(t[..., :rot], pos, cos, sin), t[..., rot:]], dim=-1)
+
+    for layer, cache_from in schedule:
+        p = f"blocks.{layer}."
+        kind = c["mixers"][layer]
+        x = plain.rmsnorm(h, w[p + "norm_a.weight"], c["eps"])
+        if kind == "mean":
+            mean = x.cumsum(0) / torch.arange(1, T + 1)[:, None]
+            a = F.linear(mean, w[p + "mix.proj.weight"])
+            kept.append(None)
+        else:
+            q = F.linear(x, w[p + "mix.q_proj.weight"]).view(T, H, d)
+            k = F.linear(x, w[p + "mix.k_proj.weight"]).view(T, KVH, d)
+            v = F.linear(x, w[p + "mix.v_proj.weight"]).view(T, KVH, d)
+            if kind != "nope":
+                q, k = rope(q), rope(k)
+            if cache_from is not None:
+                k, v = kept[cache_from]
+            kept.append((k, v))
+            a = plain.attention(q, k, v, c.get("scale", d ** -0.5), c.get("window") if kind == "window" else None)
+            a = F.linear(a, w[p + "mix.o_proj.weight"], w[p + "mix.o_proj.bias"])
+        h = h + a
+        x = plain.rmsnorm(h, w[p + "norm_b.weight"], c["eps"])
+        h = h + plain.mlp(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+    return F.linear(plain.rmsnorm(h, w["norm_out.weight"], c["eps"]), w["head.weight"]).float()
+
+
+TOY = {"width": 48, "heads": 6, "kv_heads": 2, "head_size": 16, "rotary_dim": 8, "ffn_width": 72, "vocab": 211,
+       "eps": 2e-5, "theta": 777.0, "max_positions": 300, "window": 9, "scale": 0.3,
+       "mixers": ["rope", "mean", "window", "nope"],
+       "schedule": [(0, None), (1, None), (2, None), (0, None), (3, None), (3, 4), (1, None)]}

@@ -13,7 +13,8 @@
 // probabilities are rounded to bfloat16 for the second product as the reference does
 // (triton_prefill_attention.py:58).  Warps keep independent online-softmax states over disjoint
 // keys and merge them through shared memory at the end; with more than one split the block
-// writes an unnormalised partial (m, l, acc) to scratch and `merge` finishes the job.
+// writes an unnormalised partial (m, l, acc) to scratch, and the block that finishes last for a
+// (request, kv head) merges the partials (no second launch, no waiting: a ticket counter).
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -30,7 +31,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
                         const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
                         const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
                         const int* __restrict__ q_start, const int* __restrict__ seq_lens, int table_width,
-                        int H, int KVH, int page, float scale, int window, int nsplit) {
+                        int H, int KVH, int page, float scale, int window, int nsplit, int* __restrict__ counters) {
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int KS = D / 16;                      // k-steps of the score product
   constexpr int NT = D / 8;                       // n-tiles of the output
@@ -233,34 +234,44 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
       }
     }
   }
-}
+  if (nsplit == 1) return;
 
-// out[b, h, :] = sum_s acc_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)   (all in 32-bit)
-__global__ void attention_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
-                                              const float* __restrict__ part_ml, const int* __restrict__ q_start,
-                                              int H, int D, int nsplit) {
-  const int h = blockIdx.x, b = blockIdx.y;
-  const size_t base = ((size_t)b * H + h) * nsplit;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  const int row = q_start[b];
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  // The block that finishes last for this (request, kv head) merges all splits, in split order:
+  //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&counters[b * KVH + kvh], 1);
+    is_last = (ticket == nsplit - 1);
+    if (is_last) counters[b * KVH + kvh] = 0;                      // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+    const int g = idx / D, d = idx % D;
+    const int h = kvh * G + g;
+    const size_t base = ((size_t)b * H + h) * nsplit;
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < nsplit; ++s2) M = fmaxf(M, __ldcg(&part_ml[(base + s2) * 2]));
     float L = 0.f, acc = 0.f;
     if (M > -INFINITY) {
-      for (int s = 0; s < nsplit; ++s) {
-        const float f = exp2f(part_ml[(base + s) * 2] - M);
-        L += part_ml[(base + s) * 2 + 1] * f;
-        acc += part_acc[(base + s) * D + d] * f;
+      for (int s2 = 0; s2 < nsplit; ++s2) {
+        const float f = exp2f(__ldcg(&part_ml[(base + s2) * 2]) - M);
+        L += __ldcg(&part_ml[(base + s2) * 2 + 1]) * f;
+        acc += __ldcg(&part_acc[(base + s2) * D + d]) * f;
       }
     }
-    out[(size_t)row * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    out[(size_t)row_q * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
 }
 
 template <int D>
 int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, const bf16* k_cache,
                   const bf16* v_cache, const int* block_tables, const int* q_start, const int* seq_lens, int B,
-                  int table_width, int H, int KVH, int page, float scale, int window, int nsplit, cudaStream_t s) {
+                  int table_width, int H, int KVH, int page, float scale, int window, int nsplit, int* counters,
+                  cudaStream_t s) {
   const size_t stage_bytes = (size_t)2 * DEC_STAGES * DEC_TILE * D * 2;
   const size_t merge_bytes = sizeof(float) * ((size_t)2 * DEC_WARPS * 16 + (size_t)DEC_WARPS * 16 * D);
   const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -272,9 +283,7 @@ int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, c
   }
   attention_decode_kernel<D><<<dim3(nsplit, KVH, B), DEC_WARPS * 32, smem, s>>>(
       out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
-      scale, window, nsplit);
-  if (nsplit > 1)
-    attention_decode_merge_kernel<<<dim3(H, B), D <= 128 ? D : 128, 0, s>>>(out, part_acc, part_ml, q_start, H, D, nsplit);
+      scale, window, nsplit, counters);
   TS_LAUNCH_CHECK();
 }
 
@@ -291,8 +300,9 @@ TS_API long long ts_attention_decode_scratch_floats(int B, int H, int D, int nsp
 }
 
 // One query token per request (rows q_start[b]); `scratch` holds ts_attention_decode_scratch_floats()
-// floats when nsplit > 1.  window <= 0: none.
-TS_API int ts_attention_decode(void* out, void* scratch, const void* qkv, const void* k_cache, const void* v_cache,
+// floats when nsplit > 1, and `counters` B * KVH ints that are zero on entry (the kernel leaves them
+// zero).  window <= 0: none.
+TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const void* qkv, const void* k_cache, const void* v_cache,
                                const int* block_tables, const int* q_start, const int* seq_lens, int B,
                                int table_width, int H, int KVH, int D, int page, float scale, int window,
                                int nsplit, void* stream) {
@@ -300,13 +310,14 @@ TS_API int ts_attention_decode(void* out, void* scratch, const void* qkv, const 
   if (!ts_attention_decode_supported(H, KVH, D, TS_BF16))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode: H=%d KVH=%d D=%d is not taken by this kernel", H, KVH, D);
   if (nsplit < 1 || nsplit > 65535 || B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode: nsplit=%d B=%d", nsplit, B);
-  if (nsplit > 1 && scratch == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_attention_decode: %d splits need scratch", nsplit);
+  if (nsplit > 1 && (scratch == nullptr || counters == nullptr))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_attention_decode: %d splits need scratch and counters", nsplit);
   float* acc = (float*)scratch;
   float* ml = acc ? acc + (size_t)B * H * nsplit * D : nullptr;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
     return launch_decode<64>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
-                             block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, s);
+                             block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
   return launch_decode<128>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
-                            block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, s);
+                            block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
 }

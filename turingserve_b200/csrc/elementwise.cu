@@ -90,11 +90,97 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* 
   }
 }
 
+// Latency-lean variant for rows whose length is a multiple of one 16-byte vector: every thread
+// loads its vectors once, keeps them in registers across the reduction, and writes once.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<bf16> { static constexpr int N = 8; };
+
+template <typename T, int N> __device__ __forceinline__ void load_vec(const T* p, float (&f)[N]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] = to_f(e[i]);
+}
+template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, const float (&f)[N]) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) e[i] = from_f<T>(f[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+template <typename T, typename WT, int CHUNKS>
+__global__ void rmsnorm_vec_kernel(T* __restrict__ out, const T* __restrict__ x, T* residual,
+                                   const WT* __restrict__ w, float eps, int hidden) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float v[CHUNKS][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * N;
+    if (i < hidden) {
+      load_vec<T, N>(x + base + i, v[c]);
+      if (residual != nullptr) {
+        float r[N];
+        load_vec<T, N>(residual + base + i, r);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[c][k] = round_to<T>(v[c][k] + r[k]);
+        store_vec<T, N>(residual + base + i, v[c]);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) ss += v[c][k] * v[c][k];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * N;
+    if (i < hidden) {
+      float y[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) y[k] = to_f(w[i + k]) * round_to<T>(v[c][k] * rstd);
+      store_vec<T, N>(out + base + i, y);
+    }
+  }
+}
+
+template <typename T, typename WT>
+bool launch_rmsnorm_vec(T* out, const T* x, T* residual, const WT* w, float eps, int rows, int hidden, cudaStream_t s) {
+  constexpr int N = Vec16<T>::N;
+  if (hidden % N) return false;
+  if (((uintptr_t)out | (uintptr_t)x | (uintptr_t)residual) & 15) return false;
+  const int vecs = hidden / N;
+  auto threads_for = [&](int chunks) { return ((vecs + chunks - 1) / chunks + 31) / 32 * 32; };
+  if (threads_for(1) <= 1024)
+    rmsnorm_vec_kernel<T, WT, 1><<<rows, threads_for(1), 0, s>>>(out, x, residual, w, eps, hidden);
+  else if (threads_for(2) <= 1024)
+    rmsnorm_vec_kernel<T, WT, 2><<<rows, threads_for(2), 0, s>>>(out, x, residual, w, eps, hidden);
+  else if (threads_for(4) <= 1024)
+    rmsnorm_vec_kernel<T, WT, 4><<<rows, threads_for(4), 0, s>>>(out, x, residual, w, eps, hidden);
+  else
+    return false;
+  return true;
+}
+
 TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, float eps, int T,
                       int hidden, int dtype, int w_dtype, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  bool done = false;
+  if (dtype == TS_F32 && w_dtype == TS_F32)
+    done = launch_rmsnorm_vec<float, float>((float*)out, (const float*)x, (float*)residual, (const float*)w, eps, T, hidden, s);
+  else if (dtype == TS_BF16 && w_dtype == TS_BF16)
+    done = launch_rmsnorm_vec<bf16, bf16>((bf16*)out, (const bf16*)x, (bf16*)residual, (const bf16*)w, eps, T, hidden, s);
+  else if (dtype == TS_BF16 && w_dtype == TS_F32)
+    done = launch_rmsnorm_vec<bf16, float>((bf16*)out, (const bf16*)x, (bf16*)residual, (const float*)w, eps, T, hidden, s);
+  if (done) {
+    TS_LAUNCH_CHECK();
+  }
   if (dtype == TS_F32 && w_dtype == TS_F32)
     rmsnorm_kernel<float, float><<<T, threads, 0, s>>>((float*)out, (const float*)x, (float*)residual,
                                                        (const float*)w, eps, hidden);
@@ -194,6 +280,66 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// Latency-lean variant for bfloat16 when half the rotary width is a multiple of 8: one thread
+// rotates 8 pairs (two 16-byte vectors) or copies one 16-byte vector of v.
+__global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                         const int* __restrict__ slots, int H, int KVH, int D, int rot, int page) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = (k_cache != nullptr) ? slots[t] : -1;
+  const int half = rot / 2;
+  const int hv = half / 8;                          // vectors per half
+  const int pv = (D - rot) / 8;                     // pass-through vectors per head
+  bf16* row = qkv + (size_t)t * (H + 2 * KVH) * D;
+  size_t cache_base = 0;
+  if (slot >= 0) cache_base = ((size_t)(slot / page) * KVH * page + (size_t)(slot % page)) * D;
+  const size_t head_stride = (size_t)page * D;
+  const int per_head = hv + pv;
+  const int qk_items = (H + KVH) * per_head;
+  const int v_items = slot >= 0 ? KVH * (D / 8) : 0;
+  for (int idx = threadIdx.x; idx < qk_items + v_items; idx += blockDim.x) {
+    if (idx < qk_items) {
+      const int head = idx / per_head, j = idx % per_head;
+      bf16* x = row + (size_t)head * D;
+      bf16* kdst = (head >= H && slot >= 0) ? k_cache + cache_base + (size_t)(head - H) * head_stride : nullptr;
+      if (j < hv) {
+        const int i = j * 8;
+        float x1[8], x2[8], o1[8], o2[8];
+        load_vec<bf16, 8>(x + i, x1);
+        load_vec<bf16, 8>(x + i + half, x2);
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i);
+        const float4 c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i);
+        const float4 s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i + 4);
+        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float c = round_to<bf16>(cs[k]), sv = round_to<bf16>(sn[k]);
+          o1[k] = x1[k] * c - x2[k] * sv;
+          o2[k] = x2[k] * c + x1[k] * sv;
+        }
+        store_vec<bf16, 8>(x + i, o1);
+        store_vec<bf16, 8>(x + i + half, o2);
+        if (kdst != nullptr) {
+          store_vec<bf16, 8>(kdst + i, o1);
+          store_vec<bf16, 8>(kdst + i + half, o2);
+        }
+      } else if (kdst != nullptr) {
+        const int d = rot + (j - hv) * 8;
+        *reinterpret_cast<uint4*>(kdst + d) = *reinterpret_cast<const uint4*>(x + d);
+      }
+    } else {
+      const int vi = idx - qk_items;
+      const int head = vi / (D / 8), d = (vi % (D / 8)) * 8;
+      const bf16* v = row + (size_t)(H + KVH) * D + (size_t)head * D + d;
+      *reinterpret_cast<uint4*>(v_cache + cache_base + (size_t)head * head_stride + d) = *reinterpret_cast<const uint4*>(v);
+    }
+  }
+}
+
 TS_API int ts_rope_kv_write(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
                             void* k_cache, void* v_cache, const int* slots, int T, int H, int KVH,
                             int D, int rot, int page, int dtype, void* stream) {
@@ -201,6 +347,15 @@ TS_API int ts_rope_kv_write(void* qkv, const int* positions, const float* cos_t,
   if (rot < 0 || rot > D || (rot & 1)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: rotary_dim %d for head_dim %d", rot, D);
   if (rot > 0 && (cos_t == nullptr || sin_t == nullptr)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: tables missing");
   cudaStream_t s = (cudaStream_t)stream;
+  const int half = rot / 2;
+  const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
+  if (dtype == TS_BF16 && rot > 0 && (half % 8) == 0 && (D % 8) == 0 && aligned) {
+    const int items = (H + KVH) * (half / 8 + (D - rot) / 8) + KVH * (D / 8);
+    const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+    rope_kv_write_vec_kernel<<<T, threads, 0, s>>>((bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
+                                                   slots, H, KVH, D, rot, page);
+    TS_LAUNCH_CHECK();
+  }
   if (dtype == TS_F32)
     rope_kv_write_kernel<float><<<T, 256, 0, s>>>((float*)qkv, positions, cos_t, sin_t, (float*)k_cache,
                                                   (float*)v_cache, slots, H, KVH, D, rot, page);

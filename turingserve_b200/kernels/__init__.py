@@ -14,6 +14,7 @@ tensor-core kernel takes the shape; float32 products always use this library's F
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -61,7 +62,7 @@ class CudaOps:
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
-            "ts_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+            "ts_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
             "ts_attention_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
             "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
@@ -77,13 +78,14 @@ class CudaOps:
         self.lib.ts_linear_tc_supported.restype = c_int
         self.lib.ts_linear_tc_status.argtypes = []
         self.lib.ts_linear_tc_status.restype = c_int
-        self.use_tc_gemm = False
+        self.use_tc_gemm = os.environ.get("TURINGSERVE_B200_GEMM", "library") == "tc"
         self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_prefill_supported.restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self.num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self._scratch: torch.Tensor | None = None
+        self._counters: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
         self.launches = 0           # kernels of this library launched (graph replays add their share)
@@ -149,15 +151,16 @@ class CudaOps:
         if self.use_fast_attention and step.num_decode > 0 and self.lib.ts_attention_decode_supported(H, KVH, D, code):
             nd = step.num_decode
             nsplit = self.decode_splits(nd, KVH, step.max_seq_len)
-            scratch = None
+            scratch = counters = None
             if nsplit > 1:
                 scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), qkv.device)
+                if self._counters is None or self._counters.numel() < nd * KVH or self._counters.device != qkv.device:
+                    self._counters = torch.zeros(max(nd * KVH, 1 << 16), dtype=torch.int32, device=qkv.device)
+                counters = self._counters
             self._check(self.lib.ts_attention_decode(
-                _ptr(out), _ptr(scratch), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                _ptr(out), _ptr(scratch), _ptr(counters), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                 _ptr(step.q_start), _ptr(step.seq_lens), nd, width, H, KVH, D, page_size, float(scale), w,
                 nsplit, self._stream()), "attention_decode")
-            if nsplit > 1:
-                self.launches += 1
         if nd == B:
             return
         if self.use_fast_attention and self.lib.ts_attention_prefill_supported(H, KVH, D, code):
