@@ -279,7 +279,7 @@ def test_linear_tensor_core(ops, M, N, K):
     x, w, b = _rand((M, K), torch.bfloat16, 30, 1.0), _rand((N, K), torch.bfloat16, 31, 0.05), _rand((N,), torch.bfloat16, 32)
     ref = (x.double() @ w.double().T + b.double()).float()
     xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
-    ops.use_tc_gemm = True
+    ops.gemm_mode = "tc"
     try:
         out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
         ops.linear(out, xd, wd, bd)
@@ -293,4 +293,4 @@ def test_linear_tensor_core(ops, M, N, K):
         torch.testing.assert_close(outr.cpu(), (ref - b.float())[rows.long()], atol=2e-3, rtol=1e-3)
         assert ops.tc_status() == 0, "a block of the tensor-core product gave up on a wait"
     finally:
-        ops.use_tc_gemm = False
+        ops.gemm_mode = "library"

@@ -32,6 +32,8 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
                         const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
                         const int* __restrict__ q_start, const int* __restrict__ seq_lens, int table_width,
                         int H, int KVH, int page, float scale, int window, int nsplit, int* __restrict__ counters) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int KS = D / 16;                      // k-steps of the score product
   constexpr int NT = D / 8;                       // n-tiles of the output
@@ -281,7 +283,7 @@ int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, c
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  attention_decode_kernel<D><<<dim3(nsplit, KVH, B), DEC_WARPS * 32, smem, s>>>(
+  ts_launch(attention_decode_kernel<D>, dim3(dim3(nsplit, KVH, B)), dim3(DEC_WARPS * 32), smem, s, 
       out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
       scale, window, nsplit, counters);
   TS_LAUNCH_CHECK();

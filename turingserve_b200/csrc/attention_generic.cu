@@ -27,6 +27,8 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ qkv, const T
                          const T* __restrict__ v_cache, const int* __restrict__ block_tables,
                          const int* __restrict__ q_start, const int* __restrict__ seq_lens,
                          int table_width, int H, int KVH, int D, int page, float scale, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = H / KVH;
@@ -162,7 +164,7 @@ int launch(void* out, const void* qkv, const void* k_cache, const void* v_cache,
     configured = smem;
   }
   dim3 grid(ceil_div(max_q_len * G, ROWS), KVH, B);
-  attention_generic_kernel<T><<<grid, NWARPS * 32, smem, s>>>(
+  ts_launch(attention_generic_kernel<T>, dim3(grid), dim3(NWARPS * 32), smem, s, 
       (T*)out, (const T*)qkv, (const T*)k_cache, (const T*)v_cache, block_tables, q_start, seq_lens,
       table_width, H, KVH, D, page, scale, window);
   TS_LAUNCH_CHECK();

@@ -30,6 +30,8 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, c
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
                          const int* __restrict__ q_start, const int* __restrict__ seq_lens, int table_width,
                          int H, int KVH, int page, float scale, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CH = D / 8, KS = D / 16, NT = D / 8;
   extern __shared__ __align__(128) unsigned char smem[];
   const int b = blockIdx.z, kvh = blockIdx.y;
@@ -243,7 +245,7 @@ int launch_prefill(bf16* out, const bf16* qkv, const bf16* k_cache, const bf16* 
   }
   const int G = H / KVH;
   dim3 grid(ceil_div(max_q_len * G, PF_ROWS), KVH, B);
-  attention_prefill_kernel<D><<<grid, PF_WARPS * 32, smem, s>>>(out, qkv, k_cache, v_cache, block_tables, q_start,
+  ts_launch(attention_prefill_kernel<D>, dim3(grid), dim3(PF_WARPS * 32), smem, s, out, qkv, k_cache, v_cache, block_tables, q_start,
                                                               seq_lens, table_width, H, KVH, page, scale, window);
   TS_LAUNCH_CHECK();
 }

@@ -73,3 +73,29 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch: a kernel launched with ts_launch may start while its predecessor
+// in the stream is still running.  Every kernel calls pdl_launch_dependents() first (its successor
+// may be scheduled) and pdl_wait() before it reads or writes anything a predecessor may touch;
+// because every kernel in a chain waits, completion stays ordered along the whole chain.  Both are
+// no-ops for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool ts_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t ts_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ts_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -32,9 +34,9 @@ TS_API int ts_embedding(void* out, const void* table, const int* ids, int T, int
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TS_F32)
-    embedding_kernel<float><<<T, 128, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab);
+    ts_launch(embedding_kernel<float>, dim3(T), dim3(128), 0, s, (float*)out, (const float*)table, ids, hidden, vocab);
   else if (dtype == TS_BF16)
-    embedding_kernel<bf16><<<T, 128, 0, s>>>((bf16*)out, (const bf16*)table, ids, hidden, vocab);
+    ts_launch(embedding_kernel<bf16>, dim3(T), dim3(128), 0, s, (bf16*)out, (const bf16*)table, ids, hidden, vocab);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_embedding: dtype %d", dtype);
   TS_LAUNCH_CHECK();
@@ -44,6 +46,8 @@ TS_API int ts_embedding(void* out, const void* table, const int* ids, int T, int
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
                                    const int* __restrict__ rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
   const T* src = x + (size_t)rows[blockIdx.x] * width;
   T* dst = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
@@ -54,9 +58,9 @@ TS_API int ts_gather_rows(void* out, const void* x, const int* rows, int S, int 
   if (S <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TS_F32)
-    gather_rows_kernel<float><<<S, 256, 0, s>>>((float*)out, (const float*)x, rows, width);
+    ts_launch(gather_rows_kernel<float>, dim3(S), dim3(256), 0, s, (float*)out, (const float*)x, rows, width);
   else if (dtype == TS_BF16)
-    gather_rows_kernel<bf16><<<S, 256, 0, s>>>((bf16*)out, (const bf16*)x, rows, width);
+    ts_launch(gather_rows_kernel<bf16>, dim3(S), dim3(256), 0, s, (bf16*)out, (const bf16*)x, rows, width);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_gather_rows: dtype %d", dtype);
   TS_LAUNCH_CHECK();
@@ -70,6 +74,8 @@ TS_API int ts_gather_rows(void* out, const void* x, const int* rows, int S, int 
 template <typename T, typename WT>
 __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* residual,
                                const WT* __restrict__ w, float eps, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
   float ss = 0.f;
@@ -113,6 +119,8 @@ template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, con
 template <typename T, typename WT, int CHUNKS>
 __global__ void rmsnorm_vec_kernel(T* __restrict__ out, const T* __restrict__ x, T* residual,
                                    const WT* __restrict__ w, float eps, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int N = Vec16<T>::N;
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
@@ -156,11 +164,11 @@ bool launch_rmsnorm_vec(T* out, const T* x, T* residual, const WT* w, float eps,
   const int vecs = hidden / N;
   auto threads_for = [&](int chunks) { return ((vecs + chunks - 1) / chunks + 31) / 32 * 32; };
   if (threads_for(1) <= 1024)
-    rmsnorm_vec_kernel<T, WT, 1><<<rows, threads_for(1), 0, s>>>(out, x, residual, w, eps, hidden);
+    ts_launch(rmsnorm_vec_kernel<T, WT, 1>, dim3(rows), dim3(threads_for(1)), 0, s, out, x, residual, w, eps, hidden);
   else if (threads_for(2) <= 1024)
-    rmsnorm_vec_kernel<T, WT, 2><<<rows, threads_for(2), 0, s>>>(out, x, residual, w, eps, hidden);
+    ts_launch(rmsnorm_vec_kernel<T, WT, 2>, dim3(rows), dim3(threads_for(2)), 0, s, out, x, residual, w, eps, hidden);
   else if (threads_for(4) <= 1024)
-    rmsnorm_vec_kernel<T, WT, 4><<<rows, threads_for(4), 0, s>>>(out, x, residual, w, eps, hidden);
+    ts_launch(rmsnorm_vec_kernel<T, WT, 4>, dim3(rows), dim3(threads_for(4)), 0, s, out, x, residual, w, eps, hidden);
   else
     return false;
   return true;
@@ -182,13 +190,13 @@ TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, f
     TS_LAUNCH_CHECK();
   }
   if (dtype == TS_F32 && w_dtype == TS_F32)
-    rmsnorm_kernel<float, float><<<T, threads, 0, s>>>((float*)out, (const float*)x, (float*)residual,
+    ts_launch(rmsnorm_kernel<float, float>, dim3(T), dim3(threads), 0, s, (float*)out, (const float*)x, (float*)residual,
                                                        (const float*)w, eps, hidden);
   else if (dtype == TS_BF16 && w_dtype == TS_BF16)
-    rmsnorm_kernel<bf16, bf16><<<T, threads, 0, s>>>((bf16*)out, (const bf16*)x, (bf16*)residual,
+    ts_launch(rmsnorm_kernel<bf16, bf16>, dim3(T), dim3(threads), 0, s, (bf16*)out, (const bf16*)x, (bf16*)residual,
                                                      (const bf16*)w, eps, hidden);
   else if (dtype == TS_BF16 && w_dtype == TS_F32)
-    rmsnorm_kernel<bf16, float><<<T, threads, 0, s>>>((bf16*)out, (const bf16*)x, (bf16*)residual,
+    ts_launch(rmsnorm_kernel<bf16, float>, dim3(T), dim3(threads), 0, s, (bf16*)out, (const bf16*)x, (bf16*)residual,
                                                       (const float*)w, eps, hidden);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_rmsnorm: dtype %d with scale dtype %d", dtype, w_dtype);
@@ -200,6 +208,8 @@ TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, f
 // (turingserve/ops/reference.py:26-28; rounding as triton_silu_mul.py:15-18).
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
@@ -217,9 +227,9 @@ TS_API int ts_silu_mul(void* out, const void* gu, int T, int inter, int dtype, v
   const size_t total = (size_t)T * inter;
   const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
   if (dtype == TS_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, inter, total);
+    ts_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)gu, inter, total);
   else if (dtype == TS_BF16)
-    silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gu, inter, total);
+    ts_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, total);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_silu_mul: dtype %d", dtype);
   TS_LAUNCH_CHECK();
@@ -238,6 +248,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      const int* __restrict__ slots, int H, int KVH, int D, int rot,
                                      int page) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = (k_cache != nullptr) ? slots[t] : -1;
@@ -286,6 +298,8 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                          const int* __restrict__ slots, int H, int KVH, int D, int rot, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = (k_cache != nullptr) ? slots[t] : -1;
@@ -352,15 +366,15 @@ TS_API int ts_rope_kv_write(void* qkv, const int* positions, const float* cos_t,
   if (dtype == TS_BF16 && rot > 0 && (half % 8) == 0 && (D % 8) == 0 && aligned) {
     const int items = (H + KVH) * (half / 8 + (D - rot) / 8) + KVH * (D / 8);
     const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
-    rope_kv_write_vec_kernel<<<T, threads, 0, s>>>((bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
+    ts_launch(rope_kv_write_vec_kernel, dim3(T), dim3(threads), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
                                                    slots, H, KVH, D, rot, page);
     TS_LAUNCH_CHECK();
   }
   if (dtype == TS_F32)
-    rope_kv_write_kernel<float><<<T, 256, 0, s>>>((float*)qkv, positions, cos_t, sin_t, (float*)k_cache,
+    ts_launch(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, s, (float*)qkv, positions, cos_t, sin_t, (float*)k_cache,
                                                   (float*)v_cache, slots, H, KVH, D, rot, page);
   else if (dtype == TS_BF16)
-    rope_kv_write_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache,
+    ts_launch(rope_kv_write_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache,
                                                  (bf16*)v_cache, slots, H, KVH, D, rot, page);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_rope_kv_write: dtype %d", dtype);

@@ -17,3 +17,8 @@ TS_API const char* ts_last_error() { return g_error; }
 
 // Compiled-for architecture and ABI version, so the Python side can refuse a stale library.
 TS_API int ts_abi_version() { return 3; }
+
+// Programmatic dependent launch for this library's kernels (on by default).
+static bool g_pdl = true;
+bool ts_pdl_enabled() { return g_pdl; }
+TS_API void ts_set_pdl(int on) { g_pdl = on != 0; }

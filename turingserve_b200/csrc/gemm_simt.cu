@@ -16,6 +16,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(TO* __restrict__ out, const TI* __restrict__ x, const TI* __restrict__ w,
                  const TI* __restrict__ bias, const int* __restrict__ rows, int M, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ __align__(16) float As[BK][BM + PAD];
   __shared__ __align__(16) float Ws[BK][BN + PAD];
   const int tid = threadIdx.x;
@@ -75,13 +77,13 @@ TS_API int ts_linear_simt(void* out, const void* x, const void* w, const void* b
   dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
   if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_linear: M = %d too large for one launch", M);
   if (dtype == TS_F32 && out_dtype == TS_F32)
-    gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>((float*)out, (const float*)x, (const float*)w,
+    ts_launch(gemm_simt_kernel<float, float>, dim3(grid), dim3(256), 0, s, (float*)out, (const float*)x, (const float*)w,
                                                         (const float*)bias, rows, M, N, K);
   else if (dtype == TS_BF16 && out_dtype == TS_BF16)
-    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, (const bf16*)w,
+    ts_launch(gemm_simt_kernel<bf16, bf16>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, (const bf16*)w,
                                                       (const bf16*)bias, rows, M, N, K);
   else if (dtype == TS_BF16 && out_dtype == TS_F32)
-    gemm_simt_kernel<bf16, float><<<grid, 256, 0, s>>>((float*)out, (const bf16*)x, (const bf16*)w,
+    ts_launch(gemm_simt_kernel<bf16, float>, dim3(grid), dim3(256), 0, s, (float*)out, (const bf16*)x, (const bf16*)w,
                                                        (const bf16*)bias, rows, M, N, K);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_linear: dtype %d -> %d", dtype, out_dtype);

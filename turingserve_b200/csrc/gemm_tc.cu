@@ -116,7 +116,7 @@ struct GemmArgs {
 
 // BN: tile columns (UMMA N).  SWAP: the tile rows are weight rows (outputs), columns are tokens.
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                const GemmArgs args) {
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -131,6 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * BM;                 // first tile row (tokens, or weight rows when SWAP)
   const int col0 = blockIdx.y * BN;
@@ -159,14 +160,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
+      // The weights do not depend on the kernel before this one: their first stages are on the
+      // way before this block waits for its predecessor; the activations follow after the wait.
+      const CUtensorMap* w_map = SWAP ? &map_rows : &map_cols;
+      const CUtensorMap* x_map = SWAP ? &map_cols : &map_rows;
+      unsigned char* w_s = SWAP ? a_s : b_s;
+      unsigned char* x_s = SWAP ? b_s : a_s;
+      constexpr uint32_t W_BYTES = SWAP ? A_BYTES : B_BYTES, X_BYTES = SWAP ? B_BYTES : A_BYTES;
+      const int w_row = SWAP ? row0 : col0, x_row = SWAP ? col0 : row0;
+      const int early = n_kb < STAGES ? n_kb : STAGES;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
+        tma_load_2d(w_s + i * W_BYTES, w_map, (kb_begin + i) * BK, w_row, &full[i]);
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(x_s + i * X_BYTES, x_map, (kb_begin + i) * BK, x_row, &full[i]);
+      for (int i = early; i < n_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, args.status, 1, abort_flag)) break;
         mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
         const int k = (kb_begin + i) * BK;
-        tma_load_2d(a_s + s * A_BYTES, &map_rows, k, row0, &full[s]);
-        tma_load_2d(b_s + s * B_BYTES, &map_cols, k, col0, &full[s]);
+        tma_load_2d(w_s + s * W_BYTES, w_map, k, w_row, &full[s]);
+        tma_load_2d(x_s + s * X_BYTES, x_map, k, x_row, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -193,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     // epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
     const int q = warp & 3;
     const int r = q * 32 + lane;                   // tile row of this thread
+    pdl_wait();                                    // nothing is written before the predecessor is done
     bool ok = n_kb > 0 && mbar_wait(accum, 0, args.status, 3, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
@@ -265,6 +283,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
 // out[m, n] = sum over splits (ascending) of part[s, m, n] + bias[n]
 __global__ void splitk_reduce_kernel(void* out, const float* __restrict__ part, const bf16* __restrict__ bias,
                                      int M, int N, int splits, int out_is_float) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)M * N;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
@@ -348,7 +368,7 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmA
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_linear_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BN, STAGES, SWAP><<<grid, GEMM_THREADS, smem, s>>>(rows_map, cols_map, args);
+  ts_launch(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map, cols_map, args);
   TS_LAUNCH_CHECK();
 }
 
@@ -405,10 +425,10 @@ TS_API int ts_linear_tc(void* out, const void* x, const void* w, const void* bia
     if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
       TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: cuTensorMapEncodeTiled failed");
     dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
-    if (bn == 16) rc = launch<16, 8, true>(rows_map, cols_map, a, grid, s);
-    else if (bn == 32) rc = launch<32, 8, true>(rows_map, cols_map, a, grid, s);
-    else if (bn == 64) rc = launch<64, 6, true>(rows_map, cols_map, a, grid, s);
-    else rc = launch<128, 5, true>(rows_map, cols_map, a, grid, s);
+    if (bn == 16) rc = launch<16, 4, true>(rows_map, cols_map, a, grid, s);
+    else if (bn == 32) rc = launch<32, 4, true>(rows_map, cols_map, a, grid, s);
+    else if (bn == 64) rc = launch<64, 4, true>(rows_map, cols_map, a, grid, s);
+    else rc = launch<128, 4, true>(rows_map, cols_map, a, grid, s);
   } else {
     if (!tensor_map(&rows_map, x, M, K, BM) || !tensor_map(&cols_map, w, N, K, 256))
       TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: cuTensorMapEncodeTiled failed");
@@ -420,7 +440,7 @@ TS_API int ts_linear_tc(void* out, const void* x, const void* w, const void* bia
   if (splits > 1) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 > 1184 ? 1184 : (total + 255) / 256);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(out, (const float*)scratch, (const bf16*)bias, M, N, splits, out_is_float);
+    ts_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, out, (const float*)scratch, (const bf16*)bias, M, N, splits, out_is_float);
     TS_LAUNCH_CHECK();
   }
   return 0;

@@ -77,6 +77,8 @@ __device__ Best block_best(Best x, Best* scratch) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* __restrict__ logits,
               const float* __restrict__ fparams, const long long* __restrict__ iparams, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ Best best_s[32];
   __shared__ float red_s[32];
   __shared__ int cnt_s[256];
@@ -222,6 +224,8 @@ sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* 
 // logit -= frequency * count_in_output; then logit -= presence * (count_in_output > 0).
 __global__ void penalize_kernel(float* __restrict__ logits, const int* __restrict__ ids,
                                 const int* __restrict__ meta, const float* __restrict__ pen, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ uint32_t bits[];           // [2][ceil(V/32)]: seen, seen-in-output
   const int words = (V + 31) / 32;
   uint32_t* seen = bits;
@@ -271,7 +275,7 @@ TS_API int ts_sample(int* out, const float* logits, const float* fparams, const 
                      int V, void* stream) {
   if (S <= 0) return 0;
   if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample: vocabulary %d", V);
-  sample_kernel<<<S, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(out, out + S, logits, fparams, iparams, V);
+  ts_launch(sample_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, fparams, iparams, V);
   TS_LAUNCH_CHECK();
 }
 
@@ -286,6 +290,6 @@ TS_API int ts_penalize(float* logits, const int* ids, const int* meta, const flo
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_penalize: %s", cudaGetErrorString(e));
     configured = smem;
   }
-  penalize_kernel<<<S, 256, smem, (cudaStream_t)stream>>>(logits, ids, meta, pen, V);
+  ts_launch(penalize_kernel, dim3(S), dim3(256), smem, (cudaStream_t)stream, logits, ids, meta, pen, V);
   TS_LAUNCH_CHECK();
 }

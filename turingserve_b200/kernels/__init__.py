@@ -78,7 +78,12 @@ class CudaOps:
         self.lib.ts_linear_tc_supported.restype = c_int
         self.lib.ts_linear_tc_status.argtypes = []
         self.lib.ts_linear_tc_status.restype = c_int
-        self.use_tc_gemm = os.environ.get("TURINGSERVE_B200_GEMM", "library") == "tc"
+        # which bfloat16 products run on this library's tcgen05 kernel: "tc" all of them, "auto" those
+        # with at most 128 rows (decode), "library" none (cuBLAS through torch.mm)
+        self.gemm_mode = os.environ.get("TURINGSERVE_B200_GEMM", "library")
+        self.lib.ts_set_pdl.argtypes = [I]
+        self.lib.ts_set_pdl.restype = None
+        self.lib.ts_set_pdl(0 if os.environ.get("TURINGSERVE_B200_PDL", "1") == "0" else 1)
         self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_prefill_supported.restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
@@ -178,11 +183,12 @@ class CudaOps:
         """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias."""
         M, N = out.shape
         K = w.shape[1]
-        if x.dtype == torch.bfloat16 and (self.use_tc_gemm or self.use_library_gemm) and rows is not None:
+        use_tc = self.gemm_mode == "tc" or (self.gemm_mode == "auto" and M <= 128)
+        if x.dtype == torch.bfloat16 and (use_tc or self.use_library_gemm) and rows is not None:
             xg = torch.empty((M, K), dtype=x.dtype, device=x.device)
             self.gather_rows(xg, x, rows)
             x, rows = xg, None
-        if (x.dtype == torch.bfloat16 and self.use_tc_gemm and self.lib.ts_linear_tc_supported(M, N, K)
+        if (x.dtype == torch.bfloat16 and use_tc and self.lib.ts_linear_tc_supported(M, N, K)
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
             splits = self.tc_splits(M, N, K)
             scratch = self.scratch(splits * M * N, x.device) if splits > 1 else None
