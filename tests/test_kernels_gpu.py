@@ -16,6 +16,7 @@ from tests.twin_ops import TwinOps, paged_attention
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
+DEFAULT_GEMM = "auto"
 TOL = {torch.float32: dict(atol=2e-5, rtol=2e-5), torch.bfloat16: dict(atol=2e-2, rtol=2e-2)}
 
 
@@ -260,6 +261,7 @@ def test_linear(ops, dtype, M, N, K):
     tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=5e-2, rtol=2e-2)
     for use_lib in ([False, True] if dtype == torch.bfloat16 else [False]):
         ops.use_library_gemm = use_lib
+        ops.gemm_mode = "library"
         try:
             out = torch.empty((M + 5, N), dtype=dtype, device="cuda")
             ops.linear(out, x.cuda(), w.cuda(), b.cuda())
@@ -270,6 +272,7 @@ def test_linear(ops, dtype, M, N, K):
             torch.testing.assert_close(out32.cpu(), ref32, atol=1e-4 if dtype == torch.float32 else 2e-3, rtol=1e-4)
         finally:
             ops.use_library_gemm = True
+            ops.gemm_mode = DEFAULT_GEMM
 
 
 @pytest.mark.parametrize("M", [1, 8, 17, 64, 128, 129, 300, 2048])
@@ -293,4 +296,36 @@ def test_linear_tensor_core(ops, M, N, K):
         torch.testing.assert_close(outr.cpu(), (ref - b.float())[rows.long()], atol=2e-3, rtol=1e-3)
         assert ops.tc_status() == 0, "a block of the tensor-core product gave up on a wait"
     finally:
-        ops.gemm_mode = "library"
+        ops.gemm_mode = DEFAULT_GEMM
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1536, 1536), (8, 1536, 8960), (64, 200, 264), (128, 4104, 72)])
+def test_deferred_product_finished_by_the_norm(ops, M, N, K):
+    """A few-token product may leave its split-K partial sums to the norm that consumes it; the
+    result equals product, then residual add, then norm, each rounded where the separate kernels round."""
+    from turingserve_b200.kernels import Deferred
+    twin = TwinOps()
+    x, w, b = _rand((M, K), torch.bfloat16, 40), _rand((N, K), torch.bfloat16, 41, 0.05), _rand((N,), torch.bfloat16, 42)
+    res, nw = _rand((M, N), torch.bfloat16, 43), (1 + 0.1 * _rand((N,), torch.float32, 44)).to(torch.bfloat16)
+    ops.gemm_mode = "tc"
+    try:
+        for bias in (None, b):
+            for with_res in (True, False):
+                out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+                d = ops.linear(out, x.cuda(), w.cuda(), None if bias is None else bias.cuda(), may_defer=True)
+                assert isinstance(d, Deferred) and d.shape == (M, N)
+                plain_out = ops.materialize(d).cpu()
+                ref_lin = torch.nn.functional.linear(x.float(), w.float(), None if bias is None else bias.float())
+                torch.testing.assert_close(plain_out.float(), ref_lin, atol=3e-2, rtol=2e-2)
+                normed = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+                r_dev = res.clone().cuda() if with_res else None
+                ops.rmsnorm(normed, d, nw.cuda(), 1e-6, r_dev)
+                ref = torch.empty((M, N), dtype=torch.bfloat16)
+                r_ref = res.clone() if with_res else None
+                twin.rmsnorm(ref, plain_out, nw, 1e-6, r_ref)
+                torch.testing.assert_close(normed.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
+                if with_res:
+                    torch.testing.assert_close(r_dev.cpu().float(), r_ref.float(), atol=2e-2, rtol=1e-2)
+        assert ops.tc_status() == 0
+    finally:
+        ops.gemm_mode = DEFAULT_GEMM

@@ -49,10 +49,11 @@ def check(got, expected, dtype):
             assert bad is None, f"first wrong place (request, position, error): {bad}, bound {tol}"
 
 
-def replay_in_process(folder, name, steps, dtype):
+def replay_in_process(folder, name, steps, dtype, gemm="library"):
     from turingserve_b200 import kernels
     from turingserve_b200.engine.replay import Replayer
     kernels.use(None)
+    kernels.ops().gemm_mode = gemm
     rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name))
     outs = {}
     with torch.inference_mode():
@@ -62,17 +63,21 @@ def replay_in_process(folder, name, steps, dtype):
                 outs[s["step"]] = o
             rp.cache.check()
     assert not rp.cache.live
+    kernels.ops().gemm_mode = "auto"
     return schedules.collect(steps, outs)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype,gemm", [("float32", "library"), ("bfloat16", "library"), ("bfloat16", "auto"),
+                                        ("bfloat16", "tc")])
 @pytest.mark.parametrize("name", ["A", "B", "W"])
 @pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed"])
-def test_schedules_match_plain(tmp_path, name, schedule, dtype):
+def test_schedules_match_plain(tmp_path, name, schedule, dtype, gemm):
+    """``gemm``: which bfloat16 products run on this library's tcgen05 kernel (none, the few-token
+    ones, all); the float32 path always uses the FFMA kernel."""
     folder = tiny.make_tiny_folder(name, tmp_path)
     reqs = requests_for(name, folder)
     steps = getattr(schedules, schedule)(reqs)
-    got = replay_in_process(folder, name, steps, dtype)
+    got = replay_in_process(folder, name, steps, dtype, gemm)
     assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
     check(got, expected_logits(folder, reqs), dtype)
 

@@ -64,11 +64,15 @@ class TwinOps:
         paged_attention(out, qkv, k_cache, v_cache, block_tables, step.q_start, step.seq_lens,
                         H, KVH, D, page_size, scale, window)
 
-    def linear(self, out, x, w, bias=None, rows=None):
+    def linear(self, out, x, w, bias=None, rows=None, may_defer=False):
         if rows is not None:
             x = x[rows.long()]
         y = F.linear(x.float(), w.float(), None if bias is None else bias.float())
         out.copy_(y.to(out.dtype))
+        return out
+
+    def materialize(self, x):
+        return x
 
     def sample(self, out, logits, fparams, iparams):
         S = logits.shape[0]

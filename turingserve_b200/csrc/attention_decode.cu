@@ -251,21 +251,42 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
-    const int g = idx / D, d = idx % D;
+  // weights of every (head, split): w = 2^(m_s - M) / sum_s l_s 2^(m_s - M), staged in shared memory
+  float* w_s = reinterpret_cast<float*>(smem);                     // [G][nsplit]
+  float* m_all = w_s + G * nsplit;                                 // [G][nsplit]
+  float* l_all = m_all + G * nsplit;                               // [G][nsplit]
+  for (int idx = threadIdx.x; idx < G * nsplit; idx += DEC_WARPS * 32) {
+    const int g = idx / nsplit, s2 = idx % nsplit;
+    const size_t pi = ((size_t)b * H + kvh * G + g) * nsplit + s2;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + pi * 2));
+    m_all[idx] = ml.x;
+    l_all[idx] = ml.y;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * nsplit; idx += DEC_WARPS * 32) {
+    const int g = idx / nsplit;
+    float M = -INFINITY, L = 0.f;
+    for (int s2 = 0; s2 < nsplit; ++s2) M = fmaxf(M, m_all[g * nsplit + s2]);
+    if (M > -INFINITY)
+      for (int s2 = 0; s2 < nsplit; ++s2) L += l_all[g * nsplit + s2] * exp2f(m_all[g * nsplit + s2] - M);
+    w_s[idx] = (L > 0.f) ? exp2f(m_all[idx] - M) / L : 0.f;
+  }
+  __syncthreads();
+  // out[g, d..d+3] = sum_s w[g, s] * acc[g, s, d..d+3]: independent 16-byte loads, split order
+  for (int idx = threadIdx.x; idx < G * (D / 4); idx += DEC_WARPS * 32) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
     const int h = kvh * G + g;
-    const size_t base = ((size_t)b * H + h) * nsplit;
-    float M = -INFINITY;
-    for (int s2 = 0; s2 < nsplit; ++s2) M = fmaxf(M, __ldcg(&part_ml[(base + s2) * 2]));
-    float L = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
-      for (int s2 = 0; s2 < nsplit; ++s2) {
-        const float f = exp2f(__ldcg(&part_ml[(base + s2) * 2]) - M);
-        L += __ldcg(&part_ml[(base + s2) * 2 + 1]) * f;
-        acc += __ldcg(&part_acc[(base + s2) * D + d]) * f;
-      }
+    const float* src = part_acc + (((size_t)b * H + h) * nsplit) * D + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s2 = 0; s2 < nsplit; ++s2) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s2 * D));
+      const float w = w_s[g * nsplit + s2];
+      acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
     }
-    out[(size_t)row_q * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    bf16* o = out + (size_t)row_q * H * D + (size_t)h * D + d;
+    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc.x, acc.y);
+    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
   }
 }
 
@@ -311,7 +332,7 @@ TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const vo
   if (B <= 0) return 0;
   if (!ts_attention_decode_supported(H, KVH, D, TS_BF16))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode: H=%d KVH=%d D=%d is not taken by this kernel", H, KVH, D);
-  if (nsplit < 1 || nsplit > 65535 || B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode: nsplit=%d B=%d", nsplit, B);
+  if (nsplit < 1 || nsplit > 128 || B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode: nsplit=%d B=%d", nsplit, B);
   if (nsplit > 1 && (scratch == nullptr || counters == nullptr))
     TS_REFUSE(TS_ERR_SHAPE, "ts_attention_decode: %d splits need scratch and counters", nsplit);
   float* acc = (float*)scratch;

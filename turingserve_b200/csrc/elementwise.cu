@@ -203,6 +203,90 @@ TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, f
   TS_LAUNCH_CHECK();
 }
 
+// The same norm, fed by a product that was left unreduced: x[row] = sum over splits (ascending) of
+// part[s, row, :] + bias, rounded to bfloat16 as the product's own epilogue would have done; then
+// residual add and norm as above.  Saves the separate reduction kernel after a split-K product.
+template <typename WT, int CHUNKS>
+__global__ void reduce_rmsnorm_kernel(bf16* __restrict__ out, const float* __restrict__ part, int splits,
+                                      size_t split_stride, const bf16* __restrict__ bias, bf16* residual,
+                                      const WT* __restrict__ w, float eps, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float v[CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    if (i < hidden) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int sp = 0; sp < splits; ++sp) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i));
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i + 4));
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+      if (bias != nullptr) {
+        float bv[8];
+        load_vec<bf16, 8>(bias + i, bv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += bv[k];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[c][k] = round_to<bf16>(acc[k]);
+      if (residual != nullptr) {
+        float r[8];
+        load_vec<bf16, 8>(residual + base + i, r);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] = round_to<bf16>(v[c][k] + r[k]);
+        store_vec<bf16, 8>(residual + base + i, v[c]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[c][k] * v[c][k];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 8;
+    if (i < hidden) {
+      float y[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = to_f(w[i + k]) * round_to<bf16>(v[c][k] * rstd);
+      store_vec<bf16, 8>(out + base + i, y);
+    }
+  }
+}
+
+// part: float [splits, T, hidden].  bfloat16 rows whose length is a multiple of 8 only.
+TS_API int ts_reduce_rmsnorm(void* out, const float* part, int splits, const void* bias, void* residual,
+                             const void* w, float eps, int T, int hidden, int w_dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (hidden % 8 || splits < 1) TS_REFUSE(TS_ERR_SHAPE, "ts_reduce_rmsnorm: hidden %d, splits %d", hidden, splits);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int vecs = hidden / 8;
+  const size_t stride = (size_t)T * hidden;
+  auto threads_for = [&](int chunks) { return ((vecs + chunks - 1) / chunks + 31) / 32 * 32; };
+#define TS_RR(WT, CH) ts_launch(reduce_rmsnorm_kernel<WT, CH>, dim3(T), dim3(threads_for(CH)), 0, s, (bf16*)out, part, \
+                                splits, stride, (const bf16*)bias, (bf16*)residual, (const WT*)w, eps, hidden)
+  if (w_dtype == TS_BF16) {
+    if (threads_for(1) <= 1024) TS_RR(bf16, 1);
+    else if (threads_for(4) <= 1024) TS_RR(bf16, 4);
+    else TS_REFUSE(TS_ERR_LIMIT, "ts_reduce_rmsnorm: hidden %d too large", hidden);
+  } else if (w_dtype == TS_F32) {
+    if (threads_for(1) <= 1024) TS_RR(float, 1);
+    else if (threads_for(4) <= 1024) TS_RR(float, 4);
+    else TS_REFUSE(TS_ERR_LIMIT, "ts_reduce_rmsnorm: hidden %d too large", hidden);
+  } else {
+    TS_REFUSE(TS_ERR_DTYPE, "ts_reduce_rmsnorm: scale dtype %d", w_dtype);
+  }
+#undef TS_RR
+  TS_LAUNCH_CHECK();
+}
+
 // ------------------------------------------------------------------------------------------
 // SiLU*mul: out[t, i] = T(silu(g)) * u with gu[t] = [g(0..I) | u(0..I)]
 // (turingserve/ops/reference.py:26-28; rounding as triton_silu_mul.py:15-18).

@@ -391,8 +391,19 @@ TS_API int ts_linear_tc_status() {
 
 // out[M, N] (bf16, or float when out_is_float) = x[M, K] . w[N, K]^T + bias.  `splits` > 1 cuts K
 // (weights-on-rows orientation only) and needs `scratch` of ts_linear_tc_scratch_floats() floats.
+// defer != 0: leave the float partial sums [splits, M, N] in `scratch` (also for one split), add no bias
+// and skip the reduction: the caller's next kernel (ts_reduce_rmsnorm) finishes the sum.  The
+// number of splits actually used is returned through *splits_used when it is not null.
+TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* bias, void* scratch, int M, int N,
+                           int K, int out_is_float, int splits, int defer, int* splits_used, void* stream);
+
 TS_API int ts_linear_tc(void* out, const void* x, const void* w, const void* bias, void* scratch, int M, int N,
                         int K, int out_is_float, int splits, void* stream) {
+  return ts_linear_tc_ex(out, x, w, bias, scratch, M, N, K, out_is_float, splits, 0, nullptr, stream);
+}
+
+TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* bias, void* scratch, int M, int N,
+                           int K, int out_is_float, int splits, int defer, int* splits_used, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!ts_linear_tc_supported(M, N, K)) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: K = %d is not a multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w) & 15) TS_REFUSE(TS_ERR_ALIGN, "ts_linear_tc: operands must be 16-byte aligned");
@@ -414,9 +425,14 @@ TS_API int ts_linear_tc(void* out, const void* x, const void* w, const void* bia
   splits = ceil_div(total_kb, per);                 // every split owns at least one k-block
   a.k_blocks_per_split = per;
   a.splits = splits;
-  if (splits > 1) {
+  if (splits_used != nullptr) *splits_used = splits;
+  if (splits > 1 || defer) {
     if (scratch == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_linear_tc: %d splits need scratch", splits);
     a.out = scratch;
+  }
+  if (defer) {
+    a.bias = nullptr;
+    a.out_is_float = 1;
   }
   CUtensorMap rows_map, cols_map;
   int rc;
@@ -437,7 +453,7 @@ TS_API int ts_linear_tc(void* out, const void* x, const void* w, const void* bia
     rc = launch<256, 4, false>(rows_map, cols_map, a, grid, s);
   }
   if (rc != 0) return rc;
-  if (splits > 1) {
+  if (splits > 1 && !defer) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 > 1184 ? 1184 : (total + 255) / 256);
     ts_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, out, (const float*)scratch, (const bf16*)bias, M, N, splits, out_is_float);

@@ -42,6 +42,16 @@ class KernelError(RuntimeError):
     pass
 
 
+class Deferred:
+    """A product whose split-K partial sums still sit in scratch ([splits, M, N] float32): the norm
+    that consumes it finishes the sum in its own kernel.  Quacks like a tensor as far as shape,
+    dtype and device go; anything else must call ``ops().materialize`` first."""
+
+    def __init__(self, part: torch.Tensor, splits: int, shape, dtype, bias) -> None:
+        self.part, self.splits, self.shape, self.dtype, self.bias = part, splits, tuple(shape), dtype, bias
+        self.device = part.device
+
+
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
@@ -65,6 +75,8 @@ class CudaOps:
             "ts_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
             "ts_attention_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
             "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
+            "ts_linear_tc_ex": [P, P, P, P, P, I, I, I, I, I, I, P, P],
+            "ts_reduce_rmsnorm": [P, P, I, P, P, P, F, I, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
             "ts_penalize": [P, P, P, P, I, I, P],
         }
@@ -80,7 +92,7 @@ class CudaOps:
         self.lib.ts_linear_tc_status.restype = c_int
         # which bfloat16 products run on this library's tcgen05 kernel: "tc" all of them, "auto" those
         # with at most 128 rows (decode), "library" none (cuBLAS through torch.mm)
-        self.gemm_mode = os.environ.get("TURINGSERVE_B200_GEMM", "library")
+        self.gemm_mode = os.environ.get("TURINGSERVE_B200_GEMM", "auto")
         self.lib.ts_set_pdl.argtypes = [I]
         self.lib.ts_set_pdl.restype = None
         self.lib.ts_set_pdl(0 if os.environ.get("TURINGSERVE_B200_PDL", "1") == "0" else 1)
@@ -91,6 +103,7 @@ class CudaOps:
         self.num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self._scratch: torch.Tensor | None = None
         self._counters: torch.Tensor | None = None
+        self._partials: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
         self.launches = 0           # kernels of this library launched (graph replays add their share)
@@ -117,7 +130,23 @@ class CudaOps:
         self._check(self.lib.ts_gather_rows(_ptr(out), _ptr(x), _ptr(rows), S, w, _code(x.dtype),
                                             self._stream()), "gather_rows")
 
+    def materialize(self, x):
+        """A plain tensor for ``x``, finishing a deferred product if it is one."""
+        if not isinstance(x, Deferred):
+            return x
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        out.copy_(x.part[: x.splits].sum(0) if x.bias is None else x.part[: x.splits].sum(0) + x.bias.float())
+        return out
+
     def rmsnorm(self, out, x, weight, eps: float, residual=None) -> None:
+        if isinstance(x, Deferred):
+            T, h = x.shape
+            if h % 8 == 0 and x.dtype == torch.bfloat16:
+                self._check(self.lib.ts_reduce_rmsnorm(
+                    _ptr(out), _ptr(x.part), x.splits, _ptr(x.bias), _ptr(residual), _ptr(weight), float(eps), T, h,
+                    _code(weight.dtype), self._stream()), "reduce_rmsnorm")
+                return
+            x = self.materialize(x)
         T, h = x.shape
         self._check(self.lib.ts_rmsnorm(_ptr(out), _ptr(x), _ptr(residual), _ptr(weight), float(eps), T, h,
                                         _code(x.dtype), _code(weight.dtype), self._stream()), "rmsnorm")
@@ -143,7 +172,7 @@ class CudaOps:
     def decode_splits(self, num_requests: int, KVH: int, max_seq_len: int) -> int:
         """How many pieces each request's keys are cut into so that the launch fills the GPU."""
         want = -(-2 * self.num_sms // max(1, num_requests * KVH))
-        return max(1, min(want, -(-max_seq_len // 256)))
+        return max(1, min(want, -(-max_seq_len // 256), 128))
 
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window) -> None:
@@ -179,8 +208,10 @@ class CudaOps:
             step.q_start.data_ptr() + 4 * nd, step.seq_lens.data_ptr() + 4 * nd, B - nd, width,
             step.max_q_len, H, KVH, D, page_size, float(scale), w, code, self._stream()), "attention")
 
-    def linear(self, out, x, w, bias=None, rows=None) -> None:
-        """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias."""
+    def linear(self, out, x, w, bias=None, rows=None, may_defer: bool = False):
+        """out[M, N] = x[rows or all, :] @ w[N, K]^T + bias.  Returns ``out``; or, when ``may_defer``
+        and the few-token tensor-core kernel takes the product, a ``Deferred`` whose sum the
+        consuming norm finishes (``out`` is then left untouched)."""
         M, N = out.shape
         K = w.shape[1]
         use_tc = self.gemm_mode == "tc" or (self.gemm_mode == "auto" and M <= 128)
@@ -191,13 +222,20 @@ class CudaOps:
         if (x.dtype == torch.bfloat16 and use_tc and self.lib.ts_linear_tc_supported(M, N, K)
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
             splits = self.tc_splits(M, N, K)
+            if may_defer and M <= 128 and N % 8 == 0 and out.dtype == torch.bfloat16:
+                part = self.partial_scratch(splits * M * N, x.device)
+                used = ctypes.c_int(0)
+                self._check(self.lib.ts_linear_tc_ex(_ptr(out), _ptr(x), _ptr(w), None, _ptr(part), M, N, K, 0, splits,
+                                                     1, ctypes.addressof(used), self._stream()), "linear_tc")
+                return Deferred(part.view(-1)[: used.value * M * N].view(used.value, M, N), used.value, (M, N),
+                                out.dtype, bias)
             scratch = self.scratch(splits * M * N, x.device) if splits > 1 else None
             self._check(self.lib.ts_linear_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(scratch), M, N, K,
                                               1 if out.dtype == torch.float32 else 0, splits, self._stream()),
                         "linear_tc")
             if splits > 1:
                 self.launches += 1
-            return
+            return out
         if x.dtype == torch.bfloat16 and self.use_library_gemm:
             if out.dtype == torch.float32:
                 torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
@@ -207,9 +245,16 @@ class CudaOps:
                 torch.addmm(bias, x, w.t(), out=out)
             else:
                 torch.mm(x, w.t(), out=out)
-            return
+            return out
         self._check(self.lib.ts_linear_simt(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows), M, N, K,
                                             _code(x.dtype), _code(out.dtype), self._stream()), "linear")
+        return out
+
+    def partial_scratch(self, floats: int, device) -> torch.Tensor:
+        """The buffer deferred products leave their partial sums in (one deferred product at a time)."""
+        if self._partials is None or self._partials.numel() < floats or self._partials.device != device:
+            self._partials = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        return self._partials
 
     def tc_splits(self, M: int, N: int, K: int) -> int:
         """Pieces K is cut into for a few-token product, so that about one tile lands on every SM."""
@@ -254,4 +299,4 @@ def use(ops_object) -> None:
     _OPS = ops_object
 
 
-__all__ = ["CudaOps", "KernelError", "build", "library_path", "ops", "use"]
+__all__ = ["CudaOps", "Deferred", "KernelError", "build", "library_path", "ops", "use"]

@@ -69,8 +69,7 @@ class Attention(Mixer):
         ops.attention(attn, qkv, cache.k, cache.v, grp.block_tables, step, self.H, self.KVH, self.D,
                       cache.page_size, self.scale, self.window)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        ops.linear(out, attn, self.w_o, self.b_o)
-        return out
+        return ops.linear(out, attn, self.w_o, self.b_o, may_defer=True)
 
 
 register("mixer", "attention", Attention)

@@ -7,10 +7,14 @@ live under is the architecture's business (``turingserve_b200.config.registry.Te
 
 Interfaces
 ----------
-Norm            forward(x, residual=None) -> y          (residual updated in place when given)
+Norm            forward(x, residual=None) -> y          (residual updated in place when given; x may be a
+                                                         product left unreduced by its kernel, which a
+                                                         norm either passes to a kernel that finishes it
+                                                         or turns into a tensor with ops().materialize)
 PositionEncoding  tables()/apply are private to the mixers that accept it
 Mixer           forward(x, step, cache, state) -> y     cache_need() / state_need() declare memory
-FeedForward     forward(x) -> y
+FeedForward     forward(x) -> y                         (mixers and feed-forwards get tensors; they may
+                                                         return what ops().linear(..., may_defer=True) gave)
 Block           forward(h, residual, step, cache, state) -> (h, residual)
 
 ``step`` is a ``StepInputs`` (turingserve_b200.engine.batch): the flat batch on the device.

@@ -44,8 +44,7 @@ class GatedMLP(FeedForward):
         act = torch.empty((T, self.inter), dtype=x.dtype, device=x.device)
         ops.silu_mul(act, gu)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        ops.linear(out, act, self.w_down, self.b_down)
-        return out
+        return ops.linear(out, act, self.w_down, self.b_down, may_defer=True)
 
 
 register("feed_forward", "gated_mlp", GatedMLP)

@@ -25,8 +25,10 @@ class RMSNorm(Norm):
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        out = torch.empty_like(x)
+    def forward(self, x, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``x`` is a tensor, or a product that its kernel left unreduced (it has shape, dtype and
+        device; the norm kernel finishes the sum)."""
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         kernels.ops().rmsnorm(out, x, self.weight, self.eps, residual)
         return out
 
