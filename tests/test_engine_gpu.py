@@ -189,10 +189,16 @@ def test_sharp_attention_shows_a_wrong_key(tmp_path, dtype):
     reqs = {"a": tiny.random_ids(400, cfg["vocab_size"], 5), "b": tiny.random_ids(333, cfg["vocab_size"], 6)}
     expected = {k: plain.forward(cfg, w, v).numpy() for k, v in reqs.items()}
     # float32 keeps the 1e-4 bound at every position: that is where a lost key shows.  In bfloat16
-    # the scores carry 16 times the usual rounding and a near-tie between two keys may flip, so single
-    # positions can be far off; a lost key (a page, a split, the window's edge) would move MOST later
-    # positions by about the size of the logits.  Bound: median error 2%, 95th percentile 8% of the
-    # largest logit.
+    # the scores carry 16 times the usual rounding and near-ties between keys flip, so the yardstick is
+    # the plain implementation itself run in bfloat16: the engine's errors (median and 95th percentile
+    # over positions, relative to the largest logit) must not exceed 1.5 times those of that plain
+    # bfloat16 run.  A lost key (a page, a split, the window's edge) would move most later positions
+    # by about the size of the logits.
+    _, w16 = plain.read_folder(folder, torch.bfloat16)
+    yard = {}
+    for rid, toks in reqs.items():
+        e = np.abs(plain.forward(cfg, w16, toks).float().numpy() - expected[rid]).max(1) / float(np.abs(expected[rid]).max())
+        yard[rid] = (float(np.median(e)), float(np.percentile(e, 95)))
     for sched in ("decode_tail", "mixed"):
         steps = getattr(schedules, sched)(reqs)
         got = replay_in_process(folder, "W", steps, dtype)
@@ -203,5 +209,5 @@ def test_sharp_attention_shows_a_wrong_key(tmp_path, dtype):
                 scale = float(np.abs(expected[rid]).max())
                 errs = np.array([np.abs(rows[p] - expected[rid][p]).max() for p in sorted(rows)]) / scale
                 assert np.isfinite(errs).all() and len(errs) == len(reqs[rid])
-                assert np.median(errs) <= 0.02 and np.percentile(errs, 95) <= 0.08, \
-                    (sched, rid, float(np.median(errs)), float(np.percentile(errs, 95)), int(errs.argmax()))
+                assert np.median(errs) <= 1.5 * yard[rid][0] and np.percentile(errs, 95) <= 1.5 * yard[rid][1], \
+                    (sched, rid, float(np.median(errs)), float(np.percentile(errs, 95)), yard[rid], int(errs.argmax()))
