@@ -17,6 +17,7 @@
 // (request, kv head) merges the partials (no second launch, no waiting: a ticket counter).
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "no_alloc.h"
 
 namespace {
 
@@ -343,4 +344,51 @@ TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const vo
                              block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
   return launch_decode<128>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
                             block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
+}
+
+// ---- the entry point that allocates nothing (see no_alloc.h) -------------------------------------
+// Scratch in the library image.  In host code this name is only a handle for the symbol, not a
+// device address: the address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float g_static_scratch[TS_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_static_counters[TS_STATIC_COUNTERS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_addr[MAX_DEVICES] = {};
+int* g_counters_addr[MAX_DEVICES] = {};
+}  // namespace
+
+TS_API int ts_attention_decode_static(void* out, const void* qkv, const void* k_cache, const void* v_cache,
+                                      const int* block_tables, const int* q_start, const int* seq_lens, int B,
+                                      int table_width, int H, int KVH, int D, int page, float scale, int window,
+                                      int nsplit, void* stream) {
+  if (B <= 0) return 0;
+  if (nsplit < 1) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_static: nsplit=%d", nsplit);
+  const long long need = ts_attention_decode_scratch_floats(B, H, D, nsplit);
+  if (need > TS_STATIC_SCRATCH_FLOATS || (long long)B * KVH > TS_STATIC_COUNTERS)
+    TS_REFUSE(TS_ERR_LIMIT,
+              "ts_attention_decode_static: B=%d H=%d D=%d nsplit=%d needs %lld scratch floats and %lld counters; "
+              "the fixed array holds %d and %d",
+              B, H, D, nsplit, need, (long long)B * KVH, TS_STATIC_SCRATCH_FLOATS, TS_STATIC_COUNTERS);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= MAX_DEVICES) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_static: device %d", dev);
+  if (g_scratch_addr[dev] == nullptr) {                // set-up, once per device, with that device current
+    float* sp = nullptr;
+    int* cp = nullptr;
+    e = cudaGetSymbolAddress((void**)&sp, g_static_scratch);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: scratch address: %s", cudaGetErrorString(e));
+    e = cudaGetSymbolAddress((void**)&cp, g_static_counters);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: counters address: %s", cudaGetErrorString(e));
+    g_counters_addr[dev] = cp;
+    g_scratch_addr[dev] = sp;
+  }
+  if (nsplit > 1) {
+    // the ticket counters must start at zero whatever an earlier (perhaps aborted) call left behind
+    e = cudaMemsetAsync(g_counters_addr[dev], 0, sizeof(int) * (size_t)B * KVH, (cudaStream_t)stream);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: clearing counters: %s", cudaGetErrorString(e));
+  }
+  return ts_attention_decode(out, g_scratch_addr[dev], g_counters_addr[dev], qkv, k_cache, v_cache, block_tables,
+                             q_start, seq_lens, B, table_width, H, KVH, D, page, scale, window, nsplit, stream);
 }
