@@ -305,11 +305,43 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// Vector variant: one thread takes 16 bytes of gate and 16 bytes of up.
+template <typename T>
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int vec_per_row,
+                                    unsigned total_vecs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int N = Vec16<T>::N;
+  for (unsigned v = blockIdx.x * blockDim.x + threadIdx.x; v < total_vecs; v += gridDim.x * blockDim.x) {
+    const unsigned t = v / vec_per_row;
+    const int i = (int)(v - t * vec_per_row) * N;
+    float g[N], u[N], o[N];
+    load_vec<T, N>(gu + (size_t)t * 2 * inter + i, g);
+    load_vec<T, N>(gu + (size_t)t * 2 * inter + inter + i, u);
+#pragma unroll
+    for (int k = 0; k < N; ++k) o[k] = round_to<T>(g[k] / (1.f + expf(-g[k]))) * u[k];
+    store_vec<T, N>(out + (size_t)t * inter + i, o);
+  }
+}
+
 TS_API int ts_silu_mul(void* out, const void* gu, int T, int inter, int dtype, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const size_t total = (size_t)T * inter;
   const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  {
+    const int n = dtype == TS_F32 ? 4 : 8;
+    const size_t vecs = total / n;
+    if ((dtype == TS_F32 || dtype == TS_BF16) && inter % n == 0 && vecs < 0xffffffffull &&
+        ((((uintptr_t)out | (uintptr_t)gu) & 15) == 0)) {
+      const int vb = (int)((vecs + 255) / 256 > 148 * 32 ? 148 * 32 : (vecs + 255) / 256);
+      if (dtype == TS_F32)
+        ts_launch(silu_mul_vec_kernel<float>, dim3(vb), dim3(256), 0, s, (float*)out, (const float*)gu, inter, inter / n, (unsigned)vecs);
+      else
+        ts_launch(silu_mul_vec_kernel<bf16>, dim3(vb), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, inter / n, (unsigned)vecs);
+      TS_LAUNCH_CHECK();
+    }
+  }
   if (dtype == TS_F32)
     ts_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)gu, inter, total);
   else if (dtype == TS_BF16)
