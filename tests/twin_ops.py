@@ -51,13 +51,14 @@ class TwinOps:
             qk[..., :half] = o1.to(qkv.dtype)
             qk[..., half:rotary_dim] = o2.to(qkv.dtype)
         if k_cache is None:
-            return
+            return qkv
         k = qkv[:, H * D:(H + KVH) * D].view(T, KVH, D)
         v = qkv[:, (H + KVH) * D:].view(T, KVH, D)
         m = slots >= 0
         sl = slots[m].long()
         k_cache[sl // page_size, :, sl % page_size, :] = k[m]
         v_cache[sl // page_size, :, sl % page_size, :] = v[m]
+        return qkv
 
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window):

@@ -24,6 +24,7 @@ namespace {
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_TILE = 64;        // keys per pipeline stage
 constexpr int DEC_STAGES = 3;
+constexpr int PAGES_S = 1024;       // block-table entries a block keeps in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <int D>
@@ -55,6 +56,19 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   unsigned char* k_s = smem;                                       // [STAGES][TILE][D] bf16
   unsigned char* v_s = smem + DEC_STAGES * DEC_TILE * D * 2;
 
+  // The block's share of the block table goes to shared memory once: the copies below then need no
+  // dependent global load per key.
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;      // pages of 2^k tokens: no division
+  __shared__ int pages_s[PAGES_S];
+  const int page_first = k_begin / page;
+  const int n_pages = k_end > k_begin ? (k_end - 1) / page - page_first + 1 : 0;
+  const bool pages_staged = n_pages <= PAGES_S;
+  if (pages_staged) {
+    for (int i = threadIdx.x; i < n_pages; i += DEC_WARPS * 32)
+      pages_s[i] = block_tables[(size_t)b * table_width + page_first + i];
+    __syncthreads();
+  }
+
   // query fragments: rows 0..G-1 of the group, zero above
   unsigned qf[KS][4];
   {
@@ -80,8 +94,9 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
       const bool ok = j < k_end;
       size_t off = 0;
       if (ok) {
-        const int pg = block_tables[(size_t)b * table_width + j / page];
-        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j % page)) * D + c * 8;
+        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+        const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
+        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
       }
       cp_async_16(ks_ + swz<D>(key, c), k_cache + off, ok);
       cp_async_16(vs_ + swz<D>(key, c), v_cache + off, ok);

@@ -22,6 +22,7 @@ constexpr int PF_WARPS = 4;
 constexpr int PF_ROWS = PF_WARPS * 16;   // query rows per block
 constexpr int PF_TILE = 64;              // keys per pipeline stage
 constexpr int PF_STAGES = 3;
+constexpr int PF_PAGES_S = 2048;        // block-table entries a block keeps in shared memory
 constexpr float PF_LOG2E = 1.4426950408889634f;
 
 template <int D>
@@ -90,6 +91,18 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, c
   const int w_first = row0 + warp * 16, w_last = min(w_first + 15, n_rows - 1);
   const int w_pos_lo = prefix + w_first / G, w_pos_hi = (w_first < n_rows) ? prefix + w_last / G : -1;
 
+  // this block's part of the block table, once, in shared memory (no dependent global load per key)
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;      // pages of 2^k tokens: no division
+  __shared__ int pages_s[PF_PAGES_S];
+  const int page_first = j_lo / page;
+  const int n_pages = n_tiles > 0 ? j_hi / page - page_first + 1 : 0;
+  const bool pages_staged = n_pages <= PF_PAGES_S;
+  if (pages_staged) {
+    for (int i = threadIdx.x; i < n_pages; i += PF_WARPS * 32)
+      pages_s[i] = block_tables[(size_t)b * table_width + page_first + i];
+    __syncthreads();
+  }
+
   auto load_tile = [&](int tile, int stage) {
     const int j0 = j_lo + tile * PF_TILE;
     unsigned char* ks_ = k_s + stage * PF_TILE * D * 2;
@@ -100,8 +113,9 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, c
       const bool ok = j <= j_hi;
       size_t off = 0;
       if (ok) {
-        const int pg = block_tables[(size_t)b * table_width + j / page];
-        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j % page)) * D + c * 8;
+        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+        const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
+        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
       }
       cp_async_16(ks_ + swz<D>(key, c), k_cache + off, ok);
       cp_async_16(vs_ + swz<D>(key, c), v_cache + off, ok);

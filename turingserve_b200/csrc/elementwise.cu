@@ -410,13 +410,45 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
 
 // Latency-lean variant for bfloat16 when half the rotary width is a multiple of 8: one thread
 // rotates 8 pairs (two 16-byte vectors) or copies one 16-byte vector of v.
+//
+// With `part` set, the q/k/v product arrives unreduced: the value of column c of token t is
+// sum over splits (ascending) of part[s, t, c] + bias[c], rounded to bfloat16 as the product's own
+// epilogue would have rounded it; the kernel then writes q, k and v into qkv as well.
+__device__ __forceinline__ void load_qkv8(const bf16* row, int col, const float* part, int splits, size_t split_stride,
+                                          size_t part_row, const bf16* bias, float (&f)[8]) {
+  if (part == nullptr) {
+    load_vec<bf16, 8>(row + col, f);
+    return;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) f[k] = 0.f;
+#pragma unroll 4
+  for (int sp = 0; sp < splits; ++sp) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + part_row + col));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + part_row + col + 4));
+    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+  }
+  if (bias != nullptr) {
+    float bv[8];
+    load_vec<bf16, 8>(bias + col, bv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] += bv[k];
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) f[k] = round_to<bf16>(f[k]);
+}
+
 __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
-                                         const int* __restrict__ slots, int H, int KVH, int D, int rot, int page) {
+                                         const int* __restrict__ slots, int H, int KVH, int D, int rot, int page,
+                                         const float* __restrict__ part, int splits, size_t split_stride,
+                                         const bf16* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  const size_t part_row = (size_t)t * (H + 2 * KVH) * D;
   const int pos = positions[t];
   const int slot = (k_cache != nullptr) ? slots[t] : -1;
   const int half = rot / 2;
@@ -427,18 +459,19 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
   if (slot >= 0) cache_base = ((size_t)(slot / page) * KVH * page + (size_t)(slot % page)) * D;
   const size_t head_stride = (size_t)page * D;
   const int per_head = hv + pv;
-  const int qk_items = (H + KVH) * per_head;
-  const int v_items = slot >= 0 ? KVH * (D / 8) : 0;
-  for (int idx = threadIdx.x; idx < qk_items + v_items; idx += blockDim.x) {
-    if (idx < qk_items) {
-      const int head = idx / per_head, j = idx % per_head;
-      bf16* x = row + (size_t)head * D;
-      bf16* kdst = (head >= H && slot >= 0) ? k_cache + cache_base + (size_t)(head - H) * head_stride : nullptr;
+  // one warp per head (q heads, k heads, then v heads), blockIdx.y * warps-per-block + warp
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (head >= H + 2 * KVH) return;
+  if (head < H + KVH) {
+    bf16* x = row + (size_t)head * D;
+    bf16* kdst = (head >= H && slot >= 0) ? k_cache + cache_base + (size_t)(head - H) * head_stride : nullptr;
+    for (int j = lane; j < per_head; j += 32) {
       if (j < hv) {
         const int i = j * 8;
         float x1[8], x2[8], o1[8], o2[8];
-        load_vec<bf16, 8>(x + i, x1);
-        load_vec<bf16, 8>(x + i + half, x2);
+        load_qkv8(row, head * D + i, part, splits, split_stride, part_row, bias, x1);
+        load_qkv8(row, head * D + i + half, part, splits, split_stride, part_row, bias, x2);
         const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i);
         const float4 c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i + 4);
         const float4 s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i);
@@ -457,35 +490,64 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
           store_vec<bf16, 8>(kdst + i, o1);
           store_vec<bf16, 8>(kdst + i + half, o2);
         }
-      } else if (kdst != nullptr) {
+      } else if (kdst != nullptr || part != nullptr) {
         const int d = rot + (j - hv) * 8;
-        *reinterpret_cast<uint4*>(kdst + d) = *reinterpret_cast<const uint4*>(x + d);
+        float pass[8];
+        load_qkv8(row, head * D + d, part, splits, split_stride, part_row, bias, pass);
+        if (part != nullptr) store_vec<bf16, 8>(x + d, pass);
+        if (kdst != nullptr) store_vec<bf16, 8>(kdst + d, pass);
       }
-    } else {
-      const int vi = idx - qk_items;
-      const int head = vi / (D / 8), d = (vi % (D / 8)) * 8;
-      const bf16* v = row + (size_t)(H + KVH) * D + (size_t)head * D + d;
-      *reinterpret_cast<uint4*>(v_cache + cache_base + (size_t)head * head_stride + d) = *reinterpret_cast<const uint4*>(v);
+    }
+  } else if (slot >= 0 || part != nullptr) {
+    const int vh = head - H - KVH;
+    for (int j = lane; j < D / 8; j += 32) {
+      const int d = j * 8;
+      const int col = (H + KVH) * D + vh * D + d;
+      float vv[8];
+      load_qkv8(row, col, part, splits, split_stride, part_row, bias, vv);
+      if (part != nullptr) store_vec<bf16, 8>(row + col, vv);
+      if (slot >= 0) store_vec<bf16, 8>(v_cache + cache_base + (size_t)vh * head_stride + d, vv);
     }
   }
 }
 
+TS_API int ts_rope_kv_write_ex(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
+                               void* k_cache, void* v_cache, const int* slots, int T, int H, int KVH, int D, int rot,
+                               int page, int dtype, const float* part, int splits, const void* bias, void* stream);
+
 TS_API int ts_rope_kv_write(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
                             void* k_cache, void* v_cache, const int* slots, int T, int H, int KVH,
                             int D, int rot, int page, int dtype, void* stream) {
+  return ts_rope_kv_write_ex(qkv, positions, cos_t, sin_t, k_cache, v_cache, slots, T, H, KVH, D, rot, page, dtype,
+                             nullptr, 0, nullptr, stream);
+}
+
+// Whether the kernel that also finishes an unreduced q/k/v product takes the shape.
+TS_API int ts_rope_kv_write_fused_supported(int D, int rot, int dtype) {
+  return dtype == TS_BF16 && rot > 0 && ((rot / 2) % 8) == 0 && (D % 8) == 0;
+}
+
+// `part` (float [splits, T, (H+2KVH)*D]) set: qkv is an OUTPUT too; see rope_kv_write_vec_kernel.
+TS_API int ts_rope_kv_write_ex(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
+                               void* k_cache, void* v_cache, const int* slots, int T, int H, int KVH, int D, int rot,
+                               int page, int dtype, const float* part, int splits, const void* bias, void* stream) {
   if (T <= 0) return 0;
+  if (part != nullptr && !ts_rope_kv_write_fused_supported(D, rot, dtype))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_rope_kv_write: unreduced input with head_dim %d, rotary_dim %d", D, rot);
   if (rot < 0 || rot > D || (rot & 1)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: rotary_dim %d for head_dim %d", rot, D);
   if (rot > 0 && (cos_t == nullptr || sin_t == nullptr)) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_kv_write: tables missing");
   cudaStream_t s = (cudaStream_t)stream;
   const int half = rot / 2;
   const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
   if (dtype == TS_BF16 && rot > 0 && (half % 8) == 0 && (D % 8) == 0 && aligned) {
-    const int items = (H + KVH) * (half / 8 + (D - rot) / 8) + KVH * (D / 8);
-    const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
-    ts_launch(rope_kv_write_vec_kernel, dim3(T), dim3(threads), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
-                                                   slots, H, KVH, D, rot, page);
+    const int heads = H + 2 * KVH;
+    const int warps = heads >= 4 ? 4 : heads;
+    ts_launch(rope_kv_write_vec_kernel, dim3(T, ceil_div(heads, warps)), dim3(warps * 32), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
+                                                   slots, H, KVH, D, rot, page, part, splits,
+                                                   (size_t)T * (H + 2 * KVH) * D, (const bf16*)bias);
     TS_LAUNCH_CHECK();
   }
+  if (part != nullptr) TS_REFUSE(TS_ERR_ALIGN, "ts_rope_kv_write: unreduced input needs 16-byte aligned buffers");
   if (dtype == TS_F32)
     ts_launch(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, s, (float*)qkv, positions, cos_t, sin_t, (float*)k_cache,
                                                   (float*)v_cache, slots, H, KVH, D, rot, page);

@@ -47,9 +47,10 @@ class Deferred:
     that consumes it finishes the sum in its own kernel.  Quacks like a tensor as far as shape,
     dtype and device go; anything else must call ``ops().materialize`` first."""
 
-    def __init__(self, part: torch.Tensor, splits: int, shape, dtype, bias) -> None:
+    def __init__(self, part: torch.Tensor, splits: int, shape, dtype, bias, out: torch.Tensor) -> None:
         self.part, self.splits, self.shape, self.dtype, self.bias = part, splits, tuple(shape), dtype, bias
         self.device = part.device
+        self.out = out                      # the buffer the finished product belongs in
 
 
 class CudaOps:
@@ -70,6 +71,7 @@ class CudaOps:
             "ts_rmsnorm": [P, P, P, P, F, I, I, I, I, P],
             "ts_silu_mul": [P, P, I, I, I, P],
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_rope_kv_write_ex": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
@@ -86,6 +88,8 @@ class CudaOps:
             fn.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_supported.restype = c_int
+        self.lib.ts_rope_kv_write_fused_supported.argtypes = [I, I, I]
+        self.lib.ts_rope_kv_write_fused_supported.restype = c_int
         self.lib.ts_linear_tc_supported.argtypes = [I, I, I]
         self.lib.ts_linear_tc_supported.restype = c_int
         self.lib.ts_linear_tc_status.argtypes = []
@@ -134,9 +138,8 @@ class CudaOps:
         """A plain tensor for ``x``, finishing a deferred product if it is one."""
         if not isinstance(x, Deferred):
             return x
-        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        out.copy_(x.part[: x.splits].sum(0) if x.bias is None else x.part[: x.splits].sum(0) + x.bias.float())
-        return out
+        x.out.copy_(x.part[: x.splits].sum(0) if x.bias is None else x.part[: x.splits].sum(0) + x.bias.float())
+        return x.out
 
     def rmsnorm(self, out, x, weight, eps: float, residual=None) -> None:
         if isinstance(x, Deferred):
@@ -157,11 +160,24 @@ class CudaOps:
                     "silu_mul")
 
     def rope_kv_write(self, qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
-                      page_size) -> None:
+                      page_size):
+        """Rotates q and k in place and writes k, v to the cache; returns the q/k/v tensor.  ``qkv`` may
+        be a deferred product: the kernel then finishes its sum on the way."""
+        if isinstance(qkv, Deferred):
+            d = qkv
+            if (self.lib.ts_rope_kv_write_fused_supported(D, rotary_dim, _code(d.dtype))
+                    and all(t is None or t.data_ptr() % 16 == 0 for t in (d.out, k_cache, v_cache, cos, sin))):
+                self._check(self.lib.ts_rope_kv_write_ex(
+                    _ptr(d.out), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
+                    d.shape[0], H, KVH, D, rotary_dim, page_size, _code(d.dtype), _ptr(d.part), d.splits,
+                    _ptr(d.bias), self._stream()), "rope_kv_write")
+                return d.out
+            qkv = self.materialize(d)
         T = qkv.shape[0]
         self._check(self.lib.ts_rope_kv_write(
             _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
             T, H, KVH, D, rotary_dim, page_size, _code(qkv.dtype), self._stream()), "rope_kv_write")
+        return qkv
 
     def scratch(self, floats: int, device) -> torch.Tensor:
         """A float32 work buffer of at least ``floats`` elements, kept between calls."""
@@ -228,7 +244,7 @@ class CudaOps:
                 self._check(self.lib.ts_linear_tc_ex(_ptr(out), _ptr(x), _ptr(w), None, _ptr(part), M, N, K, 0, splits,
                                                      1, ctypes.addressof(used), self._stream()), "linear_tc")
                 return Deferred(part.view(-1)[: used.value * M * N].view(used.value, M, N), used.value, (M, N),
-                                out.dtype, bias)
+                                out.dtype, bias, out)
             scratch = self.scratch(splits * M * N, x.device) if splits > 1 else None
             self._check(self.lib.ts_linear_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(scratch), M, N, K,
                                               1 if out.dtype == torch.float32 else 0, splits, self._stream()),
@@ -264,7 +280,9 @@ class CudaOps:
         k_blocks = -(-K // 64)
         if tiles >= self.num_sms // 2:
             return 1
-        return max(1, min(self.num_sms // tiles, k_blocks // 2))
+        # partial sums cost 8*M*N bytes per split (written, read back): keep that below the weights' 2*N*K
+        traffic_cap = max(1, K // (4 * M))
+        return max(1, min(self.num_sms // tiles, k_blocks // 2, traffic_cap))
 
     def tc_status(self) -> int:
         """0 when no tensor-core GEMM block ever gave up on a wait (synchronises the device)."""
