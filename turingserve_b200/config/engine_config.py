@@ -29,6 +29,9 @@ class EngineConfig:
     watermark: float = 0.01
     cuda_graphs: bool = True
     graph_batch_sizes: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128)
+    # launch the next decode step before the host has read the current step's tokens (they are fed
+    # back on the device); a request that stops on a token then runs one step in vain
+    async_decode: bool = True
     seed: int = 0
 
     @property
@@ -95,6 +98,11 @@ def add_engine_arguments(s: argparse.ArgumentParser) -> None:
     g.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false")
     s.set_defaults(cuda_graphs=d.cuda_graphs)
     s.add_argument("--graph-batch-sizes", default=",".join(map(str, d.graph_batch_sizes)))
+    g2 = s.add_mutually_exclusive_group()
+    g2.add_argument("--async-decode", dest="async_decode", action="store_true",
+                    help="launch the next decode step before reading this step's tokens")
+    g2.add_argument("--no-async-decode", dest="async_decode", action="store_false")
+    s.set_defaults(async_decode=d.async_decode)
     s.add_argument("--seed", type=int, default=d.seed)
 
 

@@ -558,3 +558,25 @@ TS_API int ts_rope_kv_write_ex(void* qkv, const int* positions, const float* cos
     TS_REFUSE(TS_ERR_DTYPE, "ts_rope_kv_write: dtype %d", dtype);
   TS_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// Token feedback: ids[rows[i]] = tokens[src[i]].  Lets a decode step take its input ids straight
+// from the previous step's sampler output on the device, so that the host can launch it before
+// it has read those tokens.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ rows, const int* __restrict__ src,
+                                   const int* __restrict__ tokens, int n, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    int t = tokens[src[i]];
+    t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+    ids[rows[i]] = t;
+  }
+}
+
+TS_API int ts_feed_tokens(int* ids, const int* rows, const int* src, const int* tokens, int n, int vocab, void* stream) {
+  if (n <= 0) return 0;
+  ts_launch(feed_tokens_kernel, dim3(ceil_div(n, 128)), dim3(128), 0, (cudaStream_t)stream, ids, rows, src, tokens, n, vocab);
+  TS_LAUNCH_CHECK();
+}

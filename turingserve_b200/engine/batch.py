@@ -29,6 +29,9 @@ class StepEntry:
     cache: RequestCache
     tokens: list[int]
     want: list[int] = field(default_factory=list)
+    # When set, the (single) token is not known to the host yet: its id is row ``feedback`` of the
+    # previous step's sampler output and is put in place on the device (``tokens`` holds a stand-in).
+    feedback: int | None = None
 
 
 @dataclass
@@ -51,6 +54,8 @@ class StepInputs:
     state_slots: torch.Tensor       # [B] int32
     sample_rows: torch.Tensor       # [S] int32 rows of the flat batch
     groups: list[GroupInputs]
+    feedback_rows: torch.Tensor     # [F] int32 rows of the flat batch whose id comes from the device
+    feedback_src: torch.Tensor      # [F] int32 rows of the previous sampler output
     # host copies, for launch geometry and for parts written in plain torch
     q_lens: list[int]
     starts: list[int]
@@ -72,7 +77,7 @@ class StepInputBuilder:
         self.max_pages = max_pages_per_request
         self.device = device
         g = len(cache.groups)
-        cap = (_align(max_tokens) * (3 + g) + _align(max_requests + 1) + 2 * _align(max_requests)
+        cap = (_align(max_tokens) * (3 + g) + _align(max_requests + 1) + 4 * _align(max_requests)
                + _align(max_tokens) + g * _align(max_requests * max_pages_per_request) + 64)
         self.capacity = cap
         pin = device is not None and torch.device(device).type == "cuda"
@@ -149,6 +154,9 @@ class StepInputBuilder:
 
         o_ids, o_pos, o_req = take(T), take(T), take(T)
         o_qs, o_sl, o_ss, o_sr = take(B + 1), take(B), take(B), take(max(S, 1))
+        fb = [(b, e.feedback) for b, e in enumerate(ents) if e.feedback is not None]
+        F = len(fb)
+        o_fr, o_fs = take(max(F, 1)), take(max(F, 1))
         o_slot = [take(T) for _ in widths]
         o_bt = [take(B * w) for w in widths]
         used = cursor
@@ -181,6 +189,12 @@ class StepInputBuilder:
             sl[b] = 0
             ss[b] = 0
         host[o_sr:o_sr + S] = sample
+        for i, (b, src) in enumerate(fb):
+            if q_lens[b] != 1:
+                raise ValueError("a token fed back on the device must be a request's only token in the step")
+            host[o_fr + i] = qs[b]
+            host[o_fs + i] = src
+            ids[qs[b]] = 0
         for gi, w in enumerate(widths):
             bt = host[o_bt[gi]:o_bt[gi] + B * w].reshape(B, w)
             bt[:] = 0
@@ -213,4 +227,5 @@ class StepInputBuilder:
             num_tokens=T, num_requests=B, num_decode=num_decode, input_ids=d(o_ids, T),
             positions=d(o_pos, T), token_request=d(o_req, T), q_start=d(o_qs, B + 1),
             seq_lens=d(o_sl, B), state_slots=d(o_ss, B), sample_rows=d(o_sr, S), groups=groups,
+            feedback_rows=d(o_fr, F), feedback_src=d(o_fs, F),
             q_lens=q_lens, starts=starts, max_q_len=max(q_lens), max_seq_len=int(sl.max()) if B else 0)

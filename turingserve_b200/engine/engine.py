@@ -33,6 +33,23 @@ class FinalOutput:
     prompt_tokens: int
 
 
+@dataclass
+class _Sampled:
+    """Tokens a sampler without a launch/finish split returned at once."""
+
+    tokens: object
+    bad: object
+
+
+@dataclass
+class _InFlight:
+    """A step that has been launched and whose tokens have not been committed yet."""
+
+    plan: BatchPlan
+    sampling: list
+    pending: object                      # PendingSample | _Sampled | None
+
+
 class StepTimer:
     """Wall-clock seconds per phase of the last step (turingserve/utils/timing.py:9-24)."""
 
@@ -58,6 +75,7 @@ class LLMEngine:
         self.eos_ids = tuple(eos_ids)
         self.max_model_len = max_model_len
         self.requests: dict[str, Request] = {}
+        self._inflight: _InFlight | None = None
         self._aborts: list[str] = []
         self._arrivals = 0
         self.timer = StepTimer()
@@ -110,47 +128,122 @@ class LLMEngine:
         self._aborts.append(request_id)
 
     def has_unfinished(self) -> bool:
-        return bool(self._aborts) or self.scheduler.has_unfinished()
+        return bool(self._aborts) or self._inflight is not None or self.scheduler.has_unfinished()
 
     # -- one step -----------------------------------------------------------------------------------
     def step(self) -> list[RequestOutput]:
+        """Commit one step's tokens and return what they produced.
+
+        With ``async_decode`` the engine keeps one step in flight: before it waits for the current
+        step's tokens it schedules and launches the next one, whose input ids for the requests that
+        just sampled are taken from the sampler's output on the device.  The host work and the launch
+        of step N+1 so overlap the GPU's work on step N.  A request that stops on a token (as opposed
+        to its length, which is known beforehand) has then run one step in vain; its row is dropped."""
         t = self.timer
         t.reset()
         outputs = self._process_aborts()
-        t.start("schedule")
-        plan = self.scheduler.schedule()
-        t.stop("schedule")
-        for req in plan.failed:
-            outputs.append(self._finish(req, "error", []))
-        self._finalize(outputs)
-        if not plan.items:
-            return outputs + self._fail_unschedulable()
-        outputs += self._run(plan)
+        cur, self._inflight = self._inflight, None
+        if cur is None:
+            cur, outs = self._schedule_and_launch(None)
+            outputs += outs
+            if cur is None:
+                return outputs + self._fail_unschedulable()
+        nxt = None
+        if self._may_look_ahead(cur):
+            self._mark_pending(cur)
+            nxt, outs = self._schedule_and_launch(cur)
+            outputs += outs
+        outputs += self._finish_step(cur)
+        self._inflight = nxt
         self.step_count += 1
         return outputs
 
+    def _schedule_and_launch(self, prev: _InFlight | None) -> tuple[_InFlight | None, list[RequestOutput]]:
+        t = self.timer
+        t.start("schedule")
+        plan = self.scheduler.schedule()
+        t.stop("schedule")
+        outputs = [self._finish(req, "error", []) for req in plan.failed]
+        self._finalize(outputs)
+        if not plan.items:
+            return None, outputs
+        return self._launch(plan, prev), outputs
+
     def _run(self, plan: BatchPlan) -> list[RequestOutput]:
+        """Run one given plan to the end (launch, wait, commit)."""
+        return self._finish_step(self._launch(plan, None))
+
+    def _launch(self, plan: BatchPlan, prev: _InFlight | None) -> _InFlight:
         t = self.timer
         t.start("forward")
         entries = []
+        prev_row = {id(r): i for i, r in enumerate(prev.sampling)} if prev is not None else {}
         for it in plan.items:
             r = it.request
             start = r.num_computed
-            entries.append(StepEntry(r.cache, r.token_ids[start:start + it.num_tokens],
-                                     [it.num_tokens - 1] if it.samples else []))
-        logits = self.runner.step(entries)
+            toks = r.token_ids[start:start + it.num_tokens]
+            feedback = None
+            if r.pending and start + it.num_tokens == len(r.token_ids):
+                feedback = prev_row[id(r)]                        # the stand-in: its id is still on the device
+            entries.append(StepEntry(r.cache, toks, [it.num_tokens - 1] if it.samples else [], feedback))
+        if prev is not None and prev.pending is not None and any(e.feedback is not None for e in entries):
+            logits = self.runner.step(entries, prev.pending.device_out[0])
+        else:
+            logits = self.runner.step(entries)
         t.stop("forward")
         sampling = [it.request for it in plan.items if it.samples]
-        tokens = bad = None
+        pending = None
         t.start("sample")
         if sampling:
-            rows = [SampleRow(r.params, r.seed, r.num_drawn, r.token_ids[:r.num_prompt_tokens],
-                              r.output_ids, self._stop_ids(r)) for r in sampling]
-            tokens, bad = self.sampler.sample(logits, rows)
+            rows = [SampleRow(r.params, r.seed, r.num_drawn + (1 if r.pending else 0),
+                              r.token_ids[:r.num_prompt_tokens], r.output_ids, self._stop_ids(r)) for r in sampling]
+            if hasattr(self.sampler, "launch"):
+                pending = self.sampler.launch(logits, rows)
+            else:
+                pending = _Sampled(*self.sampler.sample(logits, rows))
+        t.stop("sample")
+        return _InFlight(plan, sampling, pending)
+
+    def _may_look_ahead(self, cur: _InFlight) -> bool:
+        if not (self.cfg.async_decode and getattr(self.runner, "supports_feedback", False)):
+            return False
+        if cur.pending is None or isinstance(cur.pending, _Sampled):
+            return False
+        for r in cur.sampling:
+            p = r.params
+            if p.uses_penalties or p.min_tokens > 0:
+                return False                                      # these read the tokens produced so far
+        return any(self._continues_after_next_token(r) for r in cur.sampling)
+
+    def _continues_after_next_token(self, req: Request) -> bool:
+        """Whether the request goes on after the token now in flight, as far as its length decides."""
+        return (req.num_output + 1 < req.params.max_tokens and len(req.token_ids) + 1 < self.max_model_len
+                and not req.finished)
+
+    def _mark_pending(self, cur: _InFlight) -> None:
+        for r in cur.sampling:
+            if self._continues_after_next_token(r):
+                r.token_ids.append(-1)                            # stand-in until the token arrives
+                r.pending = True
+
+    def _finish_step(self, cur: _InFlight) -> list[RequestOutput]:
+        t = self.timer
+        outputs: list[RequestOutput] = []
+        if cur.pending is None:
+            return outputs
+        t.start("sample")
+        if isinstance(cur.pending, _Sampled):
+            tokens, bad = cur.pending.tokens, cur.pending.bad
+        else:
+            tokens, bad = self.sampler.finish(cur.pending)
         t.stop("sample")
         t.start("output")
-        outputs: list[RequestOutput] = []
-        for row, req in enumerate(sampling):
+        for row, req in enumerate(cur.sampling):
+            if req.finished:                                      # stopped or aborted while this step ran
+                continue
+            if req.pending:
+                req.token_ids.pop()
+                req.pending = False
             if bad[row]:
                 outputs.append(self._finish(req, "error", []))
                 continue

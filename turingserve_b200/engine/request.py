@@ -27,6 +27,7 @@ class Request:
     status: Status = Status.WAITING
     finish_reason: str | None = None
     num_drawn: int = 0                   # tokens sampled so far = position in its random stream
+    pending: bool = False                # the last entry of token_ids is a stand-in for a token in flight
     num_preemptions: int = 0
 
     @property

@@ -31,6 +31,8 @@ def run_needs(model: DecoderModel) -> list[RunNeeds]:
 
 
 class ModelRunner:
+    supports_feedback = True            # entries may take their token id from the previous sampler output
+
     def __init__(self, model: DecoderModel, cache: CacheManager, max_tokens: int, max_requests: int,
                  max_model_len: int, graph_batch_sizes: tuple[int, ...] = ()) -> None:
         self.model, self.cache = model, cache
@@ -42,21 +44,31 @@ class ModelRunner:
         self._graphs: dict[int, _DecodeGraph] = {}
 
     # -- the step ---------------------------------------------------------------------------------
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """Logits [sum(len(e.want)), vocab] fp32 in the order of ``entries`` and of each ``want``
-        (None when nothing is wanted).  Grows each request's pages, runs, then advances the cache."""
+        (None when nothing is wanted).  Grows each request's pages, runs, then advances the cache.
+        ``prev_tokens``: the previous step's sampled tokens on the device, for entries whose token
+        is fed back there (``StepEntry.feedback``)."""
         self._check(entries)
+        if prev_tokens is None and any(e.feedback is not None for e in entries):
+            raise ValueError("entries with device feedback need the previous step's tokens")
         for e in entries:
             self.cache.grow(e.cache, len(e.tokens))
         graph_size = self._graph_size(entries)
         if graph_size is not None:
-            logits = self._replay(graph_size, entries)
+            logits = self._replay(graph_size, entries, prev_tokens)
         else:
             step = self.builder.build(entries)
+            self._feed(step, prev_tokens)
             logits = self.forward(step)
         for e in entries:
             self.cache.advance(e.cache, len(e.tokens))
         return logits
+
+    def _feed(self, step: StepInputs, prev_tokens: torch.Tensor | None) -> None:
+        if step.feedback_rows.shape[0]:
+            kernels.ops().feed_tokens(step.input_ids, step.feedback_rows, step.feedback_src, prev_tokens,
+                                      self.model.cfg.vocab_size)
 
     def forward(self, step: StepInputs) -> torch.Tensor | None:
         hidden = self.model.forward(step, self.views, self.cache.states)
@@ -75,6 +87,8 @@ class ModelRunner:
                 raise ValueError(f"request {e.cache.request_id!r} brings no tokens")
             if e.cache.num_tokens + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.cache.request_id!r} would exceed max_model_len {self.max_model_len}")
+            if e.feedback is not None:
+                continue
             lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.cache.request_id!r}: token id outside [0, {vocab})")
@@ -91,11 +105,11 @@ class ModelRunner:
                 return s
         return None
 
-    def _replay(self, size: int, entries: list[StepEntry]) -> torch.Tensor:
+    def _replay(self, size: int, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
         g = self._graphs.get(size)
         if g is None:
             g = self._graphs[size] = _DecodeGraph(self, size)
-        return g.run(entries)
+        return g.run(entries, prev_tokens)
 
 
 class _DecodeGraph:
@@ -118,8 +132,9 @@ class _DecodeGraph:
         # launch geometry must not depend on this step's lengths: size it for the longest context
         return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len)
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
         step = self._build(entries)
+        self.runner._feed(step, prev_tokens)
         ops = kernels.ops()
         if self.graph is None:
             r = self.runner

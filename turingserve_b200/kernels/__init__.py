@@ -79,6 +79,7 @@ class CudaOps:
             "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_linear_tc_ex": [P, P, P, P, P, I, I, I, I, I, I, P, P],
             "ts_reduce_rmsnorm": [P, P, I, P, P, P, F, I, I, I, P],
+            "ts_feed_tokens": [P, P, P, P, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
             "ts_penalize": [P, P, P, P, I, I, P],
         }
@@ -287,6 +288,11 @@ class CudaOps:
     def tc_status(self) -> int:
         """0 when no tensor-core GEMM block ever gave up on a wait (synchronises the device)."""
         return int(self.lib.ts_linear_tc_status())
+
+    def feed_tokens(self, ids, rows, src, tokens, vocab: int) -> None:
+        """ids[rows[i]] = tokens[src[i]] on the device (all int32)."""
+        self._check(self.lib.ts_feed_tokens(_ptr(ids), _ptr(rows), _ptr(src), _ptr(tokens), rows.shape[0], vocab,
+                                            self._stream()), "feed_tokens")
 
     def sample(self, out, logits, fparams, iparams) -> None:
         S, V = logits.shape

@@ -43,14 +43,78 @@ class SampleRow:
     stop_ids: tuple[int, ...] = ()  # eos + stop_token_ids, masked while num_output < min_tokens
 
 
+@dataclass
+class PendingSample:
+    """A draw that has been launched: tokens and flags are on their way to the host."""
+
+    device_out: torch.Tensor        # [2, S] int32 on the device: tokens, then bad flags
+    host_out: torch.Tensor          # the same, in pinned host memory (valid after ``event``)
+    event: object
+    count: int
+
+
 class Sampler:
     def __init__(self, device) -> None:
         self.device = torch.device(device)
+        self._host_ring: list[torch.Tensor] = []
+        self._turn = 0
+        # parameter staging: pinned host memory (a copy from pageable memory would first wait for
+        # everything queued on the stream, and so undo the overlap of steps)
+        self._param_ring: list[tuple[torch.Tensor, torch.Tensor, object]] = []
+        self._param_turn = 0
 
-    @torch.inference_mode()
     def sample(self, logits: torch.Tensor, rows: list[SampleRow]) -> tuple[np.ndarray, np.ndarray]:
         """logits [S, V] fp32 on the device -> (tokens[S], bad[S]) on the host.  ``bad`` marks rows
-        with a non-finite logit; their token is the argmax of zeros, as sampler.py:73-74."""
+        with a NaN or +inf logit; their token is 0 (the reference zeroes such rows, sampler.py:73-74)."""
+        return self.finish(self.launch(logits, rows))
+
+    def finish(self, pending: PendingSample) -> tuple[np.ndarray, np.ndarray]:
+        """Wait for a launched draw (only for it, not for work queued after it)."""
+        if pending.event is not None:
+            pending.event.synchronize()
+        host = pending.host_out.numpy()
+        return host[0, :pending.count].astype(np.int64), host[1, :pending.count].astype(bool)
+
+    def _param_buffers(self, S: int) -> tuple[torch.Tensor, torch.Tensor]:
+        pin = self.device.type == "cuda"
+        if len(self._param_ring) < 4:
+            self._param_ring.append((torch.zeros((max(S, 256), 2), dtype=torch.float32, pin_memory=pin),
+                                     torch.zeros((max(S, 256), 4), dtype=torch.int64, pin_memory=pin), None))
+        k = self._param_turn % len(self._param_ring)
+        fh, ih, ev = self._param_ring[k]
+        if ev is not None:
+            ev.synchronize()                                       # the copy that last used these has run
+        if fh.shape[0] < S:
+            fh = torch.zeros((S, 2), dtype=torch.float32, pin_memory=pin)
+            ih = torch.zeros((S, 4), dtype=torch.int64, pin_memory=pin)
+        self._param_ring[k] = (fh, ih, None)
+        return fh, ih
+
+    def _param_copied(self) -> None:
+        k = self._param_turn % len(self._param_ring)
+        fh, ih, _ = self._param_ring[k]
+        ev = None
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+        self._param_ring[k] = (fh, ih, ev)
+        self._param_turn += 1
+
+    def _host_buffer(self, S: int) -> torch.Tensor:
+        """A contiguous pinned [2, S] int32 buffer (contiguous, so that the copy into it is one
+        asynchronous transfer)."""
+        if len(self._host_ring) < 4:
+            pin = self.device.type == "cuda"
+            self._host_ring.append(torch.empty(2 * max(S, 256), dtype=torch.int32, pin_memory=pin))
+        k = self._turn % len(self._host_ring)
+        if self._host_ring[k].numel() < 2 * S:
+            self._host_ring[k] = torch.empty(2 * S, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._turn += 1
+        return self._host_ring[k][: 2 * S].view(2, S)
+
+    @torch.inference_mode()
+    def launch(self, logits: torch.Tensor, rows: list[SampleRow]) -> PendingSample:
+        """Edit the logits, draw, and start the copy of tokens and flags to the host; no waiting."""
         ops = kernels.ops()
         S, V = logits.shape
         assert S == len(rows)
@@ -58,8 +122,10 @@ class Sampler:
         if any(r.params.uses_penalties or len(r.output_ids) < r.params.min_tokens for r in rows):
             logits = logits.clone()
             self._edit_logits(ops, logits, rows)
-        f = np.zeros((S, 2), dtype=np.float32)
-        i = np.zeros((S, 4), dtype=np.int64)
+        fh, ih = self._param_buffers(S)
+        f, i = fh.numpy()[:S], ih.numpy()[:S]
+        f[:] = 0
+        i[:] = 0
         for n, r in enumerate(rows):
             p = r.params
             f[n, 0] = 0.0 if p.greedy else p.temperature
@@ -67,12 +133,18 @@ class Sampler:
             i[n, 0] = p.top_k
             i[n, 1] = np.int64(np.uint64(r.seed & _MASK64).astype(np.int64))
             i[n, 2] = r.num_drawn
-        fp = torch.from_numpy(f).to(dev, non_blocking=True)
-        ip = torch.from_numpy(i).to(dev, non_blocking=True)
+        fp = fh[:S].to(dev, non_blocking=True)
+        ip = ih[:S].to(dev, non_blocking=True)
+        self._param_copied()
         out = torch.empty((2, S), dtype=torch.int32, device=dev)
         ops.sample(out, logits, fp, ip)
-        host = out.cpu().numpy()                       # the one device-to-host copy of the step
-        return host[0].astype(np.int64), host[1].astype(bool)
+        host = self._host_buffer(S)
+        host.copy_(out, non_blocking=True)             # the one device-to-host copy of the step
+        event = None
+        if dev.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+        return PendingSample(out, host, event, S)
 
     def _edit_logits(self, ops, logits: torch.Tensor, rows: list[SampleRow]) -> None:
         """Penalties (penalties.py:20-45), then stop tokens masked to -inf while fewer than
