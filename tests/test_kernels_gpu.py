@@ -160,7 +160,7 @@ def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, nee
     return qkv.to(dtype), kc.to(dtype), vc.to(dtype), bt, qs, sl
 
 
-def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True):
+def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True, tc=True):
     qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle)
     T = qkv.shape[0]
     scale = D ** -0.5
@@ -170,10 +170,13 @@ def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=N
     step = FakeStep(qs.cuda(), sl.cuda(), len(q_lens), max(q_lens), int(sl.max()), nd)
     out = torch.full((T, H * D), float("nan"), dtype=dtype, device="cuda")
     ops.use_fast_attention = fast
+    tc_before = ops.use_tc_attention
+    ops.use_tc_attention = tc and tc_before
     try:
         ops.attention(out, qkv.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, H, KVH, D, page, scale, window)
     finally:
         ops.use_fast_attention = True
+        ops.use_tc_attention = tc_before
     ref = torch.empty((T, H * D), dtype=torch.float32)
     paged_attention(ref, qkv.float(), kc.float(), vc.float(), bt, qs, sl, H, KVH, D, page, scale, window)
     return out.cpu().float(), ref, (qkv, kc, vc, bt, qs, sl)
@@ -210,9 +213,9 @@ def test_attention_decode_split_counts(ops, B, ctx, window):
 @pytest.mark.parametrize("case", [[(1, 0)], [(15, 16)], [(16, 37)], [(17, 1000)], [(300, 0)],
                                   [(1, 5), (1, 99), (40, 0), (2, 31), (33, 64)]])
 def test_attention_chunks(ops, dtype, H, KVH, D, page, case):
-    for fast in (True, False):
+    for fast, tc in ((True, True), (True, False), (False, False)):
         out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [c[0] for c in case], [c[1] for c in case], 12,
-                                     fast=fast)
+                                     fast=fast, tc=tc)
         torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
 
 
@@ -221,9 +224,10 @@ def test_attention_chunks(ops, dtype, H, KVH, D, page, case):
 def test_attention_long_portions(ops, H, KVH, D, window):
     """Portions of hundreds of tokens after long prefixes, several requests of different shape in
     one launch, group sizes that are no power of two (and one above 16)."""
-    out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, 16, [1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129],
-                                 16, window=window)
-    torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+    for tc in (True, False):
+        out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, 16, [1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129],
+                                     16, window=window, tc=tc)
+        torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -329,3 +333,25 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
         assert ops.tc_status() == 0
     finally:
         ops.gemm_mode = DEFAULT_GEMM
+
+
+@pytest.mark.parametrize("H,KVH", [(12, 2), (28, 4), (5, 5), (40, 2)])
+@pytest.mark.parametrize("page", [16, 32])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_tensor_core_portions(ops, H, KVH, page, window):
+    """The tcgen05 prompt-portion kernel (head size 128): portions after prefixes, several requests,
+    group sizes that are no power of two, a needle far back."""
+    D = 128
+    ops.use_tc_attention = True
+    try:
+        for q_lens, prefixes in (([300], [0]), ([1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129]), ([17, 40], [1000, 3])):
+            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 21, window=window)
+            torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+        if window is None:
+            for needle in (0, 15, 16, 63, 64, 65, 127, 500):
+                out, ref, (qkv, kc, vc, bt, qs, sl) = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [9, 130], [891, 770],
+                                                                   22, needle=needle)
+                torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+        assert ops.tc_status() == 0, "a block of the tensor-core attention gave up on a wait"
+    finally:
+        ops.use_tc_attention = True

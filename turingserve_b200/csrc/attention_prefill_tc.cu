@@ -1,0 +1,406 @@
+// Paged grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor cores:
+// S = Q.K^T and O += P.V are tcgen05.mma products with their accumulators in tensor memory;
+// key/value tiles come from the paged cache by TMA (one box per page and half head), P goes
+// through shared memory.  Same semantics as attention_prefill.cu (the reference's
+// turingserve/ops/triton_prefill_attention.py:17-79 and turingserve/ops/reference.py:60-77,94-111,
+// plus the optional window); bfloat16, head size 128, pages that are a multiple of 16 tokens.
+//
+// One block = 128 query ROWS (a row is one (token, head-in-group) pair of one kv head, so a
+// group shares its key/value tiles).  Warps 0-3: thread r owns row r and tensor-memory lane r.
+// Warp 4 (one lane): TMA loads and product issue.  Per 64-key tile:
+//   warp 4   : S[128x64] = Q[128x128] . K[64x128]^T            (tcgen05.mma, K-major operands)
+//   warps 0-3: read S from tensor memory, mask, online softmax in 32-bit, write P (bfloat16)
+//              into shared memory in the 128-byte-swizzled layout the next product expects;
+//              rescale O in tensor memory when a row's maximum moved; arrive on a barrier
+//   warp 4   : O[128x128] += P[128x64] . V[64x128]               (V is MN-major: as TMA left it)
+// Two blocks share an SM, so one block's softmax overlaps the other's products.  Every barrier
+// wait is bounded; a block that gives up records where, stops, and frees its tensor memory.
+#include "common.cuh"
+#include "tc_utils.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int TQ = 128;            // query rows per block = TMEM lanes
+constexpr int TK = 64;             // keys per tile
+constexpr int HD = 128;            // head size
+constexpr int KV_STAGES = 2;
+constexpr int BOX_ROWS = 16;       // keys per TMA box
+constexpr uint32_t Q_BYTES = TQ * HD * 2;                 // 2 halves x [128 rows][128 B]
+constexpr uint32_t P_BYTES = TQ * TK * 2;                 // [128 rows][128 B]
+constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;           // 2 halves x [64 keys][128 B]
+constexpr uint32_t HALF_K = TK * 128;                     // bytes between the two 64-column halves of a K/V tile
+constexpr uint32_t HALF_Q = TQ * 128;
+constexpr uint32_t TMEM_COLS = 256;                       // S: columns 0..63, O: columns 64..191
+constexpr uint32_t S_COL = 0, O_COL = 64;
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+__device__ int g_attn_status = 0;   // 0 = fine; otherwise the wait that ran out
+
+// Shared-memory descriptor for an MN-major operand ([k rows][64 elements = 128 B], 128-byte swizzle):
+// 8-row groups along K are 1024 B apart (SBO), the next 64 elements along MN are `lbo` bytes away.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+struct AttnArgs {
+  bf16* out;
+  const bf16* qkv;
+  const int* block_tables;
+  const int* q_start;
+  const int* seq_lens;
+  int table_width, H, KVH, page;
+  float scale;
+  int window;
+  int* status;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+constexpr int ATT_THREADS = TQ + 32;      // warps 0-3: one query row per thread; warp 4: TMA and MMA issue
+
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                            const AttnArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* q_s = smem;                               // [2][128][128 B]
+  unsigned char* p_s = q_s + Q_BYTES;                      // [128][128 B]
+  unsigned char* k_s = p_s + P_BYTES;                      // [STAGES][2][64][128 B]
+  unsigned char* v_s = k_s + KV_STAGES * KV_TILE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * KV_TILE_BYTES);
+  uint64_t* empty = full + KV_STAGES;
+  uint64_t* bar_s = empty + KV_STAGES;                     // S of a tile (and every product issued before it) is complete
+  uint64_t* bar_p = bar_s + 1;                             // all 128 rows have consumed S and written P
+  uint64_t* bar_o = bar_p + 1;                             // the last O product is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int G = a.H / a.KVH;
+  const int qs = a.q_start[b];
+  const int q_len = a.q_start[b + 1] - qs;
+  const int seq_len = a.seq_lens[b];
+  const int n_rows = q_len * G;
+  const int n_row_tiles = (n_rows + TQ - 1) / TQ;
+  if ((int)blockIdx.x >= n_row_tiles) return;
+  const int row0 = (n_row_tiles - 1 - blockIdx.x) * TQ;     // longest tiles first
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int prefix = seq_len - q_len;
+
+  if ((smem_u32(smem) & 1023u) != 0) {                       // the swizzled tiles need 1024-byte alignment
+    if (tid == 0) atomicCAS(a.status, 0, 9);
+    return;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, TQ);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  // key range of the block, its start aligned down to a TMA box
+  const int last_row = min(row0 + TQ, n_rows) - 1;
+  const int j_hi = prefix + last_row / G;
+  int j_lo = a.window > 0 ? max(0, prefix + row0 / G - a.window + 1) : 0;
+  j_lo &= ~(BOX_ROWS - 1);
+  const int n_tiles = (seq_len > 0 && j_hi >= j_lo) ? (j_hi - j_lo) / TK + 1 : 0;
+
+  // a softmax thread's row
+  const int row = row0 + tid;
+  const bool row_ok = tid < TQ && row < n_rows;
+  const int tok = row_ok ? row / G : 0, g = row_ok ? row % G : 0;
+  const int pos = row_ok ? prefix + tok : -1;
+
+  pdl_wait();                                               // q/k/v of this step are written by earlier kernels
+
+  // Q rows -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7))
+  if (tid < TQ) {
+    const bf16* src = a.qkv + (size_t)(qs + tok) * (a.H + 2 * a.KVH) * HD + (size_t)(kvh * G + g) * HD;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row_ok) v = *reinterpret_cast<const uint4*>(src + c * 8);
+      const int half = c >> 3, cc = c & 7;
+      *reinterpret_cast<uint4*>(q_s + half * HALF_Q + tid * 128 + ((cc ^ (tid & 7)) << 4)) = v;
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ================= controller: TMA loads and tcgen05.mma issue, one lane =================
+    if ((tid & 31) == 0 && n_tiles > 0) {
+      // one TMA box per (16 keys, 64 columns): 8 boxes for K and 8 for V per tile
+      auto load_tile = [&](int t, int stage) {
+        mbar_expect_tx(&full[stage], 2 * KV_TILE_BYTES);
+        const int j0 = j_lo + t * TK;
+        for (int bx = 0; bx < TK / BOX_ROWS; ++bx) {
+          const int j = j0 + bx * BOX_ROWS;
+          const int lp = j / a.page;
+          const int pg = lp < a.table_width ? a.block_tables[(size_t)b * a.table_width + lp] : 0;
+          const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t off = stage * KV_TILE_BYTES + half * HALF_K + bx * BOX_ROWS * 128;
+            tma_load_2d(k_s + off, &k_map, half * 64, y, &full[stage]);
+            tma_load_2d(v_s + off, &v_map, half * 64, y, &full[stage]);
+          }
+        }
+      };
+      // S = Q . K^T for the tile in `stage`: 8 k-steps of 16 columns, 4 per 64-column half
+      auto issue_s = [&](int stage) {
+        constexpr uint32_t idesc = instr_desc(TK);
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + stage * KV_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off_q = (ks >> 2) * HALF_Q + (ks & 3) * 32;
+          const uint32_t off_k = (ks >> 2) * HALF_K + (ks & 3) * 32;
+          umma(tmem + S_COL, smem_desc(qa + off_q), smem_desc(ka + off_k), idesc, ks > 0 ? 1u : 0u);
+        }
+      };
+      // O += P . V: 4 k-steps of 16 keys; V is MN-major (rows = keys, 128 B of head columns per row)
+      auto issue_o = [&](int stage, bool accumulate) {
+        constexpr uint32_t idesc = instr_desc(HD, true);
+        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + stage * KV_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < TK / 16; ++kk)
+          umma(tmem + O_COL, smem_desc(pa + kk * 32), smem_desc_mn(va + kk * 16 * 128, HALF_K), idesc,
+               (accumulate || kk > 0) ? 1u : 0u);
+      };
+
+      load_tile(0, 0);
+      if (n_tiles > 1) load_tile(1, 1);
+      bool ok = mbar_wait(&full[0], 0, a.status, 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        umma_commit(bar_s);
+      }
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int stage = t % KV_STAGES;
+        ok = mbar_wait(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place, S(t) is consumed
+        if (!ok) break;
+        tc_fence_after();
+        issue_o(stage, t > 0);
+        umma_commit(&empty[stage]);                           // K/V of this stage are free once this product is done
+        if (t + 1 < n_tiles) {
+          ok = mbar_wait(&full[(t + 1) % KV_STAGES], (uint32_t)(((t + 1) / KV_STAGES) & 1), a.status, 3, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s((t + 1) % KV_STAGES);
+          umma_commit(bar_s);
+          if (t + 2 < n_tiles) {
+            ok = mbar_wait(&empty[stage], (uint32_t)((t / KV_STAGES) & 1), a.status, 4, abort_flag);
+            if (!ok) break;
+            load_tile(t + 2, stage);
+          }
+        } else {
+          umma_commit(bar_o);
+        }
+      }
+    }
+  } else {
+    // ================= softmax warps: thread = row = tensor-memory lane =================
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = a.scale * LOG2E_F;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      // S of this tile; the commit behind it also covers the O product of the tile before
+      ok = mbar_wait(bar_s, (uint32_t)(t & 1), a.status, 2, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int j0 = j_lo + t * TK;
+      uint32_t sv[2][32];
+      tmem_ld32(tmem + lane_addr + S_COL, sv[0]);
+      tmem_ld32(tmem + lane_addr + S_COL + 32, sv[1]);
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      // tiles wholly before every row of the warp (the common case away from the diagonal) need no mask
+      const bool all_visible = __all_sync(0xffffffffu, (j0 + TK - 1 <= pos) && (a.window <= 0 || j0 > pos - a.window));
+      if (all_visible) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(sv[h][i]) * sc;
+            sv[h][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int j = j0 + h * 32 + i;
+            const bool vis = (j <= pos) && (a.window <= 0 || j > pos - a.window);
+            const float v = vis ? __uint_as_float(sv[h][i]) * sc : -INFINITY;
+            sv[h][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m_run - m_use);
+      m_run = m_new;
+      float rs = 0.f;
+      // P (bfloat16) -> shared memory, row `tid`, 8 chunks of 8 keys, swizzled
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i0 = c * 8 + e * 2;
+          const float p0 = exp2f(__uint_as_float(sv[i0 >> 5][i0 & 31]) - m_use);
+          const float p1 = exp2f(__uint_as_float(sv[(i0 + 1) >> 5][(i0 + 1) & 31]) - m_use);
+          rs += p0 + p1;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          w[e] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(p_s + tid * 128 + ((c ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run = l_run * corr + rs;
+      // rescale O where a maximum moved (skipped when no row of the warp needs it)
+      if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t ov[32];
+          tmem_ld32(tmem + lane_addr + O_COL + c, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+          tmem_st32(tmem + lane_addr + O_COL + c, ov);
+        }
+        tmem_wait_st();
+      }
+      fence_async_smem();                                     // P is read by the tensor core (async proxy)
+      tc_fence_before();
+      mbar_arrive(bar_p);
+    }
+    // epilogue: O / l -> bfloat16 -> global, one 256-byte row per thread
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(bar_o, 0, a.status, 5, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      bf16* dst = a.out + (size_t)(qs + tok) * a.H * HD + (size_t)(kvh * G + g) * HD;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t ov[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem + lane_addr + O_COL + c, ov);       // the whole warp loads; rows without a query store nothing
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * e]) * inv, __uint_as_float(ov[i + 2 * e + 1]) * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+int* attn_status_word() {
+  static int* p = nullptr;
+  if (p == nullptr && cudaGetSymbolAddress((void**)&p, g_attn_status) != cudaSuccess) p = nullptr;
+  return p;
+}
+
+}  // namespace
+
+TS_API int ts_attention_prefill_tc_supported(int H, int KVH, int D, int page, int dtype) {
+  return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && D == HD && page >= BOX_ROWS && page % BOX_ROWS == 0;
+}
+
+// 0 when no block ever gave up on a wait (synchronises the device).
+TS_API int ts_attention_prefill_tc_status() {
+  int* p = attn_status_word();
+  int v = -1;
+  if (p != nullptr) cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+// num_pages: pages in the pool (rows of the cache = num_pages * KVH * page).
+TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cache, const void* v_cache,
+                                   const int* block_tables, const int* q_start, const int* seq_lens, int B,
+                                   int table_width, int max_q_len, int H, int KVH, int D, int page, int num_pages,
+                                   float scale, int window, void* stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (!ts_attention_prefill_tc_supported(H, KVH, D, page, TS_BF16))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: H=%d KVH=%d D=%d page=%d is not taken by this kernel", H, KVH, D, page);
+  if (B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_prefill_tc: %d requests / %d kv heads", B, KVH);
+  if ((((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
+    TS_REFUSE(TS_ERR_ALIGN, "ts_attention_prefill_tc: buffers must be 16-byte aligned");
+  int* status = attn_status_word();
+  if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_prefill_tc: no status word");
+  CUtensorMap k_map, v_map;
+  const long long rows = (long long)num_pages * KVH * page;
+  if (rows > 0x7fffffffLL) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_prefill_tc: cache of %lld rows", rows);
+  if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, BOX_ROWS) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, BOX_ROWS))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
+  constexpr size_t smem = Q_BYTES + P_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + (2 * KV_STAGES + 3) * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_prefill_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  AttnArgs a;
+  a.out = (bf16*)out;
+  a.qkv = (const bf16*)qkv;
+  a.block_tables = block_tables;
+  a.q_start = q_start;
+  a.seq_lens = seq_lens;
+  a.table_width = table_width;
+  a.H = H;
+  a.KVH = KVH;
+  a.page = page;
+  a.scale = scale;
+  a.window = window;
+  a.status = status;
+  const int G = H / KVH;
+  dim3 grid(ceil_div(max_q_len * G, TQ), KVH, B);
+  ts_launch(attention_prefill_tc_kernel, grid, dim3(ATT_THREADS), smem, (cudaStream_t)stream, k_map, v_map, a);
+  TS_LAUNCH_CHECK();
+}

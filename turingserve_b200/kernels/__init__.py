@@ -76,6 +76,7 @@ class CudaOps:
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
             "ts_attention_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+            "ts_attention_prefill_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
             "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_linear_tc_ex": [P, P, P, P, P, I, I, I, I, I, I, P, P],
             "ts_reduce_rmsnorm": [P, P, I, P, P, P, F, I, I, I, P],
@@ -101,6 +102,12 @@ class CudaOps:
         self.lib.ts_set_pdl.argtypes = [I]
         self.lib.ts_set_pdl.restype = None
         self.lib.ts_set_pdl(0 if os.environ.get("TURINGSERVE_B200_PDL", "1") == "0" else 1)
+        self.lib.ts_attention_prefill_tc_supported.argtypes = [I, I, I, I, I]
+        self.lib.ts_attention_prefill_tc_supported.restype = c_int
+        self.lib.ts_attention_prefill_tc_status.argtypes = []
+        self.lib.ts_attention_prefill_tc_status.restype = c_int
+        # prompt-portion attention on tcgen05 (head size 128, pages of a multiple of 16 tokens) or mma.sync
+        self.use_tc_attention = os.environ.get("TURINGSERVE_B200_ATTENTION", "tc") == "tc"
         self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_prefill_supported.restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
@@ -214,6 +221,14 @@ class CudaOps:
                 nsplit, self._stream()), "attention_decode")
         if nd == B:
             return
+        if (self.use_fast_attention and self.use_tc_attention
+                and self.lib.ts_attention_prefill_tc_supported(H, KVH, D, page_size, code)):
+            self._check(self.lib.ts_attention_prefill_tc(
+                _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), block_tables.data_ptr() + 4 * nd * width,
+                step.q_start.data_ptr() + 4 * nd, step.seq_lens.data_ptr() + 4 * nd, B - nd, width,
+                step.max_q_len, H, KVH, D, page_size, k_cache.shape[0], float(scale), w, self._stream()),
+                "attention_prefill_tc")
+            return
         if self.use_fast_attention and self.lib.ts_attention_prefill_supported(H, KVH, D, code):
             self._check(self.lib.ts_attention_prefill(
                 _ptr(out), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), block_tables.data_ptr() + 4 * nd * width,
@@ -286,8 +301,8 @@ class CudaOps:
         return max(1, min(self.num_sms // tiles, k_blocks // 2, traffic_cap))
 
     def tc_status(self) -> int:
-        """0 when no tensor-core GEMM block ever gave up on a wait (synchronises the device)."""
-        return int(self.lib.ts_linear_tc_status())
+        """0 when no tensor-core block (GEMM or attention) ever gave up on a wait (synchronises the device)."""
+        return int(self.lib.ts_linear_tc_status()) or int(self.lib.ts_attention_prefill_tc_status())
 
     def feed_tokens(self, ids, rows, src, tokens, vocab: int) -> None:
         """ids[rows[i]] = tokens[src[i]] on the device (all int32)."""
