@@ -221,12 +221,28 @@ __global__ void reduce_rmsnorm_kernel(bf16* __restrict__ out, const float* __res
     const int i = (c * blockDim.x + threadIdx.x) * 8;
     if (i < hidden) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int sp = 0; sp < splits; ++sp) {
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i));
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i + 4));
-        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      if (splits <= 16) {
+        // all loads first (one round trip), then the sums in ascending split order
+        float4 a[16], b[16];
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp)
+          if (sp < splits) {
+            a[sp] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i));
+            b[sp] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i + 4));
+          }
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp)
+          if (sp < splits) {
+            acc[0] += a[sp].x; acc[1] += a[sp].y; acc[2] += a[sp].z; acc[3] += a[sp].w;
+            acc[4] += b[sp].x; acc[5] += b[sp].y; acc[6] += b[sp].z; acc[7] += b[sp].w;
+          }
+      } else {
+        for (int sp = 0; sp < splits; ++sp) {
+          const float4 a = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i));
+          const float4 b = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i + 4));
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+          acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
       }
       if (bias != nullptr) {
         float bv[8];
@@ -422,12 +438,21 @@ __device__ __forceinline__ void load_qkv8(const bf16* row, int col, const float*
   }
 #pragma unroll
   for (int k = 0; k < 8; ++k) f[k] = 0.f;
-#pragma unroll 4
-  for (int sp = 0; sp < splits; ++sp) {
-    const float4 a = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + part_row + col));
-    const float4 b = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + part_row + col + 4));
-    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+  // eight splits' loads at a time (one round trip per eight), sums in ascending split order
+  for (int s0 = 0; s0 < splits; s0 += 8) {
+    float4 a[8], b[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (s0 + u < splits) {
+        a[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col));
+        b[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col + 4));
+      }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (s0 + u < splits) {
+        f[0] += a[u].x; f[1] += a[u].y; f[2] += a[u].z; f[3] += a[u].w;
+        f[4] += b[u].x; f[5] += b[u].y; f[6] += b[u].z; f[7] += b[u].w;
+      }
   }
   if (bias != nullptr) {
     float bv[8];

@@ -15,6 +15,8 @@
 // tcgen05.ld and write the result.  Stages are handed over through mbarriers; every wait is
 // bounded: when a barrier does not flip in time the block records where in `status`, stops, and
 // still frees its tensor memory.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -37,7 +39,9 @@ struct GemmArgs {
 };
 
 // BN: tile columns (UMMA N).  SWAP: the tile rows are weight rows (outputs), columns are tokens.
-template <int BN, int STAGES, bool SWAP>
+// KSUB: 64-column k-blocks per pipeline stage (their TMA boxes are issued back to back, so a weight
+// row is touched KSUB * 128 contiguous bytes at a time).
+template <int BN, int STAGES, bool SWAP, int KSUB>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                const GemmArgs args) {
@@ -46,8 +50,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* a_s = smem;
-  unsigned char* b_s = smem + STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * B_BYTES);
+  constexpr uint32_t STAGE_A = KSUB * A_BYTES, STAGE_B = KSUB * B_BYTES;
+  unsigned char* b_s = smem + STAGES * STAGE_A;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * STAGE_B);
   uint64_t* empty = full + STAGES;
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
@@ -61,6 +66,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
   const int kb_begin = blockIdx.z * args.k_blocks_per_split;
   const int kb_end = min(total_kb, kb_begin + args.k_blocks_per_split);
   const int n_kb = kb_end - kb_begin;
+  const int n_it = (n_kb + KSUB - 1) / KSUB;          // pipeline iterations: KSUB k-blocks each (the last may hold fewer)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -89,41 +95,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
       unsigned char* w_s = SWAP ? a_s : b_s;
       unsigned char* x_s = SWAP ? b_s : a_s;
       constexpr uint32_t W_BYTES = SWAP ? A_BYTES : B_BYTES, X_BYTES = SWAP ? B_BYTES : A_BYTES;
+      constexpr uint32_t W_STAGE = KSUB * W_BYTES, X_STAGE = KSUB * X_BYTES;
       const int w_row = SWAP ? row0 : col0, x_row = SWAP ? col0 : row0;
-      const int early = n_kb < STAGES ? n_kb : STAGES;
+      const int early = n_it < STAGES ? n_it : STAGES;
       for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
-        tma_load_2d(w_s + i * W_BYTES, w_map, (kb_begin + i) * BK, w_row, &full[i]);
+        const int subs = min(KSUB, n_kb - i * KSUB);
+        mbar_expect_tx(&full[i], subs * (A_BYTES + B_BYTES));
+        for (int u = 0; u < subs; ++u)
+          tma_load_2d(w_s + i * W_STAGE + u * W_BYTES, w_map, (kb_begin + i * KSUB + u) * BK, w_row, &full[i]);
       }
       pdl_wait();
-      for (int i = 0; i < early; ++i)
-        tma_load_2d(x_s + i * X_BYTES, x_map, (kb_begin + i) * BK, x_row, &full[i]);
-      for (int i = early; i < n_kb; ++i) {
+      for (int i = 0; i < early; ++i) {
+        const int subs = min(KSUB, n_kb - i * KSUB);
+        for (int u = 0; u < subs; ++u)
+          tma_load_2d(x_s + i * X_STAGE + u * X_BYTES, x_map, (kb_begin + i * KSUB + u) * BK, x_row, &full[i]);
+      }
+      for (int i = early; i < n_it; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, args.status, 1, abort_flag)) break;
-        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-        const int k = (kb_begin + i) * BK;
-        tma_load_2d(w_s + s * W_BYTES, w_map, k, w_row, &full[s]);
-        tma_load_2d(x_s + s * X_BYTES, x_map, k, x_row, &full[s]);
+        const int subs = min(KSUB, n_kb - i * KSUB);
+        mbar_expect_tx(&full[s], subs * (A_BYTES + B_BYTES));
+        for (int u = 0; u < subs; ++u) {
+          const int k = (kb_begin + i * KSUB + u) * BK;
+          tma_load_2d(w_s + s * W_STAGE + u * W_BYTES, w_map, k, w_row, &full[s]);
+          tma_load_2d(x_s + s * X_STAGE + u * X_BYTES, x_map, k, x_row, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
+      for (int i = 0; i < n_it && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         ok = mbar_wait(&full[s], ph, args.status, 2, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = smem_desc(smem_u32(a_s + s * A_BYTES));
-        const uint64_t db = smem_desc(smem_u32(b_s + s * B_BYTES));
+        const int subs = min(KSUB, n_kb - i * KSUB);
+        for (int u = 0; u < subs; ++u) {
+          const uint64_t da = smem_desc(smem_u32(a_s + s * STAGE_A + u * A_BYTES));
+          const uint64_t db = smem_desc(smem_u32(b_s + s * STAGE_B + u * B_BYTES));
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma(tmem_base, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
-               (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem_base, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
+                 (i > 0 || u > 0 || k > 0) ? 1u : 0u);
+        }
         umma_commit(&empty[s]);                    // the stage is free once these MMAs have read it
       }
       umma_commit(accum);                          // the accumulator is complete
@@ -225,16 +243,16 @@ int* status_word() {
   return p;
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int KSUB = 1>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmArgs& args, dim3 grid, cudaStream_t s) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_linear_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  ts_launch(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map, cols_map, args);
+  ts_launch(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map, cols_map, args);
   TS_LAUNCH_CHECK();
 }
 
@@ -307,7 +325,12 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
     if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
       TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: cuTensorMapEncodeTiled failed");
     dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
-    if (bn == 16) rc = launch<16, 4, true>(rows_map, cols_map, a, grid, s);
+    static const int stages16 = getenv("TS_GEMM_STAGES16") ? atoi(getenv("TS_GEMM_STAGES16")) : 4;
+    if (bn == 16 && stages16 == 23) rc = launch<16, 3, true, 2>(rows_map, cols_map, a, grid, s);
+    else if (bn == 16 && stages16 == 24) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
+    else if (bn == 16 && stages16 == 42) rc = launch<16, 2, true, 4>(rows_map, cols_map, a, grid, s);
+    else if (bn == 16 && stages16 == 43) rc = launch<16, 3, true, 4>(rows_map, cols_map, a, grid, s);
+    else if (bn == 16) rc = launch<16, 4, true>(rows_map, cols_map, a, grid, s);
     else if (bn == 32) rc = launch<32, 4, true>(rows_map, cols_map, a, grid, s);
     else if (bn == 64) rc = launch<64, 4, true>(rows_map, cols_map, a, grid, s);
     else rc = launch<128, 4, true>(rows_map, cols_map, a, grid, s);
