@@ -68,13 +68,40 @@ def test_greedy_generation_bfloat16(tmp_path, graphs):
         tokens_are_best(cfg, w, p, o.token_ids, 0.05)
 
 
-def test_cuda_graphs_do_not_change_tokens(tmp_path):
+def test_cuda_graphs_and_look_ahead_do_not_change_tokens(tmp_path):
+    """Requests of different lengths finish at different steps, so captured batch sizes are padded
+    and the number of rows fed back on the device changes from step to step: graphs on or off, the
+    next step launched ahead or not, the tokens are the same."""
+    from turingserve_b200 import SamplingParams
     folder = tiny.make_tiny_folder("B", tmp_path)
     cfg, _ = plain.read_folder(folder)
-    prompts = [tiny.random_ids(n, cfg["vocab_size"], 40 + n) for n in (7, 21, 2, 50, 11)]
-    a = engine(folder, "bfloat16", cuda_graphs=True, block_size=8).generate(prompts, greedy(20))
-    b = engine(folder, "bfloat16", cuda_graphs=False, block_size=8).generate(prompts, greedy(20))
-    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    prompts = [tiny.random_ids(n, cfg["vocab_size"], 40 + n) for n in (7, 21, 2, 50, 11, 33, 5)]
+    params = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for m in (20, 3, 31, 9, 14, 1, 26)]
+    runs = {}
+    for graphs in (True, False):
+        for ahead in (True, False):
+            eng = engine(folder, "bfloat16", cuda_graphs=graphs, async_decode=ahead, block_size=8, max_num_seqs=8,
+                         graph_batch_sizes=(1, 2, 4, 8), max_num_batched_tokens=32)
+            runs[(graphs, ahead)] = [o.token_ids for o in eng.generate(prompts, params)]
+            assert not eng.cache.live
+    base = runs[(False, False)]
+    assert [len(t) for t in base] == [20, 3, 31, 9, 14, 1, 26]
+    for key, got in runs.items():
+        assert got == base, key
+    # stop tokens under look-ahead: a request that stops on a token has run one step in vain; its output is the same
+    stop = base[2][5]
+    stopped = {}
+    for ahead in (True, False):
+        eng = engine(folder, "bfloat16", async_decode=ahead, block_size=8)
+        outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=31, stop_token_ids=[stop])] * len(prompts))
+        stopped[ahead] = [(o.token_ids, o.finish_reason) for o in outs]
+        for toks, reason in stopped[ahead]:
+            assert (stop in toks) == (reason == "stop")
+            if stop in toks:
+                assert toks.index(stop) == len(toks) - 1
+        assert not eng.cache.live
+    assert stopped[True] == stopped[False]
+    assert stopped[True][2][0] == base[2][:base[2].index(stop) + 1]
 
 
 def test_entry_points_and_command_line(tmp_path):

@@ -1,7 +1,7 @@
 // Paged grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor cores:
 // S = Q.K^T and O += P.V are tcgen05.mma products with their accumulators in tensor memory;
-// key/value tiles come from the paged cache by TMA (one box per page and half head), P goes
-// through shared memory.  Same semantics as attention_prefill.cu (the reference's
+// key/value tiles come from the paged cache by TMA (one box per page and half head); P never
+// leaves tensor memory (the second product reads its A operand from there).  Same semantics as attention_prefill.cu (the reference's
 // turingserve/ops/triton_prefill_attention.py:17-79 and turingserve/ops/reference.py:60-77,94-111,
 // plus the optional window); bfloat16, head size 128, pages that are a multiple of 16 tokens.
 //
@@ -9,10 +9,9 @@
 // group shares its key/value tiles).  Warps 0-3: thread r owns row r and tensor-memory lane r.
 // Warp 4 (one lane): TMA loads and product issue.  Per 64-key tile:
 //   warp 4   : S[128x64] = Q[128x128] . K[64x128]^T            (tcgen05.mma, K-major operands)
-//   warps 0-3: read S from tensor memory, mask, online softmax in 32-bit, write P (bfloat16)
-//              into shared memory in the 128-byte-swizzled layout the next product expects;
-//              rescale O in tensor memory when a row's maximum moved; arrive on a barrier
-//   warp 4   : O[128x128] += P[128x64] . V[64x128]               (V is MN-major: as TMA left it)
+//   warps 0-3: read S from tensor memory, mask, online softmax in 32-bit, write P (bfloat16 pairs)
+//              back to tensor memory; rescale O there when a row's maximum moved; arrive on a barrier
+//   warp 4   : O[128x128] += P[128x64] . V[64x128]   (P from tensor memory, V MN-major as TMA left it)
 // Two blocks share an SM, so one block's softmax overlaps the other's products.  Every barrier
 // wait is bounded; a block that gives up records where, stops, and frees its tensor memory.
 #include "common.cuh"
@@ -28,12 +27,11 @@ constexpr int HD = 128;            // head size
 constexpr int KV_STAGES = 2;
 constexpr int BOX_ROWS = 16;       // keys per TMA box
 constexpr uint32_t Q_BYTES = TQ * HD * 2;                 // 2 halves x [128 rows][128 B]
-constexpr uint32_t P_BYTES = TQ * TK * 2;                 // [128 rows][128 B]
 constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;           // 2 halves x [64 keys][128 B]
 constexpr uint32_t HALF_K = TK * 128;                     // bytes between the two 64-column halves of a K/V tile
 constexpr uint32_t HALF_Q = TQ * 128;
-constexpr uint32_t TMEM_COLS = 256;                       // S: columns 0..63, O: columns 64..191
-constexpr uint32_t S_COL = 0, O_COL = 64;
+constexpr uint32_t TMEM_COLS = 256;                       // S: columns 0..63, O: 64..191, P (bf16 pairs): 192..223
+constexpr uint32_t S_COL = 0, O_COL = 64, P_COL = 192;
 constexpr float LOG2E_F = 1.4426950408889634f;
 
 __device__ int g_attn_status = 0;   // 0 = fine; otherwise the wait that ran out
@@ -62,6 +60,14 @@ struct AttnArgs {
   int* status;
 };
 
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (here P) is read from tensor memory.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -74,8 +80,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                               // [2][128][128 B]
-  unsigned char* p_s = q_s + Q_BYTES;                      // [128][128 B]
-  unsigned char* k_s = p_s + P_BYTES;                      // [STAGES][2][64][128 B]
+  unsigned char* k_s = q_s + Q_BYTES;                      // [STAGES][2][64][128 B]
   unsigned char* v_s = k_s + KV_STAGES * KV_TILE_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * KV_TILE_BYTES);
   uint64_t* empty = full + KV_STAGES;
@@ -183,11 +188,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       // O += P . V: 4 k-steps of 16 keys; V is MN-major (rows = keys, 128 B of head columns per row)
       auto issue_o = [&](int stage, bool accumulate) {
         constexpr uint32_t idesc = instr_desc(HD, true);
-        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + stage * KV_TILE_BYTES);
+        const uint32_t va = smem_u32(v_s + stage * KV_TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < TK / 16; ++kk)
-          umma(tmem + O_COL, smem_desc(pa + kk * 32), smem_desc_mn(va + kk * 16 * 128, HALF_K), idesc,
-               (accumulate || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < TK / 16; ++kk)                  // 16 keys = 8 columns of bfloat16 pairs
+          umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, smem_desc_mn(va + kk * 16 * 128, HALF_K), idesc,
+                  (accumulate || kk > 0) ? 1u : 0u);
       };
 
       load_tile(0, 0);
@@ -200,7 +205,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       }
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int stage = t % KV_STAGES;
-        ok = mbar_wait(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place, S(t) is consumed
+        ok = mbar_wait_spin(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place, S(t) is consumed
         if (!ok) break;
         tc_fence_after();
         issue_o(stage, t > 0);
@@ -229,7 +234,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       // S of this tile; the commit behind it also covers the O product of the tile before
-      ok = mbar_wait(bar_s, (uint32_t)(t & 1), a.status, 2, abort_flag);
+      ok = mbar_wait_spin(bar_s, (uint32_t)(t & 1), a.status, 2, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -267,21 +272,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       const float corr = exp2f(m_run - m_use);
       m_run = m_new;
       float rs = 0.f;
-      // P (bfloat16) -> shared memory, row `tid`, 8 chunks of 8 keys, swizzled
+      // P (bfloat16 pairs) -> tensor memory, lane = row, 32 words for the 64 keys; the second product
+      // reads its A operand from there
+      uint32_t pw[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i0 = c * 8 + e * 2;
-          const float p0 = exp2f(__uint_as_float(sv[i0 >> 5][i0 & 31]) - m_use);
-          const float p1 = exp2f(__uint_as_float(sv[(i0 + 1) >> 5][(i0 + 1) & 31]) - m_use);
-          rs += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          w[e] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        *reinterpret_cast<uint4*>(p_s + tid * 128 + ((c ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 32; ++i) {
+        const int i0 = 2 * i;
+        const float p0 = exp2f(__uint_as_float(sv[i0 >> 5][i0 & 31]) - m_use);
+        const float p1 = exp2f(__uint_as_float(sv[(i0 + 1) >> 5][(i0 + 1) & 31]) - m_use);
+        rs += p0 + p1;
+        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        pw[i] = *reinterpret_cast<uint32_t*>(&pk);
       }
+      tmem_st32(tmem + lane_addr + P_COL, pw);
       l_run = l_run * corr + rs;
       // rescale O where a maximum moved (skipped when no row of the warp needs it)
       if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
@@ -294,9 +297,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
           tmem_st32(tmem + lane_addr + O_COL + c, ov);
         }
-        tmem_wait_st();
       }
-      fence_async_smem();                                     // P is read by the tensor core (async proxy)
+      tmem_wait_st();                                         // P (and a rescaled O) are in tensor memory
       tc_fence_before();
       mbar_arrive(bar_p);
     }
@@ -379,7 +381,7 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   if (rows > 0x7fffffffLL) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_prefill_tc: cache of %lld rows", rows);
   if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, BOX_ROWS) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, BOX_ROWS))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
-  constexpr size_t smem = Q_BYTES + P_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + (2 * KV_STAGES + 3) * 8 + 16;
+  constexpr size_t smem = Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + (2 * KV_STAGES + 3) * 8 + 16;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -207,7 +207,7 @@ TS_API int ts_rmsnorm(void* out, const void* x, void* residual, const void* w, f
 // part[s, row, :] + bias, rounded to bfloat16 as the product's own epilogue would have done; then
 // residual add and norm as above.  Saves the separate reduction kernel after a split-K product.
 template <typename WT, int CHUNKS>
-__global__ void reduce_rmsnorm_kernel(bf16* __restrict__ out, const float* __restrict__ part, int splits,
+__global__ void __launch_bounds__(256) reduce_rmsnorm_kernel(bf16* __restrict__ out, const float* __restrict__ part, int splits,
                                       size_t split_stride, const bf16* __restrict__ bias, bf16* residual,
                                       const WT* __restrict__ w, float eps, int hidden) {
   pdl_launch_dependents();
@@ -288,13 +288,18 @@ TS_API int ts_reduce_rmsnorm(void* out, const float* part, int splits, const voi
   auto threads_for = [&](int chunks) { return ((vecs + chunks - 1) / chunks + 31) / 32 * 32; };
 #define TS_RR(WT, CH) ts_launch(reduce_rmsnorm_kernel<WT, CH>, dim3(T), dim3(threads_for(CH)), 0, s, (bf16*)out, part, \
                                 splits, stride, (const bf16*)bias, (bf16*)residual, (const WT*)w, eps, hidden)
+  // at most 256 threads per row (the kernel keeps up to 16 partial sums per thread in registers)
   if (w_dtype == TS_BF16) {
-    if (threads_for(1) <= 1024) TS_RR(bf16, 1);
-    else if (threads_for(4) <= 1024) TS_RR(bf16, 4);
+    if (threads_for(1) <= 256) TS_RR(bf16, 1);
+    else if (threads_for(2) <= 256) TS_RR(bf16, 2);
+    else if (threads_for(4) <= 256) TS_RR(bf16, 4);
+    else if (threads_for(8) <= 256) TS_RR(bf16, 8);
     else TS_REFUSE(TS_ERR_LIMIT, "ts_reduce_rmsnorm: hidden %d too large", hidden);
   } else if (w_dtype == TS_F32) {
-    if (threads_for(1) <= 1024) TS_RR(float, 1);
-    else if (threads_for(4) <= 1024) TS_RR(float, 4);
+    if (threads_for(1) <= 256) TS_RR(float, 1);
+    else if (threads_for(2) <= 256) TS_RR(float, 2);
+    else if (threads_for(4) <= 256) TS_RR(float, 4);
+    else if (threads_for(8) <= 256) TS_RR(float, 8);
     else TS_REFUSE(TS_ERR_LIMIT, "ts_reduce_rmsnorm: hidden %d too large", hidden);
   } else {
     TS_REFUSE(TS_ERR_DTYPE, "ts_reduce_rmsnorm: scale dtype %d", w_dtype);

@@ -15,8 +15,6 @@
 // tcgen05.ld and write the result.  Stages are handed over through mbarriers; every wait is
 // bounded: when a barrier does not flip in time the block records where in `status`, stops, and
 // still frees its tensor memory.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -325,12 +323,7 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
     if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
       TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: cuTensorMapEncodeTiled failed");
     dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
-    static const int stages16 = getenv("TS_GEMM_STAGES16") ? atoi(getenv("TS_GEMM_STAGES16")) : 4;
-    if (bn == 16 && stages16 == 23) rc = launch<16, 3, true, 2>(rows_map, cols_map, a, grid, s);
-    else if (bn == 16 && stages16 == 24) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
-    else if (bn == 16 && stages16 == 42) rc = launch<16, 2, true, 4>(rows_map, cols_map, a, grid, s);
-    else if (bn == 16 && stages16 == 43) rc = launch<16, 3, true, 4>(rows_map, cols_map, a, grid, s);
-    else if (bn == 16) rc = launch<16, 4, true>(rows_map, cols_map, a, grid, s);
+    if (bn == 16) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
     else if (bn == 32) rc = launch<32, 4, true>(rows_map, cols_map, a, grid, s);
     else if (bn == 64) rc = launch<64, 4, true>(rows_map, cols_map, a, grid, s);
     else rc = launch<128, 4, true>(rows_map, cols_map, a, grid, s);

@@ -152,11 +152,14 @@ class StepInputBuilder:
             cursor += _align(n)
             return a
 
+        # With a caller-owned arena (a captured graph reads it at fixed addresses) the layout may depend
+        # only on T, B and the table widths, never on how many rows are wanted or fed back.
+        static = arena is not None
         o_ids, o_pos, o_req = take(T), take(T), take(T)
-        o_qs, o_sl, o_ss, o_sr = take(B + 1), take(B), take(B), take(max(S, 1))
+        o_qs, o_sl, o_ss, o_sr = take(B + 1), take(B), take(B), take(T if static else max(S, 1))
         fb = [(b, e.feedback) for b, e in enumerate(ents) if e.feedback is not None]
         F = len(fb)
-        o_fr, o_fs = take(max(F, 1)), take(max(F, 1))
+        o_fr, o_fs = take(B if static else max(F, 1)), take(B if static else max(F, 1))
         o_slot = [take(T) for _ in widths]
         o_bt = [take(B * w) for w in widths]
         used = cursor

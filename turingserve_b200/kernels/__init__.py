@@ -118,6 +118,7 @@ class CudaOps:
         self._partials: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
+        self.max_splits = 16        # the fused reduce kernels load up to 16 partial sums in one go
         self.launches = 0           # kernels of this library launched (graph replays add their share)
 
     # -- plumbing -----------------------------------------------------------------------------------
@@ -152,7 +153,7 @@ class CudaOps:
     def rmsnorm(self, out, x, weight, eps: float, residual=None) -> None:
         if isinstance(x, Deferred):
             T, h = x.shape
-            if h % 8 == 0 and x.dtype == torch.bfloat16:
+            if h % 8 == 0 and h <= 16384 and x.dtype == torch.bfloat16:
                 self._check(self.lib.ts_reduce_rmsnorm(
                     _ptr(out), _ptr(x.part), x.splits, _ptr(x.bias), _ptr(residual), _ptr(weight), float(eps), T, h,
                     _code(weight.dtype), self._stream()), "reduce_rmsnorm")
@@ -298,7 +299,7 @@ class CudaOps:
             return 1
         # partial sums cost 8*M*N bytes per split (written, read back): keep that below the weights' 2*N*K
         traffic_cap = max(1, K // (4 * M))
-        return max(1, min(self.num_sms // tiles, k_blocks // 2, traffic_cap))
+        return max(1, min(self.num_sms // tiles, k_blocks // 2, traffic_cap, self.max_splits))
 
     def tc_status(self) -> int:
         """0 when no tensor-core block (GEMM or attention) ever gave up on a wait (synchronises the device)."""
