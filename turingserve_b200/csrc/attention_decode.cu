@@ -34,8 +34,10 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
                         const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
                         const int* __restrict__ q_start, const int* __restrict__ seq_lens, int table_width,
                         int H, int KVH, int page, float scale, int window, int nsplit, int* __restrict__ counters) {
+  // Everything up to pdl_wait() reads only what no kernel of this step writes: the step's index
+  // arrays (copied from the host before the step's first kernel) and cache rows of earlier steps.
+  // The one row this step writes, the new token's at seq_len - 1, is fetched after the wait.
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int KS = D / 16;                      // k-steps of the score product
   constexpr int NT = D / 8;                       // n-tiles of the output
@@ -69,6 +71,46 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     __syncthreads();
   }
 
+  auto load_tile = [&](int tile, int stage, int key_limit) {
+    const int j0 = k_begin + tile * DEC_TILE;
+    unsigned char* ks_ = k_s + stage * DEC_TILE * D * 2;
+    unsigned char* vs_ = v_s + stage * DEC_TILE * D * 2;
+    for (int idx = threadIdx.x; idx < DEC_TILE * CH; idx += DEC_WARPS * 32) {
+      const int key = idx / CH, c = idx % CH;
+      const int j = j0 + key;
+      const bool ok = j < key_limit;
+      size_t off = 0;
+      if (ok) {
+        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+        const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
+        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
+      }
+      cp_async_16(ks_ + swz<D>(key, c), k_cache + off, ok);
+      cp_async_16(vs_ + swz<D>(key, c), v_cache + off, ok);
+    }
+  };
+
+  // First tiles of the pipeline, without the new token's row (zero-filled for now).
+  const int old_end = min(k_end, seq_len - 1);
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_tiles) load_tile(s, s, old_end);
+    cp_async_commit();
+  }
+  pdl_wait();
+  // The new token's row, if it lies in a tile fetched above; later tiles take it with them.
+  const int new_tile = (k_end == seq_len && n_tiles > 0) ? (seq_len - 1 - k_begin) / DEC_TILE : -1;
+  const bool patch = new_tile >= 0 && new_tile < DEC_STAGES - 1;       // block-uniform
+  if (patch && threadIdx.x < CH) {
+    const int j = seq_len - 1, key = j - k_begin - new_tile * DEC_TILE, c = threadIdx.x;
+    const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+    const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
+    const size_t off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
+    cp_async_16(k_s + new_tile * DEC_TILE * D * 2 + swz<D>(key, c), k_cache + off, true);
+    cp_async_16(v_s + new_tile * DEC_TILE * D * 2 + swz<D>(key, c), v_cache + off, true);
+  }
+  if (patch) cp_async_commit();
+
   // query fragments: rows 0..G-1 of the group, zero above
   unsigned qf[KS][4];
   {
@@ -84,40 +126,19 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     }
   }
 
-  auto load_tile = [&](int tile, int stage) {
-    const int j0 = k_begin + tile * DEC_TILE;
-    unsigned char* ks_ = k_s + stage * DEC_TILE * D * 2;
-    unsigned char* vs_ = v_s + stage * DEC_TILE * D * 2;
-    for (int idx = threadIdx.x; idx < DEC_TILE * CH; idx += DEC_WARPS * 32) {
-      const int key = idx / CH, c = idx % CH;
-      const int j = j0 + key;
-      const bool ok = j < k_end;
-      size_t off = 0;
-      if (ok) {
-        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
-        const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
-        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
-      }
-      cp_async_16(ks_ + swz<D>(key, c), k_cache + off, ok);
-      cp_async_16(vs_ + swz<D>(key, c), v_cache + off, ok);
-    }
-  };
-
   float o[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float sc = scale * LOG2E;
 
-#pragma unroll
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(s, s);
-    cp_async_commit();
-  }
   for (int t = 0; t < n_tiles; ++t) {
-    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES);
+    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES, k_end);
     cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
+    // Groups, oldest first: the STAGES-1 first tiles, the patch group if there is one, then one per
+    // iteration.  The patched tile needs the patch group too, hence the full wait up to it.
+    if (patch && t <= new_tile) cp_async_wait<0>();
+    else cp_async_wait<DEC_STAGES - 1>();
     __syncthreads();
     const unsigned char* ks_ = k_s + (t % DEC_STAGES) * DEC_TILE * D * 2;
     const unsigned char* vs_ = v_s + (t % DEC_STAGES) * DEC_TILE * D * 2;
