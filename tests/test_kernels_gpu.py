@@ -160,8 +160,23 @@ def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, nee
     return qkv.to(dtype), kc.to(dtype), vc.to(dtype), bt, qs, sl
 
 
-def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True, tc=True):
+def _poison_unwritten(kc, vc, bt, sl, page):
+    """NaN in every cache row that holds no key of any request: what a pool that was never cleared
+    may hold.  No such row may reach an output."""
+    written = torch.zeros(kc.shape[0], page, dtype=torch.bool)
+    for b in range(bt.shape[0]):
+        for j in range(int(sl[b])):
+            written[int(bt[b, j // page]), j % page] = True
+    hole = ~written[:, None, :, None].expand_as(kc)
+    kc[hole] = float("nan")
+    vc[hole] = float("nan")
+
+
+def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True, tc=True,
+                   tma=True, poison=False):
     qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle)
+    if poison:
+        _poison_unwritten(kc, vc, bt, sl, page)
     T = qkv.shape[0]
     scale = D ** -0.5
     nd = 0
@@ -172,13 +187,18 @@ def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=N
     ops.use_fast_attention = fast
     tc_before = ops.use_tc_attention
     ops.use_tc_attention = tc and tc_before
+    kernel_before = ops.decode_kernel
+    ops.decode_kernel = "tma" if tma else "cp"
     try:
         ops.attention(out, qkv.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), step, H, KVH, D, page, scale, window)
     finally:
         ops.use_fast_attention = True
         ops.use_tc_attention = tc_before
+        ops.decode_kernel = kernel_before
+    assert ops.tc_status() == 0, "a tensor-core or TMA block gave up on a wait"
     ref = torch.empty((T, H * D), dtype=torch.float32)
-    paged_attention(ref, qkv.float(), kc.float(), vc.float(), bt, qs, sl, H, KVH, D, page, scale, window)
+    paged_attention(ref, qkv.float().nan_to_num(0.0), kc.float().nan_to_num(0.0), vc.float().nan_to_num(0.0), bt, qs, sl,
+                    H, KVH, D, page, scale, window)
     return out.cpu().float(), ref, (qkv, kc, vc, bt, qs, sl)
 
 
@@ -190,9 +210,9 @@ ATT_TOL = {torch.float32: dict(atol=2e-5, rtol=1e-4), torch.bfloat16: dict(atol=
                                           (5, 5, 48, 4), (3, 1, 256, 16), (6, 1, 80, 32)])
 def test_attention_decode(ops, dtype, H, KVH, D, page):
     lens = [1, 2, 15, 16, 17, 100, 1000, 0, 33, 64, 65, 257, 4000]
-    for fast in (True, False):
+    for fast, tma in ((True, True), (True, False), (False, False)):
         out, ref, _ = _run_attention(ops, dtype, H, KVH, D, page, [1] * len(lens),
-                                     [max(l - 1, 0) if l else -1 for l in lens], 11, fast=fast)
+                                     [max(l - 1, 0) if l else -1 for l in lens], 11, fast=fast, tma=tma)
         torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
         assert torch.all(out[7] == 0), "a padding row (context 0) gives zeros"
 
@@ -204,7 +224,29 @@ def test_attention_decode_split_counts(ops, B, ctx, window):
     H, KVH, D, page = 12, 2, 128, 16
     lens = [max(ctx - 7 * i, 1 + i) for i in range(B)]
     assert ops.decode_splits(1, KVH, 3000) > 4 and ops.decode_splits(256, KVH, 90) == 1
-    out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * B, [l - 1 for l in lens], 15, window=window)
+    assert ops.decode_splits_tma(1, KVH, D, 3000) > 4 and ops.decode_splits_tma(256, KVH, D, 90) == 1
+    for tma in (True, False):
+        out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * B, [l - 1 for l in lens], 15,
+                                     window=window, tma=tma)
+        torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+
+
+@pytest.mark.parametrize("H,KVH,D,page", [(12, 2, 128, 16), (14, 2, 64, 32), (16, 1, 128, 48), (9, 3, 64, 64), (7, 1, 128, 128)])
+@pytest.mark.parametrize("nsplit,stages", [(1, 2), (1, 6), (3, 3), (7, 8), (128, 6)])
+@pytest.mark.parametrize("window", [None, 1, 130])
+def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, stages, window):
+    """The TMA decode kernel with every way its ring of stages and its split count can fall: more
+    tiles than stages (stages reused several times), more splits than tiles (blocks that leave at
+    once), contexts that end on and around tile and page edges, a window whose low edge cuts a
+    tile, and a cache whose unwritten rows hold NaN."""
+    if stages * 2 * 64 * D * 2 > 220 * 1024:
+        pytest.skip("more stages than shared memory holds at this head size")
+    lens = [1, 63, 64, 65, 128, 129, 1000, 1024, 1025, 2500, 16, 17]
+    monkeypatch.setattr(ops, "decode_splits_tma", lambda *a: nsplit)
+    monkeypatch.setattr(ops, "decode_stages", stages)
+    out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens), [l - 1 for l in lens], 17,
+                                 window=window, poison=True)
+    assert torch.isfinite(out).all()
     torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
 
 
@@ -244,9 +286,10 @@ def test_attention_needle(ops, dtype, needle):
     """One far key among hundreds carries all the weight: the output is that key's value
     (reference tests/kernels/test_kernels.py:135-154)."""
     H, KVH, D, page = 12, 2, 128, 16
-    out, ref, (qkv, kc, vc, bt, qs, sl) = _run_attention(ops, dtype, H, KVH, D, page, [1, 9], [899, 891], 14,
-                                                       needle=needle)
-    torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
+    for tma in (True, False):
+        out, ref, (qkv, kc, vc, bt, qs, sl) = _run_attention(ops, dtype, H, KVH, D, page, [1, 9], [899, 891], 14,
+                                                           needle=needle, tma=tma)
+        torch.testing.assert_close(out, ref, **ATT_TOL[dtype])
     for b in range(2):
         last = int(qs[b + 1]) - 1
         pg = int(bt[b, needle // page])

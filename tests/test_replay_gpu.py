@@ -20,7 +20,8 @@ from tests import schedules, tiny
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31]}
+LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31],
+           "K": [5, 130, 200, 70, 257, 64], "L": [3, 150, 77, 260, 128, 31]}
 # float32: the reference's own bound for logits (tests/correctness/test_vs_hf.py:40-48).
 # bfloat16: 8 bits of mantissa; logits of these models reach |2.5|; the bound is 3% of the largest
 # expected logit of the request, about eight bfloat16 roundings.
@@ -49,10 +50,11 @@ def check(got, expected, dtype):
             assert bad is None, f"first wrong place (request, position, error): {bad}, bound {tol}"
 
 
-def replay_in_process(folder, name, steps, dtype, gemm="library"):
+def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True):
     from turingserve_b200 import kernels
     from turingserve_b200.engine.replay import Replayer
-    kernels.use(None)
+    if fresh_ops:
+        kernels.use(None)
     kernels.ops().gemm_mode = gemm
     rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name))
     outs = {}
@@ -80,6 +82,29 @@ def test_schedules_match_plain(tmp_path, name, schedule, dtype, gemm):
     got = replay_in_process(folder, name, steps, dtype, gemm)
     assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
     check(got, expected_logits(folder, reqs), dtype)
+
+
+@pytest.mark.parametrize("decode", ["cp", "tma"])
+@pytest.mark.parametrize("portions", ["tc", "mma"])
+@pytest.mark.parametrize("name", ["K", "L"])
+@pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed"])
+def test_schedules_on_the_tensor_core_attention_kernels(tmp_path, monkeypatch, name, schedule, decode, portions):
+    """Models whose head size and pages the fast bfloat16 attention kernels take, through every
+    schedule: both decode kernels (the chain-length one, the streaming one with TMA) and both
+    prompt-portion kernels (tcgen05 where the head size is 128, mma.sync)."""
+    from turingserve_b200 import kernels
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = getattr(schedules, schedule)(reqs)
+    kernels.use(None)
+    ops = kernels.ops()
+    monkeypatch.setattr(ops, "decode_kernel", decode)
+    monkeypatch.setattr(ops, "use_tc_attention", portions == "tc")
+    before = ops.launches
+    got = replay_in_process(folder, name, steps, "bfloat16", "auto", fresh_ops=False)
+    assert ops.launches > before and ops.tc_status() == 0
+    assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
+    check(got, expected_logits(folder, reqs), "bfloat16")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -26,6 +26,14 @@ TINY = {
                head_dim=48, vocab_size=301, rope_theta=50000.0, rms_norm_eps=3e-6,
                tie_word_embeddings=False, max_position_embeddings=512, sliding_window=24,
                max_window_layers=1), 2, 16, 0.08),
+    # two with the head sizes and pages the tensor-core and TMA attention kernels take (the three
+    # above go to the any-size kernel): 128 with groups of two, 64 with groups of three and a window
+    "K": (dict(hidden_size=192, intermediate_size=320, num_layers=2, num_heads=4, num_kv_heads=2,
+               head_dim=128, vocab_size=300, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+               max_position_embeddings=512), 3, 16, 0.03),
+    "L": (dict(hidden_size=160, intermediate_size=272, num_layers=3, num_heads=9, num_kv_heads=3,
+               head_dim=64, vocab_size=333, rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=False,
+               max_position_embeddings=512, sliding_window=70, max_window_layers=1), 4, 32, 0.03),
 }
 
 

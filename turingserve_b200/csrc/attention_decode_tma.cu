@@ -1,0 +1,576 @@
+// Paged grouped-query DECODE attention in bfloat16 (one new token per request) with key/value
+// tiles brought in by TMA: the kernel the engine uses when pages are multiples of 16 tokens.
+//
+// Counterpart of the reference's split-K flash-decoding kernels
+// (turingserve/ops/triton_decode_attention.py:101-163: partial (m, l, acc) per partition, then a
+// reduce kernel; :60-95: the G query heads of a kv head share every key/value tile).  Semantics as
+// turingserve/ops/reference.py:60-77,94-111 for q_len = 1.
+//
+// Work split: one block per (key split, kv head, request).  The request's keys are seen as tiles
+// of 64 at absolute positions (tile i holds keys 64i .. 64i+63); the tiles that hold visible keys
+// are dealt out evenly over the splits that get at least one, and the remaining splits leave at
+// once.  Inside a block one producer warp issues TMA box copies (16 keys x 64 columns, 128-byte
+// swizzle) into a ring of stages and four consumer warps each take WHOLE tiles (the tiles of stage
+// s go to warp s % 4): a warp waits for its tile's mbarrier, computes S = Q K^T for 16 x 64 with
+// mma.sync m16n8k16 (the G heads in the 16 rows), one online-softmax update per 64 keys, then
+// O += P V, and hands the stage back.  No block-wide barrier and no per-thread address
+// arithmetic in the loop.  The warps' states merge through shared memory; with several splits the
+// block writes an unnormalised partial and the block that finishes last for a (request, kv head)
+// merges them (a ticket counter: no second launch, nobody waits).
+//
+// Before the wait for the preceding kernel the producer already fetches every box of its first
+// stages except the one holding the new token's row: the step's index arrays come from the host
+// and earlier rows of the cache from earlier steps, so no kernel of this step writes them.
+#include "common.cuh"
+#include "mma_utils.cuh"
+#include "tc_utils.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int TILE = 64;             // keys per tile
+constexpr int MIN_BOX = 16;          // keys per TMA box: 64, 32 or 16, the largest that divides the page
+constexpr int NT_S = TILE / 8;       // n-tiles of the score product
+constexpr int CWARPS = 4;            // consumer warps at most: min(4, stages) of them, then the producer warp
+constexpr int MAX_THREADS = (CWARPS + 1) * 32;
+constexpr int MAX_STAGES = 8;
+constexpr float LOG2E_D = 1.4426950408889634f;
+
+__device__ int g_dec_status = 0;     // 0 = fine; otherwise the wait that ran out
+
+struct DecArgs {
+  bf16* out;
+  float* part_acc;
+  float* part_ml;
+  const bf16* qkv;
+  const int* block_tables;
+  const int* q_start;
+  const int* seq_lens;
+  int table_width, H, KVH, page;
+  float scale;
+  int window, nsplit, stages, box_shift, v_first;
+  int* counters;
+  int* status;
+};
+
+// A stage holds 64/box boxes; one box is what ONE TMA copy brings: `box` key rows of K, whole
+// (D * 2 bytes each), then the same rows of V, written with the 128-byte swizzle (16-byte chunk q
+// of the 128-byte line n sits at chunk q ^ (n & 7); boxes start on multiples of 1024 bytes, so n
+// counts from the box).  Byte offset of 16-byte chunk c of key row `key` of K; V is box * D * 2
+// bytes further (or the other way round, see v_first).
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int key, int c, int box_shift) {
+  constexpr int LPR = D / 64;                                    // 128-byte lines per row
+  const int grp = key >> box_shift, within = key & ((1 << box_shift) - 1);
+  const int line = within * LPR + (c >> 3);
+  return (uint32_t)(grp * (2 * D * 2) << box_shift) + (uint32_t)(line * 128 + (((c & 7) ^ (line & 7)) << 4));
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const DecArgs a) {
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+  constexpr int KS = D / 16;                      // k-steps of the score product
+  constexpr int NT = D / 8;                       // n-tiles of the output
+  constexpr uint32_t STAGE_BYTES = 2 * TILE * D * 2;          // K and V rows of one tile
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES];
+  __shared__ int abort_word;
+  __shared__ int is_last;
+  volatile int* abort_flag = &abort_word;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = a.H / a.KVH;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int stages = a.stages;
+  const int cw = min(CWARPS, stages);             // consumer warps; warp `cw` is the producer
+  const int THREADS = (cw + 1) * 32;
+  const int seq_len = a.seq_lens[b];
+  const int row_q = a.q_start[b];                 // the request's single query token
+  const int lo = (a.window > 0) ? max(0, seq_len - a.window) : 0;
+
+  if (seq_len <= 0) {                             // nothing to attend to: zeros, from split 0
+    pdl_wait();
+    if (split == 0)
+      for (int idx = threadIdx.x; idx < G * D; idx += THREADS)
+        a.out[(size_t)row_q * a.H * D + (size_t)kvh * G * D + idx] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  // tiles with visible keys, dealt out evenly over `eff` splits
+  const int tile_first = lo / TILE, tile_last = (seq_len - 1) / TILE;
+  const int total = tile_last - tile_first + 1;
+  const int per = (total + a.nsplit - 1) / a.nsplit;
+  const int eff = (total + per - 1) / per;
+  if (split >= eff) return;
+  const int base = total / eff, rem = total % eff;
+  const int my_first = tile_first + split * base + min(split, rem);
+  const int n_tiles = base + (split < rem ? 1 : 0);              // >= 1
+  const int k_lo = max(lo, my_first * TILE);                     // visible keys of this block
+  const int k_end = min(seq_len, (my_first + n_tiles) * TILE);
+
+  if ((smem_u32(smem) & 1023u) != 0) {                           // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, 9);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  if (warp == cw) {
+    // ===================== producer: lanes 0..3 each own one box of every tile =====================
+    const int new_pos = seq_len - 1;                             // the row this step writes
+    const int BOX = 1 << a.box_shift, BOXES = TILE >> a.box_shift;
+    auto box_y = [&](int j) {                                    // cache row of key j (j a multiple of BOX)
+      const int lp = j / a.page;
+      const int pg = lp < a.table_width ? a.block_tables[(size_t)b * a.table_width + lp] : 0;
+      return (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
+    };
+    auto issue_box = [&](int stage, int bx, int j) {
+      const int y = box_y(j);
+      // one copy: [2 (K, V)][BOX rows][D / 64 lines][64 columns]
+      tma_load_4d(smem + (size_t)stage * STAGE_BYTES + (size_t)bx * (2 * BOX * D * 2), &kv_map, 0, 0, y, 0, &full[stage]);
+    };
+    // boxes of tile i that hold visible keys of this block
+    auto issue_tile = [&](int i, bool skip_new) {
+      const int stage = i % stages;
+      const int j0 = (my_first + i) * TILE;
+      int n_valid = 0;
+      for (int bx = 0; bx < BOXES; ++bx) n_valid += (j0 + bx * BOX + BOX > k_lo && j0 + bx * BOX < k_end) ? 1 : 0;
+      if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)n_valid * BOX * D * 2 * 2);
+      __syncwarp();
+      if (lane < BOXES) {
+        const int j = j0 + lane * BOX;
+        const bool valid = j + BOX > k_lo && j < k_end;
+        const bool holds_new = new_pos >= j && new_pos < j + BOX;
+        if (valid && !(skip_new && holds_new)) issue_box(stage, lane, j);
+      }
+    };
+    const int ahead = min(n_tiles, stages);
+    for (int i = 0; i < ahead; ++i) issue_tile(i, true);
+    pdl_wait();
+    {
+      const int i_new = new_pos / TILE - my_first;               // tile of the new row, if it is one of the above
+      if (i_new >= 0 && i_new < ahead && lane == 0) issue_box(i_new % stages, (new_pos % TILE) / BOX, new_pos & ~(BOX - 1));
+    }
+    bool ok = true;
+    for (int i = ahead; i < n_tiles && ok; ++i) {
+      ok = mbar_wait(&empty[i % stages], (uint32_t)((i / stages - 1) & 1), a.status, 2, abort_flag);
+      if (ok) issue_tile(i, false);
+    }
+  } else {
+    // ===================== consumers: whole tiles; stage s belongs to warp s % cw =====================
+    // A stage's barriers are thus waited on by one warp, phase after phase: a parity wait tells
+    // apart only neighbouring phases, so no waiter may ever be two phases behind.
+    pdl_wait();
+    // query fragments: rows 0..G-1 of the group, zero above
+    unsigned qf[KS][4];
+    {
+      const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
+      const bf16* qbase = a.qkv + (size_t)row_q * (a.H + 2 * a.KVH) * D + (size_t)kvh * G * D;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int k = ks * 16 + kc;
+        qf[ks][0] = r0 < G ? *reinterpret_cast<const unsigned*>(qbase + r0 * D + k) : 0u;
+        qf[ks][1] = r1 < G ? *reinterpret_cast<const unsigned*>(qbase + r1 * D + k) : 0u;
+        qf[ks][2] = r0 < G ? *reinterpret_cast<const unsigned*>(qbase + r0 * D + k + 8) : 0u;
+        qf[ks][3] = r1 < G ? *reinterpret_cast<const unsigned*>(qbase + r1 * D + k + 8) : 0u;
+      }
+    }
+    const bool two = G > 8;                                      // rows 8..15 hold heads too
+    const float sc = a.scale * LOG2E_D;
+    const int mat = lane >> 3, r8 = lane & 7;
+    bool ok = true;
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int stage = i % stages;
+      if (stage % cw != warp) continue;
+      ok = mbar_wait_spin(&full[stage], (uint32_t)((i / stages) & 1), a.status, 1, abort_flag);
+      if (!ok) break;
+      const uint32_t box_bytes = (uint32_t)(D * 2) << a.box_shift;  // the K rows (or the V rows) of one box
+      unsigned char* ks_ = smem + (size_t)stage * STAGE_BYTES + (a.v_first ? box_bytes : 0u);
+      unsigned char* vs_ = smem + (size_t)stage * STAGE_BYTES + (a.v_first ? 0u : box_bytes);
+      const int bs = a.box_shift;
+      const int j0 = (my_first + i) * TILE;
+      const bool edge = j0 < k_lo || j0 + TILE > k_end;           // warp-uniform
+      if (edge) {
+        // Rows outside the visible range were perhaps never fetched: their probabilities are exactly
+        // zero, and zero times whatever shared memory held must stay zero.
+        constexpr int CPR = D / 8;                                 // 16-byte chunks per row
+        for (int idx = lane; idx < TILE * CPR; idx += 32) {
+          const int key = idx / CPR, j = j0 + key;
+          if (j >= k_lo && j < k_end) continue;
+          *reinterpret_cast<uint4*>(vs_ + tile_off<D>(key, idx % CPR, bs)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
+      // scores S[16 x 64] = Q . K^T
+      float s_acc[NT_S][4];
+#pragma unroll
+      for (int nt = 0; nt < NT_S; ++nt) s_acc[nt][0] = s_acc[nt][1] = s_acc[nt][2] = s_acc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int kg = 0; kg < TILE / 16; ++kg) {
+          // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+          const int key = kg * 16 + (mat >> 1) * 8 + r8;
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, ks_ + tile_off<D>(key, ks * 2 + (mat & 1), bs));
+          mma_bf16(s_acc[kg * 2], qf[ks], b0, b1);
+          mma_bf16(s_acc[kg * 2 + 1], qf[ks], b2, b3);
+        }
+      }
+      // mask, online softmax (rows lane/4 and lane/4 + 8; columns (lane%4)*2 + {0,1} of each n-tile)
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s_acc[nt][e] * sc;
+          if (edge) {
+            const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            v = (j >= k_lo && j < k_end) ? v : -INFINITY;
+          }
+          s_acc[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);                // finite: every tile has a visible key
+        corr[r] = exp2f(m_run[r] - m_new);                         // exp2(-inf) = 0 on the first tile
+        m_run[r] = m_new;
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < NT_S; ++nt) {
+        s_acc[nt][0] = exp2f(s_acc[nt][0] - m_run[0]);
+        s_acc[nt][1] = exp2f(s_acc[nt][1] - m_run[0]);
+        rs[0] += s_acc[nt][0] + s_acc[nt][1];
+        if (two) {
+          s_acc[nt][2] = exp2f(s_acc[nt][2] - m_run[1]);
+          s_acc[nt][3] = exp2f(s_acc[nt][3] - m_run[1]);
+          rs[1] += s_acc[nt][2] + s_acc[nt][3];
+        } else {
+          s_acc[nt][2] = s_acc[nt][3] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        l_run[r] = l_run[r] * corr[r] + rs[r];
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        o[t][0] *= corr[0];
+        o[t][1] *= corr[0];
+        if (two) {
+          o[t][2] *= corr[1];
+          o[t][3] *= corr[1];
+        }
+      }
+      // O += P . V, P rounded to bfloat16 as the A operand (16 rows x 16 keys per step)
+#pragma unroll
+      for (int kg = 0; kg < TILE / 16; ++kg) {
+        unsigned pf[4];
+        pf[0] = pack_bf16(s_acc[kg * 2][0], s_acc[kg * 2][1]);
+        pf[1] = pack_bf16(s_acc[kg * 2][2], s_acc[kg * 2][3]);
+        pf[2] = pack_bf16(s_acc[kg * 2 + 1][0], s_acc[kg * 2 + 1][1]);
+        pf[3] = pack_bf16(s_acc[kg * 2 + 1][2], s_acc[kg * 2 + 1][3]);
+#pragma unroll
+        for (int t = 0; t < NT; t += 2) {
+          // matrices: (keys 0-7, d tile t), (keys 8-15, d tile t), (keys 0-7, d tile t+1), (keys 8-15, d tile t+1)
+          const int key = kg * 16 + (mat & 1) * 8 + r8;
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + tile_off<D>(key, t + (mat >> 1), bs));
+          mma_bf16(o[t], pf, b0, b1);
+          mma_bf16(o[t + 1], pf, b2, b3);
+        }
+      }
+      if (edge) fence_async_smem();                                // the zeros above, before a TMA refill
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);                   // the stage may be refilled
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+
+  // merge the four warps' states through shared memory (every fetched tile has been consumed)
+  float* m_s = reinterpret_cast<float*>(smem);                     // [CWARPS][16]
+  float* l_s = m_s + CWARPS * 16;                                  // [CWARPS][16]
+  float* o_s = l_s + CWARPS * 16;                                  // [CWARPS][16][D]
+  if (warp < cw) {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    if ((lane & 3) == 0) {
+      m_s[warp * 16 + r0] = m_run[0];
+      m_s[warp * 16 + r1] = m_run[1];
+      l_s[warp * 16 + r0] = l_run[0];
+      l_s[warp * 16 + r1] = l_run[1];
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int d = t * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + r0) * D + d) = make_float2(o[t][0], o[t][1]);
+      if (r1 < G) *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + r1) * D + d) = make_float2(o[t][2], o[t][3]);
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+    for (int w = 0; w < cw; ++w) M = fmaxf(M, m_s[w * 16 + g]);
+    float L = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+      for (int w = 0; w < cw; ++w) {
+        const float mw = m_s[w * 16 + g];
+        if (mw == -INFINITY) continue;                             // a warp without a tile
+        const float f = exp2f(mw - M);
+        L += l_s[w * 16 + g] * f;
+        acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+      }
+    }
+    const int h = kvh * G + g;
+    if (eff == 1) {
+      a.out[(size_t)row_q * a.H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * a.H + h) * a.nsplit + split;
+      a.part_acc[pi * D + d] = acc;
+      if (d == 0) {
+        a.part_ml[pi * 2 + 0] = M;
+        a.part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+  if (eff == 1) return;
+
+  // The block that finishes last for this (request, kv head) merges all splits, in split order:
+  //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&a.counters[b * a.KVH + kvh], 1);
+    is_last = (ticket == eff - 1);
+    if (is_last) a.counters[b * a.KVH + kvh] = 0;                  // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* w_s = reinterpret_cast<float*>(smem);                     // [G][eff]
+  float* m_all = w_s + G * eff;                                    // [G][eff]
+  float* l_all = m_all + G * eff;                                  // [G][eff]
+  for (int idx = threadIdx.x; idx < G * eff; idx += THREADS) {
+    const int g = idx / eff, s2 = idx % eff;
+    const size_t pi = ((size_t)b * a.H + kvh * G + g) * a.nsplit + s2;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + pi * 2));
+    m_all[idx] = ml.x;
+    l_all[idx] = ml.y;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * eff; idx += THREADS) {
+    const int g = idx / eff;
+    float M = -INFINITY, L = 0.f;
+    for (int s2 = 0; s2 < eff; ++s2) M = fmaxf(M, m_all[g * eff + s2]);
+    if (M > -INFINITY)
+      for (int s2 = 0; s2 < eff; ++s2) L += l_all[g * eff + s2] * exp2f(m_all[g * eff + s2] - M);
+    w_s[idx] = (L > 0.f) ? exp2f(m_all[idx] - M) / L : 0.f;
+  }
+  __syncthreads();
+  // out[g, d..d+3] = sum_s w[g, s] * acc[g, s, d..d+3]: independent 16-byte loads, split order
+  for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    const int h = kvh * G + g;
+    const float* src = a.part_acc + (((size_t)b * a.H + h) * a.nsplit) * D + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s2 = 0; s2 < eff; ++s2) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s2 * D));
+      const float w = w_s[g * eff + s2];
+      acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+    }
+    bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)h * D + d;
+    *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x, acc.y);
+    *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+  }
+}
+
+// K and V caches ([rows, D] bfloat16 each, `gap` bytes apart) as one tensor of
+// [2][rows][D / 64][64] copied in boxes of [2][box_rows][D / 64][64] with the 128-byte swizzle.
+bool kv_tensor_map(CUtensorMap* out, const void* lo_ptr, unsigned long long gap, int rows, int D, int box_rows) {
+  struct Key {
+    const void* ptr;
+    unsigned long long gap;
+    int rows, D, box;
+    bool operator==(const Key& o) const { return ptr == o.ptr && gap == o.gap && rows == o.rows && D == o.D && box == o.box; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ std::hash<unsigned long long>()(k.gap * 31 + (unsigned)k.rows) ^ ((size_t)k.D << 50) ^ ((size_t)k.box << 40);
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{lo_ptr, gap, rows, D, box_rows};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  tc::EncodeTiledFn fn = tc::encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {64, (cuuint64_t)(D / 64), (cuuint64_t)rows, 2};
+  cuuint64_t strides[3] = {128, (cuuint64_t)D * 2, (cuuint64_t)gap};
+  cuuint32_t box[4] = {64, (cuuint32_t)(D / 64), (cuuint32_t)box_rows, 2};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(lo_ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+int* dec_status_word() {
+  static int* p = nullptr;
+  if (p == nullptr && cudaGetSymbolAddress((void**)&p, g_dec_status) != cudaSuccess) p = nullptr;
+  return p;
+}
+
+template <int D>
+int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t s) {
+  const size_t smem = (size_t)a.stages * 2 * TILE * D * 2;
+  static size_t configured = 0;
+  if (smem != configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_tma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  const int threads = ((a.stages < CWARPS ? a.stages : CWARPS) + 1) * 32;
+  ts_launch(attention_decode_tma_kernel<D>, dim3(a.nsplit, a.KVH, B), dim3(threads), smem, s, kv_map, a);
+  TS_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+// Whether this kernel takes the shape (else the caller uses ts_attention_decode or the generic kernel).
+TS_API int ts_attention_decode_tma_supported(int H, int KVH, int D, int page, int dtype) {
+  return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && H / KVH <= 16 && (D == 64 || D == 128) && page >= MIN_BOX &&
+         page % MIN_BOX == 0;
+}
+
+// 0 when no block ever gave up on a wait (synchronises the device).
+TS_API int ts_attention_decode_tma_status() {
+  int* p = dec_status_word();
+  int v = -1;
+  if (p != nullptr) cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+// Blocks of this kernel that fit one SM at `stages` stages: what the caller sizes nsplit with.
+TS_API int ts_attention_decode_tma_blocks_per_sm(int D, int stages) {
+  if ((D != 64 && D != 128) || stages < 2 || stages > MAX_STAGES) return 0;
+  const size_t smem = (size_t)stages * 2 * TILE * D * 2;
+  const int threads = ((stages < CWARPS ? stages : CWARPS) + 1) * 32;
+  int n = 0;
+  cudaError_t e;
+  if (D == 64) {
+    cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_tma_kernel<64>, threads, smem);
+  } else {
+    cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_tma_kernel<128>, threads, smem);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// One query token per request (rows q_start[b]).  `scratch` holds
+// ts_attention_decode_scratch_floats(B, H, D, nsplit) floats when nsplit > 1, and `counters`
+// B * KVH ints that are zero on entry (the kernel leaves them zero).  num_pages: pages in the pool
+// (rows of the cache = num_pages * KVH * page).  window <= 0: none.  stages: 2..8 tiles of
+// 64 keys in flight per block.
+TS_API int ts_attention_decode_tma(void* out, void* scratch, int* counters, const void* qkv, const void* k_cache,
+                                   const void* v_cache, const int* block_tables, const int* q_start,
+                                   const int* seq_lens, int B, int table_width, int H, int KVH, int D, int page,
+                                   int num_pages, float scale, int window, int nsplit, int stages, void* stream) {
+  if (B <= 0) return 0;
+  if (!ts_attention_decode_tma_supported(H, KVH, D, page, TS_BF16))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode_tma: H=%d KVH=%d D=%d page=%d is not taken by this kernel", H, KVH, D, page);
+  if (nsplit < 1 || nsplit > 128 || B > 65535 || KVH > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: nsplit=%d B=%d", nsplit, B);
+  if (stages < 2 || stages > MAX_STAGES || (size_t)stages * 2 * TILE * D * 2 > 220 * 1024)
+    TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: %d stages at head_dim %d", stages, D);
+  if (nsplit > 1 && (scratch == nullptr || counters == nullptr))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_attention_decode_tma: %d splits need scratch and counters", nsplit);
+  if ((((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
+    TS_REFUSE(TS_ERR_ALIGN, "ts_attention_decode_tma: buffers must be 16-byte aligned");
+  // the merges reuse the stage buffers: 3 * G * nsplit floats and (2 + D) * 64 floats must fit
+  const int G = H / KVH;
+  const size_t smem = (size_t)stages * 2 * TILE * D * 2;
+  if (sizeof(float) * 3 * G * nsplit > smem || sizeof(float) * (2 + D) * CWARPS * 16 > smem)
+    TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: %d stages are too few for the merge buffers", stages);
+  int* status = dec_status_word();
+  if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: no status word");
+  const long long rows = (long long)num_pages * KVH * page;
+  if (rows <= 0 || rows > 0x7fffffffLL) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: cache of %lld rows", rows);
+  const int box_shift = page % 64 == 0 ? 6 : (page % 32 == 0 ? 5 : 4);
+  // K and V as one tensor [2][rows][D / 64][64]: the lower address first
+  const bool v_first = (uintptr_t)v_cache < (uintptr_t)k_cache;
+  const void* lo_ptr = v_first ? v_cache : k_cache;
+  const unsigned long long gap = v_first ? (uintptr_t)k_cache - (uintptr_t)v_cache : (uintptr_t)v_cache - (uintptr_t)k_cache;
+  if (gap < (unsigned long long)rows * D * 2 || gap >= (1ull << 40))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode_tma: key and value caches %llu bytes apart", gap);
+  CUtensorMap kv_map;
+  if (!kv_tensor_map(&kv_map, lo_ptr, gap, (int)rows, D, 1 << box_shift))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_decode_tma: cuTensorMapEncodeTiled failed");
+  DecArgs a;
+  a.out = (bf16*)out;
+  a.part_acc = (float*)scratch;
+  a.part_ml = a.part_acc ? a.part_acc + (size_t)B * H * nsplit * D : nullptr;
+  a.qkv = (const bf16*)qkv;
+  a.block_tables = block_tables;
+  a.q_start = q_start;
+  a.seq_lens = seq_lens;
+  a.table_width = table_width;
+  a.H = H;
+  a.KVH = KVH;
+  a.page = page;
+  a.scale = scale;
+  a.window = window;
+  a.nsplit = nsplit;
+  a.stages = stages;
+  a.box_shift = box_shift;
+  a.v_first = v_first ? 1 : 0;
+  a.counters = counters;
+  a.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64) return launch_tma<64>(kv_map, a, B, s);
+  return launch_tma<128>(kv_map, a, B, s);
+}

@@ -476,11 +476,13 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
                                          const float* __restrict__ part, int splits, size_t split_stride,
                                          const bf16* __restrict__ bias) {
   pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x;
   const size_t part_row = (size_t)t * (H + 2 * KVH) * D;
+  // The step's index arrays come from the host before the step's first kernel: no kernel writes
+  // them, so they are read ahead of the wait for the preceding kernel.
   const int pos = positions[t];
   const int slot = (k_cache != nullptr) ? slots[t] : -1;
+  pdl_wait();
   const int half = rot / 2;
   const int hv = half / 8;                          // vectors per half
   const int pv = (D - rot) / 8;                     // pass-through vectors per head

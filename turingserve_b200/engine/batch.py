@@ -61,6 +61,19 @@ class StepInputs:
     starts: list[int]
     max_q_len: int
     max_seq_len: int
+    # The single-token requests together read this many keys or more: their attention should be the
+    # kernel built for streaming, not the one built for the shortest chain.  Set from the real
+    # lengths; a captured step keeps one graph for each value.
+    streaming_decode: bool = False
+
+
+# From about this many keys under the decode rows of a step (requests x longest context), reading them
+# takes longer than the fixed chain of a decode-attention launch.
+STREAMING_DECODE_KEYS = 32768
+
+
+def streaming_decode(num_decode: int, longest_context: int) -> bool:
+    return num_decode * longest_context >= STREAMING_DECODE_KEYS
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -231,4 +244,5 @@ class StepInputBuilder:
             positions=d(o_pos, T), token_request=d(o_req, T), q_start=d(o_qs, B + 1),
             seq_lens=d(o_sl, B), state_slots=d(o_ss, B), sample_rows=d(o_sr, S), groups=groups,
             feedback_rows=d(o_fr, F), feedback_src=d(o_fs, F),
-            q_lens=q_lens, starts=starts, max_q_len=max(q_lens), max_seq_len=int(sl.max()) if B else 0)
+            q_lens=q_lens, starts=starts, max_q_len=max(q_lens), max_seq_len=int(sl.max()) if B else 0,
+            streaming_decode=streaming_decode(num_decode, int(sl[:num_decode].max()) if num_decode else 0))

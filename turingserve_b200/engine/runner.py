@@ -17,7 +17,7 @@ import torch
 
 from turingserve_b200 import kernels
 from turingserve_b200.cache.manager import CacheManager, RunNeeds
-from turingserve_b200.engine.batch import StepEntry, StepInputBuilder, StepInputs
+from turingserve_b200.engine.batch import StepEntry, StepInputBuilder, StepInputs, streaming_decode
 from turingserve_b200.parts.model import DecoderModel
 
 
@@ -41,7 +41,7 @@ class ModelRunner:
         self.builder = StepInputBuilder(cache, max_tokens, max_requests, self.max_pages, model.device)
         self.views = cache.views()
         self.graph_batch_sizes = tuple(sorted(graph_batch_sizes))
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, bool], _DecodeGraph] = {}
 
     # -- the step ---------------------------------------------------------------------------------
     def step(self, entries: list[StepEntry], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
@@ -106,17 +106,20 @@ class ModelRunner:
         return None
 
     def _replay(self, size: int, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
-        g = self._graphs.get(size)
+        # which attention kernel the decode rows get is part of what a graph captures
+        streaming = streaming_decode(len(entries), max(e.cache.num_tokens for e in entries) + 1)
+        g = self._graphs.get((size, streaming))
         if g is None:
-            g = self._graphs[size] = _DecodeGraph(self, size)
+            g = self._graphs[(size, streaming)] = _DecodeGraph(self, size, streaming)
         return g.run(entries, prev_tokens)
 
 
 class _DecodeGraph:
-    """One captured decode step for ``size`` requests: static input arena, static logits."""
+    """One captured decode step for ``size`` requests and one choice of decode-attention kernel:
+    static input arena, static logits."""
 
-    def __init__(self, runner: ModelRunner, size: int) -> None:
-        self.runner, self.size = runner, size
+    def __init__(self, runner: ModelRunner, size: int, streaming: bool) -> None:
+        self.runner, self.size, self.streaming = runner, size, streaming
         b = runner.builder
         self.arena = torch.zeros(b.capacity, dtype=torch.int32, device=runner.model.device)
         self.graph: torch.cuda.CUDAGraph | None = None
@@ -130,7 +133,8 @@ class _DecodeGraph:
         step = r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - len(entries),
                                arena=self.arena)
         # launch geometry must not depend on this step's lengths: size it for the longest context
-        return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len)
+        return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len,
+                                   streaming_decode=self.streaming)
 
     def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
         step = self._build(entries)

@@ -14,6 +14,7 @@ tensor-core kernel takes the shape; float32 products always use this library's F
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 
 import torch
@@ -57,6 +58,7 @@ class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
     ABI = 3
+    UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
         self.lib_path = lib_path
@@ -75,6 +77,7 @@ class CudaOps:
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
             "ts_linear_simt": [P, P, P, P, P, I, I, I, I, I, P],
             "ts_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+            "ts_attention_decode_tma": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
             "ts_attention_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
             "ts_attention_prefill_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
             "ts_linear_tc": [P, P, P, P, P, I, I, I, I, I, P],
@@ -90,6 +93,16 @@ class CudaOps:
             fn.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_supported.restype = c_int
+        self.lib.ts_attention_decode_tma_supported.argtypes = [I, I, I, I, I]
+        self.lib.ts_attention_decode_tma_supported.restype = c_int
+        self.lib.ts_attention_decode_tma_status.argtypes = []
+        self.lib.ts_attention_decode_tma_status.restype = c_int
+        self.lib.ts_attention_decode_tma_blocks_per_sm.argtypes = [I, I]
+        self.lib.ts_attention_decode_tma_blocks_per_sm.restype = c_int
+        # decode attention: "tma" the kernel built for streaming many keys (pages of a multiple of 16
+        # tokens), "cp" the one built for the shortest chain, "auto" by the step's streaming_decode
+        self.decode_kernel = os.environ.get("TURINGSERVE_B200_DECODE_ATTENTION", "auto")
+        self.decode_stages = int(os.environ.get("TURINGSERVE_B200_DECODE_STAGES", "3"))
         self.lib.ts_rope_kv_write_fused_supported.argtypes = [I, I, I]
         self.lib.ts_rope_kv_write_fused_supported.restype = c_int
         self.lib.ts_linear_tc_supported.argtypes = [I, I, I]
@@ -116,6 +129,7 @@ class CudaOps:
         self._scratch: torch.Tensor | None = None
         self._counters: torch.Tensor | None = None
         self._partials: torch.Tensor | None = None
+        self._decode_slots: dict = {}
         self.use_fast_attention = True
         self.use_library_gemm = True
         self.max_splits = 16        # the fused reduce kernels load up to 16 partial sums in one go
@@ -195,27 +209,61 @@ class CudaOps:
         return self._scratch
 
     def decode_splits(self, num_requests: int, KVH: int, max_seq_len: int) -> int:
-        """How many pieces each request's keys are cut into so that the launch fills the GPU."""
+        """How many pieces each request's keys are cut into so that the launch fills the GPU
+        (the cp.async decode kernel: two blocks per SM, pieces of at least 256 keys)."""
         want = -(-2 * self.num_sms // max(1, num_requests * KVH))
         return max(1, min(want, -(-max_seq_len // 256), 128))
 
+    def decode_splits_tma(self, num_requests: int, KVH: int, D: int, max_seq_len: int) -> int:
+        """The most pieces a request's keys may be cut into by the TMA decode kernel, which deals
+        tiles of 64 keys out evenly over as many of them as get a tile: as many as one wave of
+        blocks holds (the kernel itself uses fewer when the contexts are short)."""
+        key = (D, self.decode_stages)
+        if key not in self._decode_slots:
+            self._decode_slots[key] = max(1, self.lib.ts_attention_decode_tma_blocks_per_sm(D, self.decode_stages))
+        slots = self.num_sms * self._decode_slots[key]
+        pairs = max(1, num_requests * KVH)
+        tiles = max(1, -(-max_seq_len // 64))
+        return max(1, min(slots // pairs, tiles, 128))
+
+    def _decode_scratch(self, nd: int, H: int, KVH: int, D: int, nsplit: int, device):
+        if nsplit <= 1:
+            return None, None
+        scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), device)
+        if self._counters is None or self._counters.numel() < nd * KVH or self._counters.device != device:
+            self._counters = torch.zeros(max(nd * KVH, 1 << 16), dtype=torch.int32, device=device)
+        return scratch, self._counters
+
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window) -> None:
-        """Rows of requests with one token (the first ``step.num_decode`` requests) go to the
-        split-key decode kernel when it takes the shape; the rest to the chunk kernels."""
+        """Rows of requests with one token (the first ``step.num_decode`` requests) go to a
+        split-key decode kernel when one takes the shape; the rest to the chunk kernels."""
         w = 0 if window is None else int(window)
         code = _code(qkv.dtype)
         B, nd = step.num_requests, 0
         width = block_tables.shape[1]
-        if self.use_fast_attention and step.num_decode > 0 and self.lib.ts_attention_decode_supported(H, KVH, D, code):
+        streaming = self.decode_kernel == "tma"
+        if self.decode_kernel == "auto":
+            streaming = getattr(step, "streaming_decode", None)
+            if streaming is None:
+                streaming = step.num_decode * step.max_seq_len >= 32768
+        if (self.use_fast_attention and streaming and step.num_decode > 0
+                and self.lib.ts_attention_decode_tma_supported(H, KVH, D, page_size, code)):
+            nd = step.num_decode
+            nsplit = self.decode_splits_tma(nd, KVH, D, step.max_seq_len)
+            scratch, counters = self._decode_scratch(nd, H, KVH, D, nsplit, qkv.device)
+            rc = self.lib.ts_attention_decode_tma(
+                _ptr(out), _ptr(scratch), _ptr(counters), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                _ptr(step.q_start), _ptr(step.seq_lens), nd, width, H, KVH, D, page_size, k_cache.shape[0],
+                float(scale), w, nsplit, self.decode_stages, self._stream())
+            if rc == self.UNSUPPORTED:          # e.g. key and value caches that no one tensor map spans
+                nd = 0
+            else:
+                self._check(rc, "attention_decode_tma")
+        if nd == 0 and self.use_fast_attention and step.num_decode > 0 and self.lib.ts_attention_decode_supported(H, KVH, D, code):
             nd = step.num_decode
             nsplit = self.decode_splits(nd, KVH, step.max_seq_len)
-            scratch = counters = None
-            if nsplit > 1:
-                scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), qkv.device)
-                if self._counters is None or self._counters.numel() < nd * KVH or self._counters.device != qkv.device:
-                    self._counters = torch.zeros(max(nd * KVH, 1 << 16), dtype=torch.int32, device=qkv.device)
-                counters = self._counters
+            scratch, counters = self._decode_scratch(nd, H, KVH, D, nsplit, qkv.device)
             self._check(self.lib.ts_attention_decode(
                 _ptr(out), _ptr(scratch), _ptr(counters), _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                 _ptr(step.q_start), _ptr(step.seq_lens), nd, width, H, KVH, D, page_size, float(scale), w,
@@ -303,7 +351,8 @@ class CudaOps:
 
     def tc_status(self) -> int:
         """0 when no tensor-core block (GEMM or attention) ever gave up on a wait (synchronises the device)."""
-        return int(self.lib.ts_linear_tc_status()) or int(self.lib.ts_attention_prefill_tc_status())
+        return (int(self.lib.ts_linear_tc_status()) or int(self.lib.ts_attention_prefill_tc_status())
+                or int(self.lib.ts_attention_decode_tma_status()))
 
     def feed_tokens(self, ids, rows, src, tokens, vocab: int) -> None:
         """ids[rows[i]] = tokens[src[i]] on the device (all int32)."""

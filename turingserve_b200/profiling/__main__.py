@@ -1,7 +1,7 @@
 """Single-kernel workloads at the sizes of a Qwen2.5-1.5B-shaped step, small enough for a profiler
 capture that ends by itself (a few hundred MB on the device, a few dozen launches).
 
-    python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048]
+    python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048] [--page 16] [--graph]
     python -m turingserve_b200.profiling prefill_attention [--tokens 2048]
     python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library]
 
@@ -41,7 +41,7 @@ def timed(fn, n: int) -> float:
     return e0.elapsed_time(e1) / n * 1e3
 
 
-def paged(batch: int, tokens_per_request: int, layers: int):
+def paged(batch: int, tokens_per_request: int, layers: int, PAGE: int = PAGE):
     per = -(-tokens_per_request // PAGE)
     pages = batch * per + 1
     caches = [(torch.randn(pages, KVH, PAGE, D, device="cuda", dtype=torch.bfloat16),
@@ -53,21 +53,33 @@ def paged(batch: int, tokens_per_request: int, layers: int):
 def decode_attention(a) -> None:
     ops = kernels.ops()
     B, ctx = a.batch, a.context
-    caches, table = paged(B, ctx + 1, LAYERS)                     # 28 layers' caches: keys come from DRAM
+    kv = B * (ctx + 1) * KVH * D * 2 * 2
+    layers = max(2, min(LAYERS, int(500e6 // kv) + 1))            # rotate caches so that keys come from DRAM
+    PAGE = a.page
+    caches, table = paged(B, ctx + 1, layers, PAGE)
     qkv = torch.randn(B, (H + 2 * KVH) * D, device="cuda", dtype=torch.bfloat16)
+    longest = max(4096, ctx + 1)
     step = Step(torch.arange(B + 1, dtype=torch.int32, device="cuda"),
-                torch.full((B,), ctx + 1, dtype=torch.int32, device="cuda"), B, 1, 4096, B)
+                torch.full((B,), ctx + 1, dtype=torch.int32, device="cuda"), B, 1, longest, B)
     out = torch.empty(B, H * D, device="cuda", dtype=torch.bfloat16)
 
     def f(i):
-        kc, vc = caches[i % LAYERS]
+        kc, vc = caches[i % layers]
         ops.attention(out, qkv, kc, vc, table, step, H, KVH, D, PAGE, D ** -0.5, None)
 
-    for i in range(LAYERS):
+    for i in range(layers):
         f(i)
-    us = timed(f, 3 * LAYERS)
-    kv = B * (ctx + 1) * KVH * D * 2 * 2
-    print(f"decode_attention batch {B} context {ctx} splits {ops.decode_splits(B, KVH, 4096)}: "
+    if a.graph:                                                    # as inside a captured decode step: no launch gaps
+        reps = max(layers, 24 // layers * layers)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(reps):
+                f(i)
+        g.replay()
+        us = timed(lambda i: g.replay(), 3) / reps
+    else:
+        us = timed(f, max(3 * layers, 24))
+    print(f"decode_attention batch {B} context {ctx} page {PAGE}{' (graph)' if a.graph else ''}: "
           f"{us:.2f} us per launch, {kv / us / 1e6:.2f} TB/s of keys and values")
 
 
@@ -115,6 +127,8 @@ def main() -> int:
     s = sub.add_parser("decode_attention")
     s.add_argument("--batch", type=int, default=8)
     s.add_argument("--context", type=int, default=2048)
+    s.add_argument("--page", type=int, default=PAGE)
+    s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
     s = sub.add_parser("prefill_attention")
     s.add_argument("--tokens", type=int, default=2048)
     s = sub.add_parser("gemm")
