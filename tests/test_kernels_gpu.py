@@ -94,9 +94,10 @@ def test_silu_mul(ops, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,KVH,D,rot", [(4, 2, 16, 16), (14, 2, 64, 64), (12, 2, 128, 128), (5, 5, 48, 48),
                                          (6, 3, 32, 16), (2, 1, 80, 0)])
-def test_rope_kv_write(ops, dtype, H, KVH, D, rot):
+@pytest.mark.parametrize("T", [37, 150])          # a few tokens: a warp per head; many: several heads per warp
+def test_rope_kv_write(ops, dtype, H, KVH, D, rot, T):
     twin = TwinOps()
-    T, page, pages = 37, 8, 12
+    page, pages = 8, 24
     qkv = _rand((T, (H + 2 * KVH) * D), dtype, 7)
     pos = torch.randint(0, 500, (T,), dtype=torch.int32)
     cos, sin = plain.rope_tables(max(rot, 2), 10000.0, 500)

@@ -474,7 +474,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                          const int* __restrict__ slots, int H, int KVH, int D, int rot, int page,
                                          const float* __restrict__ part, int splits, size_t split_stride,
-                                         const bf16* __restrict__ bias) {
+                                         const bf16* __restrict__ bias, int lph) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const size_t part_row = (size_t)t * (H + 2 * KVH) * D;
@@ -491,14 +491,17 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
   if (slot >= 0) cache_base = ((size_t)(slot / page) * KVH * page + (size_t)(slot % page)) * D;
   const size_t head_stride = (size_t)page * D;
   const int per_head = hv + pv;
-  // one warp per head (q heads, k heads, then v heads), blockIdx.y * warps-per-block + warp
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  // `lph` lanes per head (q heads, k heads, then v heads): a whole warp where a few tokens must
+  // spread over many blocks (and each lane has several partial sums to fetch), else just enough
+  // lanes for a head's vectors so that no lane idles over a long prompt portion.
+  const int hpw = 32 / lph;                                       // heads per warp
+  const int head = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * hpw + (threadIdx.x & 31) / lph;
+  const int lane = (threadIdx.x & 31) % lph;
   if (head >= H + 2 * KVH) return;
   if (head < H + KVH) {
     bf16* x = row + (size_t)head * D;
     bf16* kdst = (head >= H && slot >= 0) ? k_cache + cache_base + (size_t)(head - H) * head_stride : nullptr;
-    for (int j = lane; j < per_head; j += 32) {
+    for (int j = lane; j < per_head; j += lph) {
       if (j < hv) {
         const int i = j * 8;
         float x1[8], x2[8], o1[8], o2[8];
@@ -532,7 +535,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
     }
   } else if (slot >= 0 || part != nullptr) {
     const int vh = head - H - KVH;
-    for (int j = lane; j < D / 8; j += 32) {
+    for (int j = lane; j < D / 8; j += lph) {
       const int d = j * 8;
       const int col = (H + KVH) * D + vh * D + d;
       float vv[8];
@@ -573,10 +576,17 @@ TS_API int ts_rope_kv_write_ex(void* qkv, const int* positions, const float* cos
   const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
   if (dtype == TS_BF16 && rot > 0 && (half % 8) == 0 && (D % 8) == 0 && aligned) {
     const int heads = H + 2 * KVH;
-    const int warps = heads >= 4 ? 4 : heads;
-    ts_launch(rope_kv_write_vec_kernel, dim3(T, ceil_div(heads, warps)), dim3(warps * 32), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
+    int lph = 32;                                                  // lanes per head, a power of two
+    if (T > 64) {
+      const int vecs = half / 8 + (D - rot) / 8;                  // of a rotated head; a value head takes two turns
+      lph = 1;
+      while (lph < vecs && lph < 32) lph *= 2;
+    }
+    const int head_warps = ceil_div(heads, 32 / lph);
+    const int warps = head_warps >= 4 ? 4 : head_warps;
+    ts_launch(rope_kv_write_vec_kernel, dim3(T, ceil_div(head_warps, warps)), dim3(warps * 32), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
                                                    slots, H, KVH, D, rot, page, part, splits,
-                                                   (size_t)T * (H + 2 * KVH) * D, (const bf16*)bias);
+                                                   (size_t)T * (H + 2 * KVH) * D, (const bf16*)bias, lph);
     TS_LAUNCH_CHECK();
   }
   if (part != nullptr) TS_REFUSE(TS_ERR_ALIGN, "ts_rope_kv_write: unreduced input needs 16-byte aligned buffers");

@@ -102,6 +102,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
         for (int u = 0; u < subs; ++u)
           tma_load_2d(w_s + i * W_STAGE + u * W_BYTES, w_map, (kb_begin + i * KSUB + u) * BK, w_row, &full[i]);
       }
+      // ... and the rest of this block's weights start towards L2
+      for (int kb = kb_begin + early * KSUB; kb < kb_end; ++kb)
+        asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(w_map), "r"(kb * BK), "r"(w_row) : "memory");
       pdl_wait();
       for (int i = 0; i < early; ++i) {
         const int subs = min(KSUB, n_kb - i * KSUB);
