@@ -71,14 +71,17 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     __syncthreads();
   }
 
-  auto load_tile = [&](int tile, int stage, int key_limit) {
+  // `skip`: a key whose row is left alone (no copy, no zero fill), to be fetched later.  Two copies
+  // into the same shared-memory bytes would land in no defined order.
+  auto load_tile = [&](int tile, int stage, int skip) {
     const int j0 = k_begin + tile * DEC_TILE;
     unsigned char* ks_ = k_s + stage * DEC_TILE * D * 2;
     unsigned char* vs_ = v_s + stage * DEC_TILE * D * 2;
     for (int idx = threadIdx.x; idx < DEC_TILE * CH; idx += DEC_WARPS * 32) {
       const int key = idx / CH, c = idx % CH;
       const int j = j0 + key;
-      const bool ok = j < key_limit;
+      if (j == skip) continue;
+      const bool ok = j < k_end;
       size_t off = 0;
       if (ok) {
         const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
@@ -90,11 +93,10 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     }
   };
 
-  // First tiles of the pipeline, without the new token's row (zero-filled for now).
-  const int old_end = min(k_end, seq_len - 1);
+  // First tiles of the pipeline, without the new token's row.
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(s, s, old_end);
+    if (s < n_tiles) load_tile(s, s, seq_len - 1);
     cp_async_commit();
   }
   pdl_wait();
@@ -133,7 +135,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   const float sc = scale * LOG2E;
 
   for (int t = 0; t < n_tiles; ++t) {
-    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES, k_end);
+    if (t + DEC_STAGES - 1 < n_tiles) load_tile(t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES, -1);
     cp_async_commit();
     // Groups, oldest first: the STAGES-1 first tiles, the patch group if there is one, then one per
     // iteration.  The patched tile needs the patch group too, hence the full wait up to it.

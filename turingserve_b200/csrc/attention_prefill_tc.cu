@@ -1,19 +1,26 @@
 // Paged grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor cores:
 // S = Q.K^T and O += P.V are tcgen05.mma products with their accumulators in tensor memory;
-// key/value tiles come from the paged cache by TMA (one box per page and half head); P never
-// leaves tensor memory (the second product reads its A operand from there).  Same semantics as attention_prefill.cu (the reference's
-// turingserve/ops/triton_prefill_attention.py:17-79 and turingserve/ops/reference.py:60-77,94-111,
-// plus the optional window); bfloat16, head size 128, pages that are a multiple of 16 tokens.
+// key/value tiles come from the paged cache by TMA (one box per page or 64 keys, and half head);
+// P never leaves tensor memory (the second product reads its A operand from there).  Same
+// semantics as attention_prefill.cu (the reference's turingserve/ops/triton_prefill_attention.py:17-79
+// and turingserve/ops/reference.py:60-77,94-111, plus the optional window); bfloat16, head size 128,
+// pages that are a multiple of 16 tokens.
 //
 // One block = 128 query ROWS (a row is one (token, head-in-group) pair of one kv head, so a
 // group shares its key/value tiles).  Warps 0-3: thread r owns row r and tensor-memory lane r.
-// Warp 4 (one lane): TMA loads and product issue.  Per 64-key tile:
-//   warp 4   : S[128x64] = Q[128x128] . K[64x128]^T            (tcgen05.mma, K-major operands)
-//   warps 0-3: read S from tensor memory, mask, online softmax in 32-bit, write P (bfloat16 pairs)
-//              back to tensor memory; rescale O there when a row's maximum moved; arrive on a barrier
-//   warp 4   : O[128x128] += P[128x64] . V[64x128]   (P from tensor memory, V MN-major as TMA left it)
-// Two blocks share an SM, so one block's softmax overlaps the other's products.  Every barrier
-// wait is bounded; a block that gives up records where, stops, and frees its tensor memory.
+// Warp 4 (one lane) issues the products, warp 5 (one lane) the TMA loads: keys into a ring of
+// three stages, values into a ring of two.  S has two buffers in tensor memory, so the score
+// product of tile t+1 runs while the softmax warps work on tile t:
+//   warp 4   : S(t)[128x64] = Q[128x128] . K(t)[64x128]^T      (issued two tiles ahead of P)
+//   warps 0-3: read S(t) from tensor memory, mask, online softmax in 32-bit, write P(t) (bfloat16
+//              pairs) over the first half of S(t)'s own columns; arrive on a barrier
+//   warp 4   : O[128x128] += P(t)[128x64] . V(t)[64x128]   (P from tensor memory, V MN-major as TMA
+//              left it), then S(t+2) into the buffer P(t) leaves
+// The running maximum that the exponentials refer to moves only when a row's true maximum has
+// grown by more than 2^8 since (P stays below 2^8, 32-bit sums keep their scale): then, and only
+// then, O is rescaled in tensor memory, after the product before it has finished.  Two blocks
+// share an SM.  Every barrier wait is bounded; a block that gives up records where, stops, and
+// frees its tensor memory.
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -24,14 +31,15 @@ using namespace tc;
 constexpr int TQ = 128;            // query rows per block = TMEM lanes
 constexpr int TK = 64;             // keys per tile
 constexpr int HD = 128;            // head size
-constexpr int KV_STAGES = 2;
-constexpr int BOX_ROWS = 16;       // keys per TMA box
+constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int BOX_ROWS = 16;       // keys per TMA box at least: 64, 32 or 16, the largest that divides the page
 constexpr uint32_t Q_BYTES = TQ * HD * 2;                 // 2 halves x [128 rows][128 B]
 constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;           // 2 halves x [64 keys][128 B]
 constexpr uint32_t HALF_K = TK * 128;                     // bytes between the two 64-column halves of a K/V tile
 constexpr uint32_t HALF_Q = TQ * 128;
-constexpr uint32_t TMEM_COLS = 256;                       // S: columns 0..63, O: 64..191, P (bf16 pairs): 192..223
-constexpr uint32_t S_COL = 0, O_COL = 64, P_COL = 192;
+constexpr uint32_t TMEM_COLS = 256;                       // S (and, over its first half, P as bf16 pairs): columns 0..63
+constexpr uint32_t S_COL = 0, S_BUF = 64, O_COL = 128;    // and 64..127, O: 128..255
+constexpr float RESCALE_STEP = 8.f;                       // log2 of how far a maximum may run ahead of its reference
 constexpr float LOG2E_F = 1.4426950408889634f;
 
 __device__ int g_attn_status = 0;   // 0 = fine; otherwise the wait that ran out
@@ -54,7 +62,7 @@ struct AttnArgs {
   const int* block_tables;
   const int* q_start;
   const int* seq_lens;
-  int table_width, H, KVH, page;
+  int table_width, H, KVH, page, box;
   float scale;
   int window;
   int* status;
@@ -72,7 +80,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int ATT_THREADS = TQ + 32;      // warps 0-3: one query row per thread; warp 4: TMA and MMA issue
+constexpr int ATT_THREADS = TQ + 64;      // warps 0-3: one query row per thread; warp 4: product issue; warp 5: TMA
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -80,13 +88,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                               // [2][128][128 B]
-  unsigned char* k_s = q_s + Q_BYTES;                      // [STAGES][2][64][128 B]
-  unsigned char* v_s = k_s + KV_STAGES * KV_TILE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * KV_TILE_BYTES);
-  uint64_t* empty = full + KV_STAGES;
-  uint64_t* bar_s = empty + KV_STAGES;                     // S of a tile (and every product issued before it) is complete
-  uint64_t* bar_p = bar_s + 1;                             // all 128 rows have consumed S and written P
-  uint64_t* bar_o = bar_p + 1;                             // the last O product is complete
+  unsigned char* k_s = q_s + Q_BYTES;                      // [K_STAGES][2][64][128 B]
+  unsigned char* v_s = k_s + K_STAGES * KV_TILE_BYTES;     // [V_STAGES][2][64][128 B]
+  uint64_t* full_k = reinterpret_cast<uint64_t*>(v_s + V_STAGES * KV_TILE_BYTES);
+  uint64_t* empty_k = full_k + K_STAGES;
+  uint64_t* full_v = empty_k + K_STAGES;
+  uint64_t* empty_v = full_v + V_STAGES;
+  uint64_t* bar_s = empty_v + V_STAGES;                    // [2]: S in that buffer (and every product issued before it) is complete
+  uint64_t* bar_p = bar_s + 2;                             // all 128 rows have consumed S and written P
+  uint64_t* bar_pv = bar_p + 1;                            // an O product is complete
+  uint64_t* bar_o = bar_pv + 1;                            // the last O product is complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -107,12 +118,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     return;
   }
   if (tid == 0) {
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&full_k[s], 1);
+      mbar_init(&empty_k[s], 1);
     }
-    mbar_init(bar_s, 1);
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(&full_v[s], 1);
+      mbar_init(&empty_v[s], 1);
+    }
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
     mbar_init(bar_p, TQ);
+    mbar_init(bar_pv, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -126,7 +143,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const int last_row = min(row0 + TQ, n_rows) - 1;
   const int j_hi = prefix + last_row / G;
   int j_lo = a.window > 0 ? max(0, prefix + row0 / G - a.window + 1) : 0;
-  j_lo &= ~(BOX_ROWS - 1);
+  const int box = a.box;
+  j_lo &= ~(box - 1);
   const int n_tiles = (seq_len > 0 && j_hi >= j_lo) ? (j_hi - j_lo) / TK + 1 : 0;
 
   // a softmax thread's row
@@ -154,94 +172,105 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
-    // ================= controller: TMA loads and tcgen05.mma issue, one lane =================
+  if (warp == 5) {
+    // ================= producer: TMA loads, one lane =================
     if ((tid & 31) == 0 && n_tiles > 0) {
-      // one TMA box per (16 keys, 64 columns): 8 boxes for K and 8 for V per tile
-      auto load_tile = [&](int t, int stage) {
-        mbar_expect_tx(&full[stage], 2 * KV_TILE_BYTES);
+      // one TMA box per (`box` keys, 64 columns)
+      auto load = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int t) {
+        mbar_expect_tx(bar, KV_TILE_BYTES);
         const int j0 = j_lo + t * TK;
-        for (int bx = 0; bx < TK / BOX_ROWS; ++bx) {
-          const int j = j0 + bx * BOX_ROWS;
+        for (int bx = 0; bx < TK / box; ++bx) {
+          const int j = j0 + bx * box;
           const int lp = j / a.page;
           const int pg = lp < a.table_width ? a.block_tables[(size_t)b * a.table_width + lp] : 0;
           const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t off = stage * KV_TILE_BYTES + half * HALF_K + bx * BOX_ROWS * 128;
-            tma_load_2d(k_s + off, &k_map, half * 64, y, &full[stage]);
-            tma_load_2d(v_s + off, &v_map, half * 64, y, &full[stage]);
-          }
+          for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
         }
       };
-      // S = Q . K^T for the tile in `stage`: 8 k-steps of 16 columns, 4 per 64-column half
-      auto issue_s = [&](int stage) {
+      // keys are needed two softmax rounds before the values of the same tile: K(t+1) goes before V(t)
+      bool ok = true;
+      load(&k_map, k_s, &full_k[0], 0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (t + 1 < n_tiles) {
+          const int sk = (t + 1) % K_STAGES;
+          if (t + 1 >= K_STAGES) ok = mbar_wait(&empty_k[sk], (uint32_t)(((t + 1) / K_STAGES - 1) & 1), a.status, 4, abort_flag);
+          if (!ok) break;
+          load(&k_map, k_s + sk * KV_TILE_BYTES, &full_k[sk], t + 1);
+        }
+        const int sv = t % V_STAGES;
+        if (t >= V_STAGES) ok = mbar_wait(&empty_v[sv], (uint32_t)((t / V_STAGES - 1) & 1), a.status, 7, abort_flag);
+        if (!ok) break;
+        load(&v_map, v_s + sv * KV_TILE_BYTES, &full_v[sv], t);
+      }
+    }
+  } else if (warp == 4) {
+    // ================= product issue, one lane =================
+    if ((tid & 31) == 0 && n_tiles > 0) {
+      // S(t) = Q . K(t)^T into buffer t & 1: 8 k-steps of 16 columns, 4 per 64-column half
+      auto issue_s = [&](int t) {
         constexpr uint32_t idesc = instr_desc(TK);
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + stage * KV_TILE_BYTES);
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + (t % K_STAGES) * KV_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off_q = (ks >> 2) * HALF_Q + (ks & 3) * 32;
           const uint32_t off_k = (ks >> 2) * HALF_K + (ks & 3) * 32;
-          umma(tmem + S_COL, smem_desc(qa + off_q), smem_desc(ka + off_k), idesc, ks > 0 ? 1u : 0u);
+          umma(tmem + S_COL + (t & 1) * S_BUF, smem_desc(qa + off_q), smem_desc(ka + off_k), idesc, ks > 0 ? 1u : 0u);
         }
+        umma_commit(&bar_s[t & 1]);
+        umma_commit(&empty_k[t % K_STAGES]);
       };
-      // O += P . V: 4 k-steps of 16 keys; V is MN-major (rows = keys, 128 B of head columns per row)
-      auto issue_o = [&](int stage, bool accumulate) {
+      // O += P(t) . V(t): 4 k-steps of 16 keys; V is MN-major (rows = keys, 128 B of head columns per row)
+      auto issue_o = [&](int t) {
         constexpr uint32_t idesc = instr_desc(HD, true);
-        const uint32_t va = smem_u32(v_s + stage * KV_TILE_BYTES);
+        const uint32_t va = smem_u32(v_s + (t % V_STAGES) * KV_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk)                  // 16 keys = 8 columns of bfloat16 pairs
-          umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, smem_desc_mn(va + kk * 16 * 128, HALF_K), idesc,
-                  (accumulate || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + O_COL, tmem + S_COL + (t & 1) * S_BUF + kk * 8, smem_desc_mn(va + kk * 16 * 128, HALF_K), idesc,
+                  (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty_v[t % V_STAGES]);
+        umma_commit(bar_pv);
+        if (t + 1 == n_tiles) umma_commit(bar_o);
       };
-
-      load_tile(0, 0);
-      if (n_tiles > 1) load_tile(1, 1);
-      bool ok = mbar_wait(&full[0], 0, a.status, 1, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        umma_commit(bar_s);
+      bool ok = true;
+      for (int t = 0; t < 2 && t < n_tiles && ok; ++t) {
+        ok = mbar_wait(&full_k[t], 0, a.status, 1, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          issue_s(t);
+        }
       }
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int stage = t % KV_STAGES;
-        ok = mbar_wait_spin(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place, S(t) is consumed
+        ok = mbar_wait_spin(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place
+        if (!ok) break;
+        ok = mbar_wait(&full_v[t % V_STAGES], (uint32_t)((t / V_STAGES) & 1), a.status, 3, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        issue_o(stage, t > 0);
-        umma_commit(&empty[stage]);                           // K/V of this stage are free once this product is done
-        if (t + 1 < n_tiles) {
-          ok = mbar_wait(&full[(t + 1) % KV_STAGES], (uint32_t)(((t + 1) / KV_STAGES) & 1), a.status, 3, abort_flag);
+        issue_o(t);
+        if (t + 2 < n_tiles) {
+          ok = mbar_wait(&full_k[(t + 2) % K_STAGES], (uint32_t)(((t + 2) / K_STAGES) & 1), a.status, 8, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_s((t + 1) % KV_STAGES);
-          umma_commit(bar_s);
-          if (t + 2 < n_tiles) {
-            ok = mbar_wait(&empty[stage], (uint32_t)((t / KV_STAGES) & 1), a.status, 4, abort_flag);
-            if (!ok) break;
-            load_tile(t + 2, stage);
-          }
-        } else {
-          umma_commit(bar_o);
+          issue_s(t + 2);                                     // over P(t), behind the product that reads it
         }
       }
     }
   } else {
     // ================= softmax warps: thread = row = tensor-memory lane =================
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;                   // the maximum the exponentials refer to; the sum in its scale
     const float sc = a.scale * LOG2E_F;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      // S of this tile; the commit behind it also covers the O product of the tile before
-      ok = mbar_wait_spin(bar_s, (uint32_t)(t & 1), a.status, 2, abort_flag);
+      const uint32_t s_addr = tmem + lane_addr + S_COL + (t & 1) * S_BUF;
+      ok = mbar_wait_spin(&bar_s[t & 1], (uint32_t)((t >> 1) & 1), a.status, 2, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const int j0 = j_lo + t * TK;
       uint32_t sv[2][32];
-      tmem_ld32(tmem + lane_addr + S_COL, sv[0]);
-      tmem_ld32(tmem + lane_addr + S_COL + 32, sv[1]);
+      tmem_ld32(s_addr, sv[0]);
+      tmem_ld32(s_addr + 32, sv[1]);
       tmem_wait_ld();
       float mx = -INFINITY;
       // tiles wholly before every row of the warp (the common case away from the diagonal) need no mask
@@ -267,13 +296,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             mx = fmaxf(mx, v);
           }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);
-      m_run = m_new;
+      // the reference maximum follows the true one only in steps (and from nothing to something)
+      const bool move = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+      float corr = 1.f;
+      if (move) {
+        corr = exp2f(m_ref - mx);                             // 0 when there was no reference yet: O and l are 0 then
+        m_ref = mx;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       float rs = 0.f;
-      // P (bfloat16 pairs) -> tensor memory, lane = row, 32 words for the 64 keys; the second product
-      // reads its A operand from there
+      // P (bfloat16 pairs), lane = row, 32 words for the 64 keys
       uint32_t pw[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
@@ -284,10 +316,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         pw[i] = *reinterpret_cast<uint32_t*>(&pk);
       }
-      tmem_st32(tmem + lane_addr + P_COL, pw);
       l_run = l_run * corr + rs;
-      // rescale O where a maximum moved (skipped when no row of the warp needs it)
-      if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+      // rescale O where a reference moved (skipped when no row of the warp needs it): the product of
+      // the tile before must be done with O first
+      if (t > 0 && __any_sync(0xffffffffu, move)) {
+        ok = mbar_wait_spin(bar_pv, (uint32_t)((t - 1) & 1), a.status, 10, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           uint32_t ov[32];
@@ -298,6 +334,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           tmem_st32(tmem + lane_addr + O_COL + c, ov);
         }
       }
+      tmem_st32(s_addr, pw);                                  // over the first half of S(t), which is in registers
       tmem_wait_st();                                         // P (and a rescaled O) are in tensor memory
       tc_fence_before();
       mbar_arrive(bar_p);
@@ -379,9 +416,10 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   CUtensorMap k_map, v_map;
   const long long rows = (long long)num_pages * KVH * page;
   if (rows > 0x7fffffffLL) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_prefill_tc: cache of %lld rows", rows);
-  if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, BOX_ROWS) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, BOX_ROWS))
+  const int box = page % 64 == 0 ? 64 : (page % 32 == 0 ? 32 : 16);
+  if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, box) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, box))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
-  constexpr size_t smem = Q_BYTES + 2 * KV_STAGES * KV_TILE_BYTES + (2 * KV_STAGES + 3) * 8 + 16;
+  constexpr size_t smem = Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + (2 * K_STAGES + 2 * V_STAGES + 5) * 8 + 16;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -398,6 +436,7 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   a.H = H;
   a.KVH = KVH;
   a.page = page;
+  a.box = box;
   a.scale = scale;
   a.window = window;
   a.status = status;

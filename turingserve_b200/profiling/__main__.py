@@ -2,7 +2,7 @@
 capture that ends by itself (a few hundred MB on the device, a few dozen launches).
 
     python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048] [--page 16] [--graph]
-    python -m turingserve_b200.profiling prefill_attention [--tokens 2048]
+    python -m turingserve_b200.profiling prefill_attention [--tokens 2048] [--page 16]
     python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library]
 
 Each prints the launches it made and, timed with CUDA events, the mean time per launch.
@@ -86,7 +86,8 @@ def decode_attention(a) -> None:
 def prefill_attention(a) -> None:
     ops = kernels.ops()
     T = a.tokens
-    caches, table = paged(1, T, 4)
+    PAGE = a.page
+    caches, table = paged(1, T, 4, PAGE)
     qkv = torch.randn(T, (H + 2 * KVH) * D, device="cuda", dtype=torch.bfloat16)
     step = Step(torch.tensor([0, T], dtype=torch.int32, device="cuda"),
                 torch.tensor([T], dtype=torch.int32, device="cuda"), 1, T, T, 0)
@@ -99,7 +100,7 @@ def prefill_attention(a) -> None:
     for i in range(4):
         f(i)
     us = timed(f, 12)
-    print(f"prefill_attention {T} tokens: {us:.1f} us per launch, {2.0 * T * T * D * H / us / 1e6:.1f} TFLOP/s (causal)")
+    print(f"prefill_attention {T} tokens page {PAGE}: {us:.1f} us per launch, {2.0 * T * T * D * H / us / 1e6:.1f} TFLOP/s (causal)")
 
 
 def gemm(a) -> None:
@@ -131,6 +132,7 @@ def main() -> int:
     s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
     s = sub.add_parser("prefill_attention")
     s.add_argument("--tokens", type=int, default=2048)
+    s.add_argument("--page", type=int, default=PAGE)
     s = sub.add_parser("gemm")
     s.add_argument("--tokens", type=int, default=8)
     s.add_argument("--n", type=int, default=17920)
