@@ -137,9 +137,9 @@ def run_ours(a) -> dict:
     with tempfile.TemporaryDirectory() as tmp:
         folder = make_model(a.model, layers, tmp)
         max_b = max(B, 64)
-        pages = max_b * (-(-ctx_len // 16)) + 8
+        pages = max_b * (-(-ctx_len // a.kv_block)) + 8
         eng = LLMEngine.from_config(EngineConfig(
-            model=folder, dtype="bfloat16", max_model_len=ctx_len, block_size=16, num_blocks=pages,
+            model=folder, dtype="bfloat16", max_model_len=ctx_len, block_size=a.kv_block, num_blocks=pages,
             max_num_seqs=max_b, max_num_batched_tokens=max(2048, max_b), graph_batch_sizes=(1, 8, 64, B),
             watermark=0.0))
     runner, cache = eng.runner, eng.cache
@@ -244,7 +244,7 @@ def run_ours(a) -> dict:
                    "hidden": kw["hidden_size"], "heads": kw["num_heads"], "kv_heads": kw["num_kv_heads"],
                    "head_dim": kw["head_dim"], "intermediate": kw["intermediate_size"], "vocab": V,
                    "global_batch": B, "seq_len": ctx_len, "prompt_len": prompt_len, "new_tokens": warmup + steps,
-                   "kv_block": 16, "parallelism": "single GPU", "cuda_graphs": True,
+                   "kv_block": a.kv_block, "parallelism": "single GPU", "cuda_graphs": True,
                    "l2": "inputs larger than L2 (weights %.2f GB per step)" % (nums["weight_bytes_decode"] / 1e9),
                    "peaks": pk_src},
         "clocks": clocks.summary(),
@@ -332,6 +332,7 @@ def main() -> int:
     ap.add_argument("--model", default="qwen2.5-1.5b", choices=sorted(SHAPES))
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--kv-block", type=int, default=64, help="tokens per cache page")
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prefill-tokens", type=int, default=2048)

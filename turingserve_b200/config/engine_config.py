@@ -4,7 +4,8 @@ Option names and meanings follow the reference's ``EngineConfig`` / ``build_pars
 (turingserve/config.py:10-47,107-156) for every option this engine has; the server, speculative,
 quantization and autopilot flags of the reference have no counterpart here.  Differences:
 ``--dtype`` is bfloat16|float32 (the reference: float16|float32, config.py:56-60), and
-``--block-size`` is free (the reference fixes 16, config.py:74-75).
+``--block-size`` is free and defaults to 64 (the reference fixes 16, config.py:74-75): a page of 64
+tokens is one TMA box of the attention kernels, which a page of 16 needs four of.
 """
 
 from __future__ import annotations
@@ -21,7 +22,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     device: str = "cuda"
     max_model_len: int | None = None          # None: the model's max_position_embeddings, at most 4096
-    block_size: int = 16
+    block_size: int = 64
     num_blocks: int | None = None             # pages per cache group (None: from free memory)
     gpu_memory_utilization: float = 0.85
     max_num_seqs: int = 128

@@ -31,7 +31,7 @@ ROUND_TO = 64
 
 class Replayer:
     def __init__(self, model_dir: str, dtype: torch.dtype, max_tokens: int, device,
-                 page_size: int = 16, max_step_tokens: int | None = None) -> None:
+                 page_size: int = 64, max_step_tokens: int | None = None) -> None:
         if ROUND_TO % page_size:
             raise ValueError(f"page size {page_size} must divide {ROUND_TO}")
         self.model, self.cfg = load_model(model_dir, dtype, device)
@@ -62,7 +62,7 @@ class Replayer:
 
 
 def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=None, stdout=None,
-        device=None, page_size: int = 16) -> int:
+        device=None, page_size: int = 64) -> int:
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype_name]
