@@ -326,7 +326,11 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
     if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
       TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc: cuTensorMapEncodeTiled failed");
     dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
-    if (bn == 16) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
+    // Several waves of blocks (the output head): three stages leave room for two blocks on an SM, so
+    // one block's pipeline fill and epilogue hide behind the other's main loop.
+    const bool waves = (long long)grid.x * grid.y * grid.z >= 592;
+    if (bn == 16 && waves) rc = launch<16, 3, true, 2>(rows_map, cols_map, a, grid, s);
+    else if (bn == 16) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
     else if (bn == 32) rc = launch<32, 4, true>(rows_map, cols_map, a, grid, s);
     else if (bn == 64) rc = launch<64, 4, true>(rows_map, cols_map, a, grid, s);
     else rc = launch<128, 4, true>(rows_map, cols_map, a, grid, s);
