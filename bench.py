@@ -224,6 +224,9 @@ def run_ours(a) -> dict:
             n_tok += sum(len(o.delta_token_ids) for o in eng.step())
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+        if n_tok != steps * B:
+            raise RuntimeError(f"end-to-end run produced {n_tok} tokens in {steps} steps of {B} requests: a request "
+                               "stopped early (bad logits?)")
         for rid in list(eng.requests):
             eng.abort(rid)
         eng.step()

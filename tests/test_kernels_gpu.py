@@ -89,6 +89,43 @@ def test_silu_mul(ops, dtype):
         ref = torch.empty((T, inter), dtype=dtype)
         twin.silu_mul(ref, gu)
         torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+    for T, inter, group in [(3, 128, 64), (70, 8960, 64), (9, 96, 8), (5, 1024, 64)]:    # interleaved blocks
+        gu = _rand((T, 2 * inter), dtype, 16, 3.0)
+        out = torch.empty((T, inter), dtype=dtype, device="cuda")
+        ops.silu_mul(out, gu.cuda(), group)
+        ref = torch.empty((T, inter), dtype=dtype)
+        twin.silu_mul(ref, gu, group)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [1, 8, 17, 40, 100, 128, 300])
+@pytest.mark.parametrize("inter,K,group", [(128, 64, 64), (8960, 1536, 64), (320, 200, 64), (96, 72, 0)])
+def test_gated_linear(ops, monkeypatch, dtype, T, inter, K, group):
+    """Gate/up product and activation as one operation: for a few bfloat16 tokens one kernel with
+    the activation in its epilogue, otherwise product then activation; either way the result is
+    that of the two steps with the product rounded to the model dtype in between."""
+    twin = TwinOps()
+    x, w = _rand((T, K), dtype, 30, 1.0), _rand((2 * inter, K), dtype, 31, 0.1)
+    out = torch.full((T, inter), float("nan"), dtype=dtype, device="cuda")
+    separate = []
+    monkeypatch.setattr(ops, "silu_mul", lambda *a, _f=ops.silu_mul: (separate.append(1), _f(*a))[1])
+    monkeypatch.setattr(ops, "fused_gate_tokens", 128)            # everything the fused kernel takes
+    ops.gated_linear(out, x.cuda(), w.cuda(), None, group)
+    fused = dtype == torch.bfloat16 and T <= 128 and group == 64
+    assert (not separate) == fused, "no activation kernel of its own exactly when the fused epilogue applies"
+    monkeypatch.undo()
+    ref = torch.empty((T, inter), dtype=dtype)
+    twin.gated_linear(ref, x, w, None, group)
+    tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)       # as test_linear
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
+    if fused and ops.tc_splits(T, 2 * inter, K) == 1:       # same sums, same roundings: the same bits
+        two = torch.empty((T, inter), dtype=dtype, device="cuda")
+        gu = torch.empty((T, 2 * inter), dtype=dtype, device="cuda")
+        ops.linear(gu, x.cuda(), w.cuda(), None)
+        ops.silu_mul(two, gu, group)
+        assert torch.equal(out, two)
+    assert ops.tc_status() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -300,6 +337,34 @@ def test_attention_needle(ops, dtype, needle):
             torch.testing.assert_close(got, v, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_tensor_core_uneven_warps(ops, page):
+    """A long portion whose last row tile ends in rows without a query: that warp masks every tile
+    element by element and falls behind the other three, which already have the next tile's scores.
+    A warp running ahead must not be counted among the rows that have finished the tile before
+    (it once was: the product then read probabilities that the slow warp had not written yet,
+    in some launches only, hence the repeats)."""
+    H, KVH, D = 12, 2, 128
+    q_lens, prefixes = [1, 2047], [2048, 0]
+    qkv, kc, vc, bt, qs, sl = _paged_case(torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 23)
+    # small queries: flat scores, no row's maximum ever jumps, so nothing makes a fast warp wait for
+    # the products of the tile before (as in a trained or N(0, 0.02) model; random queries hide it)
+    qkv[:, : H * D] = (qkv[:, : H * D].float() * 0.02).to(qkv.dtype)
+    step = FakeStep(qs.cuda(), sl.cuda(), 2, 2047, int(sl.max()), 1)
+    ref = torch.empty((qkv.shape[0], H * D), dtype=torch.float32)
+    paged_attention(ref, qkv.float(), kc.float(), vc.float(), bt, qs, sl, H, KVH, D, page, D ** -0.5, None)
+    ref = ref.cuda()
+    q_d, bt_d = qkv.cuda(), bt.cuda()
+    copies = [(kc.cuda(), vc.cuda()) for _ in range(48)]          # rotated: keys and values come from DRAM, as in a model
+    ops.use_tc_attention = True
+    for i in range(96):
+        out = torch.full((qkv.shape[0], H * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        k_d, v_d = copies[i % len(copies)]
+        ops.attention(out, q_d, k_d, v_d, bt_d, step, H, KVH, D, page, D ** -0.5, None)
+        torch.testing.assert_close(out.float(), ref, **ATT_TOL[torch.bfloat16])
+    assert ops.tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 300, 130), (65, 129, 257), (130, 70, 1000), (3, 1000, 48)])
 def test_linear(ops, dtype, M, N, K):
@@ -380,7 +445,7 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
 
 
 @pytest.mark.parametrize("H,KVH", [(12, 2), (28, 4), (5, 5), (40, 2)])
-@pytest.mark.parametrize("page", [16, 32])
+@pytest.mark.parametrize("page", [16, 32, 64, 128])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attention_tensor_core_portions(ops, H, KVH, page, window):
     """The tcgen05 prompt-portion kernel (head size 128): portions after prefixes, several requests,

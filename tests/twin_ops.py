@@ -33,9 +33,19 @@ class TwinOps:
         y = (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
         out.copy_((weight.float() * y.float()).to(x.dtype))
 
-    def silu_mul(self, out, gu):
+    def silu_mul(self, out, gu, group=0):
         i = gu.shape[-1] // 2
-        out.copy_(F.silu(gu[..., :i]) * gu[..., i:])
+        if group:
+            blocks = gu.reshape(gu.shape[0], i // group, 2, group)
+            g, u = blocks[:, :, 0].reshape(-1, i), blocks[:, :, 1].reshape(-1, i)
+        else:
+            g, u = gu[..., :i], gu[..., i:]
+        out.copy_(F.silu(g) * u)
+
+    def gated_linear(self, out, x, w, bias, group):
+        gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype)
+        self.linear(gu, x, w, bias)
+        self.silu_mul(out, gu, group)
 
     def rope_kv_write(self, qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                       page_size):

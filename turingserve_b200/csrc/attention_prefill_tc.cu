@@ -95,8 +95,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   uint64_t* full_v = empty_k + K_STAGES;
   uint64_t* empty_v = full_v + V_STAGES;
   uint64_t* bar_s = empty_v + V_STAGES;                    // [2]: S in that buffer (and every product issued before it) is complete
-  uint64_t* bar_p = bar_s + 2;                             // all 128 rows have consumed S and written P
-  uint64_t* bar_pv = bar_p + 1;                            // an O product is complete
+  // [2]: all 128 rows have consumed S(t) and written P(t), t & 1 choosing the barrier: a warp that is
+  // done with tile t may go on to tile t+1 (its S is there already), and its arrivals for t+1 must not
+  // count towards tile t, which a slower warp has yet to finish
+  uint64_t* bar_p = bar_s + 2;
+  uint64_t* bar_pv = bar_p + 2;                            // an O product is complete
   uint64_t* bar_o = bar_pv + 1;                            // the last O product is complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -128,7 +131,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
     mbar_init(&bar_s[0], 1);
     mbar_init(&bar_s[1], 1);
-    mbar_init(bar_p, TQ);
+    mbar_init(&bar_p[0], TQ);
+    mbar_init(&bar_p[1], TQ);
     mbar_init(bar_pv, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
@@ -241,7 +245,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         }
       }
       for (int t = 0; t < n_tiles && ok; ++t) {
-        ok = mbar_wait_spin(bar_p, (uint32_t)(t & 1), a.status, 6, abort_flag);     // P(t) is in place
+        ok = mbar_wait_spin(&bar_p[t & 1], (uint32_t)((t >> 1) & 1), a.status, 6, abort_flag);     // P(t) is in place
         if (!ok) break;
         ok = mbar_wait(&full_v[t % V_STAGES], (uint32_t)((t / V_STAGES) & 1), a.status, 3, abort_flag);
         if (!ok) break;
@@ -337,7 +341,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       tmem_st32(s_addr, pw);                                  // over the first half of S(t), which is in registers
       tmem_wait_st();                                         // P (and a rescaled O) are in tensor memory
       tc_fence_before();
-      mbar_arrive(bar_p);
+      mbar_arrive(&bar_p[t & 1]);
     }
     // epilogue: O / l -> bfloat16 -> global, one 256-byte row per thread
     if (ok && n_tiles > 0) {
@@ -419,7 +423,7 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   const int box = page % 64 == 0 ? 64 : (page % 32 == 0 ? 32 : 16);
   if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, box) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, box))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
-  constexpr size_t smem = Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + (2 * K_STAGES + 2 * V_STAGES + 5) * 8 + 16;
+  constexpr size_t smem = Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + (2 * K_STAGES + 2 * V_STAGES + 6) * 8 + 16;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -309,18 +309,25 @@ TS_API int ts_reduce_rmsnorm(void* out, const float* part, int splits, const voi
 }
 
 // ------------------------------------------------------------------------------------------
-// SiLU*mul: out[t, i] = T(silu(g)) * u with gu[t] = [g(0..I) | u(0..I)]
-// (turingserve/ops/reference.py:26-28; rounding as triton_silu_mul.py:15-18).
+// SiLU*mul: out[t, i] = T(silu(g_i)) * u_i (turingserve/ops/reference.py:26-28; rounding as
+// triton_silu_mul.py:15-18).  Layout of gu[t]: group = 0: [g(0..I) | u(0..I)]; group = 64: blocks
+// of 128 columns, each the 64 gates j*64.. then the 64 ups j*64.. (what a product with
+// block-interleaved weight rows gives; the few-token tensor-core product applies the activation to
+// such a tile in its own epilogue).
+__device__ __forceinline__ size_t gate_col(int i, int group) { return group ? (size_t)(i / group) * 2 * group + i % group : (size_t)i; }
+
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t total, int group) {
   pdl_launch_dependents();
   pdl_wait();
+  const int up_off = group ? group : inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
     const int i = (int)(idx - t * inter);
-    const float g = to_f(gu[t * 2 * inter + i]);
-    const float u = to_f(gu[t * 2 * inter + inter + i]);
+    const size_t gc = t * 2 * inter + gate_col(i, group);
+    const float g = to_f(gu[gc]);
+    const float u = to_f(gu[gc + up_off]);
     const float s = round_to<T>(g / (1.f + expf(-g)));
     out[idx] = from_f<T>(s * u);
   }
@@ -329,24 +336,35 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
 // Vector variant: one thread takes 16 bytes of gate and 16 bytes of up.
 template <typename T>
 __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int vec_per_row,
-                                    unsigned total_vecs) {
+                                    unsigned total_vecs, int group) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int N = Vec16<T>::N;
+  const int up_off = group ? group : inter;
   for (unsigned v = blockIdx.x * blockDim.x + threadIdx.x; v < total_vecs; v += gridDim.x * blockDim.x) {
     const unsigned t = v / vec_per_row;
     const int i = (int)(v - t * vec_per_row) * N;
     float g[N], u[N], o[N];
-    load_vec<T, N>(gu + (size_t)t * 2 * inter + i, g);
-    load_vec<T, N>(gu + (size_t)t * 2 * inter + inter + i, u);
+    const size_t gc = (size_t)t * 2 * inter + gate_col(i, group);
+    load_vec<T, N>(gu + gc, g);
+    load_vec<T, N>(gu + gc + up_off, u);
 #pragma unroll
     for (int k = 0; k < N; ++k) o[k] = round_to<T>(g[k] / (1.f + expf(-g[k]))) * u[k];
     store_vec<T, N>(out + (size_t)t * inter + i, o);
   }
 }
 
+TS_API int ts_silu_mul_ex(void* out, const void* gu, int T, int inter, int group, int dtype, void* stream);
+
 TS_API int ts_silu_mul(void* out, const void* gu, int T, int inter, int dtype, void* stream) {
+  return ts_silu_mul_ex(out, gu, T, inter, 0, dtype, stream);
+}
+
+// group: 0, or the block size of an interleaved layout (a multiple of 8 that divides inter).
+TS_API int ts_silu_mul_ex(void* out, const void* gu, int T, int inter, int group, int dtype, void* stream) {
   if (T <= 0) return 0;
+  if (group < 0 || (group > 0 && (inter % group != 0 || group % 8 != 0)))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_silu_mul: blocks of %d columns for a width of %d", group, inter);
   cudaStream_t s = (cudaStream_t)stream;
   const size_t total = (size_t)T * inter;
   const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
@@ -357,16 +375,16 @@ TS_API int ts_silu_mul(void* out, const void* gu, int T, int inter, int dtype, v
         ((((uintptr_t)out | (uintptr_t)gu) & 15) == 0)) {
       const int vb = (int)((vecs + 255) / 256 > 148 * 32 ? 148 * 32 : (vecs + 255) / 256);
       if (dtype == TS_F32)
-        ts_launch(silu_mul_vec_kernel<float>, dim3(vb), dim3(256), 0, s, (float*)out, (const float*)gu, inter, inter / n, (unsigned)vecs);
+        ts_launch(silu_mul_vec_kernel<float>, dim3(vb), dim3(256), 0, s, (float*)out, (const float*)gu, inter, inter / n, (unsigned)vecs, group);
       else
-        ts_launch(silu_mul_vec_kernel<bf16>, dim3(vb), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, inter / n, (unsigned)vecs);
+        ts_launch(silu_mul_vec_kernel<bf16>, dim3(vb), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, inter / n, (unsigned)vecs, group);
       TS_LAUNCH_CHECK();
     }
   }
   if (dtype == TS_F32)
-    ts_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)gu, inter, total);
+    ts_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)gu, inter, total, group);
   else if (dtype == TS_BF16)
-    ts_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, total);
+    ts_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, total, group);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_silu_mul: dtype %d", dtype);
   TS_LAUNCH_CHECK();

@@ -33,6 +33,7 @@ struct GemmArgs {
   int k_blocks_per_split;
   int splits;
   int out_is_float;
+  int gated;              // weights-on-rows only: the tile's rows are 64 gates then 64 ups; out is bf16 [M, N / 2]
   int* status;
 };
 
@@ -154,7 +155,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     pdl_wait();                                    // nothing is written before the predecessor is done
     bool ok = n_kb > 0 && mbar_wait(accum, 0, args.status, 3, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    if (SWAP && args.gated) {
+      // act[m, 64 * tile + i] = bf16(silu(bf16(gate_i))) * bf16(up_i): the roundings of the unfused
+      // path (product rounded to bfloat16, then the activation kernel's).  The up rows (lanes
+      // 64..127) go through shared memory to the threads that hold the gate rows; the stage
+      // buffers are free by now.  All four warps take the barrier, whether they gave up or not.
+      float* ex = reinterpret_cast<float*>(a_s);               // [64][BN]
+      constexpr int CW = BN >= 32 ? 32 : 16;
+      if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok && q >= 2) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+          if constexpr (CW == 32) {
+            tmem_ld32(taddr, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld16(taddr, v16);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v16[i];
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < CW; ++i) ex[(r - 64) * BN + c + i] = __uint_as_float(v[i]);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && q < 2) {
+        const int I = args.N / 2;
+        const int n = (int)blockIdx.x * 64 + r;                // output column
+        bf16* outb = reinterpret_cast<bf16*>(args.out);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+          if constexpr (CW == 32) {
+            tmem_ld32(taddr, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld16(taddr, v16);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v16[i];
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < CW; ++i) {
+            const int m = col0 + c + i;                        // token
+            if (n < I && m < args.M) {
+              const float g = round_to<bf16>(__uint_as_float(v[i]));
+              const float u = round_to<bf16>(ex[r * BN + c + i]);
+              const float sl = round_to<bf16>(g / (1.f + expf(-g)));
+              outb[(size_t)m * I + n] = __float2bfloat16_rn(sl * u);
+            }
+          }
+        }
+      }
+    } else if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int M = args.M, N = args.N;
       float* outf = reinterpret_cast<float*>(args.out);
@@ -301,6 +358,7 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
   a.bias = (const bf16*)bias;
   a.M = M; a.N = N; a.K = K;
   a.out_is_float = out_is_float;
+  a.gated = 0;
   a.status = status;
   const bool swap = M <= 128;
   if (!swap) splits = 1;
@@ -349,4 +407,36 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
     TS_LAUNCH_CHECK();
   }
   return 0;
+}
+
+// act[M, N2 / 2] (bf16) = silu(g) * u where [g | u] = x[M, K] . w[N2, K]^T and the rows of w come in
+// blocks of 128: the 64 gate rows j*64.. then the 64 up rows j*64...  At most 128 tokens, N2 a
+// multiple of 128, no bias: what the fused epilogue takes (TS_ERR_UNSUPPORTED otherwise, and the
+// caller does product and activation apart).
+TS_API int ts_linear_tc_gated(void* act, const void* x, const void* w, int M, int N2, int K, void* stream) {
+  if (M <= 0 || N2 <= 0) return 0;
+  if (M > 128 || N2 % 128 != 0 || !ts_linear_tc_supported(M, N2, K))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_gated: M=%d N=%d K=%d is not taken by this kernel", M, N2, K);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) TS_REFUSE(TS_ERR_ALIGN, "ts_linear_tc_gated: operands must be 16-byte aligned");
+  int* status = status_word();
+  if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_linear_tc_gated: no status word");
+  GemmArgs a;
+  a.out = act;
+  a.bias = nullptr;
+  a.M = M; a.N = N2; a.K = K;
+  a.out_is_float = 0;
+  a.gated = 1;
+  a.status = status;
+  a.k_blocks_per_split = ceil_div(K, BK);
+  a.splits = 1;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap rows_map, cols_map;
+  if (!tensor_map(&rows_map, w, N2, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_gated: cuTensorMapEncodeTiled failed");
+  dim3 grid(N2 / BM, ceil_div(M, bn), 1);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 16) return launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
+  if (bn == 32) return launch<32, 4, true>(rows_map, cols_map, a, grid, s);
+  if (bn == 64) return launch<64, 4, true>(rows_map, cols_map, a, grid, s);
+  return launch<128, 4, true>(rows_map, cols_map, a, grid, s);
 }

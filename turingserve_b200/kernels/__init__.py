@@ -72,6 +72,8 @@ class CudaOps:
             "ts_gather_rows": [P, P, P, I, I, I, P],
             "ts_rmsnorm": [P, P, P, P, F, I, I, I, I, P],
             "ts_silu_mul": [P, P, I, I, I, P],
+            "ts_silu_mul_ex": [P, P, I, I, I, I, P],
+            "ts_linear_tc_gated": [P, P, P, I, I, I, P],
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write_ex": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
@@ -177,10 +179,35 @@ class CudaOps:
         self._check(self.lib.ts_rmsnorm(_ptr(out), _ptr(x), _ptr(residual), _ptr(weight), float(eps), T, h,
                                         _code(x.dtype), _code(weight.dtype), self._stream()), "rmsnorm")
 
-    def silu_mul(self, out, gu) -> None:
+    def silu_mul(self, out, gu, group: int = 0) -> None:
+        """out = silu(gate) * up.  ``group`` 0: gu = [gates | ups]; else gu comes in blocks of
+        2 * group columns, group gates then the matching group ups."""
         T, inter = out.shape
-        self._check(self.lib.ts_silu_mul(_ptr(out), _ptr(gu), T, inter, _code(gu.dtype), self._stream()),
+        self._check(self.lib.ts_silu_mul_ex(_ptr(out), _ptr(gu), T, inter, group, _code(gu.dtype), self._stream()),
                     "silu_mul")
+
+    GATE_GROUP = 64      # rows of gates, then of ups, in one 128-row tile of the few-token product
+    # up to this many tokens the activation goes into the product's epilogue (the kernel takes 128; above
+    # 16 its epilogue, two of four warps doing the activation, costs more than the kernel it saves:
+    # 24.0k against 24.7k tok/s at batch 64, 1.550 against 1.559 ms a step at batch 8)
+    fused_gate_tokens = 16
+
+    def gated_linear(self, out, x, w, bias, group: int) -> None:
+        """out[T, I] = silu(g) * u with [g, u] = x @ w[2I, K]^T + bias, the rows of ``w`` (and
+        ``bias``) laid out as ``silu_mul`` describes.  A few bfloat16 tokens and blocks of 64: one
+        kernel, the activation in the product's epilogue; otherwise product, then activation."""
+        T, inter = out.shape
+        K = w.shape[1]
+        use_tc = self.gemm_mode == "tc" or (self.gemm_mode == "auto" and T <= 128)
+        if (x.dtype == torch.bfloat16 and use_tc and bias is None and group == self.GATE_GROUP and T <= self.fused_gate_tokens
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            rc = self.lib.ts_linear_tc_gated(_ptr(out), _ptr(x), _ptr(w), T, 2 * inter, K, self._stream())
+            if rc != self.UNSUPPORTED:
+                self._check(rc, "linear_tc_gated")
+                return
+        gu = torch.empty((T, 2 * inter), dtype=x.dtype, device=x.device)
+        self.linear(gu, x, w, bias)
+        self.silu_mul(out, gu, group)
 
     def rope_kv_write(self, qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                       page_size):
