@@ -194,6 +194,40 @@ def test_real_layer_sizes_float32(tmp_path):
         assert bad is None, (sched, bad)
 
 
+@pytest.mark.parametrize("page", [16, 64])
+def test_real_layer_sizes_bfloat16(tmp_path, page):
+    """Two layers of the Qwen2.5-1.5B shape in bfloat16 with N(0, 0.02) weights, long prompts in
+    portions and mixed with decoding: the tensor-core and TMA kernels on activations as a model
+    makes them (flat scores, maxima that settle early), which random kernel inputs are not."""
+    from turingserve_b200.models.qwen2 import make_config
+    from turingserve_b200.weights import write_random_model
+    from turingserve_b200.engine.replay import Replayer
+    from turingserve_b200 import kernels
+    folder = str(tmp_path / "real16")
+    write_random_model(folder, make_config(hidden_size=1536, intermediate_size=8960, num_layers=2, num_heads=12,
+                                           num_kv_heads=2, vocab_size=2000, rope_theta=1e6, rms_norm_eps=1e-6,
+                                           tie_word_embeddings=True, max_position_embeddings=4096), seed=4)
+    cfg, w = plain.read_folder(folder)
+    reqs = {"a": tiny.random_ids(1100, 2000, 1), "b": tiny.random_ids(700, 2000, 2), "c": tiny.random_ids(90, 2000, 3)}
+    expected = {k: plain.forward(cfg, w, v).numpy() for k, v in reqs.items()}
+    kernels.use(None)
+    for sched in ("whole", "decode_tail", "mixed"):
+        steps = getattr(schedules, sched)(reqs)
+        rp = Replayer(folder, torch.bfloat16, schedules.peak_tokens(steps), "cuda", page_size=page)
+        outs = {}
+        with torch.inference_mode():
+            for s in steps:
+                o = rp.step(s)
+                if o is not None:
+                    outs[s["step"]] = o
+        got = schedules.collect(steps, outs)
+        for rid, rows in got.items():
+            tol = BF16_REL * float(np.abs(expected[rid]).max())
+            bad = schedules.first_bad({rid: rows}, expected, tol)
+            assert bad is None, (sched, page, bad, tol)
+    assert kernels.ops().tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sharp_attention_shows_a_wrong_key(tmp_path, dtype):
     """With query and key projections scaled up, each query puts nearly all its weight on one key,
