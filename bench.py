@@ -35,6 +35,7 @@ SHAPES = {
                        head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
                        tie_word_embeddings=False, max_position_embeddings=32768),
 }
+SHAPE_NAMES = {"qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B"}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -231,15 +232,15 @@ def run_ours(a) -> dict:
             eng.abort(rid)
         eng.step()
         # per step: the input arena (ids, positions, request index, starts, lengths, slots, rows, slot
-        # map, block tables) goes up; sampler parameters go up; tokens and flags come back
+        # map, block tables) goes up (greedy rows need no sampler parameters); tokens and flags come back
         width = runner.max_pages
-        h2d = 4 * (4 * B + (B + 1) + 3 * B + B * width) + B * (2 * 4 + 4 * 8)
+        h2d = 4 * (4 * B + (B + 1) + 3 * B + B * width)
         d2h = 2 * B * 4
         e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(1e3 * e2e_s / steps, 4)}
 
     return {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts, bf16)",
+        "metric": f"decode tok/s at batch {B} ({SHAPE_NAMES[a.model]} shape, {prompt_len:,}-token prompts, bf16)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, N(0,0.02) random weights", "impl": "ours",
@@ -312,7 +313,7 @@ def run_reference(a) -> dict:
             torch.cuda.synchronize()
             wall = time.perf_counter() - t0
         ms = e0.elapsed_time(e1) / steps
-        return {"metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts)",
+        return {"metric": f"decode tok/s at batch {B} ({SHAPE_NAMES[a.model]} shape, {prompt_len:,}-token prompts)",
                 "value": round(n_tok / (ms * steps / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
                 "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "fp16", "data": "synthetic: uniform random token ids, N(0,0.02) random weights",

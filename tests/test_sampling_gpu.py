@@ -34,6 +34,43 @@ def test_greedy_is_first_maximum():
     assert not bad.any()
 
 
+@pytest.mark.parametrize("S,V", [(1, 7), (8, 151936), (3, 4097), (64, 32000), (5, 262147)])
+def test_all_greedy_rows_take_the_many_block_path(S, V):
+    """A step whose rows are all greedy goes to the kernel that cuts each row into parts; it answers
+    as the one-block-per-row kernel does: first index of the maximum (ties across part edges, -inf
+    entries), a NaN or +inf anywhere flags the row, and repeated calls leave the counters clean."""
+    from turingserve_b200 import kernels
+    ops = kernels.ops()
+    g = torch.Generator().manual_seed(S * 1000 + V)
+    logits = torch.randn(S, V, generator=g)
+    parts = ops.lib.ts_sample_greedy_parts(V)
+    edge = -(-V // parts)
+    if V > 10:
+        logits[0, min(edge, V - 1)] = logits[0, min(edge, V - 1) - 1] = logits[0, 3] = 50.0     # a tie across a part edge
+        logits[S - 1, : V // 2] = float("-inf")
+    dev = logits.cuda()
+    s = Sampler("cuda")
+    for _ in range(3):
+        toks, bad = s.sample(dev, _rows([SamplingParams(temperature=0.0)] * S, [0] * S))
+        assert toks.tolist() == logits.argmax(-1).tolist() and not bad.any()
+    if V > 10:
+        assert toks[0] == 3
+    general = torch.empty((2, S), dtype=torch.int32, device="cuda")
+    ops.sample(general, dev, torch.zeros((S, 2), device="cuda"), torch.zeros((S, 4), dtype=torch.int64, device="cuda"))
+    assert general[0].cpu().tolist() == toks.tolist()
+    if S >= 3:
+        logits[1, V - 1] = float("inf")
+        logits[2, V // 3] = float("nan")
+        toks, bad = s.sample(logits.cuda(), _rows([SamplingParams(temperature=0.0)] * S, [0] * S))
+        assert bad.tolist() == [False, True, True] + [False] * (S - 3) and toks[1] == 0 and toks[2] == 0
+        assert toks[0] == logits[0].argmax()
+    # one row with a temperature: the whole step goes to the general kernel, greedy rows unchanged
+    mixed = [SamplingParams(temperature=0.0)] * (S - 1) + [SamplingParams(temperature=0.8)]
+    logits2 = torch.randn(S, V, generator=g)
+    toks2, _ = s.sample(logits2.cuda(), _rows(mixed, list(range(S))))
+    assert toks2[: S - 1].tolist() == logits2[: S - 1].argmax(-1).tolist()
+
+
 @pytest.mark.parametrize("V", [256, 301, 151936])
 def test_temperature_matches_plain(V):
     s = Sampler("cuda")

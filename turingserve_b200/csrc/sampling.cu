@@ -218,6 +218,69 @@ sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* 
   if (threadIdx.x == 0) tokens[row] = w.i;
 }
 
+// Greedy rows only: the row's vocabulary is cut into gridDim.x parts, one block each, so that a
+// handful of rows still reads at the speed of many SMs; the block that finishes last for a row
+// (a ticket counter: nobody waits) picks among the parts' candidates.  Same result as
+// sample_kernel with temperature 0: first index of the maximum, or token 0 and the bad flag when the
+// row holds a NaN or +inf.
+constexpr int GREEDY_THREADS = 256;
+
+__global__ void __launch_bounds__(GREEDY_THREADS)
+sample_greedy_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* __restrict__ logits, int V,
+                     float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ counters) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ Best best_s[32];
+  __shared__ int any_bad;
+  __shared__ int is_last;
+  const int row = blockIdx.y, part = blockIdx.x, P = gridDim.x;
+  const float* x = logits + (size_t)row * V;
+  const int len = (V + P - 1) / P;
+  const int lo = part * len, hi = min(V, lo + len);
+  if (threadIdx.x == 0) any_bad = 0;
+  __syncthreads();
+  Best b{-INFINITY, 0x7fffffff};
+  bool bad = false;
+  for (int i = lo + threadIdx.x; i < hi; i += GREEDY_THREADS) {
+    const float v = x[i];
+    if (isnan(v) || v == INFINITY) bad = true;
+    b = better(b, Best{v, i});
+  }
+  if (bad) any_bad = 1;
+  b = block_best(b, best_s);
+  if (threadIdx.x == 0) {
+    part_v[row * P + part] = b.v;
+    part_i[row * P + part] = any_bad ? -1 : b.i;          // -1: this part saw a bad value
+    __threadfence();
+    const int ticket = atomicAdd(&counters[row], 1);
+    is_last = (ticket == P - 1);
+    if (is_last) counters[row] = 0;                        // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last || threadIdx.x >= 32) return;
+  __threadfence();
+  Best w{-INFINITY, 0x7fffffff};
+  bool row_bad = false;
+  for (int p = threadIdx.x; p < P; p += 32) {
+    const float v = __ldcg(part_v + row * P + p);
+    const int i = __ldcg(part_i + row * P + p);
+    if (i < 0) row_bad = true;
+    else w = better(w, Best{v, i});
+  }
+  row_bad = __any_sync(0xffffffffu, row_bad);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, w.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, w.i, o);
+    w = better(w, y);
+  }
+  if (threadIdx.x == 0) {
+    tokens[row] = row_bad ? 0 : w.i;
+    bad_out[row] = row_bad ? 1 : 0;
+  }
+}
+
 // Logit edits.  meta[row] = {a, b, c, d}: ids[a:b] prompt tokens, ids[b:c] output tokens (both
 // empty when the row has no penalties), ids[c:d] tokens to mask to -inf.  pen[row] = {repetition,
 // presence, frequency}.  seen = prompt or output: logit > 0 ? logit / rep : logit * rep; then
@@ -276,6 +339,26 @@ TS_API int ts_sample(int* out, const float* logits, const float* fparams, const 
   if (S <= 0) return 0;
   if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample: vocabulary %d", V);
   ts_launch(sample_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, fparams, iparams, V);
+  TS_LAUNCH_CHECK();
+}
+
+// Parts a row is cut into by ts_sample_greedy: scratch holds 2 * S * parts 4-byte words, counters S
+// ints that are zero on entry (the kernel leaves them zero).
+TS_API int ts_sample_greedy_parts(int V) {
+  const int p = (V + 4095) / 4096;
+  return p < 1 ? 1 : (p > 64 ? 64 : p);
+}
+
+// Every row greedy: out[0:S] tokens, out[S:2S] bad flags, as ts_sample with temperature 0 gives them.
+TS_API int ts_sample_greedy(int* out, const float* logits, int S, int V, void* scratch, int* counters, void* stream) {
+  if (S <= 0) return 0;
+  if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample_greedy: vocabulary %d", V);
+  if (S > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_sample_greedy: %d rows", S);
+  if (scratch == nullptr || counters == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_sample_greedy: scratch and counters are needed");
+  const int P = ts_sample_greedy_parts(V);
+  float* pv = (float*)scratch;
+  int* pi = (int*)scratch + (size_t)S * P;
+  ts_launch(sample_greedy_kernel, dim3(P, S), dim3(GREEDY_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, V, pv, pi, counters);
   TS_LAUNCH_CHECK();
 }
 

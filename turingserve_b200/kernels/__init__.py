@@ -88,6 +88,7 @@ class CudaOps:
             "ts_feed_tokens": [P, P, P, P, I, I, P],
             "ts_sample": [P, P, P, P, I, I, P],
             "ts_penalize": [P, P, P, P, I, I, P],
+            "ts_sample_greedy": [P, P, I, I, P, P, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -105,6 +106,8 @@ class CudaOps:
         # tokens), "cp" the one built for the shortest chain, "auto" by the step's streaming_decode
         self.decode_kernel = os.environ.get("TURINGSERVE_B200_DECODE_ATTENTION", "auto")
         self.decode_stages = int(os.environ.get("TURINGSERVE_B200_DECODE_STAGES", "3"))
+        self.lib.ts_sample_greedy_parts.argtypes = [I]
+        self.lib.ts_sample_greedy_parts.restype = c_int
         self.lib.ts_rope_kv_write_fused_supported.argtypes = [I, I, I]
         self.lib.ts_rope_kv_write_fused_supported.restype = c_int
         self.lib.ts_linear_tc_supported.argtypes = [I, I, I]
@@ -132,6 +135,8 @@ class CudaOps:
         self._counters: torch.Tensor | None = None
         self._partials: torch.Tensor | None = None
         self._decode_slots: dict = {}
+        self._greedy_scratch: torch.Tensor | None = None
+        self._greedy_counters: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
         self.max_splits = 16        # the fused reduce kernels load up to 16 partial sums in one go
@@ -390,6 +395,17 @@ class CudaOps:
         S, V = logits.shape
         self._check(self.lib.ts_sample(_ptr(out), _ptr(logits), _ptr(fparams), _ptr(iparams), S, V,
                                        self._stream()), "sample")
+
+    def sample_greedy(self, out, logits) -> None:
+        """Every row greedy: the draw without parameters, each row spread over many blocks."""
+        S, V = logits.shape
+        need = 2 * S * self.lib.ts_sample_greedy_parts(V)
+        if self._greedy_scratch is None or self._greedy_scratch.numel() < need or self._greedy_scratch.device != logits.device:
+            self._greedy_scratch = torch.empty(max(need, 2 * 256 * 64), dtype=torch.int32, device=logits.device)
+        if self._greedy_counters is None or self._greedy_counters.numel() < S or self._greedy_counters.device != logits.device:
+            self._greedy_counters = torch.zeros(max(S, 1024), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.ts_sample_greedy(_ptr(out), _ptr(logits), S, V, _ptr(self._greedy_scratch),
+                                              _ptr(self._greedy_counters), self._stream()), "sample_greedy")
 
     def penalize(self, logits, ids, meta, pen) -> None:
         S, V = logits.shape

@@ -122,6 +122,11 @@ class Sampler:
         if any(r.params.uses_penalties or len(r.output_ids) < r.params.min_tokens for r in rows):
             logits = logits.clone()
             self._edit_logits(ops, logits, rows)
+        if all(r.params.greedy for r in rows) and hasattr(ops, "sample_greedy"):
+            # no parameters to send, and the rows spread over many blocks instead of one each
+            out = torch.empty((2, S), dtype=torch.int32, device=dev)
+            ops.sample_greedy(out, logits)
+            return self._copy_out(out, S)
         fh, ih = self._param_buffers(S)
         f, i = fh.numpy()[:S], ih.numpy()[:S]
         f[:] = 0
@@ -138,10 +143,13 @@ class Sampler:
         self._param_copied()
         out = torch.empty((2, S), dtype=torch.int32, device=dev)
         ops.sample(out, logits, fp, ip)
+        return self._copy_out(out, S)
+
+    def _copy_out(self, out: torch.Tensor, S: int) -> PendingSample:
         host = self._host_buffer(S)
         host.copy_(out, non_blocking=True)             # the one device-to-host copy of the step
         event = None
-        if dev.type == "cuda":
+        if self.device.type == "cuda":
             event = torch.cuda.Event()
             event.record()
         return PendingSample(out, host, event, S)
