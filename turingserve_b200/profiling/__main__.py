@@ -4,6 +4,7 @@ capture that ends by itself (a few hundred MB on the device, a few dozen launche
     python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048] [--page 16] [--graph]
     python -m turingserve_b200.profiling prefill_attention [--tokens 2048] [--page 16]
     python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library]
+    python -m turingserve_b200.profiling timeline [--batch 8] [--context 2048] [--layers 28]
 
 Each prints the launches it made and, timed with CUDA events, the mean time per launch.
 """
@@ -122,6 +123,74 @@ def gemm(a) -> None:
           f"{2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
 
 
+def timeline(a) -> None:
+    """Where a captured decode step's time goes: every kernel of one graph replay with the moment
+    it ended (CUPTI through torch.profiler), and per kernel the increment of the end time over the
+    kernel that ended before it.  With programmatic dependent launch kernels start long before
+    their predecessor ends, so durations overlap; the end-time increments add up to the step."""
+    import collections
+    import re
+    import tempfile
+
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+
+    from turingserve_b200 import EngineConfig, LLMEngine, SamplingParams
+    from turingserve_b200.models.qwen2 import make_config
+    from turingserve_b200.weights.random_init import write_random_model
+
+    B, ctx = a.batch, a.context
+    with tempfile.TemporaryDirectory() as tmp:
+        write_random_model(tmp, make_config(hidden_size=1536, intermediate_size=8960, num_layers=a.layers, num_heads=H,
+                                            num_kv_heads=KVH, head_dim=D, vocab_size=151936, rope_theta=1e6,
+                                            rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768), seed=0)
+        eng = LLMEngine.from_config(EngineConfig(model=tmp, dtype="bfloat16", max_model_len=2 * ctx,
+                                                 num_blocks=B * (2 * ctx // 64) + 8, max_num_seqs=B,
+                                                 max_num_batched_tokens=max(2048, B), graph_batch_sizes=(B,), watermark=0.0))
+    rng = np.random.default_rng(0)
+    params = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    for i in range(B):
+        eng.add_request(f"r{i}", rng.integers(0, 151936, size=ctx).tolist(), params)
+    while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
+        eng.step()
+    for _ in range(8):
+        eng.step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(5):
+            eng.step()
+        torch.cuda.synchronize()
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                 key=lambda e: e.time_range.start)
+    firsts = [i for i, e in enumerate(evs) if "embedding_kernel" in e.name]
+    step = sorted(evs[firsts[2]:firsts[3]], key=lambda e: e.time_range.end)
+
+    def short(name: str) -> str:
+        m = re.search(r"(gemm_tc_kernel<[^>]*>|attention_\w+_kernel|reduce_rmsnorm_kernel|rope_kv_write\w*|rmsnorm\w*|"
+                      r"silu_mul\w*|embedding_kernel|gather_rows_kernel|feed_tokens_kernel|sample\w*|splitk_reduce_kernel|"
+                      r"Memcpy \w+|nvjet\w*)", name)
+        return m.group(1) if m else name[:50]
+
+    t0 = min(e.time_range.start for e in step)
+    prev, share, rows = t0, collections.OrderedDict(), []
+    for e in step:
+        d = e.time_range.end - prev
+        prev = e.time_range.end
+        n = short(e.name)
+        share.setdefault(n, [0, 0.0])
+        share[n][0] += 1
+        share[n][1] += d
+        rows.append((e.time_range.start - t0, e.time_range.end - t0, d, n))
+    print(f"timeline batch {B} context {ctx} layers {a.layers}: one step = {prev - t0:.1f} us, {len(step)} kernels and copies")
+    print("end-time increments, summed per kernel:")
+    for n, (c, d) in sorted(share.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {d:8.1f} us  {c:4d} x {d / c:6.2f}  {n}")
+    print("second layer (start, end, increment):")
+    per_layer = (len(step) - 10) // max(a.layers, 1)
+    for r in rows[3 + per_layer: 3 + 2 * per_layer]:
+        print(f"  {r[0]:8.2f} {r[1]:8.2f}  +{r[2]:5.2f}  {r[3]}")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(prog="python -m turingserve_b200.profiling")
     sub = ap.add_subparsers(dest="workload", required=True)
@@ -138,8 +207,13 @@ def main() -> int:
     s.add_argument("--n", type=int, default=17920)
     s.add_argument("--k", type=int, default=1536)
     s.add_argument("--mode", default="auto", choices=["auto", "tc", "library"])
+    s = sub.add_parser("timeline")
+    s.add_argument("--batch", type=int, default=8)
+    s.add_argument("--context", type=int, default=2048)
+    s.add_argument("--layers", type=int, default=28)
     a = ap.parse_args()
-    {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm": gemm}[a.workload](a)
+    {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm": gemm,
+     "timeline": timeline}[a.workload](a)
     return 0
 
 
