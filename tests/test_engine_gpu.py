@@ -104,6 +104,35 @@ def test_cuda_graphs_and_look_ahead_do_not_change_tokens(tmp_path):
     assert stopped[True][2][0] == base[2][:base[2].index(stop) + 1]
 
 
+def test_decode_kernel_choice_switches_inside_a_generation(tmp_path, monkeypatch):
+    """The keys under the decode rows grow past the point where the streaming (TMA) decode-attention
+    kernel takes over from the short-chain one, in the middle of a generation and with captured
+    graphs (one graph per batch size and choice): the tokens are those of the generated text's own
+    best next tokens under the plain implementation, and the pool is clean afterwards."""
+    from turingserve_b200 import SamplingParams, kernels
+    from turingserve_b200.engine import batch, runner
+    folder = tiny.make_tiny_folder("K", tmp_path)
+    cfg, w = plain.read_folder(folder)
+    prompts = [tiny.random_ids(n, cfg["vocab_size"], 60 + n) for n in (70, 5, 130, 33)]
+    # 4 requests: below the threshold while the longest context is under 150 keys, above from there on
+    monkeypatch.setattr(batch, "STREAMING_DECODE_KEYS", 600)
+    seen = set()
+    real = runner._DecodeGraph.__init__
+
+    def spy(self, r, size, streaming):
+        seen.add((size, streaming))
+        real(self, r, size, streaming)
+    monkeypatch.setattr(runner._DecodeGraph, "__init__", spy)
+    kernels.use(None)
+    eng = engine(folder, "bfloat16", cuda_graphs=True, graph_batch_sizes=(1, 2, 4), max_num_seqs=4)
+    outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)] * 4)
+    assert not eng.cache.live
+    assert (4, False) in seen and (4, True) in seen, seen
+    for p, o in zip(prompts, outs):
+        tokens_are_best(cfg, w, p, o.token_ids, 0.05)
+    assert kernels.ops().tc_status() == 0
+
+
 def test_entry_points_and_command_line(tmp_path):
     import turingserve_b200
     folder = tiny.make_tiny_folder("W", tmp_path)
