@@ -9,9 +9,13 @@
 // Work split: one block per (key split, kv head, request).  The request's keys are seen as tiles
 // of 64 at absolute positions (tile i holds keys 64i .. 64i+63); the tiles that hold visible keys
 // are dealt out evenly over the splits that get at least one, and the remaining splits leave at
-// once.  Inside a block one producer warp issues TMA box copies (16 keys x 64 columns, 128-byte
-// swizzle) into a ring of stages and four consumer warps each take WHOLE tiles (the tiles of stage
-// s go to warp s % 4): a warp waits for its tile's mbarrier, computes S = Q K^T for 16 x 64 with
+// once.  Inside a block one producer warp issues TMA copies, ONE per box: a box is the keys AND the
+// values of one page (or of 64 keys where pages are larger), all head columns, through a 4-D tensor
+// map over both caches with the 128-byte swizzle; a copy costs the TMA unit about 100 cycles
+// whatever its size, so fewer and larger ones matter.  The boxes go into a ring of stages
+// (2..8; three by default, which lets two blocks share an SM) and min(4, stages) consumer warps each
+// take WHOLE tiles (the tiles of stage s go to warp s % warps, so that a stage's barriers are waited
+// on by one warp, phase after phase): a warp waits for its tile's mbarrier, computes S = Q K^T for 16 x 64 with
 // mma.sync m16n8k16 (the G heads in the 16 rows), one online-softmax update per 64 keys, then
 // O += P V, and hands the stage back.  No block-wide barrier and no per-thread address
 // arithmetic in the loop.  The warps' states merge through shared memory; with several splits the
