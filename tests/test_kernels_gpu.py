@@ -160,6 +160,43 @@ def test_rope_kv_write(ops, dtype, H, KVH, D, rot, T):
     torch.testing.assert_close(q_d2.cpu().float(), q_r.float(), **tol)
 
 
+@pytest.mark.parametrize("T", [1, 3, 8, 16, 40, 128])
+@pytest.mark.parametrize("H,KVH,K,bias", [(12, 2, 1536, True), (4, 2, 192, True), (5, 1, 200, False), (28, 4, 3584, True)])
+def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, T, H, KVH, K, bias):
+    """The q/k/v product of a few tokens with heads of 128 finishes itself (split sums, bias,
+    rotation, cache write in its epilogue): bit for bit what the product followed by the rotary
+    kernel gives, in the q/k/v tensor and in the cache pages."""
+    D, page, pages = 128, 16, 40
+    N = (H + 2 * KVH) * D
+    x = _rand((T, K), torch.bfloat16, 50, 1.0).cuda()
+    w = _rand((N, K), torch.bfloat16, 51, 0.05).cuda()
+    b = _rand((N,), torch.bfloat16, 52, 0.5).cuda() if bias else None
+    pos = torch.randint(0, 600, (T,), dtype=torch.int32)
+    cos, sin = plain.rope_tables(D, 1e6, 600)
+    slots = (torch.randperm(page * (pages - 1))[:T].to(torch.int32) + page)
+    if T > 2:
+        slots[1] = -1
+    kc0, vc0 = _rand((pages, KVH, page, D), torch.bfloat16, 53), _rand((pages, KVH, page, D), torch.bfloat16, 54)
+    got = {}
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "fused_qkv_tokens", 128 if fused else 0)
+        kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
+        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        launches = ops.launches
+        for _ in range(2):                                         # twice: the counters come back to zero
+            q = ops.qkv_rope(out, x, w, b, pos.cuda(), cos.cuda(), sin.cuda(), H, KVH, D, D, kc, vc, slots.cuda(), page)
+        assert (ops.launches - launches == 2) == fused
+        got[fused] = (q.clone(), kc, vc)
+    for a, c in zip(got[True], got[False]):
+        assert torch.equal(a, c)
+    # rotate only (a run that reads another run's cache): no cache write
+    monkeypatch.setattr(ops, "fused_qkv_tokens", 128)
+    out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    q = ops.qkv_rope(out, x, w, b, pos.cuda(), cos.cuda(), sin.cuda(), H, KVH, D, D, None, None, slots.cuda(), page)
+    assert torch.equal(q, got[True][0])
+    assert ops.tc_status() == 0
+
+
 def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None):
     """Random q/k/v for several requests, laid into a shuffled paged cache."""
     g = torch.Generator().manual_seed(seed)

@@ -47,6 +47,11 @@ class TwinOps:
         self.linear(gu, x, w, bias)
         self.silu_mul(out, gu, group)
 
+    def qkv_rope(self, out, x, w, bias, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
+                 page_size):
+        self.linear(out, x, w, bias)
+        return self.rope_kv_write(out, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots, page_size)
+
     def rope_kv_write(self, qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                       page_size):
         T = qkv.shape[0]

@@ -35,6 +35,20 @@ struct GemmArgs {
   int out_is_float;
   int gated;              // weights-on-rows only: the tile's rows are 64 gates then 64 ups; out is bf16 [M, N / 2]
   int* status;
+  // weights-on-rows q/k/v product that finishes itself (rope != 0): a tile is one head of 128; every
+  // block leaves its partial sums in rope_part, the block that comes last for a tile (ticket counter)
+  // adds them up in split order, adds the bias, rotates q and k heads and writes q/k/v to `out` and the
+  // new keys and values into the cache pages: what ts_rope_kv_write_ex does in a kernel of its own.
+  int rope;
+  float* rope_part;       // [tiles][token blocks][splits][BN][128]
+  int* rope_counters;     // [tiles][token blocks], zero on entry and on exit
+  const int* positions;
+  const float* cos_t;     // [positions][64]
+  const float* sin_t;
+  const int* slots;       // cache slot of every token, < 0: not written
+  bf16* k_cache;
+  bf16* v_cache;
+  int page, H, KVH;
 };
 
 // BN: tile columns (UMMA N).  SWAP: the tile rows are weight rows (outputs), columns are tokens.
@@ -56,6 +70,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,7 +170,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     pdl_wait();                                    // nothing is written before the predecessor is done
     bool ok = n_kb > 0 && mbar_wait(accum, 0, args.status, 3, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    if (SWAP && args.gated) {
+    if (SWAP && args.rope) {
+      constexpr int CW = BN >= 32 ? 32 : 16;
+      const int slot_id = blockIdx.x * gridDim.y + blockIdx.y;
+      float* mine = args.rope_part + ((size_t)slot_id * args.splits + blockIdx.z) * BN * 128;
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+          if constexpr (CW == 32) {
+            tmem_ld32(taddr, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld16(taddr, v16);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v16[i];
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < CW; ++i)
+            if (col0 + c + i < args.M) mine[(size_t)(c + i) * 128 + r] = __uint_as_float(v[i]);
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (r == 0) {
+        const int ticket = atomicAdd(&args.rope_counters[slot_id], 1);
+        *last_flag = (ticket == args.splits - 1);
+        if (ticket == args.splits - 1) args.rope_counters[slot_id] = 0;      // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        const int head = blockIdx.x;                           // a tile is a head: q heads, then k, then v
+        const int p = r & 63, tg = r >> 6;                     // the pair (p, p + 64) of tokens tg, tg + 2, ...
+        const float* base = args.rope_part + (size_t)slot_id * args.splits * BN * 128;
+        const int N = args.N;
+        const float b1 = args.bias != nullptr ? to_f(args.bias[head * 128 + p]) : 0.f;
+        const float b2 = args.bias != nullptr ? to_f(args.bias[head * 128 + p + 64]) : 0.f;
+        const bool rotate = head < args.H + args.KVH;
+        bf16* qkv = reinterpret_cast<bf16*>(args.out);
+        const int tokens = min(BN, args.M - col0);
+        for (int tok = tg; tok < tokens; tok += 2) {
+          float lo[16], hi[16];
+#pragma unroll
+          for (int sp = 0; sp < 16; ++sp)
+            if (sp < args.splits) {
+              lo[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + p);
+              hi[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + p + 64);
+            }
+          float x1 = 0.f, x2 = 0.f;
+#pragma unroll
+          for (int sp = 0; sp < 16; ++sp)
+            if (sp < args.splits) {
+              x1 += lo[sp];
+              x2 += hi[sp];
+            }
+          x1 = round_to<bf16>(x1 + b1);
+          x2 = round_to<bf16>(x2 + b2);
+          const int m = col0 + tok;
+          float o1 = x1, o2 = x2;
+          if (rotate) {
+            const int pos = args.positions[m];
+            const float cs = round_to<bf16>(args.cos_t[(size_t)pos * 64 + p]);
+            const float sn = round_to<bf16>(args.sin_t[(size_t)pos * 64 + p]);
+            o1 = x1 * cs - x2 * sn;
+            o2 = x2 * cs + x1 * sn;
+          }
+          const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
+          qkv[(size_t)m * N + head * 128 + p] = w1;
+          qkv[(size_t)m * N + head * 128 + p + 64] = w2;
+          if (head >= args.H && args.k_cache != nullptr) {
+            const int slot = args.slots[m];
+            if (slot >= 0) {
+              const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * 128;
+              const bool is_k = head < args.H + args.KVH;
+              bf16* dst = (is_k ? args.k_cache : args.v_cache) + cache_base +
+                          (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * 128;
+              dst[p] = w1;
+              dst[p + 64] = w2;
+            }
+          }
+        }
+      }
+    } else if (SWAP && args.gated) {
       // act[m, 64 * tile + i] = bf16(silu(bf16(gate_i))) * bf16(up_i): the roundings of the unfused
       // path (product rounded to bfloat16, then the activation kernel's).  The up rows (lanes
       // 64..127) go through shared memory to the threads that hold the gate rows; the stage
@@ -303,7 +403,7 @@ int* status_word() {
 
 template <int BN, int STAGES, bool SWAP, int KSUB = 1>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmArgs& args, dim3 grid, cudaStream_t s) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -359,6 +459,7 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
   a.M = M; a.N = N; a.K = K;
   a.out_is_float = out_is_float;
   a.gated = 0;
+  a.rope = 0;
   a.status = status;
   const bool swap = M <= 128;
   if (!swap) splits = 1;
@@ -426,6 +527,7 @@ TS_API int ts_linear_tc_gated(void* act, const void* x, const void* w, int M, in
   a.M = M; a.N = N2; a.K = K;
   a.out_is_float = 0;
   a.gated = 1;
+  a.rope = 0;
   a.status = status;
   a.k_blocks_per_split = ceil_div(K, BK);
   a.splits = 1;
@@ -434,6 +536,71 @@ TS_API int ts_linear_tc_gated(void* act, const void* x, const void* w, int M, in
   if (!tensor_map(&rows_map, w, N2, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_gated: cuTensorMapEncodeTiled failed");
   dim3 grid(N2 / BM, ceil_div(M, bn), 1);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 16) return launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
+  if (bn == 32) return launch<32, 4, true>(rows_map, cols_map, a, grid, s);
+  if (bn == 64) return launch<64, 4, true>(rows_map, cols_map, a, grid, s);
+  return launch<128, 4, true>(rows_map, cols_map, a, grid, s);
+}
+
+// Floats of scratch for ts_linear_tc_qkv_rope.
+TS_API long long ts_linear_tc_qkv_rope_scratch_floats(int M, int heads, int splits) {
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  return (long long)heads * ceil_div(M, bn) * splits * bn * 128;
+}
+
+// qkv[M, (H + 2 KVH) * 128] = x[M, K] . w^T + bias with q and k heads rotated (full-width rotate-half,
+// tables [positions][64] float, rounded to bfloat16 at use) and the new keys and values written into
+// the cache pages (slot < 0: not written; k_cache null: no cache write), all in the product's own
+// epilogue.  Head size 128, at most 128 tokens, up to 16 splits over K.  `scratch` holds
+// ts_linear_tc_qkv_rope_scratch_floats() floats, `counters` one zero int per (head, block of tokens).
+TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const void* bias, void* scratch, int* counters,
+                                 const int* positions, const float* cos_t, const float* sin_t, const int* slots,
+                                 void* k_cache, void* v_cache, int M, int H, int KVH, int page, int K, int splits,
+                                 void* stream) {
+  if (M <= 0) return 0;
+  const int heads = H + 2 * KVH, N = heads * 128;
+  if (M > 128 || H <= 0 || KVH <= 0 || !ts_linear_tc_supported(M, N, K))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: M=%d heads=%d K=%d is not taken by this kernel", M, heads, K);
+  if (scratch == nullptr || counters == nullptr || positions == nullptr || cos_t == nullptr || sin_t == nullptr)
+    TS_REFUSE(TS_ERR_SHAPE, "ts_linear_tc_qkv_rope: scratch, counters, positions and tables are needed");
+  if (k_cache != nullptr && (v_cache == nullptr || slots == nullptr || page <= 0))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_linear_tc_qkv_rope: the cache write needs both caches, slots and the page size");
+  if (((uintptr_t)x | (uintptr_t)w) & 15) TS_REFUSE(TS_ERR_ALIGN, "ts_linear_tc_qkv_rope: operands must be 16-byte aligned");
+  int* status = status_word();
+  if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_linear_tc_qkv_rope: no status word");
+  const int total_kb = ceil_div(K, BK);
+  if (splits < 1) splits = 1;
+  if (splits > 16) splits = 16;
+  if (splits > total_kb) splits = total_kb;
+  const int per = ceil_div(total_kb, splits);
+  splits = ceil_div(total_kb, per);
+  GemmArgs a;
+  a.out = qkv;
+  a.bias = (const bf16*)bias;
+  a.M = M; a.N = N; a.K = K;
+  a.out_is_float = 0;
+  a.gated = 0;
+  a.rope = 1;
+  a.status = status;
+  a.k_blocks_per_split = per;
+  a.splits = splits;
+  a.rope_part = (float*)scratch;
+  a.rope_counters = counters;
+  a.positions = positions;
+  a.cos_t = cos_t;
+  a.sin_t = sin_t;
+  a.slots = slots;
+  a.k_cache = (bf16*)k_cache;
+  a.v_cache = (bf16*)v_cache;
+  a.page = page;
+  a.H = H;
+  a.KVH = KVH;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap rows_map, cols_map;
+  if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: cuTensorMapEncodeTiled failed");
+  dim3 grid(heads, ceil_div(M, bn), splits);
   cudaStream_t s = (cudaStream_t)stream;
   if (bn == 16) return launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
   if (bn == 32) return launch<32, 4, true>(rows_map, cols_map, a, grid, s);

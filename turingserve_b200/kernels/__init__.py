@@ -74,6 +74,7 @@ class CudaOps:
             "ts_silu_mul": [P, P, I, I, I, P],
             "ts_silu_mul_ex": [P, P, I, I, I, I, P],
             "ts_linear_tc_gated": [P, P, P, I, I, I, P],
+            "ts_linear_tc_qkv_rope": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write_ex": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
@@ -106,6 +107,8 @@ class CudaOps:
         # tokens), "cp" the one built for the shortest chain, "auto" by the step's streaming_decode
         self.decode_kernel = os.environ.get("TURINGSERVE_B200_DECODE_ATTENTION", "auto")
         self.decode_stages = int(os.environ.get("TURINGSERVE_B200_DECODE_STAGES", "3"))
+        self.lib.ts_linear_tc_qkv_rope_scratch_floats.argtypes = [I, I, I]
+        self.lib.ts_linear_tc_qkv_rope_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_sample_greedy_parts.argtypes = [I]
         self.lib.ts_sample_greedy_parts.restype = c_int
         self.lib.ts_rope_kv_write_fused_supported.argtypes = [I, I, I]
@@ -136,6 +139,8 @@ class CudaOps:
         self._partials: torch.Tensor | None = None
         self._decode_slots: dict = {}
         self._greedy_scratch: torch.Tensor | None = None
+        self._qkv_part: torch.Tensor | None = None
+        self._qkv_counters: torch.Tensor | None = None
         self._greedy_counters: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
@@ -233,6 +238,37 @@ class CudaOps:
             _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
             T, H, KVH, D, rotary_dim, page_size, _code(qkv.dtype), self._stream()), "rope_kv_write")
         return qkv
+
+    # up to this many tokens the q/k/v product finishes itself (sum over its splits, bias, rotation,
+    # cache write in the epilogue of the block that comes last for a head) instead of leaving that to the
+    # rotary kernel
+    fused_qkv_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_QKV_TOKENS", "16"))
+
+    def qkv_rope(self, out, x, w, bias, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
+                 page_size):
+        """out[T, (H + 2 KVH) D] = x @ w^T + bias with q and k rotated, and the new keys and values
+        written to the cache: one kernel for a few bfloat16 tokens with heads of 128 rotated over
+        their full width, otherwise the product and then ``rope_kv_write``.  Returns the q/k/v tensor."""
+        T, K = x.shape[0], w.shape[1]
+        use_tc = self.gemm_mode == "tc" or (self.gemm_mode == "auto" and T <= 128)
+        if (x.dtype == torch.bfloat16 and use_tc and T <= self.fused_qkv_tokens and D == 128 and rotary_dim == D
+                and cos is not None and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and self.lib.ts_linear_tc_supported(T, (H + 2 * KVH) * D, K)):
+            splits = self.tc_splits(T, (H + 2 * KVH) * D, K)
+            need = self.lib.ts_linear_tc_qkv_rope_scratch_floats(T, H + 2 * KVH, splits)
+            if self._qkv_part is None or self._qkv_part.numel() < need or self._qkv_part.device != x.device:
+                self._qkv_part = torch.empty(max(int(need), 1 << 18), dtype=torch.float32, device=x.device)
+                self._qkv_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
+            if (H + 2 * KVH) * -(-T // 16) <= self._qkv_counters.numel():
+                rc = self.lib.ts_linear_tc_qkv_rope(
+                    _ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(self._qkv_part), _ptr(self._qkv_counters),
+                    _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), T, H, KVH,
+                    page_size, K, splits, self._stream())
+                if rc != self.UNSUPPORTED:
+                    self._check(rc, "linear_tc_qkv_rope")
+                    return out
+        qkv = self.linear(out, x, w, bias, may_defer=True)
+        return self.rope_kv_write(qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots, page_size)
 
     def scratch(self, floats: int, device) -> torch.Tensor:
         """A float32 work buffer of at least ``floats`` elements, kept between calls."""

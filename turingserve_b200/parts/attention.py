@@ -57,12 +57,11 @@ class Attention(Mixer):
         ops = kernels.ops()
         T = x.shape[0]
         qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
-        qkv = ops.linear(qkv, x, self.w_qkv, self.b_qkv, may_defer=True)
         grp = step.groups[cache.group]
         pos = self.position
-        qkv = ops.rope_kv_write(
-            qkv, step.positions, None if pos is None else pos.cos, None if pos is None else pos.sin,
-            self.H, self.KVH, self.D, 0 if pos is None else pos.rotary_dim,
+        qkv = ops.qkv_rope(
+            qkv, x, self.w_qkv, self.b_qkv, step.positions, None if pos is None else pos.cos,
+            None if pos is None else pos.sin, self.H, self.KVH, self.D, 0 if pos is None else pos.rotary_dim,
             cache.k if cache.writable else None, cache.v if cache.writable else None,
             grp.slot_mapping, cache.page_size)
         attn = torch.empty((T, self.q_dim), dtype=x.dtype, device=x.device)
