@@ -133,7 +133,8 @@ class CudaOps:
         self.lib.ts_attention_prefill_supported.restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
-        self.num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self._device_index = torch.cuda.current_device()
+        self.num_sms = torch.cuda.get_device_properties(self._device_index).multi_processor_count
         self._scratch: torch.Tensor | None = None
         self._counters: torch.Tensor | None = None
         self._partials: torch.Tensor | None = None
@@ -148,9 +149,10 @@ class CudaOps:
         self.launches = 0           # kernels of this library launched (graph replays add their share)
 
     # -- plumbing -----------------------------------------------------------------------------------
-    @staticmethod
-    def _stream() -> int:
-        return torch.cuda.current_stream().cuda_stream
+    def _stream(self) -> int:
+        # the raw handle of the current stream: a tenth of the cost of building a torch.cuda.Stream
+        # object for it, and every kernel launch asks
+        return torch._C._cuda_getCurrentRawStream(self._device_index)
 
     def _check(self, rc: int, what: str) -> None:
         self.launches += 1
