@@ -491,7 +491,7 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
     if (bn == 16 && waves) rc = launch<16, 3, true, 2>(rows_map, cols_map, a, grid, s);
     else if (bn == 16) rc = launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
     else if (bn == 32) rc = launch<32, 4, true>(rows_map, cols_map, a, grid, s);
-    else if (bn == 64) rc = launch<64, 4, true>(rows_map, cols_map, a, grid, s);
+    else if (bn == 64) rc = launch<64, 4, true, 2>(rows_map, cols_map, a, grid, s);
     else rc = launch<128, 4, true>(rows_map, cols_map, a, grid, s);
   } else {
     if (!tensor_map(&rows_map, x, M, K, BM) || !tensor_map(&cols_map, w, N, K, 256))
