@@ -26,10 +26,11 @@ def _requests(name, cfg, lengths):
     return {f"r{i}": tiny.random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(lengths)}
 
 
-LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31]}
+LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31],
+           "X": [2, 33, 100, 64, 7, 129]}
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "X"])
 @pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed"])
 def test_schedules_match_plain(tmp_path, twin_ops, name, schedule):
     folder = tiny.make_tiny_folder(name, tmp_path)

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LENGTHS = {"A": [5, 17, 33, 70, 41, 64], "B": [1, 9, 40, 70, 97, 33], "W": [3, 50, 77, 120, 64, 31],
-           "K": [5, 130, 200, 70, 257, 64], "L": [3, 150, 77, 260, 128, 31]}
+           "K": [5, 130, 200, 70, 257, 64], "L": [3, 150, 77, 260, 128, 31], "X": [2, 33, 100, 64, 7, 129]}
 # float32: the reference's own bound for logits (tests/correctness/test_vs_hf.py:40-48).
 # bfloat16: 8 bits of mantissa; logits of these models reach |2.5|; the bound is 3% of the largest
 # expected logit of the request, about eight bfloat16 roundings.
@@ -71,7 +71,7 @@ def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True
 
 @pytest.mark.parametrize("dtype,gemm", [("float32", "library"), ("bfloat16", "library"), ("bfloat16", "auto"),
                                         ("bfloat16", "tc")])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "X"])
 @pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed"])
 def test_schedules_match_plain(tmp_path, name, schedule, dtype, gemm):
     """``gemm``: which bfloat16 products run on this library's tcgen05 kernel (none, the few-token

@@ -34,6 +34,11 @@ TINY = {
     "L": (dict(hidden_size=160, intermediate_size=272, num_layers=3, num_heads=9, num_kv_heads=3,
                head_dim=64, vocab_size=333, rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=False,
                max_position_embeddings=512, sliding_window=70, max_window_layers=1), 4, 32, 0.03),
+    # sizes in steps of 16 that nothing else has: heads of 80, a width, a feed-forward width and a
+    # vocabulary that are odd multiples, more key/value heads than groups
+    "X": (dict(hidden_size=208, intermediate_size=136, num_layers=2, num_heads=6, num_kv_heads=3,
+               head_dim=80, vocab_size=1001, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+               max_position_embeddings=256), 5, 32, 0.04),
 }
 
 
