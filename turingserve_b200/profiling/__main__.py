@@ -3,7 +3,7 @@ capture that ends by itself (a few hundred MB on the device, a few dozen launche
 
     python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048] [--page 16] [--graph]
     python -m turingserve_b200.profiling prefill_attention [--tokens 2048] [--page 16]
-    python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library]
+    python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated] [--graph]
     python -m turingserve_b200.profiling timeline [--batch 8] [--context 2048] [--layers 28]
 
 Each prints the launches it made and, timed with CUDA events, the mean time per launch.
@@ -113,14 +113,27 @@ def gemm(a) -> None:
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
 
+    act = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+
     def f(i):
-        ops.linear(out, x, ws[i % copies], None)
+        if a.gated:                                               # block-interleaved gate/up rows, SiLU*mul in the epilogue
+            ops.gated_linear(act, x, ws[i % copies], None, 64)
+        else:
+            ops.linear(out, x, ws[i % copies], None)
 
     for i in range(copies):
         f(i)
-    us = timed(f, 3 * copies)
-    print(f"gemm {M}x{N}x{K} mode {a.mode}: {us:.2f} us per launch, {N * K * 2 / us / 1e6:.2f} TB/s of weights, "
-          f"{2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
+    if a.graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(copies):
+                f(i)
+        g.replay()
+        us = timed(lambda i: g.replay(), 5) / copies
+    else:
+        us = timed(f, 3 * copies)
+    print(f"gemm {M}x{N}x{K} mode {a.mode}{' gated' if a.gated else ''}{' (graph)' if a.graph else ''}: {us:.2f} us per launch, "
+          f"{N * K * 2 / us / 1e6:.2f} TB/s of weights, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
 
 
 def timeline(a) -> None:
@@ -207,6 +220,8 @@ def main() -> int:
     s.add_argument("--n", type=int, default=17920)
     s.add_argument("--k", type=int, default=1536)
     s.add_argument("--mode", default="auto", choices=["auto", "tc", "library"])
+    s.add_argument("--gated", action="store_true", help="gate/up product with the activation in its epilogue")
+    s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
     s = sub.add_parser("timeline")
     s.add_argument("--batch", type=int, default=8)
     s.add_argument("--context", type=int, default=2048)
