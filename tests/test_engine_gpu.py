@@ -179,6 +179,51 @@ def test_preemption_on_the_gpu_gives_the_same_tokens(tmp_path):
     assert small_eng.scheduler.num_preemptions > 0
 
 
+@pytest.mark.parametrize("name,seed", [("K", 0), ("K", 1), ("L", 2)])
+def test_random_serving_workload_on_the_fast_kernels(tmp_path, monkeypatch, name, seed):
+    """Everything at once, on the models whose shapes the tensor-core and TMA kernels take: a dozen
+    requests of random length and budget, added while others run, prompts cut into portions,
+    a pool so small that requests are preempted and recomputed, graphs and look-ahead on, the
+    decode-attention choice flipping as contexts grow.  Every produced token is (within bfloat16
+    slack) the plain implementation's best next token for the text so far, nothing is lost, and
+    the pool is whole afterwards."""
+    from turingserve_b200 import SamplingParams, kernels
+    from turingserve_b200.engine import batch
+    rng = np.random.default_rng(seed)
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    cfg, w = plain.read_folder(folder)
+    monkeypatch.setattr(batch, "STREAMING_DECODE_KEYS", 900)
+    page = tiny.page_size(name)
+    n = 12
+    lens = [int(x) for x in rng.integers(3, 200, size=n)]
+    budgets = [int(x) for x in rng.integers(10, 60, size=n)]
+    prompts = [tiny.random_ids(L, cfg["vocab_size"], 500 + 13 * seed + i) for i, L in enumerate(lens)]
+    eng = engine(folder, "bfloat16", cuda_graphs=True, graph_batch_sizes=(1, 2, 4, 8), max_num_seqs=8,
+                 max_num_batched_tokens=96, block_size=page, num_blocks=(512 // page) + 1, max_model_len=320,
+                 watermark=0.0)
+    done, got, added, steps = {}, {}, 0, 0
+    while len(done) < n:
+        while added < n and (steps % 3 == 0 or not eng.requests):          # arrivals in the middle of decoding
+            eng.add_request(f"q{added}", prompts[added],
+                            SamplingParams(temperature=0.0, max_tokens=budgets[added], ignore_eos=True))
+            added += 1
+            if steps % 3:
+                break
+        for o in eng.step():
+            got.setdefault(o.request_id, []).extend(o.delta_token_ids)
+            if o.finished:
+                done[o.request_id] = o
+        steps += 1
+        assert steps < 4000
+    assert not eng.cache.live and eng.cache.min_free() == eng.cache.num_pages - 1
+    assert eng.scheduler.num_preemptions > 0, "the pool was meant to run out"
+    for i in range(n):
+        o = done[f"q{i}"]
+        assert o.finish_reason == "length" and o.completion_tokens == budgets[i] == len(got[f"q{i}"])
+        tokens_are_best(cfg, w, prompts[i], got[f"q{i}"], 0.06)
+    assert kernels.ops().tc_status() == 0
+
+
 def test_seeded_sampling_is_reproducible_alone_and_in_a_batch(tmp_path):
     from turingserve_b200 import SamplingParams
     folder = tiny.make_tiny_folder("B", tmp_path)
