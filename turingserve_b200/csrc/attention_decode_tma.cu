@@ -204,30 +204,45 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
-    const int g = idx / D, d = idx % D;
+  // each warp's weight 2^(m_w - M) and the block's (M, L), once per head; then 16 bytes a thread
+  float* f_s = o_s + CWARPS * 16 * D;                              // [CWARPS][16]
+  float* M_s = f_s + CWARPS * 16;                                  // [16]
+  float* L_s = M_s + 16;                                           // [16]
+  if ((int)threadIdx.x < cw * G) {
+    const int v = threadIdx.x / G, g = threadIdx.x % G;
     float M = -INFINITY;
-    for (int w = 0; w < cw; ++w) M = fmaxf(M, m_s[w * 16 + g]);
-    float L = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
-      for (int w = 0; w < cw; ++w) {
-        const float mw = m_s[w * 16 + g];
-        if (mw == -INFINITY) continue;                             // a warp without a tile
-        const float f = exp2f(mw - M);
-        L += l_s[w * 16 + g] * f;
-        acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+    for (int u = 0; u < cw; ++u) M = fmaxf(M, m_s[u * 16 + g]);
+    const float mv = m_s[v * 16 + g];
+    f_s[v * 16 + g] = (mv == -INFINITY) ? 0.f : exp2f(mv - M);     // a warp without a tile weighs nothing
+    if (v == 0) {
+      float L = 0.f;
+      for (int u = 0; u < cw; ++u) {
+        const float mu = m_s[u * 16 + g];
+        if (mu != -INFINITY) L += l_s[u * 16 + g] * exp2f(mu - M);
       }
+      M_s[g] = M;
+      L_s[g] = L;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int v = 0; v < cw; ++v) {
+      const float f = f_s[v * 16 + g];
+      const float4 x = *reinterpret_cast<const float4*>(o_s + ((size_t)v * 16 + g) * D + d);
+      acc.x += x.x * f; acc.y += x.y * f; acc.z += x.z * f; acc.w += x.w * f;
     }
     const int h = kvh * G + g;
     if (eff == 1) {
-      a.out[(size_t)row_q * a.H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      const float L = L_s[g], inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)h * D + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     } else {
       const size_t pi = ((size_t)b * a.H + h) * a.nsplit + split;
-      a.part_acc[pi * D + d] = acc;
-      if (d == 0) {
-        a.part_ml[pi * 2 + 0] = M;
-        a.part_ml[pi * 2 + 1] = L;
-      }
+      *reinterpret_cast<float4*>(a.part_acc + pi * D + d) = acc;
+      if (d == 0) *reinterpret_cast<float2*>(a.part_ml + pi * 2) = make_float2(M_s[g], L_s[g]);
     }
   }
   if (eff == 1) return;
@@ -399,7 +414,7 @@ TS_API int ts_attention_decode_tma(void* out, void* scratch, int* counters, cons
   // the merges reuse the stage buffers: 3 * G * nsplit floats and (2 + D) * 64 floats must fit
   const int G = H / KVH;
   const size_t smem = (size_t)stages * 2 * TILE * D * 2;
-  if (sizeof(float) * 3 * G * nsplit > smem || sizeof(float) * (2 + D) * CWARPS * 16 > smem)
+  if (sizeof(float) * 3 * G * nsplit > smem || sizeof(float) * ((3 + D) * CWARPS * 16 + 32) > smem)
     TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: %d stages are too few for the merge buffers", stages);
   int* status = dec_status_word();
   if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: no status word");
