@@ -249,30 +249,48 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
-    const int g = idx / D, d = idx % D;
+  // each warp's weight 2^(m_w - M) and the block's (M, L), once per head; then 16 bytes a thread
+  float* f_s = o_s + DEC_WARPS * 16 * D;                           // [WARPS][16]
+  float* M_s = f_s + DEC_WARPS * 16;                               // [16]
+  float* L_s = M_s + 16;                                           // [16]
+  if ((int)threadIdx.x < DEC_WARPS * G) {
+    const int v = threadIdx.x / G, g = threadIdx.x % G;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, m_s[w * 16 + g]);
-    float L = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
+    for (int u = 0; u < DEC_WARPS; ++u) M = fmaxf(M, m_s[u * 16 + g]);
+    const float mv = m_s[v * 16 + g];
+    f_s[v * 16 + g] = (mv == -INFINITY) ? 0.f : exp2f(mv - M);     // a warp without a key weighs nothing
+    if (v == 0) {
+      float L = 0.f;
 #pragma unroll
-      for (int w = 0; w < DEC_WARPS; ++w) {
-        const float f = exp2f(m_s[w * 16 + g] - M);
-        L += l_s[w * 16 + g] * f;
-        acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+      for (int u = 0; u < DEC_WARPS; ++u) {
+        const float mu = m_s[u * 16 + g];
+        if (mu != -INFINITY) L += l_s[u * 16 + g] * exp2f(mu - M);
       }
+      M_s[g] = M;
+      L_s[g] = L;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * (D / 4); idx += DEC_WARPS * 32) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int v = 0; v < DEC_WARPS; ++v) {
+      const float f = f_s[v * 16 + g];
+      const float4 x = *reinterpret_cast<const float4*>(o_s + ((size_t)v * 16 + g) * D + d);
+      acc.x += x.x * f; acc.y += x.y * f; acc.z += x.z * f; acc.w += x.w * f;
     }
     const int h = kvh * G + g;
     if (nsplit == 1) {
-      out[(size_t)row_q * H * D + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      const float L = L_s[g], inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* op = out + (size_t)row_q * H * D + (size_t)h * D + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     } else {
       const size_t pi = ((size_t)b * H + h) * nsplit + split;
-      part_acc[pi * D + d] = acc;
-      if (d == 0) {
-        part_ml[pi * 2 + 0] = M;
-        part_ml[pi * 2 + 1] = L;
-      }
+      *reinterpret_cast<float4*>(part_acc + pi * D + d) = acc;
+      if (d == 0) *reinterpret_cast<float2*>(part_ml + pi * 2) = make_float2(M_s[g], L_s[g]);
     }
   }
   if (nsplit == 1) return;
@@ -335,7 +353,7 @@ int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, c
                   int table_width, int H, int KVH, int page, float scale, int window, int nsplit, int* counters,
                   cudaStream_t s) {
   const size_t stage_bytes = (size_t)2 * DEC_STAGES * DEC_TILE * D * 2;
-  const size_t merge_bytes = sizeof(float) * ((size_t)2 * DEC_WARPS * 16 + (size_t)DEC_WARPS * 16 * D);
+  const size_t merge_bytes = sizeof(float) * ((size_t)3 * DEC_WARPS * 16 + 32 + (size_t)DEC_WARPS * 16 * D);
   const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
