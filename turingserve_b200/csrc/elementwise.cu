@@ -211,6 +211,29 @@ __global__ void __launch_bounds__(256) reduce_rmsnorm_kernel(bf16* __restrict__ 
                                       size_t split_stride, const bf16* __restrict__ bias, bf16* residual,
                                       const WT* __restrict__ w, float eps, int hidden) {
   pdl_launch_dependents();
+  // the scale and the bias are weights: their trip to memory overlaps the product's tail (the widest
+  // rows, which have no registers to spare, fetch them where they are used instead)
+  constexpr bool EARLY = CHUNKS < 8;
+  float wv[EARLY ? CHUNKS : 1][8], bv[EARLY ? CHUNKS : 1][8];
+  auto load_scale_bias = [&](int i, float (&ws)[8], float (&bs)[8]) {
+#pragma unroll
+    for (int k = 0; k < 8; k += Vec16<WT>::N) {
+      float t[Vec16<WT>::N];
+      load_vec<WT, Vec16<WT>::N>(w + i + k, t);
+#pragma unroll
+      for (int j = 0; j < Vec16<WT>::N; ++j) ws[k + j] = t[j];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) bs[k] = 0.f;
+    if (bias != nullptr) load_vec<bf16, 8>(bias + i, bs);
+  };
+  if constexpr (EARLY) {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int i = (c * blockDim.x + threadIdx.x) * 8;
+      if (i < hidden) load_scale_bias(i, wv[c], bv[c]);
+    }
+  }
   pdl_wait();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
@@ -244,14 +267,19 @@ __global__ void __launch_bounds__(256) reduce_rmsnorm_kernel(bf16* __restrict__ 
           acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
         }
       }
-      if (bias != nullptr) {
-        float bv[8];
-        load_vec<bf16, 8>(bias + i, bv);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += bv[k];
+      for (int k = 0; k < 8; ++k) v[c][k] = acc[k];
+      if constexpr (EARLY) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] += bv[c][k];
+      } else if (bias != nullptr) {
+        float bl[8];
+        load_vec<bf16, 8>(bias + i, bl);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] += bl[k];
       }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[c][k] = round_to<bf16>(acc[k]);
+      for (int k = 0; k < 8; ++k) v[c][k] = round_to<bf16>(v[c][k]);
       if (residual != nullptr) {
         float r[8];
         load_vec<bf16, 8>(residual + base + i, r);
@@ -271,7 +299,8 @@ __global__ void __launch_bounds__(256) reduce_rmsnorm_kernel(bf16* __restrict__ 
     if (i < hidden) {
       float y[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) y[k] = to_f(w[i + k]) * round_to<bf16>(v[c][k] * rstd);
+      for (int k = 0; k < 8; ++k)
+        y[k] = (EARLY ? wv[EARLY ? c : 0][k] : to_f(w[i + k])) * round_to<bf16>(v[c][k] * rstd);
       store_vec<bf16, 8>(out + base + i, y);
     }
   }
