@@ -325,6 +325,31 @@ def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, s
     torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
 
 
+@pytest.mark.parametrize("H,KVH,D,page", [(12, 2, 128, 16), (14, 2, 64, 32), (16, 1, 128, 64), (9, 3, 64, 64)])
+@pytest.mark.parametrize("nsplit", [1, 2, 3, 4, 8, 16, 24])
+@pytest.mark.parametrize("window", [None, 1, 130])
+def test_attention_decode_merge_of_splits(ops, monkeypatch, H, KVH, D, page, nsplit, window):
+    """The cp.async decode kernel's two ways of merging its key splits: 2, 4, 8 or 16 splits as one
+    thread-block cluster that reads its blocks' shared memory, and any count through scratch and a
+    ticket counter.  More splits than tiles (blocks without a key), contexts on and around tile
+    edges, a window, NaN in unwritten rows; the two ways agree to rounding."""
+    monkeypatch.setattr(ops, "decode_splits", lambda *a: nsplit)
+    # many requests, and one (clusters of 16 are used only while they are few)
+    for lens in ([1, 63, 64, 65, 128, 129, 1000, 1024, 1025, 2500, 16, 17], [2500]):
+        outs = []
+        try:
+            for clusters in (1, 0):
+                ops.lib.ts_set_decode_clusters(clusters)
+                out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens),
+                                             [l - 1 for l in lens], 19, window=window, tma=False, poison=True)
+                assert torch.isfinite(out).all()
+                torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+                outs.append(out)
+        finally:
+            ops.lib.ts_set_decode_clusters(1)
+        torch.testing.assert_close(outs[0], outs[1], atol=4e-3, rtol=8e-3)     # one bfloat16 step
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,KVH,D,page", [(4, 2, 16, 16), (12, 2, 128, 16), (14, 2, 64, 8), (5, 5, 48, 16)])
 @pytest.mark.parametrize("case", [[(1, 0)], [(15, 16)], [(16, 37)], [(17, 1000)], [(300, 0)],

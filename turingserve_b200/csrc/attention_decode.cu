@@ -27,7 +27,31 @@ constexpr int DEC_STAGES = 3;
 constexpr int PAGES_S = 1024;       // block-table entries a block keeps in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int D>
+// Thread-block clusters: the splits of one (request, kv head) are the blocks of one cluster and read
+// each other's merged states from shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned peer_shared(const void* own, unsigned rank) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(own);
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(unsigned addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_v4(unsigned addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// CLUSTER: the grid's x dimension (the splits) is one cluster; nsplit is then a power of two <= 16.
+template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
@@ -253,6 +277,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   float* f_s = o_s + DEC_WARPS * 16 * D;                           // [WARPS][16]
   float* M_s = f_s + DEC_WARPS * 16;                               // [16]
   float* L_s = M_s + 16;                                           // [16]
+  float* c_acc = L_s + 16;                                         // [G][D], read by the cluster's blocks
   if ((int)threadIdx.x < DEC_WARPS * G) {
     const int v = threadIdx.x / G, g = threadIdx.x % G;
     float M = -INFINITY;
@@ -287,6 +312,8 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
       bf16* op = out + (size_t)row_q * H * D + (size_t)h * D + d;
       *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
       *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    } else if (CLUSTER) {
+      *reinterpret_cast<float4*>(c_acc + g * D + d) = acc;
     } else {
       const size_t pi = ((size_t)b * H + h) * nsplit + split;
       *reinterpret_cast<float4*>(part_acc + pi * D + d) = acc;
@@ -294,6 +321,52 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
     }
   }
   if (nsplit == 1) return;
+
+  if constexpr (CLUSTER) {
+    // Block r of the cluster finishes the 16-byte pieces r, r + nsplit, ... of the output; the
+    // nsplit lanes of a group each fetch one split's state of that piece and sum by butterfly:
+    //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+    cluster_sync_all();
+    constexpr int QD = D / 4;
+    const int pieces = G * QD, rank = split;
+    const int mine = pieces > rank ? (pieces - rank + nsplit - 1) / nsplit : 0;
+    const int total = mine * nsplit;
+    const int shift = 31 - __clz(nsplit);
+    for (int p0 = 0; p0 < total; p0 += DEC_WARPS * 32) {           // block-uniform trip count
+      const int p = p0 + threadIdx.x;
+      const bool valid = p < total;
+      const int s2 = p & (nsplit - 1);
+      const int piece = valid ? rank + ((p >> shift) << shift) : 0;
+      const int g = piece / QD, d = (piece % QD) * 4;
+      float m = -INFINITY, l = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid) {
+        m = ld_peer_f32(peer_shared(M_s + g, s2));
+        l = ld_peer_f32(peer_shared(L_s + g, s2));
+        acc = ld_peer_v4(peer_shared(c_acc + g * D + d, s2));
+      }
+      float M = m;
+      for (int x = 1; x < nsplit; x <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
+      const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      l *= f;
+      acc.x *= f; acc.y *= f; acc.z *= f; acc.w *= f;
+      for (int x = 1; x < nsplit; x <<= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, x);
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, x);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, x);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, x);
+        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, x);
+      }
+      if (valid && s2 == 0) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* op = out + (size_t)row_q * H * D + (size_t)(kvh * G + g) * D + d;
+        *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+      }
+    }
+    cluster_sync_all();                                            // no block leaves while a peer still reads it
+    return;
+  }
 
   // The block that finishes last for this (request, kv head) merges all splits, in split order:
   //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
@@ -347,23 +420,66 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   }
 }
 
+// Whether the splits may be one cluster: 2, 4, 8 or 16 of them, and the device can hold such a cluster
+// of this kernel (asked once per size).  0: no, 1: yes.
+template <int D>
+int cluster_ok(int nsplit, size_t smem) {
+  static int known[5] = {-1, -1, -1, -1, -1};                      // by log2(nsplit)
+  if (nsplit < 2 || nsplit > 16 || (nsplit & (nsplit - 1))) return 0;
+  int idx = 0;
+  while ((1 << idx) < nsplit) ++idx;
+  if (known[idx] < 0) {
+    known[idx] = 0;
+    auto kernel = attention_decode_kernel<D, true>;
+    bool ok = true;
+    if (nsplit > 8)
+      ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (ok) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(nsplit, 1, 1);
+      cfg.blockDim = dim3(DEC_WARPS * 32);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)nsplit;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[idx] = 1;
+    }
+    cudaGetLastError();                                            // a refusal above is an answer, not an error
+  }
+  return known[idx];
+}
+
 template <int D>
 int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, const bf16* k_cache,
                   const bf16* v_cache, const int* block_tables, const int* q_start, const int* seq_lens, int B,
                   int table_width, int H, int KVH, int page, float scale, int window, int nsplit, int* counters,
                   cudaStream_t s) {
   const size_t stage_bytes = (size_t)2 * DEC_STAGES * DEC_TILE * D * 2;
-  const size_t merge_bytes = sizeof(float) * ((size_t)3 * DEC_WARPS * 16 + 32 + (size_t)DEC_WARPS * 16 * D);
+  const size_t merge_bytes = sizeof(float) * ((size_t)3 * DEC_WARPS * 16 + 32 + (size_t)(DEC_WARPS + 1) * 16 * D);
   const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  ts_launch(attention_decode_kernel<D>, dim3(dim3(nsplit, KVH, B)), dim3(DEC_WARPS * 32), smem, s, 
-      out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
-      scale, window, nsplit, counters);
+  // Clusters of 16 are worth it only while there are a handful of them: a step with 16 of them was
+  // a sixth slower than with the ticket merge (they fit few places on the chip), one with 2 faster.
+  if (ts_decode_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && cluster_ok<D>(nsplit, smem))
+    ts_launch_cluster(attention_decode_kernel<D, true>, nsplit, dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
+        out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
+        scale, window, nsplit, counters);
+  else
+    ts_launch(attention_decode_kernel<D, false>, dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
+        out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
+        scale, window, nsplit, counters);
   TS_LAUNCH_CHECK();
 }
 

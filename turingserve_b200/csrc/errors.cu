@@ -22,3 +22,9 @@ TS_API int ts_abi_version() { return 3; }
 static bool g_pdl = true;
 bool ts_pdl_enabled() { return g_pdl; }
 TS_API void ts_set_pdl(int on) { g_pdl = on != 0; }
+
+// Thread-block clusters for the decode attention's merge of its splits (on by default; off: the
+// ticket counter and scratch path at every split count).
+static bool g_decode_clusters = true;
+bool ts_decode_clusters_enabled() { return g_decode_clusters; }
+TS_API void ts_set_decode_clusters(int on) { g_decode_clusters = on != 0; }

@@ -63,6 +63,9 @@ def decode_attention(a) -> None:
     step = Step(torch.arange(B + 1, dtype=torch.int32, device="cuda"),
                 torch.full((B,), ctx + 1, dtype=torch.int32, device="cuda"), B, 1, longest, B)
     out = torch.empty(B, H * D, device="cuda", dtype=torch.bfloat16)
+    if a.splits:                                                   # instead of the rule's own count
+        ops.decode_splits = lambda *args: a.splits
+        ops.decode_splits_tma = lambda *args: a.splits
 
     def f(i):
         kc, vc = caches[i % layers]
@@ -212,6 +215,7 @@ def main() -> int:
     s.add_argument("--context", type=int, default=2048)
     s.add_argument("--page", type=int, default=PAGE)
     s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
+    s.add_argument("--splits", type=int, default=0, help="key splits per request (0: the rule's count)")
     s = sub.add_parser("prefill_attention")
     s.add_argument("--tokens", type=int, default=2048)
     s.add_argument("--page", type=int, default=PAGE)
