@@ -482,9 +482,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
 // With `part` set, the q/k/v product arrives unreduced: the value of column c of token t is
 // sum over splits (ascending) of part[s, t, c] + bias[c], rounded to bfloat16 as the product's own
 // epilogue would have rounded it; the kernel then writes q, k and v into qkv as well.
+template <bool PART>
 __device__ __forceinline__ void load_qkv8(const bf16* row, int col, const float* part, int splits, size_t split_stride,
                                           size_t part_row, const bf16* bias, float (&f)[8]) {
-  if (part == nullptr) {
+  if constexpr (!PART) {
     load_vec<bf16, 8>(row + col, f);
     return;
   }
@@ -516,6 +517,10 @@ __device__ __forceinline__ void load_qkv8(const bf16* row, int col, const float*
   for (int k = 0; k < 8; ++k) f[k] = round_to<bf16>(f[k]);
 }
 
+// PART: the product arrives unreduced (`part` set).  A kernel of its own, because the partial sums
+// held in registers would otherwise limit the plain kernel to a few resident warps (250 registers
+// against 40: a 2,048-token portion took 22 us instead of 6).
+template <bool PART>
 __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
@@ -552,8 +557,8 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
       if (j < hv) {
         const int i = j * 8;
         float x1[8], x2[8], o1[8], o2[8];
-        load_qkv8(row, head * D + i, part, splits, split_stride, part_row, bias, x1);
-        load_qkv8(row, head * D + i + half, part, splits, split_stride, part_row, bias, x2);
+        load_qkv8<PART>(row, head * D + i, part, splits, split_stride, part_row, bias, x1);
+        load_qkv8<PART>(row, head * D + i + half, part, splits, split_stride, part_row, bias, x2);
         const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i);
         const float4 c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i + 4);
         const float4 s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i);
@@ -572,22 +577,22 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
           store_vec<bf16, 8>(kdst + i, o1);
           store_vec<bf16, 8>(kdst + i + half, o2);
         }
-      } else if (kdst != nullptr || part != nullptr) {
+      } else if (kdst != nullptr || PART) {
         const int d = rot + (j - hv) * 8;
         float pass[8];
-        load_qkv8(row, head * D + d, part, splits, split_stride, part_row, bias, pass);
-        if (part != nullptr) store_vec<bf16, 8>(x + d, pass);
+        load_qkv8<PART>(row, head * D + d, part, splits, split_stride, part_row, bias, pass);
+        if (PART) store_vec<bf16, 8>(x + d, pass);
         if (kdst != nullptr) store_vec<bf16, 8>(kdst + d, pass);
       }
     }
-  } else if (slot >= 0 || part != nullptr) {
+  } else if (slot >= 0 || PART) {
     const int vh = head - H - KVH;
     for (int j = lane; j < D / 8; j += lph) {
       const int d = j * 8;
       const int col = (H + KVH) * D + vh * D + d;
       float vv[8];
-      load_qkv8(row, col, part, splits, split_stride, part_row, bias, vv);
-      if (part != nullptr) store_vec<bf16, 8>(row + col, vv);
+      load_qkv8<PART>(row, col, part, splits, split_stride, part_row, bias, vv);
+      if (PART) store_vec<bf16, 8>(row + col, vv);
       if (slot >= 0) store_vec<bf16, 8>(v_cache + cache_base + (size_t)vh * head_stride + d, vv);
     }
   }
@@ -631,9 +636,14 @@ TS_API int ts_rope_kv_write_ex(void* qkv, const int* positions, const float* cos
     }
     const int head_warps = ceil_div(heads, 32 / lph);
     const int warps = head_warps >= 4 ? 4 : head_warps;
-    ts_launch(rope_kv_write_vec_kernel, dim3(T, ceil_div(head_warps, warps)), dim3(warps * 32), 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache,
-                                                   slots, H, KVH, D, rot, page, part, splits,
-                                                   (size_t)T * (H + 2 * KVH) * D, (const bf16*)bias, lph);
+    const dim3 grid(T, ceil_div(head_warps, warps)), block(warps * 32);
+    const size_t stride = (size_t)T * (H + 2 * KVH) * D;
+    if (part != nullptr)
+      ts_launch(rope_kv_write_vec_kernel<true>, grid, block, 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache,
+                (bf16*)v_cache, slots, H, KVH, D, rot, page, part, splits, stride, (const bf16*)bias, lph);
+    else
+      ts_launch(rope_kv_write_vec_kernel<false>, grid, block, 0, s, (bf16*)qkv, positions, cos_t, sin_t, (bf16*)k_cache,
+                (bf16*)v_cache, slots, H, KVH, D, rot, page, part, splits, stride, (const bf16*)bias, lph);
     TS_LAUNCH_CHECK();
   }
   if (part != nullptr) TS_REFUSE(TS_ERR_ALIGN, "ts_rope_kv_write: unreduced input needs 16-byte aligned buffers");
