@@ -47,6 +47,13 @@ __device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f(float x);
 template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+// silu(g) = g / (1 + e^-g) on its way to a rounding to T.  For bfloat16 the hardware's approximate
+// exponential and reciprocal serve: their error (about 2^-21 relative) is far inside half a
+// bfloat16 step (2^-9), and the exact ones cost as much issue time as the activation kernel's
+// memory traffic takes.  The 32-bit path keeps the exact ones.
+template <typename T> __device__ __forceinline__ float silu_for(float g) { return g / (1.f + expf(-g)); }
+template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 // Round a 32-bit value to the storage type and back (the model-dtype rounding points).
 template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f(from_f<T>(x)); }
 

@@ -357,7 +357,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     const size_t gc = t * 2 * inter + gate_col(i, group);
     const float g = to_f(gu[gc]);
     const float u = to_f(gu[gc + up_off]);
-    const float s = round_to<T>(g / (1.f + expf(-g)));
+    const float s = round_to<T>(silu_for<T>(g));
     out[idx] = from_f<T>(s * u);
   }
 }
@@ -378,7 +378,7 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ g
     load_vec<T, N>(gu + gc, g);
     load_vec<T, N>(gu + gc + up_off, u);
 #pragma unroll
-    for (int k = 0; k < N; ++k) o[k] = round_to<T>(g[k] / (1.f + expf(-g[k]))) * u[k];
+    for (int k = 0; k < N; ++k) o[k] = round_to<T>(silu_for<T>(g[k])) * u[k];
     store_vec<T, N>(out + (size_t)t * inter + i, o);
   }
 }

@@ -305,7 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
             if (n < I && m < args.M) {
               const float g = round_to<bf16>(__uint_as_float(v[i]));
               const float u = round_to<bf16>(ex[r * BN + c + i]);
-              const float sl = round_to<bf16>(g / (1.f + expf(-g)));
+              const float sl = round_to<bf16>(silu_for<bf16>(g));
               outb[(size_t)m * I + n] = __float2bfloat16_rn(sl * u);
             }
           }
