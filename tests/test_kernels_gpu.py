@@ -178,17 +178,25 @@ def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, 
         slots[1] = -1
     kc0, vc0 = _rand((pages, KVH, page, D), torch.bfloat16, 53), _rand((pages, KVH, page, D), torch.bfloat16, 54)
     got = {}
-    for fused in (True, False):
+    # fused with its splits as one thread-block cluster (where the split count allows), fused with
+    # scratch and a ticket counter, and product and rotary kernel apart
+    for fused, clusters in ((True, 1), ("ticket", 0), (False, 1)):
         monkeypatch.setattr(ops, "fused_qkv_tokens", 128 if fused else 0)
-        kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
-        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-        launches = ops.launches
-        for _ in range(2):                                         # twice: the counters come back to zero
-            q = ops.qkv_rope(out, x, w, b, pos.cuda(), cos.cuda(), sin.cuda(), H, KVH, D, D, kc, vc, slots.cuda(), page)
-        assert (ops.launches - launches == 2) == fused
+        ops.lib.ts_set_clusters(clusters)
+        try:
+            kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
+            out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            launches = ops.launches
+            for _ in range(2):                                     # twice: the counters come back to zero
+                q = ops.qkv_rope(out, x, w, b, pos.cuda(), cos.cuda(), sin.cuda(), H, KVH, D, D, kc, vc, slots.cuda(),
+                                 page)
+        finally:
+            ops.lib.ts_set_clusters(1)
+        assert (ops.launches - launches == 2) == bool(fused)
         got[fused] = (q.clone(), kc, vc)
-    for a, c in zip(got[True], got[False]):
-        assert torch.equal(a, c)
+    for other in ("ticket", False):
+        for a, c in zip(got[True], got[other]):
+            assert torch.equal(a, c)
     # rotate only (a run that reads another run's cache): no cache write
     monkeypatch.setattr(ops, "fused_qkv_tokens", 128)
     out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
@@ -339,14 +347,14 @@ def test_attention_decode_merge_of_splits(ops, monkeypatch, H, KVH, D, page, nsp
         outs = []
         try:
             for clusters in (1, 0):
-                ops.lib.ts_set_decode_clusters(clusters)
+                ops.lib.ts_set_clusters(clusters)
                 out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens),
                                              [l - 1 for l in lens], 19, window=window, tma=False, poison=True)
                 assert torch.isfinite(out).all()
                 torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
                 outs.append(out)
         finally:
-            ops.lib.ts_set_decode_clusters(1)
+            ops.lib.ts_set_clusters(1)
         torch.testing.assert_close(outs[0], outs[1], atol=4e-3, rtol=8e-3)     # one bfloat16 step
 
 

@@ -29,27 +29,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 // Thread-block clusters: the splits of one (request, kv head) are the blocks of one cluster and read
 // each other's merged states from shared memory.
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ unsigned peer_shared(const void* own, unsigned rank) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(own);
-  unsigned r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ float ld_peer_f32(unsigned addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_peer_v4(unsigned addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-
 // CLUSTER: the grid's x dimension (the splits) is one cluster; nsplit is then a power of two <= 16.
 template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -472,8 +451,8 @@ int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, c
   }
   // Clusters of 16 are worth it only while there are a handful of them: a step with 16 of them was
   // a sixth slower than with the ticket merge (they fit few places on the chip), one with 2 faster.
-  if (ts_decode_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && cluster_ok<D>(nsplit, smem))
-    ts_launch_cluster(attention_decode_kernel<D, true>, nsplit, dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
+  if (ts_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && cluster_ok<D>(nsplit, smem))
+    ts_launch_cluster(attention_decode_kernel<D, true>, dim3(nsplit, 1, 1), dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
         out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
         scale, window, nsplit, counters);
   else

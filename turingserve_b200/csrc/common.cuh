@@ -89,13 +89,37 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-bool ts_pdl_enabled();
-bool ts_decode_clusters_enabled();
+// Thread-block clusters: every thread of every block of the cluster takes the barrier; a block's
+// shared memory may be read by its peers between two of them.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of block `rank`'s copy of this block's `own`.
+__device__ __forceinline__ unsigned peer_shared(const void* own, unsigned rank) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(own);
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(unsigned addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_v4(unsigned addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 
-// cluster_x > 1: the blocks of a row of the grid form thread-block clusters of that many (grid.x
-// must be a multiple of it).
+bool ts_pdl_enabled();
+bool ts_clusters_enabled();
+
+// cluster: the shape of the thread-block clusters the grid is cut into (each grid dimension must be
+// a multiple of the cluster's); (1, 1, 1): none.
 template <typename... KArgs, typename... Args>
-inline cudaError_t ts_launch_cluster(void (*kernel)(KArgs...), int cluster_x, dim3 grid, dim3 block, size_t smem,
+inline cudaError_t ts_launch_cluster(void (*kernel)(KArgs...), dim3 cluster, dim3 grid, dim3 block, size_t smem,
                                      cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
@@ -109,11 +133,11 @@ inline cudaError_t ts_launch_cluster(void (*kernel)(KArgs...), int cluster_x, di
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_x > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = (unsigned)cluster_x;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = 1;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
     ++n;
   }
   cfg.attrs = attr;
@@ -124,5 +148,5 @@ inline cudaError_t ts_launch_cluster(void (*kernel)(KArgs...), int cluster_x, di
 template <typename... KArgs, typename... Args>
 inline cudaError_t ts_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args&&... args) {
-  return ts_launch_cluster(kernel, 1, grid, block, smem, stream, static_cast<Args&&>(args)...);
+  return ts_launch_cluster(kernel, dim3(1, 1, 1), grid, block, smem, stream, static_cast<Args&&>(args)...);
 }

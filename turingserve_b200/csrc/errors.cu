@@ -23,8 +23,9 @@ static bool g_pdl = true;
 bool ts_pdl_enabled() { return g_pdl; }
 TS_API void ts_set_pdl(int on) { g_pdl = on != 0; }
 
-// Thread-block clusters for the decode attention's merge of its splits (on by default; off: the
-// ticket counter and scratch path at every split count).
-static bool g_decode_clusters = true;
-bool ts_decode_clusters_enabled() { return g_decode_clusters; }
-TS_API void ts_set_decode_clusters(int on) { g_decode_clusters = on != 0; }
+// Thread-block clusters where the splits of a kernel merge through distributed shared memory (the
+// decode attention, the q/k/v product that rotates): on by default; off: scratch and a ticket
+// counter at every split count.
+static bool g_clusters = true;
+bool ts_clusters_enabled() { return g_clusters; }
+TS_API void ts_set_clusters(int on) { g_clusters = on != 0; }

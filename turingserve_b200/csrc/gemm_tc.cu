@@ -54,6 +54,37 @@ struct GemmArgs {
 // BN: tile columns (UMMA N).  SWAP: the tile rows are weight rows (outputs), columns are tokens.
 // KSUB: 64-column k-blocks per pipeline stage (their TMA boxes are issued back to back, so a weight
 // row is touched KSUB * 128 contiguous bytes at a time).
+// Columns p and p + 64 of token m of a head (q heads, then k, then v), given their sums with the
+// bias: rounded to bfloat16 as a product's epilogue rounds, rotated (q and k), written to the q/k/v
+// tensor and, for k and v, into the cache page of the token's slot.
+__device__ __forceinline__ void rope_finish(const GemmArgs& args, int head, int p, int m, float x1, float x2) {
+  x1 = round_to<bf16>(x1);
+  x2 = round_to<bf16>(x2);
+  float o1 = x1, o2 = x2;
+  if (head < args.H + args.KVH) {
+    const int pos = args.positions[m];
+    const float cs = round_to<bf16>(args.cos_t[(size_t)pos * 64 + p]);
+    const float sn = round_to<bf16>(args.sin_t[(size_t)pos * 64 + p]);
+    o1 = x1 * cs - x2 * sn;
+    o2 = x2 * cs + x1 * sn;
+  }
+  const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
+  bf16* qkv = reinterpret_cast<bf16*>(args.out);
+  qkv[(size_t)m * args.N + head * 128 + p] = w1;
+  qkv[(size_t)m * args.N + head * 128 + p + 64] = w2;
+  if (head >= args.H && args.k_cache != nullptr) {
+    const int slot = args.slots[m];
+    if (slot >= 0) {
+      const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * 128;
+      const bool is_k = head < args.H + args.KVH;
+      bf16* dst = (is_k ? args.k_cache : args.v_cache) + cache_base +
+                  (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * 128;
+      dst[p] = w1;
+      dst[p + 64] = w2;
+    }
+  }
+}
+
 template <int BN, int STAGES, bool SWAP, int KSUB>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
@@ -170,7 +201,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     pdl_wait();                                    // nothing is written before the predecessor is done
     bool ok = n_kb > 0 && mbar_wait(accum, 0, args.status, 3, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    if (SWAP && args.rope) {
+    if (SWAP && args.rope == 2) {
+      // The splits of this tile are one cluster: the partial sums stay in shared memory (the stage
+      // buffers are free by now) for the peers to read; see the end of the kernel.
+      constexpr int CW = BN >= 32 ? 32 : 16;
+      float* ex = reinterpret_cast<float*>(a_s);                // [BN][128]
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+          if constexpr (CW == 32) {
+            tmem_ld32(taddr, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld16(taddr, v16);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v16[i];
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < CW; ++i) ex[(c + i) * 128 + r] = __uint_as_float(v[i]);
+        }
+      }
+    } else if (SWAP && args.rope) {
       constexpr int CW = BN >= 32 ? 32 : 16;
       const int slot_id = blockIdx.x * gridDim.y + blockIdx.y;
       float* mine = args.rope_part + ((size_t)slot_id * args.splits + blockIdx.z) * BN * 128;
@@ -207,11 +262,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
         const int head = blockIdx.x;                           // a tile is a head: q heads, then k, then v
         const int p = r & 63, tg = r >> 6;                     // the pair (p, p + 64) of tokens tg, tg + 2, ...
         const float* base = args.rope_part + (size_t)slot_id * args.splits * BN * 128;
-        const int N = args.N;
         const float b1 = args.bias != nullptr ? to_f(args.bias[head * 128 + p]) : 0.f;
         const float b2 = args.bias != nullptr ? to_f(args.bias[head * 128 + p + 64]) : 0.f;
-        const bool rotate = head < args.H + args.KVH;
-        bf16* qkv = reinterpret_cast<bf16*>(args.out);
         const int tokens = min(BN, args.M - col0);
         for (int tok = tg; tok < tokens; tok += 2) {
           float lo[16], hi[16];
@@ -228,31 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
               x1 += lo[sp];
               x2 += hi[sp];
             }
-          x1 = round_to<bf16>(x1 + b1);
-          x2 = round_to<bf16>(x2 + b2);
-          const int m = col0 + tok;
-          float o1 = x1, o2 = x2;
-          if (rotate) {
-            const int pos = args.positions[m];
-            const float cs = round_to<bf16>(args.cos_t[(size_t)pos * 64 + p]);
-            const float sn = round_to<bf16>(args.sin_t[(size_t)pos * 64 + p]);
-            o1 = x1 * cs - x2 * sn;
-            o2 = x2 * cs + x1 * sn;
-          }
-          const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
-          qkv[(size_t)m * N + head * 128 + p] = w1;
-          qkv[(size_t)m * N + head * 128 + p + 64] = w2;
-          if (head >= args.H && args.k_cache != nullptr) {
-            const int slot = args.slots[m];
-            if (slot >= 0) {
-              const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * 128;
-              const bool is_k = head < args.H + args.KVH;
-              bf16* dst = (is_k ? args.k_cache : args.v_cache) + cache_base +
-                          (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * 128;
-              dst[p] = w1;
-              dst[p + 64] = w2;
-            }
-          }
+          rope_finish(args, head, p, col0 + tok, x1 + b1, x2 + b2);
         }
       }
     } else if (SWAP && args.gated) {
@@ -371,6 +399,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
       }
     }
   }
+  if (SWAP && args.rope == 2) {
+    // Block z of the cluster finishes tokens z, z + splits, ...: each thread sums one pair of columns
+    // out of every peer's shared memory, in split order (the sums of the ticket path, bit for bit).
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int r = (warp & 3) * 32 + lane;
+      const int head = blockIdx.x, p = r & 63, tg = r >> 6;
+      const float* ex = reinterpret_cast<const float*>(a_s);
+      const float b1 = args.bias != nullptr ? to_f(args.bias[head * 128 + p]) : 0.f;
+      const float b2 = args.bias != nullptr ? to_f(args.bias[head * 128 + p + 64]) : 0.f;
+      const int tokens = min(BN, args.M - col0);
+      for (int tok = (int)blockIdx.z + tg * args.splits; tok < tokens; tok += 2 * args.splits) {
+        float lo[8], hi[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) {
+            lo[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + p, sp));
+            hi[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + p + 64, sp));
+          }
+        float x1 = 0.f, x2 = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) {
+            x1 += lo[sp];
+            x2 += hi[sp];
+          }
+        rope_finish(args, head, p, col0 + tok, x1 + b1, x2 + b2);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();                              // no block leaves while a peer still reads it
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -402,7 +463,8 @@ int* status_word() {
 }
 
 template <int BN, int STAGES, bool SWAP, int KSUB = 1>
-int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmArgs& args, dim3 grid, cudaStream_t s) {
+int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmArgs& args, dim3 grid, cudaStream_t s,
+           dim3 cluster = dim3(1, 1, 1)) {
   constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
   static bool configured = false;
   if (!configured) {
@@ -410,8 +472,38 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmA
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_linear_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  ts_launch(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map, cols_map, args);
+  ts_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cluster, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map,
+                    cols_map, args);
   TS_LAUNCH_CHECK();
+}
+
+// Whether `splits` blocks of this kernel can be one cluster on this device (asked once per count).
+template <int BN, int STAGES, bool SWAP, int KSUB = 1>
+bool cluster_fits(int splits) {
+  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
+  static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (splits < 2 || splits > 8) return false;
+  if (known[splits] < 0) {
+    known[splits] = 0;
+    auto kernel = gemm_tc_kernel<BN, STAGES, SWAP, KSUB>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 1, splits);
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = (unsigned)splits;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[splits] = 1;
+    }
+    cudaGetLastError();                              // a refusal above is an answer, not an error
+  }
+  return known[splits] == 1;
 }
 
 }  // namespace
@@ -602,8 +694,21 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: cuTensorMapEncodeTiled failed");
   dim3 grid(heads, ceil_div(M, bn), splits);
   cudaStream_t s = (cudaStream_t)stream;
-  if (bn == 16) return launch<16, 4, true, 2>(rows_map, cols_map, a, grid, s);
-  if (bn == 32) return launch<32, 4, true>(rows_map, cols_map, a, grid, s);
-  if (bn == 64) return launch<64, 4, true>(rows_map, cols_map, a, grid, s);
-  return launch<128, 4, true>(rows_map, cols_map, a, grid, s);
+  // 2 to 8 splits of a tile as one thread-block cluster: the partial sums cross through shared
+  // memory instead of scratch, a fence and a ticket.
+  const bool want_cluster = ts_clusters_enabled() && splits >= 2 && splits <= 8;
+  const dim3 cl(1, 1, splits);
+#define TS_ROPE_LAUNCH(...)                                           \
+  do {                                                                \
+    if (want_cluster && cluster_fits<__VA_ARGS__>(splits)) {          \
+      a.rope = 2;                                                     \
+      return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s, cl); \
+    }                                                                 \
+    return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s);       \
+  } while (0)
+  if (bn == 16) TS_ROPE_LAUNCH(16, 4, true, 2);
+  if (bn == 32) TS_ROPE_LAUNCH(32, 4, true);
+  if (bn == 64) TS_ROPE_LAUNCH(64, 4, true);
+  TS_ROPE_LAUNCH(128, 4, true);
+#undef TS_ROPE_LAUNCH
 }

@@ -123,9 +123,9 @@ class CudaOps:
         self.lib.ts_set_pdl.argtypes = [I]
         self.lib.ts_set_pdl.restype = None
         self.lib.ts_set_pdl(0 if os.environ.get("TURINGSERVE_B200_PDL", "1") == "0" else 1)
-        self.lib.ts_set_decode_clusters.argtypes = [I]
-        self.lib.ts_set_decode_clusters.restype = None
-        self.lib.ts_set_decode_clusters(0 if os.environ.get("TURINGSERVE_B200_DECODE_CLUSTERS", "1") == "0" else 1)
+        self.lib.ts_set_clusters.argtypes = [I]
+        self.lib.ts_set_clusters.restype = None
+        self.lib.ts_set_clusters(0 if os.environ.get("TURINGSERVE_B200_CLUSTERS", "1") == "0" else 1)
         self.lib.ts_attention_prefill_tc_supported.argtypes = [I, I, I, I, I]
         self.lib.ts_attention_prefill_tc_supported.restype = c_int
         self.lib.ts_attention_prefill_tc_status.argtypes = []
