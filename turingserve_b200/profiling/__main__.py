@@ -17,6 +17,7 @@ import dataclasses
 import torch
 
 from turingserve_b200 import kernels
+from turingserve_b200.engine.batch import streaming_decode
 
 H, KVH, D, PAGE, LAYERS = 12, 2, 128, 16, 28
 
@@ -29,6 +30,7 @@ class Step:
     max_q_len: int
     max_seq_len: int
     num_decode: int
+    streaming_decode: bool | None = None     # which decode kernel, as the engine decides it from the live contexts
 
 
 def timed(fn, n: int) -> float:
@@ -61,7 +63,8 @@ def decode_attention(a) -> None:
     qkv = torch.randn(B, (H + 2 * KVH) * D, device="cuda", dtype=torch.bfloat16)
     longest = max(4096, ctx + 1)
     step = Step(torch.arange(B + 1, dtype=torch.int32, device="cuda"),
-                torch.full((B,), ctx + 1, dtype=torch.int32, device="cuda"), B, 1, longest, B)
+                torch.full((B,), ctx + 1, dtype=torch.int32, device="cuda"), B, 1, longest, B,
+                streaming_decode(B, ctx + 1))
     out = torch.empty(B, H * D, device="cuda", dtype=torch.bfloat16)
     if a.splits:                                                   # instead of the rule's own count
         ops.decode_splits = lambda *args: a.splits
