@@ -696,7 +696,9 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
   cudaStream_t s = (cudaStream_t)stream;
   // 2 to 8 splits of a tile as one thread-block cluster: the partial sums cross through shared
   // memory instead of scratch, a fence and a ticket.
-  const bool want_cluster = ts_clusters_enabled() && splits >= 2 && splits <= 8;
+  // (a step of 1 or 2 tokens is about 2 % slower with the cluster than with the ticket, one of 4 or 8
+  // tokens 1 % faster, one of 16 tokens 10 % faster: the ticket's last block sums token after token)
+  const bool want_cluster = ts_clusters_enabled() && splits >= 2 && splits <= 8 && M >= 4;
   const dim3 cl(1, 1, splits);
 #define TS_ROPE_LAUNCH(...)                                           \
   do {                                                                \

@@ -203,9 +203,9 @@ class CudaOps:
 
     GATE_GROUP = 64      # rows of gates, then of ups, in one 128-row tile of the few-token product
     # up to this many tokens the activation goes into the product's epilogue (the kernel takes 128; above
-    # 16 its epilogue, two of four warps doing the activation, costs more than the kernel it saves:
-    # 24.0k against 24.7k tok/s at batch 64, 1.550 against 1.559 ms a step at batch 8)
-    fused_gate_tokens = 16
+    # 32 its epilogue, two of four warps doing the activation, costs more than the kernel it saves:
+    # 2.69 against 2.47 ms a step at batch 64, 2.001 against 2.012 ms at batch 32)
+    fused_gate_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_GATE_TOKENS", "32"))
 
     def gated_linear(self, out, x, w, bias, group: int) -> None:
         """out[T, I] = silu(g) * u with [g, u] = x @ w[2I, K]^T + bias, the rows of ``w`` (and
@@ -245,9 +245,9 @@ class CudaOps:
         return qkv
 
     # up to this many tokens the q/k/v product finishes itself (sum over its splits, bias, rotation,
-    # cache write in the epilogue of the block that comes last for a head) instead of leaving that to the
-    # rotary kernel
-    fused_qkv_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_QKV_TOKENS", "16"))
+    # cache write in its own epilogue) instead of leaving that to the rotary kernel (batch 24: 1.93
+    # against 2.09 ms a step, batch 32: 2.01 against 2.15 ms; batch 64: 2.50 against 2.47 ms)
+    fused_qkv_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_QKV_TOKENS", "32"))
 
     def qkv_rope(self, out, x, w, bias, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                  page_size):
