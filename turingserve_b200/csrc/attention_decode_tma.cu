@@ -48,6 +48,7 @@ struct DecArgs {
   int table_width, H, KVH, page;
   float scale;
   int window, nsplit, stages, box_shift, v_first;
+  int cluster;            // the splits of a (request, kv head) are one thread-block cluster (2..8 of them)
   int* counters;
   int* status;
 };
@@ -76,11 +77,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
   const int row_q = a.q_start[b];                 // the request's single query token
   const int lo = (a.window > 0) ? max(0, seq_len - a.window) : 0;
 
+  // A block of a cluster that leaves early still takes the cluster's two barriers (every branch that
+  // leaves is uniform over the block), so that its peers' barriers complete.
+  auto leave = [&]() {
+    if (a.cluster) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
+  };
   if (seq_len <= 0) {                             // nothing to attend to: zeros, from split 0
     pdl_wait();
     if (split == 0)
       for (int idx = threadIdx.x; idx < G * D; idx += THREADS)
         a.out[(size_t)row_q * a.H * D + (size_t)kvh * G * D + idx] = __float2bfloat16_rn(0.f);
+    __syncthreads();
+    leave();
     return;
   }
   // tiles with visible keys, dealt out evenly over `eff` splits
@@ -88,7 +99,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
   const int total = tile_last - tile_first + 1;
   const int per = (total + a.nsplit - 1) / a.nsplit;
   const int eff = (total + per - 1) / per;
-  if (split >= eff) return;
+  if (split >= eff) {
+    leave();
+    return;
+  }
   const int base = total / eff, rem = total % eff;
   const int my_first = tile_first + split * base + min(split, rem);
   const int n_tiles = base + (split < rem ? 1 : 0);              // >= 1
@@ -97,6 +111,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
 
   if ((smem_u32(smem) & 1023u) != 0) {                           // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(a.status, 0, 9);
+    __syncthreads();
+    leave();
     return;
   }
   if (threadIdx.x == 0) {
@@ -182,7 +198,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
     }
   }
   __syncthreads();
-  if (*abort_flag) return;
+  if (*abort_flag) {
+    leave();
+    return;
+  }
 
   // merge the four warps' states through shared memory (every fetched tile has been consumed)
   float* m_s = reinterpret_cast<float*>(smem);                     // [CWARPS][16]
@@ -208,6 +227,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
   float* f_s = o_s + CWARPS * 16 * D;                              // [CWARPS][16]
   float* M_s = f_s + CWARPS * 16;                                  // [16]
   float* L_s = M_s + 16;                                           // [16]
+  float* c_acc = L_s + 16;                                         // [G][D], read by the cluster's blocks
   if ((int)threadIdx.x < cw * G) {
     const int v = threadIdx.x / G, g = threadIdx.x % G;
     float M = -INFINITY;
@@ -239,13 +259,59 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
       bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)h * D + d;
       *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
       *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    } else if (a.cluster) {
+      *reinterpret_cast<float4*>(c_acc + g * D + d) = acc;
     } else {
       const size_t pi = ((size_t)b * a.H + h) * a.nsplit + split;
       *reinterpret_cast<float4*>(a.part_acc + pi * D + d) = acc;
       if (d == 0) *reinterpret_cast<float2*>(a.part_ml + pi * 2) = make_float2(M_s[g], L_s[g]);
     }
   }
-  if (eff == 1) return;
+  if (eff == 1) {
+    __syncthreads();
+    leave();
+    return;
+  }
+
+  if (a.cluster) {
+    // Block `split` finishes the 16-byte pieces split, split + eff, ... of the output out of the
+    // shared memory of the eff blocks that got tiles, in split order:
+    //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+    __syncthreads();
+    cluster_sync_all();
+    for (int piece = split + eff * (int)threadIdx.x; piece < G * (D / 4); piece += eff * THREADS) {
+      const int g = piece / (D / 4), d = (piece % (D / 4)) * 4;
+      float m[8], l[8];
+      float4 x[8];
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2)
+        if (s2 < eff) {
+          m[s2] = ld_peer_f32(peer_shared(M_s + g, s2));
+          l[s2] = ld_peer_f32(peer_shared(L_s + g, s2));
+          x[s2] = ld_peer_v4(peer_shared(c_acc + g * D + d, s2));
+        }
+      float M = -INFINITY;
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2)
+        if (s2 < eff) M = fmaxf(M, m[s2]);
+      float L = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2)
+        if (s2 < eff) {
+          const float f = (m[s2] == -INFINITY) ? 0.f : exp2f(m[s2] - M);
+          L += l[s2] * f;
+          acc.x += x[s2].x * f; acc.y += x[s2].y * f; acc.z += x[s2].z * f; acc.w += x[s2].w * f;
+        }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)(kvh * G + g) * D + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    }
+    __syncthreads();
+    cluster_sync_all();                                            // no block leaves while a peer still reads it
+    return;
+  }
 
   // The block that finishes last for this (request, kv head) merges all splits, in split order:
   //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
@@ -351,7 +417,33 @@ int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t 
     configured = smem;
   }
   const int threads = ((a.stages < CWARPS ? a.stages : CWARPS) + 1) * 32;
-  ts_launch(attention_decode_tma_kernel<D>, dim3(a.nsplit, a.KVH, B), dim3(threads), smem, s, kv_map, a);
+  // 2 to 8 splits: one thread-block cluster per (request, kv head), if the device can hold one
+  DecArgs b = a;
+  b.cluster = 0;
+  if (ts_clusters_enabled() && a.nsplit >= 2 && a.nsplit <= 8) {
+    static int known[MAX_STAGES + 1][9];                           // 0: not asked, 1: fits, 2: does not
+    int& k = known[a.stages][a.nsplit];
+    if (k == 0) {
+      k = 2;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(a.nsplit, 1, 1);
+      cfg.blockDim = dim3(threads);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)a.nsplit;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_tma_kernel<D>, &cfg) == cudaSuccess && clusters >= 1) k = 1;
+      cudaGetLastError();                                          // a refusal is an answer, not an error
+    }
+    b.cluster = (k == 1);
+  }
+  ts_launch_cluster(attention_decode_tma_kernel<D>, dim3(b.cluster ? a.nsplit : 1, 1, 1), dim3(a.nsplit, a.KVH, B),
+                    dim3(threads), smem, s, kv_map, b);
   TS_LAUNCH_CHECK();
 }
 
@@ -414,7 +506,7 @@ TS_API int ts_attention_decode_tma(void* out, void* scratch, int* counters, cons
   // the merges reuse the stage buffers: 3 * G * nsplit floats and (2 + D) * 64 floats must fit
   const int G = H / KVH;
   const size_t smem = (size_t)stages * 2 * TILE * D * 2;
-  if (sizeof(float) * 3 * G * nsplit > smem || sizeof(float) * ((3 + D) * CWARPS * 16 + 32) > smem)
+  if (sizeof(float) * 3 * G * nsplit > smem || sizeof(float) * ((3 + D) * CWARPS * 16 + 32 + 16 * D) > smem)
     TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: %d stages are too few for the merge buffers", stages);
   int* status = dec_status_word();
   if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_tma: no status word");
