@@ -14,7 +14,9 @@
 // (triton_prefill_attention.py:58).  Warps keep independent online-softmax states over disjoint
 // keys and merge them through shared memory at the end; with more than one split the block
 // writes an unnormalised partial (m, l, acc) to scratch, and the block that finishes last for a
-// (request, kv head) merges the partials (no second launch, no waiting: a ticket counter).
+// (request, kv head) merges the partials (no second launch, no waiting: a ticket counter).  With 2,
+// 4 or 8 splits (16 in a launch of few blocks) the splits are one thread-block cluster instead: the
+// partial stays in shared memory and every block sums its share of the output out of its peers'.
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include "no_alloc.h"

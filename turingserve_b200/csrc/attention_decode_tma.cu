@@ -20,7 +20,10 @@
 // O += P V, and hands the stage back.  No block-wide barrier and no per-thread address
 // arithmetic in the loop.  The warps' states merge through shared memory; with several splits the
 // block writes an unnormalised partial and the block that finishes last for a (request, kv head)
-// merges them (a ticket counter: no second launch, nobody waits).
+// merges them (a ticket counter: no second launch, nobody waits).  With 2 to 8 splits the blocks of
+// a (request, kv head) are one thread-block cluster instead: the partial stays in shared memory and
+// block r sums the 16-byte pieces r, r + n, ... of the output out of its peers' (two cluster
+// barriers, which blocks that leave early take too).
 //
 // Before the wait for the preceding kernel the producer already fetches every box of its first
 // stages except the one holding the new token's row: the step's index arrays come from the host
