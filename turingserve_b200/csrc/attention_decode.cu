@@ -401,8 +401,8 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   }
 }
 
-// Whether the splits may be one cluster: 2, 4, 8 or 16 of them, and the device can hold such a cluster
-// of this kernel (asked once per size).  0: no, 1: yes.
+// How many clusters of `nsplit` blocks of this kernel the device holds at once (asked once per size);
+// 0 when the splits cannot be one cluster (not 2, 4, 8 or 16 of them, or the device refuses).
 template <int D>
 int cluster_ok(int nsplit, size_t smem) {
   static int known[5] = {-1, -1, -1, -1, -1};                      // by log2(nsplit)
@@ -428,7 +428,7 @@ int cluster_ok(int nsplit, size_t smem) {
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int clusters = 0;
-      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[idx] = 1;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[idx] = clusters;
     }
     cudaGetLastError();                                            // a refusal above is an answer, not an error
   }
@@ -451,9 +451,10 @@ int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, c
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  // Clusters of 16 are worth it only while there are a handful of them: a step with 16 of them was
-  // a sixth slower than with the ticket merge (they fit few places on the chip), one with 2 faster.
-  if (ts_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && cluster_ok<D>(nsplit, smem))
+  // Clusters only while all of them fit the chip at once: a launch whose clusters come in two waves
+  // loses more than the merge gains (16 clusters of 16 blocks: a step a sixth slower than with the
+  // ticket; they fit few places on the chip).  Clusters of 16 only while there are a handful.
+  if (ts_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && B * KVH <= cluster_ok<D>(nsplit, smem))
     ts_launch_cluster(attention_decode_kernel<D, true>, dim3(nsplit, 1, 1), dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
         out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
         scale, window, nsplit, counters);

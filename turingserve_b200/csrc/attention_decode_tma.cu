@@ -420,32 +420,42 @@ int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t 
     configured = smem;
   }
   const int threads = ((a.stages < CWARPS ? a.stages : CWARPS) + 1) * 32;
-  // 2 to 8 splits: one thread-block cluster per (request, kv head), if the device can hold one
+  // Up to 8 splits can be one thread-block cluster per (request, kv head), but only while all clusters
+  // fit the chip at once: clusters that come in two waves lose more than the merge gains (batch 24 x
+  // 2 kv heads: clusters of 6 25 us, 6 splits with the ticket 21 us, clusters of 4 17 us).  So: the
+  // largest count from the wanted one down to 0.6 of it whose clusters all fit; none: the ticket.
   DecArgs b = a;
   b.cluster = 0;
-  if (ts_clusters_enabled() && a.nsplit >= 2 && a.nsplit <= 8) {
-    static int known[MAX_STAGES + 1][9];                           // 0: not asked, 1: fits, 2: does not
-    int& k = known[a.stages][a.nsplit];
-    if (k == 0) {
-      k = 2;
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(a.nsplit, 1, 1);
-      cfg.blockDim = dim3(threads);
-      cfg.dynamicSmemBytes = smem;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = (unsigned)a.nsplit;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      int clusters = 0;
-      if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_tma_kernel<D>, &cfg) == cudaSuccess && clusters >= 1) k = 1;
-      cudaGetLastError();                                          // a refusal is an answer, not an error
+  if (ts_clusters_enabled() && a.nsplit >= 2) {
+    static int known[MAX_STAGES + 1][9];                           // 0: not asked, -1: no cluster, else how many fit at once
+    const int pairs = B * a.KVH;
+    for (int n = a.nsplit < 8 ? a.nsplit : 8; n >= 2 && 10 * n >= 6 * a.nsplit; --n) {
+      int& k = known[a.stages][n];
+      if (k == 0) {
+        k = -1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n, 1, 1);
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)n;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_tma_kernel<D>, &cfg) == cudaSuccess && clusters >= 1) k = clusters;
+        cudaGetLastError();                                        // a refusal is an answer, not an error
+      }
+      if (k >= pairs) {
+        b.cluster = 1;
+        b.nsplit = n;
+        break;
+      }
     }
-    b.cluster = (k == 1);
   }
-  ts_launch_cluster(attention_decode_tma_kernel<D>, dim3(b.cluster ? a.nsplit : 1, 1, 1), dim3(a.nsplit, a.KVH, B),
+  ts_launch_cluster(attention_decode_tma_kernel<D>, dim3(b.cluster ? b.nsplit : 1, 1, 1), dim3(b.nsplit, a.KVH, B),
                     dim3(threads), smem, s, kv_map, b);
   TS_LAUNCH_CHECK();
 }

@@ -477,12 +477,12 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmA
   TS_LAUNCH_CHECK();
 }
 
-// Whether `splits` blocks of this kernel can be one cluster on this device (asked once per count).
+// How many clusters of `splits` blocks of this kernel the device holds at once (asked once per count; 0: none).
 template <int BN, int STAGES, bool SWAP, int KSUB = 1>
-bool cluster_fits(int splits) {
+int cluster_fits(int splits) {
   constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
   static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
-  if (splits < 2 || splits > 8) return false;
+  if (splits < 2 || splits > 8) return 0;
   if (known[splits] < 0) {
     known[splits] = 0;
     auto kernel = gemm_tc_kernel<BN, STAGES, SWAP, KSUB>;
@@ -499,11 +499,11 @@ bool cluster_fits(int splits) {
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int clusters = 0;
-      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[splits] = 1;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1) known[splits] = clusters;
     }
     cudaGetLastError();                              // a refusal above is an answer, not an error
   }
-  return known[splits] == 1;
+  return known[splits];
 }
 
 }  // namespace
@@ -702,7 +702,7 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
   const dim3 cl(1, 1, splits);
 #define TS_ROPE_LAUNCH(...)                                           \
   do {                                                                \
-    if (want_cluster && cluster_fits<__VA_ARGS__>(splits)) {          \
+    if (want_cluster && (int)(grid.x * grid.y) <= cluster_fits<__VA_ARGS__>(splits)) { \
       a.rope = 2;                                                     \
       return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s, cl); \
     }                                                                 \
