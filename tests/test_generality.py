@@ -1,5 +1,6 @@
 """(c)'s generality: parts chosen layer by layer, a mixer with state of its own registered from
-the test, a position-free layer, partial rotary, a layer that runs twice, a run that reads another
+the test, a feed-forward that routes and a position encoding registered from the test, a
+position-free layer, partial rotary, a layer that runs twice, a run that reads another
 run's cache, two cache groups.  Runs on the CPU with the kernel twins and, marked gpu, on the GPU."""
 
 from __future__ import annotations
@@ -18,21 +19,21 @@ from turingserve_b200.engine.replay import Replayer
 from turingserve_b200.weights import write_random_model
 
 
-def _toy_folder(tmp_path):
+def _toy_folder(tmp_path, c=toy.TOY):
     folder = str(tmp_path / "toy")
-    write_random_model(folder, toy.make(toy.TOY), seed=5, std=0.1)
+    write_random_model(folder, toy.make(c), seed=5, std=0.1)
     return folder
 
 
-def _run_toy(folder, device, dtype, tol):
+def _run_toy(folder, device, dtype, tol, c=toy.TOY, groups=2, states=2):
     cfg_json, w = plain.read_folder(folder)
-    reqs = {f"r{i}": tiny.random_ids(n, toy.TOY["vocab"], 50 + i) for i, n in enumerate([40, 7, 61, 23, 35])}
-    expected = {rid: toy.plain_forward(toy.TOY, w, t).numpy() for rid, t in reqs.items()}
+    reqs = {f"r{i}": tiny.random_ids(n, c["vocab"], 50 + i) for i, n in enumerate([40, 7, 61, 23, 35])}
+    expected = {rid: toy.plain_forward(c, w, t).numpy() for rid, t in reqs.items()}
     for sched in ("whole", "decode_tail", "portions", "mixed"):
         steps = getattr(schedules, sched)(reqs)
         rp = Replayer(folder, dtype, schedules.peak_tokens(steps), device, page_size=8)
-        assert len(rp.cache.groups) == 2, "full and windowed attention runs live in separate groups"
-        assert sum(s is not None for s in rp.cache.states) == 2, "the running-mean layer runs twice: two states"
+        assert len(rp.cache.groups) == groups, "full and windowed attention runs live in separate groups"
+        assert sum(s is not None for s in rp.cache.states) == states, "one state per run of a running-mean layer"
         outs = {}
         with torch.inference_mode():
             for s in steps:
@@ -58,6 +59,16 @@ def test_toy_architecture_on_cpu(tmp_path):
 def test_toy_architecture_on_gpu(tmp_path, dtype, tol):
     kernels.use(None)
     _run_toy(_toy_folder(tmp_path), "cuda", dtype, tol)
+
+
+def test_toy_with_routed_feed_forward_and_its_own_position_encoding_on_cpu(tmp_path):
+    """A feed-forward with routing and a position encoding, both registered by the test, are built from
+    the configuration layer by layer and stepped like the built-in parts."""
+    kernels.use(TwinOps())
+    try:
+        _run_toy(_toy_folder(tmp_path, toy.TOY_ROUTED), "cpu", torch.float32, 1e-4, toy.TOY_ROUTED, groups=1, states=1)
+    finally:
+        kernels.use(None)
 
 
 def test_schedule_that_repeats_and_shares_on_qwen2(tmp_path):

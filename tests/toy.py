@@ -1,7 +1,8 @@
 """A toy architecture defined entirely in the test-suite: it registers a mixer with per-request state
-of its own (a running mean), a position-free attention layer, and a run schedule that names a
-layer twice and lets a run read another run's cache.  Nothing under ``turingserve_b200`` knows
-about it; it is no model of anyone's.
+of its own (a running mean), a feed-forward that routes every token to one of several small
+experts, a position encoding of its own (rotation by a fraction of the position), a position-free
+attention layer, and a run schedule that names a layer twice and lets a run read another run's
+cache.  Nothing under ``turingserve_b200`` knows about it; it is no model of anyone's.
 """
 
 from __future__ import annotations
@@ -14,7 +15,7 @@ import torch.nn.functional as F
 from turingserve_b200.config.model_config import (
     AttentionSpec, GatedMLPSpec, LayerRun, LayerSpec, ModelConfig, RMSNormSpec, RotarySpec)
 from turingserve_b200.config.registry import Architecture, LayerTensorNames, TensorNames, register_architecture
-from turingserve_b200.parts.base import BuildContext, Mixer, ParamSpec, StateNeed, register
+from turingserve_b200.parts.base import BuildContext, FeedForward, Mixer, ParamSpec, StateNeed, register
 
 NAME = "ToyStateLM"
 
@@ -64,19 +65,101 @@ class RunningMeanMixer(Mixer):
 register("mixer", "running_mean", RunningMeanMixer)
 
 
+@dataclass(frozen=True)
+class OneOfExpertsSpec:
+    """y = p_e(x) . down_e(silu(gate_e(x)) * up_e(x)) for the expert e with the largest router logit;
+    p = softmax of the router logits, in 32-bit."""
+
+    num_experts: int
+    intermediate_size: int
+    kind: str = "one_of_experts"
+
+
+class OneOfExperts(FeedForward):
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.h, self.n, self.inter = ctx.hidden_size, int(spec.num_experts), int(spec.intermediate_size)
+        self.t = None
+
+    def parameters(self):
+        p = {"router.weight": ParamSpec((self.n, self.h), compute_dtype=False)}
+        for e in range(self.n):
+            p[f"experts.{e}.gate_proj.weight"] = ParamSpec((self.inter, self.h))
+            p[f"experts.{e}.up_proj.weight"] = ParamSpec((self.inter, self.h))
+            p[f"experts.{e}.down_proj.weight"] = ParamSpec((self.h, self.inter))
+        return p
+
+    def load(self, t):
+        self.t = t
+
+    def forward(self, x):
+        probs = F.linear(x.float(), self.t["router.weight"].float()).softmax(-1)       # 32-bit routing
+        weight, choice = probs.max(-1)
+        out = torch.zeros_like(x)
+        for e in range(self.n):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            xe = x[rows]
+            g = F.linear(xe, self.t[f"experts.{e}.gate_proj.weight"])
+            u = F.linear(xe, self.t[f"experts.{e}.up_proj.weight"])
+            y = F.linear(F.silu(g) * u, self.t[f"experts.{e}.down_proj.weight"])
+            out[rows] = (y.float() * weight[rows, None]).to(x.dtype)
+        return out
+
+
+register("feed_forward", "one_of_experts", OneOfExperts)
+
+
+@dataclass(frozen=True)
+class SlowRotarySpec:
+    """Rotate-half rotation whose angle is position / slowdown times the usual frequency."""
+
+    theta: float
+    rotary_dim: int
+    max_positions: int
+    slowdown: float
+    kind: str = "slow_rope"
+
+
+class SlowRotary:
+    """What the attention mixer asks of a position encoding: rotary_dim and 32-bit cos / sin tables
+    [positions, rotary_dim / 2] on the device."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.rotary_dim = int(spec.rotary_dim)
+        n = min(int(spec.max_positions), ctx.max_positions) if ctx.max_positions else int(spec.max_positions)
+        self.max_positions = n
+        self.cos, self.sin = (t.to(ctx.device).contiguous()
+                              for t in slow_tables(self.rotary_dim, float(spec.theta), n, float(spec.slowdown)))
+
+
+def slow_tables(rot: int, theta: float, n: int, slowdown: float):
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    freqs = torch.outer(torch.arange(n).float() / slowdown, inv_freq)
+    return freqs.cos(), freqs.sin()
+
+
+register("position", "slow_rope", SlowRotary)
+
+
 def parse_config(c: dict, gen=None) -> ModelConfig:
     h, heads, kv, d = c["width"], c["heads"], c["kv_heads"], c["head_size"]
     norm = RMSNormSpec(eps=c["eps"])
-    ffn = GatedMLPSpec(intermediate_size=c["ffn_width"])
+    dense = GatedMLPSpec(intermediate_size=c["ffn_width"])
     rope = RotarySpec(theta=c["theta"], rotary_dim=c.get("rotary_dim", d), max_positions=c["max_positions"])
+    slow = SlowRotarySpec(theta=c["theta"], rotary_dim=c.get("rotary_dim", d), max_positions=c["max_positions"],
+                          slowdown=c.get("slowdown", 1.0))
+    ffns = c.get("ffns", ["dense"] * len(c["mixers"]))
     layers = []
-    for kind in c["mixers"]:
+    for kind, ffn_kind in zip(c["mixers"], ffns):
         if kind == "mean":
             mixer = RunningMeanSpec()
         else:
+            position = None if kind == "nope" else (slow if kind == "slow" else rope)
             mixer = AttentionSpec(num_heads=heads, num_kv_heads=kv, head_dim=d, scale=c.get("scale", d ** -0.5),
-                                  qkv_bias=False, out_bias=True, position=None if kind == "nope" else rope,
+                                  qkv_bias=False, out_bias=True, position=position,
                                   window=c.get("window") if kind == "window" else None)
+        ffn = dense if ffn_kind == "dense" else OneOfExpertsSpec(c["experts"], c["expert_width"])
         layers.append(LayerSpec(mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm))
     schedule = tuple(LayerRun(l, f) for l, f in c.get("schedule", [(i, None) for i in range(len(layers))]))
     return ModelConfig(architecture=NAME, hidden_size=h, vocab_size=c["vocab"], layers=tuple(layers),
@@ -117,14 +200,26 @@ def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
     d, H, KVH = c["head_size"], c["heads"], c["kv_heads"]
     rot = c.get("rotary_dim", d)
     cos, sin = plain.rope_tables(rot, c["theta"], T)
+    slow_cos, slow_sin = slow_tables(rot, c["theta"], T, c.get("slowdown", 1.0))
+    ffns = c.get("ffns", ["dense"] * len(c["mixers"]))
     pos = torch.arange(T)
     kept = []
     schedule = c.get("schedule", [(i, None) for i in range(len(c["mixers"]))])
 
-    def rope(t):
+    def rope(t, cs, sn):
         if rot == d:
-            return plain.apply_rope(t, pos, cos, sin)
-        return torch.cat([plain.apply_rope(t[..., :rot], pos, cos, sin), t[..., rot:]], dim=-1)
+            return plain.apply_rope(t, pos, cs, sn)
+        return torch.cat([plain.apply_rope(t[..., :rot], pos, cs, sn), t[..., rot:]], dim=-1)
+
+    def experts(x, p):
+        probs = F.linear(x, w[p + "router.weight"]).softmax(-1)
+        weight, choice = probs.max(-1)
+        rows = []
+        for t in range(x.shape[0]):
+            e = f"{p}experts.{int(choice[t])}."
+            rows.append(weight[t] * plain.mlp(x[t:t + 1], w[e + "gate_proj.weight"], w[e + "up_proj.weight"],
+                                              w[e + "down_proj.weight"])[0])
+        return torch.stack(rows)
 
     for layer, cache_from in schedule:
         p = f"blocks.{layer}."
@@ -138,8 +233,10 @@ def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
             q = F.linear(x, w[p + "mix.q_proj.weight"]).view(T, H, d)
             k = F.linear(x, w[p + "mix.k_proj.weight"]).view(T, KVH, d)
             v = F.linear(x, w[p + "mix.v_proj.weight"]).view(T, KVH, d)
-            if kind != "nope":
-                q, k = rope(q), rope(k)
+            if kind == "slow":
+                q, k = rope(q, slow_cos, slow_sin), rope(k, slow_cos, slow_sin)
+            elif kind != "nope":
+                q, k = rope(q, cos, sin), rope(k, cos, sin)
             if cache_from is not None:
                 k, v = kept[cache_from]
             kept.append((k, v))
@@ -147,7 +244,10 @@ def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
             a = F.linear(a, w[p + "mix.o_proj.weight"], w[p + "mix.o_proj.bias"])
         h = h + a
         x = plain.rmsnorm(h, w[p + "norm_b.weight"], c["eps"])
-        h = h + plain.mlp(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        if ffns[layer] == "dense":
+            h = h + plain.mlp(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        else:
+            h = h + experts(x, p + "ffn.")
     return F.linear(plain.rmsnorm(h, w["norm_out.weight"], c["eps"]), w["head.weight"]).float()
 
 
@@ -155,3 +255,9 @@ TOY = {"width": 48, "heads": 6, "kv_heads": 2, "head_size": 16, "rotary_dim": 8,
        "eps": 2e-5, "theta": 777.0, "max_positions": 300, "window": 9, "scale": 0.3,
        "mixers": ["rope", "mean", "window", "nope"],
        "schedule": [(0, None), (1, None), (2, None), (0, None), (3, None), (3, 4), (1, None)]}
+
+# A second toy: a routed feed-forward in two of its layers and the slowed rotation in one.  Compared in
+# 32-bit only: in bfloat16 a token whose two best router logits nearly tie may go to the other expert.
+TOY_ROUTED = {"width": 40, "heads": 4, "kv_heads": 1, "head_size": 32, "ffn_width": 56, "vocab": 157,
+              "eps": 1e-5, "theta": 5000.0, "max_positions": 200, "slowdown": 3.5, "experts": 3, "expert_width": 24,
+              "mixers": ["slow", "mean", "rope"], "ffns": ["experts", "dense", "experts"]}
