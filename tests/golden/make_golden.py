@@ -1,7 +1,7 @@
 """Compares the plain implementation (tests/plain_qwen2.py) ONCE with the reference's own model
 code on tiny random models, and stores the reference's outputs beside this script.
 
-    python tests/golden/make_golden.py [/path/to/TuringServe]
+    python tests/golden/make_golden.py /path/to/TuringServe
 
 It imports ``turingserve`` from the given checkout (CPU, float32, ``get_ops("reference")``), builds
 each tiny model folder with this repository's random-weights writer, runs the reference's
@@ -26,7 +26,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/TuringServe")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 sys.path.insert(0, ROOT)              # this repository's ``tests`` package wins over the reference's
 
