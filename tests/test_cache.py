@@ -56,7 +56,7 @@ def test_groups_are_formed_by_need_and_shared_runs_own_nothing():
     assert v0.group == 0 and v0.writable and v1.group == 1
     assert v3.group == 1 and not v3.writable and v3.k.data_ptr() == v1.k.data_ptr()
     assert v4 is None
-    assert m.states[4].shape == (3, 3) and m.states[5].shape == (3, 2, 2) and m.states[0] is None
+    assert m.states[4].shape == (4, 3) and m.states[5].shape == (4, 2, 2) and m.states[0] is None  # 3 requests + the null slot
     with pytest.raises(ValueError, match="has none"):
         CacheManager([RunNeeds(None, None), RunNeeds(FULL, None, cache_from=0)], 8, 4, 2)
 

@@ -71,6 +71,64 @@ def test_toy_with_routed_feed_forward_and_its_own_position_encoding_on_cpu(tmp_p
         kernels.use(None)
 
 
+def test_toy_with_a_third_norm_and_a_model_class_of_its_own_on_cpu(tmp_path):
+    """A block arrangement that names a part in a role the built-in one does not have (a third norm,
+    with its own checkpoint prefix), and a model class registered with the architecture that scales the
+    embeddings and caps the logits: built, loaded and stepped without a change to the framework."""
+    kernels.use(TwinOps())
+    try:
+        c = toy.TOY_SANDWICH
+        folder = _toy_folder(tmp_path, c)
+        from safetensors import safe_open
+        with safe_open(os.path.join(folder, "model.safetensors"), "pt") as f:
+            assert "blocks.1.norm_mid.weight" in set(f.keys())
+        _run_toy(folder, "cpu", torch.float32, 1e-4, c, groups=1, states=1)
+    finally:
+        kernels.use(None)
+
+
+@pytest.mark.gpu
+def test_toy_with_a_third_norm_and_a_model_class_of_its_own_on_gpu(tmp_path):
+    kernels.use(None)
+    c = toy.TOY_SANDWICH
+    _run_toy(_toy_folder(tmp_path, c), "cuda", torch.float32, 1e-4, c, groups=1, states=1)
+    _run_toy(_toy_folder(tmp_path, c), "cuda", torch.bfloat16, 0.06, c, groups=1, states=1)
+
+
+def test_padding_rows_of_a_captured_batch_leave_live_state_alone(tmp_path):
+    """A decode batch padded to a captured size: the padding rows carry the null state slot, so a
+    mixer with state of its own neither reads nor resets the state of the request in slot 0."""
+    from turingserve_b200.engine.batch import StepEntry
+    from turingserve_b200.engine.runner import ModelRunner, run_needs
+    from turingserve_b200.cache import CacheManager
+    from turingserve_b200.weights.loader import load_model
+    kernels.use(TwinOps())
+    try:
+        c = toy.TOY
+        folder = _toy_folder(tmp_path)
+        _, w = plain.read_folder(folder)
+        model, cfg = load_model(folder, torch.float32, "cpu")
+        cache = CacheManager(run_needs(model), 8, 40, 4, torch.float32, "cpu")
+        runner = ModelRunner(model, cache, 64, 4, 128)
+        ids = tiny.random_ids(12, c["vocab"], 3)
+        rc = cache.admit("a")
+        assert rc.slot == 0 and cache.null_slot == 4
+        with torch.inference_mode():
+            runner.step([StepEntry(rc, ids[:9], [])])
+            rows = []
+            for t in ids[9:]:
+                entries = [StepEntry(rc, [t], [0])]
+                cache.grow(rc, 1)
+                step = runner.builder.build(entries, pad_requests=3)
+                assert step.state_slots.tolist() == [0, 4, 4, 4] and step.num_requests == 4
+                rows.append(runner.forward(step)[0])
+                cache.advance(rc, 1)
+        want = toy.plain_forward(c, w, ids)[9:]
+        assert (torch.stack(rows) - want).abs().max() < 1e-4
+    finally:
+        kernels.use(None)
+
+
 def test_schedule_that_repeats_and_shares_on_qwen2(tmp_path):
     """The run order is data: the same Qwen2 weights with a layer run twice and a shared cache."""
     from turingserve_b200.config import LayerRun

@@ -2,7 +2,9 @@
 of its own (a running mean), a feed-forward that routes every token to one of several small
 experts, a position encoding of its own (rotation by a fraction of the position), a position-free
 attention layer, and a run schedule that names a layer twice and lets a run read another run's
-cache.  Nothing under ``turingserve_b200`` knows about it; it is no model of anyone's.
+cache; a block arrangement with a third norm (a part in a role the built-in arrangement does not
+have) and a model class that scales its embeddings and caps its logits, registered with the
+architecture.  Nothing under ``turingserve_b200`` knows about it; it is no model of anyone's.
 """
 
 from __future__ import annotations
@@ -15,7 +17,9 @@ import torch.nn.functional as F
 from turingserve_b200.config.model_config import (
     AttentionSpec, GatedMLPSpec, LayerRun, LayerSpec, ModelConfig, RMSNormSpec, RotarySpec)
 from turingserve_b200.config.registry import Architecture, LayerTensorNames, TensorNames, register_architecture
-from turingserve_b200.parts.base import BuildContext, FeedForward, Mixer, ParamSpec, StateNeed, register
+from turingserve_b200 import kernels
+from turingserve_b200.parts.base import BuildContext, FeedForward, Mixer, ParamSpec, StateNeed, build, register
+from turingserve_b200.parts.model import DecoderModel
 
 NAME = "ToyStateLM"
 
@@ -142,6 +146,49 @@ def slow_tables(rot: int, theta: float, n: int, slowdown: float):
 register("position", "slow_rope", SlowRotary)
 
 
+class SandwichBlock:
+    """h += after(mixer(before(h))); h += ffn(norm(h)): a third norm, in a role of its own
+    ("mixer_after_norm"), and residual adds done on the spot instead of deferred."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.before = build("norm", spec.mixer_norm, ctx)
+        self.mixer = build("mixer", spec.mixer, ctx)
+        self.after = build("norm", spec.mixer_after_norm, ctx)
+        self.ffn_norm = build("norm", spec.ffn_norm, ctx)
+        self.feed_forward = build("feed_forward", spec.feed_forward, ctx)
+
+    def parts(self):
+        return {"mixer_norm": self.before, "mixer": self.mixer, "mixer_after_norm": self.after,
+                "ffn_norm": self.ffn_norm, "feed_forward": self.feed_forward}
+
+    @staticmethod
+    def _tensor(x):
+        ops = kernels.ops()
+        return ops.materialize(x) if hasattr(ops, "materialize") else x
+
+    def forward(self, h, residual, step, cache, state):
+        assert residual is None
+        a = self.mixer.forward(self.before.forward(h), step, cache, state)
+        h = h + self.after.forward(self._tensor(a))
+        h = h + self._tensor(self.feed_forward.forward(self.ffn_norm.forward(h)))
+        return h, None
+
+
+register("block", "sandwich", SandwichBlock)
+
+
+class ScaledModel(DecoderModel):
+    """The plain decoder with its embeddings multiplied by a constant and its logits capped by
+    cap * tanh(logits / cap); both constants come from the configuration's extras."""
+
+    def embed(self, step):
+        return (super().embed(step).float() * float(self.cfg.extra("embedding_multiplier", 1.0))).to(self.dtype)
+
+    def finish_logits(self, logits):
+        cap = self.cfg.extra("logit_cap")
+        return logits if cap is None else float(cap) * torch.tanh(logits / float(cap))
+
+
 def parse_config(c: dict, gen=None) -> ModelConfig:
     h, heads, kv, d = c["width"], c["heads"], c["kv_heads"], c["head_size"]
     norm = RMSNormSpec(eps=c["eps"])
@@ -160,16 +207,23 @@ def parse_config(c: dict, gen=None) -> ModelConfig:
                                   qkv_bias=False, out_bias=True, position=position,
                                   window=c.get("window") if kind == "window" else None)
         ffn = dense if ffn_kind == "dense" else OneOfExpertsSpec(c["experts"], c["expert_width"])
-        layers.append(LayerSpec(mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm))
+        if c.get("arrangement", "pre_norm") == "sandwich":
+            layers.append(LayerSpec("sandwich", mixer=mixer, feed_forward=ffn, mixer_norm=norm,
+                                    mixer_after_norm=RMSNormSpec(eps=10 * c["eps"]), ffn_norm=norm))
+        else:
+            layers.append(LayerSpec(mixer=mixer, feed_forward=ffn, mixer_norm=norm, ffn_norm=norm))
     schedule = tuple(LayerRun(l, f) for l, f in c.get("schedule", [(i, None) for i in range(len(layers))]))
+    extras = tuple((k, c[k]) for k in ("embedding_multiplier", "logit_cap") if k in c)
     return ModelConfig(architecture=NAME, hidden_size=h, vocab_size=c["vocab"], layers=tuple(layers),
                        schedule=schedule, final_norm=norm, tie_word_embeddings=False,
-                       max_position_embeddings=c["max_positions"])
+                       max_position_embeddings=c["max_positions"], extras=extras)
 
 
 def tensor_names(cfg: ModelConfig) -> TensorNames:
     layers = tuple(LayerTensorNames(mixer=f"blocks.{i}.mix.", feed_forward=f"blocks.{i}.ffn.",
-                                    mixer_norm=f"blocks.{i}.norm_a.", ffn_norm=f"blocks.{i}.norm_b.")
+                                    mixer_norm=f"blocks.{i}.norm_a.", ffn_norm=f"blocks.{i}.norm_b.",
+                                    **({"mixer_after_norm": f"blocks.{i}.norm_mid."}
+                                       if "mixer_after_norm" in cfg.layers[i].roles else {}))
                    for i in range(len(cfg.layers)))
     return TensorNames(embedding="embed.weight", lm_head="head.weight", final_norm="norm_out.", layers=layers)
 
@@ -188,7 +242,7 @@ def make(c: dict) -> ModelConfig:
     return cfg
 
 
-register_architecture(Architecture(NAME, parse_config, tensor_names, to_config_json))
+register_architecture(Architecture(NAME, parse_config, tensor_names, to_config_json, build_model=ScaledModel))
 
 
 # -- a plain whole-sequence implementation of the toy model (for the tests only) ------------------------
@@ -196,7 +250,8 @@ def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
     from tests import plain_qwen2 as plain
     x_ids = torch.as_tensor(ids, dtype=torch.long)
     T = len(ids)
-    h = w["embed.weight"][x_ids]
+    h = w["embed.weight"][x_ids] * c.get("embedding_multiplier", 1.0)
+    sandwich = c.get("arrangement", "pre_norm") == "sandwich"
     d, H, KVH = c["head_size"], c["heads"], c["kv_heads"]
     rot = c.get("rotary_dim", d)
     cos, sin = plain.rope_tables(rot, c["theta"], T)
@@ -242,13 +297,18 @@ def plain_forward(c: dict, w: dict, ids: list[int]) -> torch.Tensor:
             kept.append((k, v))
             a = plain.attention(q, k, v, c.get("scale", d ** -0.5), c.get("window") if kind == "window" else None)
             a = F.linear(a, w[p + "mix.o_proj.weight"], w[p + "mix.o_proj.bias"])
+        if sandwich:
+            a = plain.rmsnorm(a, w[p + "norm_mid.weight"], 10 * c["eps"])
         h = h + a
         x = plain.rmsnorm(h, w[p + "norm_b.weight"], c["eps"])
         if ffns[layer] == "dense":
             h = h + plain.mlp(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
         else:
             h = h + experts(x, p + "ffn.")
-    return F.linear(plain.rmsnorm(h, w["norm_out.weight"], c["eps"]), w["head.weight"]).float()
+    logits = F.linear(plain.rmsnorm(h, w["norm_out.weight"], c["eps"]), w["head.weight"]).float()
+    if "logit_cap" in c:
+        logits = c["logit_cap"] * torch.tanh(logits / c["logit_cap"])
+    return logits
 
 
 TOY = {"width": 48, "heads": 6, "kv_heads": 2, "head_size": 16, "rotary_dim": 8, "ffn_width": 72, "vocab": 211,
@@ -261,3 +321,9 @@ TOY = {"width": 48, "heads": 6, "kv_heads": 2, "head_size": 16, "rotary_dim": 8,
 TOY_ROUTED = {"width": 40, "heads": 4, "kv_heads": 1, "head_size": 32, "ffn_width": 56, "vocab": 157,
               "eps": 1e-5, "theta": 5000.0, "max_positions": 200, "slowdown": 3.5, "experts": 3, "expert_width": 24,
               "mixers": ["slow", "mean", "rope"], "ffns": ["experts", "dense", "experts"]}
+
+# A third toy: every layer in the arrangement with three norms, embeddings scaled and logits capped by
+# the model class the architecture registers.
+TOY_SANDWICH = {"width": 56, "heads": 2, "kv_heads": 2, "head_size": 24, "ffn_width": 88, "vocab": 173,
+                "eps": 3e-6, "theta": 9000.0, "max_positions": 160, "arrangement": "sandwich",
+                "embedding_multiplier": 7.5, "logit_cap": 1.5, "mixers": ["rope", "mean", "nope"]}

@@ -12,9 +12,11 @@ Slot arithmetic as turingserve/kv/kv_manager.py:17-40:
 slot(pos) = table[pos // page] * page + pos % page; pages needed = ceil(tokens / page) - held.
 
 State slots: every live request owns one slot index in [0, max_requests); each run whose mixer
-declares a ``StateNeed`` has a tensor ``[max_requests, *shape]`` indexed by it.  A slot is zeroed
-when a request is admitted (so recompute after preemption starts clean).  The reference has no
-per-request state; the slot is assigned for every request even when no mixer uses it.
+declares a ``StateNeed`` has a tensor ``[max_requests + 1, *shape]`` indexed by it.  A slot is zeroed
+when a request is admitted (so recompute after preemption starts clean).  The extra last slot
+(``null_slot``) is never handed out: rows that only pad a batch to a captured size point at it, as
+their block tables point at the null page.  The reference has no per-request state; the slot is
+assigned for every request even when no mixer uses it.
 """
 
 from __future__ import annotations
@@ -106,8 +108,9 @@ class CacheManager:
                                         grp.need.head_dim), dtype=dtype, device=device)
             for r, n in enumerate(needs):
                 if n.state is not None:
-                    self.states[r] = torch.zeros((max_requests, *n.state.shape), dtype=n.state.dtype,
+                    self.states[r] = torch.zeros((max_requests + 1, *n.state.shape), dtype=n.state.dtype,
                                                  device=device)
+        self.null_slot = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.live: dict[str, RequestCache] = {}
 

@@ -67,20 +67,43 @@ class GatedMLPSpec:
     kind: str = "gated_mlp"
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: a mixer and a feed-forward, each behind a norm.
+    """One decoder layer: the spec of each of its parts under a ROLE name, and the arrangement that
+    wires them.
 
-    ``arrangement`` names how they are wired; "pre_norm" is
-    ``h += mixer(norm(h)); h += ffn(norm(h))`` with the residual add deferred into the next norm
-    (turingserve/model/qwen2.py:44-57).
+    The roles are whatever the arrangement asks for.  "pre_norm" wants ``mixer``, ``feed_forward``,
+    ``mixer_norm`` and ``ffn_norm``: ``h += mixer(norm(h)); h += ffn(norm(h))`` with the residual add
+    deferred into the next norm (turingserve/model/qwen2.py:44-57).  An arrangement registered
+    elsewhere may name others (a third norm, a second feed-forward); the same role names key the
+    checkpoint prefixes in ``LayerTensorNames``.  A role's spec reads as an attribute: ``spec.mixer``.
     """
 
-    mixer: Any
-    feed_forward: Any
-    mixer_norm: Any
-    ffn_norm: Any
-    arrangement: str = "pre_norm"
+    def __init__(self, arrangement: str = "pre_norm", **roles: Any) -> None:
+        if not roles:
+            raise ValueError("a layer needs at least one part")
+        object.__setattr__(self, "arrangement", arrangement)
+        object.__setattr__(self, "roles", dict(roles))
+
+    def __getattr__(self, role: str) -> Any:
+        try:
+            return self.__dict__["roles"][role]
+        except KeyError:
+            raise AttributeError(f"this layer has no part in role {role!r} (it has: "
+                                 f"{', '.join(self.__dict__.get('roles', {}))})") from None
+
+    def __setattr__(self, name: str, value: Any) -> None:
+        raise AttributeError("LayerSpec is immutable")
+
+    def __eq__(self, other: object) -> bool:
+        return (isinstance(other, LayerSpec) and self.arrangement == other.arrangement
+                and self.roles == other.roles)
+
+    def __hash__(self) -> int:
+        return hash((self.arrangement, tuple(sorted(self.roles))))
+
+    def __repr__(self) -> str:
+        inner = ", ".join(f"{k}={v!r}" for k, v in self.roles.items())
+        return f"LayerSpec(arrangement={self.arrangement!r}, {inner})"
 
 
 @dataclass(frozen=True)
@@ -108,6 +131,12 @@ class ModelConfig:
     max_position_embeddings: int
     eos_token_ids: tuple[int, ...] = ()
     bos_token_id: int | None = None
+    # constants of the architecture that no part's spec holds (what a model class registered with the
+    # architecture reads: an embedding multiplier, a cap on the logits); plain data from config.json
+    extras: tuple[tuple[str, Any], ...] = ()
+
+    def extra(self, key: str, default: Any = None) -> Any:
+        return dict(self.extras).get(key, default)
 
     def __post_init__(self) -> None:
         if not self.layers:
@@ -136,6 +165,8 @@ class ModelConfig:
 
 def spec_to_dict(spec: Any) -> Any:
     """Plain-data view of a spec tree (for logs and for the ``config`` key of the benchmark)."""
+    if isinstance(spec, LayerSpec):
+        return {"arrangement": spec.arrangement, **{k: spec_to_dict(v) for k, v in spec.roles.items()}}
     if is_dataclass(spec) and not isinstance(spec, type):
         return {f.name: spec_to_dict(getattr(spec, f.name)) for f in fields(spec)}
     if isinstance(spec, (tuple, list)):

@@ -15,14 +15,34 @@ from typing import Callable
 from turingserve_b200.config.model_config import ModelConfig
 
 
-@dataclass(frozen=True)
 class LayerTensorNames:
-    """Checkpoint prefixes of the four parts of one layer (each ends with '.' or is '')."""
+    """Checkpoint prefix of every part of one layer, by the part's role in the layer (the role
+    names of its ``LayerSpec``); each prefix ends with '.' or is ''.  ``names["mixer"]`` or
+    ``names.mixer``."""
 
-    mixer: str
-    feed_forward: str
-    mixer_norm: str
-    ffn_norm: str
+    def __init__(self, **prefixes: str) -> None:
+        self._prefixes = dict(prefixes)
+
+    def __getitem__(self, role: str) -> str:
+        try:
+            return self._prefixes[role]
+        except KeyError:
+            raise KeyError(f"the architecture names no checkpoint prefix for the layer part {role!r} "
+                           f"(named: {', '.join(self._prefixes)})") from None
+
+    def __getattr__(self, role: str) -> str:
+        if role.startswith("_"):
+            raise AttributeError(role)
+        try:
+            return self._prefixes[role]
+        except KeyError:
+            raise AttributeError(role) from None
+
+    def roles(self) -> tuple[str, ...]:
+        return tuple(self._prefixes)
+
+    def __repr__(self) -> str:
+        return f"LayerTensorNames({self._prefixes!r})"
 
 
 @dataclass(frozen=True)
@@ -44,6 +64,10 @@ class Architecture:
     tensor_names: Callable[[ModelConfig], TensorNames]
     # inverse of parse_config, used by the random-weights writer
     to_config_json: Callable[[ModelConfig], dict]
+    # the model class: called as build_model(cfg, dtype, device, max_positions); None = the plain
+    # decoder (turingserve_b200.parts.model.DecoderModel).  A family that scales its embeddings or
+    # caps its logits registers a subclass that overrides ``embed`` / ``finish_logits``.
+    build_model: Callable | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

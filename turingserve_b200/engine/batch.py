@@ -203,7 +203,7 @@ class StepInputBuilder:
             t += 1
             qs[b + 1] = t
             sl[b] = 0
-            ss[b] = 0
+            ss[b] = self.cache.null_slot
         host[o_sr:o_sr + S] = sample
         for i, (b, src) in enumerate(fb):
             if q_lens[b] != 1:

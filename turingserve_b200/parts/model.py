@@ -35,7 +35,7 @@ class DecoderModel:
             out[names.lm_head] = ParamSpec((c.vocab_size, c.hidden_size))
         for block, ln in zip(self.blocks, names.layers):
             for role, part in block.parts().items():
-                prefix = getattr(ln, role)
+                prefix = ln[role]
                 for local, spec in part.parameters().items():
                     out[prefix + local] = spec
         for local, spec in self.final_norm.parameters().items():
@@ -49,7 +49,7 @@ class DecoderModel:
         self.lm_head = self.embedding if c.tie_word_embeddings else tensors[names.lm_head].contiguous()
         for block, ln in zip(self.blocks, names.layers):
             for role, part in block.parts().items():
-                prefix = getattr(ln, role)
+                prefix = ln[role]
                 part.load({local: tensors[prefix + local] for local in part.parameters()})
         self.final_norm.load({local: tensors[names.final_norm + local]
                               for local in self.final_norm.parameters()})
@@ -64,16 +64,26 @@ class DecoderModel:
 
         ``cache_views[r]`` / ``states[r]``: the cache view and the state tensor of run r (or None).
         """
-        ops = kernels.ops()
-        h = torch.empty((step.num_tokens, self.cfg.hidden_size), dtype=self.dtype, device=self.device)
-        ops.embedding(h, self.embedding, step.input_ids)
+        h = self.embed(step)
         residual = None
         for r, run in enumerate(self.cfg.schedule):
             h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r])
         return self.final_norm.forward(h, residual)
 
+    def embed(self, step) -> torch.Tensor:
+        """The rows of the embedding table for the step's token ids, [T, hidden].  A model class that
+        scales or adds to its embeddings overrides this."""
+        h = torch.empty((step.num_tokens, self.cfg.hidden_size), dtype=self.dtype, device=self.device)
+        kernels.ops().embedding(h, self.embedding, step.input_ids)
+        return h
+
     def logits(self, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """fp32 logits [S, V] of the hidden rows named by ``rows`` (int32 indices on the device)."""
         out = torch.empty((rows.shape[0], self.cfg.vocab_size), dtype=torch.float32, device=self.device)
         kernels.ops().linear(out, hidden, self.lm_head, None, rows)
-        return out
+        return self.finish_logits(out)
+
+    def finish_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """What happens to the head's output before anyone sees it (nothing here; a cap or a scale in
+        a model class that overrides this)."""
+        return logits

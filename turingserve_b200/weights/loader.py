@@ -113,6 +113,6 @@ def load_model(model_dir: str, dtype: torch.dtype, device, max_positions: int | 
     cfg_json, gen = read_config_json(model_dir)
     arch = architecture_of(cfg_json)
     cfg = arch.parse_config(cfg_json, gen)
-    model = DecoderModel(cfg, dtype, device, max_positions or cfg.max_position_embeddings)
+    model = (arch.build_model or DecoderModel)(cfg, dtype, device, max_positions or cfg.max_position_embeddings)
     load_into(model, model_dir, arch.tensor_names(cfg))
     return model, cfg
