@@ -89,6 +89,37 @@ def mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, tail
     return steps
 
 
+def batched_tail(requests: dict[str, list[int]], tail: int = 24, seed: int = 0, max_live: int = 4) -> list[dict]:
+    """Up to ``max_live`` requests at a time: each one's head in a step of its own, then their last
+    ``tail`` tokens one a step, all live requests of a step decoding together but for some left out at
+    random.  These are the steps a captured decode graph serves: 1 to ``max_live`` single tokens, so a
+    graph of 4 is also run with 3 (a padding row)."""
+    rng = np.random.default_rng(seed)
+    steps = []
+    items = list(requests.items())
+    for base in range(0, len(items), max_live):
+        group = items[base:base + max_live]
+        at = {}
+        for rid, toks in group:
+            head = max(1, len(toks) - tail)
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[:head], "want": list(range(head))}],
+                          "end": [rid] if head == len(toks) else []})
+            if head < len(toks):
+                at[rid] = head
+        toks_of = dict(group)
+        while at:
+            ids = [rid for rid in at if len(at) == 1 or rng.random() < 0.8] or [next(iter(at))]
+            entries, end = [], []
+            for rid in ids:
+                entries.append({"id": rid, "tokens": [toks_of[rid][at[rid]]], "want": [0]})
+                at[rid] += 1
+                if at[rid] == len(toks_of[rid]):
+                    end.append(rid)
+                    del at[rid]
+            steps.append({"step": len(steps), "entries": entries, "end": end})
+    return steps
+
+
 def peak_tokens(steps: list[dict], round_to: int = 64) -> int:
     """The most tokens live requests hold at any time, each rounded up to ``round_to``."""
     held: dict[str, int] = {}

@@ -117,3 +117,13 @@ def test_engine_config_validation_and_cli():
             EngineConfig(**{"model": "m", **bad}).validate()
     assert EngineConfig(model="m").resolve_max_model_len(32768) == 4096
     assert EngineConfig(model="m").resolve_max_model_len(128) == 128
+
+
+def test_a_head_size_no_attention_kernel_takes_is_refused_when_the_model_is_built():
+    import torch
+
+    from turingserve_b200.parts.model import DecoderModel
+    cfg = qwen2.parse_config({**BASE, "hidden_size": 96, "num_attention_heads": 3, "head_dim": 272})
+    with pytest.raises(ValueError, match="head sizes up to 256"):
+        DecoderModel(cfg, torch.float32, "cpu", 16)
+    DecoderModel(qwen2.parse_config({**BASE, "head_dim": 256}), torch.float32, "cpu", 16)

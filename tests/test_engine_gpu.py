@@ -241,7 +241,7 @@ def test_seeded_sampling_is_reproducible_alone_and_in_a_batch(tmp_path):
 
 def test_real_layer_sizes_float32(tmp_path):
     """Two layers of the Qwen2.5-1.5B shape (1536 wide, 12 heads over 2 kv heads of 128, 8960 inner),
-    float32, in portions and decoded: logits within 1e-4 of the plain implementation."""
+    float32, under all four ways of cutting the work: logits within 1e-4 of the plain implementation."""
     from turingserve_b200.models.qwen2 import make_config
     from turingserve_b200.weights import write_random_model
     folder = str(tmp_path / "real")
@@ -251,7 +251,7 @@ def test_real_layer_sizes_float32(tmp_path):
     cfg, w = plain.read_folder(folder)
     reqs = {"a": tiny.random_ids(150, 2000, 1), "b": tiny.random_ids(90, 2000, 2)}
     expected = {k: plain.forward(cfg, w, v).numpy() for k, v in reqs.items()}
-    for sched in ("portions", "mixed"):
+    for sched in ("whole", "decode_tail", "portions", "mixed"):
         steps = getattr(schedules, sched)(reqs)
         kernel_page = 16
         from turingserve_b200.engine.replay import Replayer
@@ -285,8 +285,10 @@ def test_real_layer_sizes_bfloat16(tmp_path, page):
     reqs = {"a": tiny.random_ids(1100, 2000, 1), "b": tiny.random_ids(700, 2000, 2), "c": tiny.random_ids(90, 2000, 3)}
     expected = {k: plain.forward(cfg, w, v).numpy() for k, v in reqs.items()}
     kernels.use(None)
-    for sched in ("whole", "decode_tail", "mixed"):
+    for sched in ("whole", "decode_tail", "portions", "mixed"):
         steps = getattr(schedules, sched)(reqs)
+        if sched == "portions":                                      # long portions, or 1,900 tokens take 300 steps
+            steps = schedules.portions(reqs, sizes=(70, 2, 160, 33, 256, 5, 111, 2, 90, 40))
         rp = Replayer(folder, torch.bfloat16, schedules.peak_tokens(steps), "cuda", page_size=page)
         outs = {}
         with torch.inference_mode():

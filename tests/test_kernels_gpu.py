@@ -489,6 +489,75 @@ def test_linear_tensor_core(ops, M, N, K):
         ops.gemm_mode = DEFAULT_GEMM
 
 
+@pytest.mark.parametrize("M", [1, 8, 16])
+@pytest.mark.parametrize("N,K", [(151936, 1536), (75800, 320)])
+def test_linear_tensor_core_output_head(ops, M, N, K):
+    """The output head's shape (turingserve/model/qwen2.py:94-99: hidden states times the whole
+    vocabulary, 32-bit logits): at most 16 rows and so many outputs that the launch is several waves of
+    blocks, which is where the kernel runs with three stages and two blocks to an SM.  One vocabulary
+    that is no multiple of the tile's 128 rows.  Against float64, at every row and column."""
+    x, w = _rand((M, K), torch.bfloat16, 33, 1.0), _rand((N, K), torch.bfloat16, 34, 0.05)
+    assert -(-N // 128) >= 592
+    xd, wd = x.cuda(), w.cuda()
+    ref = (xd.double() @ wd.double().T).float()
+    ops.gemm_mode = "auto"
+    try:
+        out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        ops.linear(out32, xd, wd, None)
+        torch.testing.assert_close(out32, ref, atol=2e-3, rtol=1e-3)
+        rows = torch.arange(M - 1, -1, -1, dtype=torch.int32, device="cuda")       # the head gathers its rows
+        ops.linear(out32, xd, wd, None, rows)
+        torch.testing.assert_close(out32, ref.flip(0), atol=2e-3, rtol=1e-3)
+        out16 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        ops.linear(out16, xd, wd, None)
+        torch.testing.assert_close(out16.float(), ref, atol=3e-2, rtol=2e-2)
+        assert ops.tc_status() == 0
+    finally:
+        ops.gemm_mode = DEFAULT_GEMM
+
+
+def test_work_buffers_outlive_the_graphs_that_captured_them(ops):
+    """A product small enough for the first work buffer is captured in a graph; a larger one then makes
+    the buffer grow.  The old buffer is set aside, not freed, so the graph's replay still computes the
+    right thing (it reads and writes the old address)."""
+    from turingserve_b200.kernels import Deferred
+    M, N, K = 4, 1536, 8960
+    x, w = _rand((M, K), torch.bfloat16, 50).cuda(), _rand((N, K), torch.bfloat16, 51, 0.05).cuda()
+    nw = torch.ones(N, dtype=torch.bfloat16, device="cuda")
+    ref = torch.nn.functional.linear(x.float(), w.float())
+    ops.gemm_mode = "auto"
+    out, normed = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    if "partials" in ops._buffers:                         # start from a buffer of the first size
+        ops._outgrown.append(ops._buffers.pop("partials"))
+
+    def small():
+        d = ops.linear(out, x, w, None, may_defer=True)
+        assert isinstance(d, Deferred)
+        ops.rmsnorm(normed, d, nw, 1e-6)
+
+    small()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        small()
+    before = ops._buffers["partials"]
+    xb = _rand((128, K), torch.bfloat16, 52).cuda()       # ten splits of 128 x 1536 partial sums: twice the first buffer
+    ob = torch.empty((128, N), dtype=torch.bfloat16, device="cuda")
+    d = ops.linear(ob, xb, w, None, may_defer=True)
+    assert isinstance(d, Deferred) and d.splits * 128 * N > before.numel()
+    ops.materialize(d)
+    assert ops._buffers["partials"] is not before and any(b is before for b in ops._outgrown)
+    torch.cuda.empty_cache()
+    junk = [torch.full((1 << 20,), float("nan"), device="cuda") for _ in range(8)]     # whoever gets freed blocks next
+    normed.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    want = torch.empty((M, N), dtype=torch.bfloat16)
+    TwinOps().rmsnorm(want, ref.to(torch.bfloat16), nw.cpu(), 1e-6)
+    torch.testing.assert_close(normed.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+    assert all(torch.isnan(j).all() for j in junk)
+    assert ops.tc_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 1536, 1536), (8, 1536, 8960), (64, 200, 264), (128, 4104, 72)])
 def test_deferred_product_finished_by_the_norm(ops, M, N, K):
     """A few-token product may leave its split-K partial sums to the norm that consumes it; the

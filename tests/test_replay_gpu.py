@@ -50,13 +50,16 @@ def check(got, expected, dtype):
             assert bad is None, f"first wrong place (request, position, error): {bad}, bound {tol}"
 
 
-def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True):
+def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True, graphs=(), replayer=None):
     from turingserve_b200 import kernels
     from turingserve_b200.engine.replay import Replayer
     if fresh_ops:
         kernels.use(None)
     kernels.ops().gemm_mode = gemm
-    rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name))
+    rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name),
+                  graph_batch_sizes=graphs)
+    if replayer is not None:
+        replayer.append(rp)
     outs = {}
     with torch.inference_mode():
         for s in steps:
@@ -107,6 +110,63 @@ def test_schedules_on_the_tensor_core_attention_kernels(tmp_path, monkeypatch, n
     check(got, expected_logits(folder, reqs), "bfloat16")
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16"),
+                                        ("K", "bfloat16"), ("L", "bfloat16")])
+@pytest.mark.parametrize("schedule", ["batched_tail", "decode_tail", "mixed"])
+def test_captured_decode_graphs_give_the_same_logits(tmp_path, monkeypatch, name, schedule, dtype):
+    """The step that generation and the benchmark run: single-token steps replayed from captured CUDA
+    graphs of sizes 1, 2 and 4 (padding rows when 3 decode together, block tables at full width, launch
+    geometry for the longest context), the decode-attention choice flipping in the middle (one graph per
+    size and choice).  Logits at every position against the plain implementation, same bounds as without
+    graphs."""
+    from turingserve_b200 import kernels
+    from turingserve_b200.engine import batch
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = getattr(schedules, schedule)(reqs)
+    monkeypatch.setattr(batch, "STREAMING_DECODE_KEYS", 150)
+    held = []
+    got = replay_in_process(folder, name, steps, dtype, "auto", graphs=(1, 2, 4), replayer=held)
+    captured = set(held[0].runner._graphs)
+    sizes = {len(s["entries"]) for s in steps if all(len(e["tokens"]) == 1 for e in s["entries"])}
+    assert {sz for sz, _ in captured} >= {1 if 1 in sizes else min(sizes)}, captured
+    if schedule == "batched_tail":
+        assert 3 in sizes and {sz for sz, _ in captured} >= {1, 2, 4}, (sizes, captured)
+        assert {st for _, st in captured} == {False, True}, captured
+    assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
+    check(got, expected_logits(folder, reqs), dtype)
+    assert kernels.ops().tc_status() == 0
+
+
+@pytest.mark.parametrize("name", ["K", "L"])
+@pytest.mark.parametrize("schedule", ["whole", "decode_tail", "portions", "mixed", "batched_tail"])
+def test_fast_kernels_are_as_close_as_a_plain_bfloat16_run(tmp_path, name, schedule):
+    """The models that reach the tensor-core and TMA attention kernels cannot show their faults in
+    32-bit (those kernels are bfloat16 only), and 3 % of the largest logit is a loose bound on its own.
+    The yardstick here is the plain implementation itself run with bfloat16 weights and activations: the
+    engine's error against the 32-bit plain logits (median and 95th percentile over positions, and the
+    worst position) may not exceed 1.5 times that run's."""
+    from turingserve_b200 import kernels
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    cfg, w = plain.read_folder(folder)
+    _, w16 = plain.read_folder(folder, torch.bfloat16)
+    expected = expected_logits(folder, reqs)
+    steps = getattr(schedules, schedule)(reqs)
+    got = replay_in_process(folder, name, steps, "bfloat16", "auto",
+                            graphs=(1, 2, 4) if schedule == "batched_tail" else ())
+    for rid, toks in reqs.items():
+        scale = float(np.abs(expected[rid]).max())
+        yard = np.abs(plain.forward(cfg, w16, toks).float().numpy() - expected[rid]).max(1) / scale
+        errs = np.array([np.abs(got[rid][p] - expected[rid][p]).max() for p in range(len(toks))]) / scale
+        assert np.isfinite(errs).all()
+        if len(toks) >= 8:
+            assert np.median(errs) <= 1.5 * np.median(yard), (rid, float(np.median(errs)), float(np.median(yard)))
+            assert np.percentile(errs, 95) <= 1.5 * np.percentile(yard, 95), (rid, int(errs.argmax()))
+        assert errs.max() <= 1.5 * yard.max() + 1e-3, (rid, int(errs.argmax()), float(errs.max()), float(yard.max()))
+    assert kernels.ops().tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(tmp_path, dtype):
     """bin/trace_run as a subprocess: steps on stdin, `done <step>` after each, files in --out."""
@@ -117,7 +177,7 @@ def test_trace_run_program(tmp_path, dtype):
     out = tmp_path / f"out_{dtype}"
     p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
                           "--out", str(out), "--max-tokens", str(schedules.peak_tokens(steps)),
-                          "--block-size", str(tiny.page_size(name))],
+                          "--block-size", str(tiny.page_size(name))] + (["--graphs", "1,2"] if dtype == "bfloat16" else []),
                          stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
     for s in steps:
         p.stdin.write(json.dumps(s) + "\n")

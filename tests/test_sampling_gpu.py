@@ -167,3 +167,30 @@ def test_penalties_and_min_tokens_match_plain():
     torch.testing.assert_close(edited[0].cpu(), exp0, atol=1e-6, rtol=1e-6)
     torch.testing.assert_close(edited[2].cpu(), exp2, atol=1e-6, rtol=1e-6)
     assert torch.isinf(edited[1, list(stop)]).all()
+
+
+def test_status_words_travel_with_the_tokens():
+    """The draw copies the status words of the kernels with bounded waits out beside the tokens: all
+    zero after healthy kernels; a word that a kernel set (here: set through the test hook, in stream
+    order, as a block that gave up would) arrives with the very next draw, greedy or not."""
+    from turingserve_b200 import kernels
+    kernels.use(None)
+    ops = kernels.ops()
+    s = Sampler("cuda")
+    logits = torch.randn(3, 1000)
+    stream = torch.cuda.current_stream().cuda_stream
+    try:
+        for params in ([SamplingParams(temperature=0.0)] * 3, [SamplingParams(temperature=0.7)] * 3):
+            p = s.launch(logits.cuda(), _rows(params, [0] * 3))
+            s.finish(p)
+            assert list(p.status()) == [0, 0, 0, 0]
+            assert ops.lib.ts_poke_status(2, 7, stream) == 0
+            p = s.launch(logits.cuda(), _rows(params, [0] * 3))
+            toks, bad = s.finish(p)
+            assert list(p.status()) == [0, 0, 7, 0] and not bad.any()
+            assert ops.lib.ts_clear_status(stream) == 0
+        p = s.launch(logits.cuda(), _rows([SamplingParams(temperature=0.0)] * 3, [0] * 3))
+        s.finish(p)
+        assert list(p.status()) == [0, 0, 0, 0]
+    finally:
+        ops.lib.ts_clear_status(stream)

@@ -195,3 +195,74 @@ def test_duplicate_and_empty_requests_are_refused():
         eng.add_request("a", [1], greedy(1))
     with pytest.raises(ValueError, match="at least one"):
         eng.add_request("b", [], greedy(1))
+
+
+def test_requests_are_checked_when_they_are_added():
+    """A prompt that leaves no room within max_model_len, or a token id outside the vocabulary, is
+    refused at add_request: the other requests never see it."""
+    eng = make_fake_engine(max_model_len=32)
+    eng.vocab_size = 1000
+    with pytest.raises(ValueError, match="max_model_len"):
+        eng.add_request("long", list(range(32)), greedy(3))
+    with pytest.raises(ValueError, match="outside"):
+        eng.add_request("bad", [1, 2, 1000], greedy(3))
+    with pytest.raises(ValueError, match="outside"):
+        eng.add_request("neg", [1, -2, 3], greedy(3))
+    out, reasons, _ = run(eng, {"ok": (list(range(10)), greedy(3))})
+    assert reasons == {"ok": "length"} and out["ok"] == expected_output(list(range(10)), 3)
+    assert not eng.cache.live and not eng.requests
+
+
+def test_a_kernel_fault_ends_the_steps_requests_and_switches_the_kernel_off():
+    """A status word that is not zero beside a step's tokens (a block of a kernel gave up on a
+    bounded wait): every request of that step finishes with "error", the kernel object is told, and
+    requests that arrive afterwards run normally."""
+    from tests.fakes import FakeSampler
+    from turingserve_b200 import kernels
+
+    class Pending:
+        def __init__(self, tokens, bad, status):
+            self.tokens, self.bad, self._status = tokens, bad, status
+            self.device_out = None
+
+        def status(self):
+            return self._status
+
+    class StatusSampler(FakeSampler):
+        calls = 0
+
+        def launch(self, logits, rows):
+            StatusSampler.calls += 1
+            tokens, bad = self.sample(logits, rows)
+            return Pending(tokens, bad, [0, 0, 7, 0] if StatusSampler.calls == 3 else [0, 0, 0, 0])
+
+        def finish(self, pending):
+            return pending.tokens, pending.bad
+
+    class FakeOps:
+        reported = []
+
+        def fault_reported(self, status):
+            FakeOps.reported.append(list(status))
+            return "decode attention gave up"
+
+    eng = make_fake_engine(budget=8)
+    eng.sampler = StatusSampler()
+    eng.cfg.async_decode = False
+    kernels.use(FakeOps())
+    try:
+        eng.add_request("a", [1, 2, 3], greedy(10))
+        eng.add_request("b", [4, 5, 6], greedy(10))
+        eng.add_request("c", list(range(30)), greedy(10))         # still in the middle of its prompt at step 3
+        reasons = {}
+        for _ in range(3):
+            for o in eng.step():
+                if o.finished:
+                    reasons[o.request_id] = o.finish_reason
+        assert reasons == {"a": "error", "b": "error", "c": "error"}
+        assert FakeOps.reported == [[0, 0, 7, 0]] and eng.faults == ["decode attention gave up"]
+        assert not eng.cache.live
+        out, reasons, _ = run(eng, {"d": ([7, 8, 9], greedy(4))})
+        assert reasons == {"d": "length"} and out["d"] == expected_output([7, 8, 9], 4)
+    finally:
+        kernels.use(None)

@@ -17,6 +17,8 @@
 // (request, kv head) merges the partials (no second launch, no waiting: a ticket counter).  With 2,
 // 4 or 8 splits (16 in a launch of few blocks) the splits are one thread-block cluster instead: the
 // partial stays in shared memory and every block sums its share of the output out of its peers'.
+#include <mutex>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include "no_alloc.h"
@@ -510,6 +512,7 @@ namespace {
 constexpr int MAX_DEVICES = 64;
 float* g_scratch_addr[MAX_DEVICES] = {};
 int* g_counters_addr[MAX_DEVICES] = {};
+std::mutex g_static_setup;          // two host threads may make a device's first call at the same time
 }  // namespace
 
 TS_API int ts_attention_decode_static(void* out, const void* qkv, const void* k_cache, const void* v_cache,
@@ -528,7 +531,9 @@ TS_API int ts_attention_decode_static(void* out, const void* qkv, const void* k_
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= MAX_DEVICES) TS_REFUSE(TS_ERR_LIMIT, "ts_attention_decode_static: device %d", dev);
-  if (g_scratch_addr[dev] == nullptr) {                // set-up, once per device, with that device current
+  {
+    std::lock_guard<std::mutex> lock(g_static_setup);
+    if (g_scratch_addr[dev] == nullptr) {              // set-up, once per device, with that device current
     float* sp = nullptr;
     int* cp = nullptr;
     e = cudaGetSymbolAddress((void**)&sp, g_static_scratch);
@@ -537,6 +542,7 @@ TS_API int ts_attention_decode_static(void* out, const void* qkv, const void* k_
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode_static: counters address: %s", cudaGetErrorString(e));
     g_counters_addr[dev] = cp;
     g_scratch_addr[dev] = sp;
+    }
   }
   if (nsplit > 1) {
     // the ticket counters must start at zero whatever an earlier (perhaps aborted) call left behind

@@ -463,6 +463,8 @@ int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t 
 }  // namespace
 
 // Whether this kernel takes the shape (else the caller uses ts_attention_decode or the generic kernel).
+int* ts_dec_status_word() { return dec_status_word(); }
+
 TS_API int ts_attention_decode_tma_supported(int H, int KVH, int D, int page, int dtype) {
   return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && H / KVH <= 16 && (D == 64 || D == 128) && page >= MIN_BOX &&
          page % MIN_BOX == 0;

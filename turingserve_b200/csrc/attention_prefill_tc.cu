@@ -392,6 +392,8 @@ int* attn_status_word() {
 
 }  // namespace
 
+int* ts_attn_status_word() { return attn_status_word(); }
+
 TS_API int ts_attention_prefill_tc_supported(int H, int KVH, int D, int page, int dtype) {
   return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && D == HD && page >= BOX_ROWS && page % BOX_ROWS == 0;
 }

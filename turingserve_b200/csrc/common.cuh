@@ -113,6 +113,18 @@ __device__ __forceinline__ float4 ld_peer_v4(unsigned addr) {
   return v;
 }
 
+// Status words of the kernels whose waits are bounded (0 = fine; otherwise which wait ran out):
+// the tcgen05 product, the tcgen05 prompt attention, the TMA decode attention.  Device addresses,
+// null when a word could not be found.  ts_sample / ts_sample_greedy copy them out beside the tokens.
+constexpr int TS_STATUS_WORDS = 4;
+struct TsStatusPtrs {
+  const int* p[TS_STATUS_WORDS];
+};
+int* ts_gemm_status_word();
+int* ts_attn_status_word();
+int* ts_dec_status_word();
+TsStatusPtrs ts_status_ptrs();
+
 bool ts_pdl_enabled();
 bool ts_clusters_enabled();
 

@@ -508,6 +508,8 @@ int cluster_fits(int splits) {
 
 }  // namespace
 
+int* ts_gemm_status_word() { return status_word(); }
+
 // Shapes this kernel takes: K a multiple of 8 (TMA rows must be 16-byte multiples), pointers 16-byte aligned.
 TS_API int ts_linear_tc_supported(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 8) == 0; }
 

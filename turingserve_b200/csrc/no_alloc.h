@@ -16,7 +16,8 @@
 //   * Shapes whose scratch would not fit (B * H * nsplit * (D + 2) floats, B * KVH counters) are
 //     refused with TS_ERR_LIMIT and a message in ts_last_error(); nothing is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
-//     with that device current).  Make that first call outside any stream capture.
+//     with that device current), under a lock, so two host threads may make it together.  Make
+//     that first call outside any stream capture.
 //   * All calls share the one array and it keeps what the last call left there.  The counters are
 //     cleared on the stream before every launch.  Two calls that may overlap on the GPU (different
 //     streams, no ordering between them) race on the array; order them.

@@ -74,11 +74,21 @@ __device__ Best block_best(Best x, Best* scratch) {
   return t;
 }
 
+// The draw is the last kernel of a step and its output the one thing the host waits for: the
+// first block copies the status words of the kernels with bounded waits out beside the tokens, so
+// that a block that gave up somewhere in the step is seen with the step's own tokens.
+__device__ __forceinline__ void report_status(bool mine, const TsStatusPtrs& src, int* __restrict__ out) {
+  if (mine && out != nullptr && threadIdx.x < TS_STATUS_WORDS)
+    out[threadIdx.x] = src.p[threadIdx.x] != nullptr ? *reinterpret_cast<const volatile int*>(src.p[threadIdx.x]) : 0;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* __restrict__ logits,
-              const float* __restrict__ fparams, const long long* __restrict__ iparams, int V) {
+              const float* __restrict__ fparams, const long long* __restrict__ iparams, int V,
+              const TsStatusPtrs status_src, int* __restrict__ status_out) {
   pdl_launch_dependents();
   pdl_wait();
+  report_status(blockIdx.x == 0, status_src, status_out);
   __shared__ Best best_s[32];
   __shared__ float red_s[32];
   __shared__ int cnt_s[256];
@@ -227,9 +237,11 @@ constexpr int GREEDY_THREADS = 256;
 
 __global__ void __launch_bounds__(GREEDY_THREADS)
 sample_greedy_kernel(int* __restrict__ tokens, int* __restrict__ bad_out, const float* __restrict__ logits, int V,
-                     float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ counters) {
+                     float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ counters,
+                     const TsStatusPtrs status_src, int* __restrict__ status_out) {
   pdl_launch_dependents();
   pdl_wait();
+  report_status(blockIdx.x == 0 && blockIdx.y == 0, status_src, status_out);
   __shared__ Best best_s[32];
   __shared__ int any_bad;
   __shared__ int is_last;
@@ -333,12 +345,14 @@ __global__ void penalize_kernel(float* __restrict__ logits, const int* __restric
 
 }  // namespace
 
-// out[0:S] tokens, out[S:2S] bad flags.
+// out[0:S] tokens, out[S:2S] bad flags; status_out (may be null): TS_STATUS_WORDS ints that receive
+// the status words of the kernels with bounded waits as they stand when the draw runs.
 TS_API int ts_sample(int* out, const float* logits, const float* fparams, const long long* iparams, int S,
-                     int V, void* stream) {
+                     int V, int* status_out, void* stream) {
   if (S <= 0) return 0;
   if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample: vocabulary %d", V);
-  ts_launch(sample_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, fparams, iparams, V);
+  ts_launch(sample_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, fparams, iparams, V,
+            ts_status_ptrs(), status_out);
   TS_LAUNCH_CHECK();
 }
 
@@ -350,7 +364,8 @@ TS_API int ts_sample_greedy_parts(int V) {
 }
 
 // Every row greedy: out[0:S] tokens, out[S:2S] bad flags, as ts_sample with temperature 0 gives them.
-TS_API int ts_sample_greedy(int* out, const float* logits, int S, int V, void* scratch, int* counters, void* stream) {
+TS_API int ts_sample_greedy(int* out, const float* logits, int S, int V, void* scratch, int* counters, int* status_out,
+                            void* stream) {
   if (S <= 0) return 0;
   if (V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_sample_greedy: vocabulary %d", V);
   if (S > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_sample_greedy: %d rows", S);
@@ -358,7 +373,8 @@ TS_API int ts_sample_greedy(int* out, const float* logits, int S, int V, void* s
   const int P = ts_sample_greedy_parts(V);
   float* pv = (float*)scratch;
   int* pi = (int*)scratch + (size_t)S * P;
-  ts_launch(sample_greedy_kernel, dim3(P, S), dim3(GREEDY_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, V, pv, pi, counters);
+  ts_launch(sample_greedy_kernel, dim3(P, S), dim3(GREEDY_THREADS), 0, (cudaStream_t)stream, out, out + S, logits, V, pv, pi, counters,
+            ts_status_ptrs(), status_out);
   TS_LAUNCH_CHECK();
 }
 

@@ -5,7 +5,9 @@ free (turingserve/engine/engine.py:96-184).  Finish rules in the reference's ord
 (turingserve/engine/output_processor.py:26-44, turingserve/engine/stop.py:8-11): a stop token
 (``stop_token_ids``, or an end-of-sequence id unless ``ignore_eos``) -> "stop"; ``max_tokens``
 produced or ``max_model_len`` reached -> "length".  A row of non-finite logits, or a request that
-can never be scheduled, finishes with "error" (engine.py:142-146,199-208).
+can never be scheduled, finishes with "error" (engine.py:142-146,199-208); so does every request
+of a step in which a kernel reported that one of its blocks gave up on a bounded wait (the step's
+logits cannot be trusted; the kernel concerned is taken off the path for the steps that follow).
 """
 
 from __future__ import annotations
@@ -18,9 +20,10 @@ import torch
 from turingserve_b200.cache.manager import CacheManager
 from turingserve_b200.config.engine_config import EngineConfig
 from turingserve_b200.engine.batch import StepEntry
-from turingserve_b200.engine.request import BatchPlan, Request, RequestOutput, Status
+from turingserve_b200.engine.request import Request, RequestOutput, Status
+from turingserve_b200.engine.scheduler import Scheduler, StepPlan
 from turingserve_b200.engine.runner import ModelRunner, run_needs
-from turingserve_b200.engine.scheduler import Scheduler
+
 from turingserve_b200.sampling.params import SamplingParams
 from turingserve_b200.sampling.sampler import Sampler, SampleRow, derive_seed
 
@@ -45,7 +48,7 @@ class _Sampled:
 class _InFlight:
     """A step that has been launched and whose tokens have not been committed yet."""
 
-    plan: BatchPlan
+    plan: StepPlan
     sampling: list
     pending: object                      # PendingSample | _Sampled | None
 
@@ -69,11 +72,13 @@ class StepTimer:
 
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, runner, cache: CacheManager, scheduler: Scheduler,
-                 sampler, eos_ids: tuple[int, ...], max_model_len: int) -> None:
+                 sampler, eos_ids: tuple[int, ...], max_model_len: int, vocab_size: int | None = None) -> None:
         self.cfg, self.runner, self.cache = cfg, runner, cache
         self.scheduler, self.sampler = scheduler, sampler
         self.eos_ids = tuple(eos_ids)
         self.max_model_len = max_model_len
+        self.vocab_size = vocab_size
+        self.faults: list[str] = []          # what kernels reported through their status words
         self.requests: dict[str, Request] = {}
         self._inflight: _InFlight | None = None
         self._aborts: list[str] = []
@@ -109,7 +114,7 @@ class LLMEngine:
                              cfg.max_num_seqs, max_len,
                              cfg.graph_batch_sizes if cfg.cuda_graphs else ())
         scheduler = Scheduler(cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, cfg.watermark)
-        return cls(cfg, runner, cache, scheduler, Sampler(device), mcfg.eos_token_ids, max_len)
+        return cls(cfg, runner, cache, scheduler, Sampler(device), mcfg.eos_token_ids, max_len, mcfg.vocab_size)
 
     # -- requests -----------------------------------------------------------------------------------
     def add_request(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams) -> Request:
@@ -117,6 +122,16 @@ class LLMEngine:
             raise ValueError(f"duplicate request id {request_id}")
         if not prompt_token_ids:
             raise ValueError("a request needs at least one prompt token")
+        # refused here, where only this request is concerned: inside a step the same fault would take
+        # the whole batch down, after pages were grown for it
+        if len(prompt_token_ids) >= self.max_model_len:
+            raise ValueError(f"request {request_id!r}: a prompt of {len(prompt_token_ids)} tokens leaves no room "
+                             f"to generate within max_model_len {self.max_model_len}")
+        if self.vocab_size is not None:
+            lo, hi = min(prompt_token_ids), max(prompt_token_ids)
+            if lo < 0 or hi >= self.vocab_size:
+                raise ValueError(f"request {request_id!r}: token id {lo if lo < 0 else hi} outside "
+                                 f"[0, {self.vocab_size})")
         seed = params.seed if params.seed is not None else derive_seed(self.cfg.seed, self._arrivals)
         self._arrivals += 1
         req = Request(request_id, list(prompt_token_ids), len(prompt_token_ids), params, seed=seed)
@@ -169,11 +184,11 @@ class LLMEngine:
             return None, outputs
         return self._launch(plan, prev), outputs
 
-    def _run(self, plan: BatchPlan) -> list[RequestOutput]:
+    def _run(self, plan: StepPlan) -> list[RequestOutput]:
         """Run one given plan to the end (launch, wait, commit)."""
         return self._finish_step(self._launch(plan, None))
 
-    def _launch(self, plan: BatchPlan, prev: _InFlight | None) -> _InFlight:
+    def _launch(self, plan: StepPlan, prev: _InFlight | None) -> _InFlight:
         t = self.timer
         t.start("forward")
         entries = []
@@ -236,6 +251,18 @@ class LLMEngine:
             tokens, bad = cur.pending.tokens, cur.pending.bad
         else:
             tokens, bad = self.sampler.finish(cur.pending)
+            status = cur.pending.status() if hasattr(cur.pending, "status") else None
+            if status is not None and any(int(v) for v in status):
+                from turingserve_b200 import kernels
+                self.faults.append(kernels.ops().fault_reported(status))
+                bad = [True] * len(cur.sampling)
+                # portions that drew nothing wrote keys and values of the same untrustworthy step
+                for p in cur.plan.items:
+                    if not p.samples and not p.request.finished:
+                        if p.request.pending:
+                            p.request.token_ids.pop()
+                            p.request.pending = False
+                        outputs.append(self._finish(p.request, "error", []))
         t.stop("sample")
         t.start("output")
         for row, req in enumerate(cur.sampling):

@@ -31,7 +31,10 @@ ROUND_TO = 64
 
 class Replayer:
     def __init__(self, model_dir: str, dtype: torch.dtype, max_tokens: int, device,
-                 page_size: int = 64, max_step_tokens: int | None = None) -> None:
+                 page_size: int = 64, max_step_tokens: int | None = None,
+                 graph_batch_sizes: tuple[int, ...] = ()) -> None:
+        """``graph_batch_sizes``: steps made of single tokens whose logits are wanted replay a captured
+        CUDA graph of the smallest of these sizes that holds them, as generation does; empty: none."""
         if ROUND_TO % page_size:
             raise ValueError(f"page size {page_size} must divide {ROUND_TO}")
         self.model, self.cfg = load_model(model_dir, dtype, device)
@@ -40,7 +43,8 @@ class Replayer:
         num_pages = max_tokens // page_size + 1                      # + the null page
         self.cache = CacheManager(needs, page_size, num_pages, MAX_LIVE, dtype, device)
         max_len = min(self.cfg.max_position_embeddings, max_tokens)
-        self.runner = ModelRunner(self.model, self.cache, max_step_tokens or max_tokens, MAX_LIVE, max_len)
+        self.runner = ModelRunner(self.model, self.cache, max_step_tokens or max_tokens, MAX_LIVE, max_len,
+                                  tuple(s for s in graph_batch_sizes if s <= MAX_LIVE))
         self.live: dict[str, object] = {}
 
     def step(self, record: dict) -> np.ndarray | None:
@@ -62,7 +66,7 @@ class Replayer:
 
 
 def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=None, stdout=None,
-        device=None, page_size: int = 64) -> int:
+        device=None, page_size: int = 64, graph_batch_sizes: tuple[int, ...] = ()) -> int:
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype_name]
@@ -71,7 +75,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
         kernels.ops()                                   # builds at the first call; raises without a GPU
         device = torch.device("cuda", torch.cuda.current_device())
     os.makedirs(out_dir, exist_ok=True)
-    rp = Replayer(model_dir, dtype, max_tokens, device, page_size)
+    rp = Replayer(model_dir, dtype, max_tokens, device, page_size, graph_batch_sizes=graph_batch_sizes)
     with torch.inference_mode():
         for line in stdin:
             line = line.strip()

@@ -1,9 +1,15 @@
-"""A request as the engine tracks it (the reference's ``Sequence``,
-turingserve/engine/sequence.py:18-56): its tokens so far, how many are in the cache, its status."""
+"""What the engine keeps per request, and what it hands back per step.
+
+The reference tracks the same facts in its ``Sequence`` (turingserve/engine/sequence.py:18-56):
+the tokens so far (prompt, then generated), how many of them are in the cache, and where the
+request stands.  Here the cache manager owns the count of cached tokens (``RequestCache``), so a
+request without a ``cache`` is by construction one that holds no pages: queued, or preempted and
+queued again.
+"""
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 
 from turingserve_b200.cache.manager import RequestCache
@@ -11,64 +17,59 @@ from turingserve_b200.sampling.params import SamplingParams
 
 
 class Status(Enum):
-    WAITING = 0
-    RUNNING = 1
-    FINISHED = 2
+    WAITING = "waiting"          # in the scheduler's queue, holding nothing
+    RUNNING = "running"          # admitted: holds a state slot and pages
+    FINISHED = "finished"
 
 
 @dataclass
 class Request:
     request_id: str
-    token_ids: list[int]                 # prompt, then generated tokens
+    token_ids: list[int]
     num_prompt_tokens: int
     params: SamplingParams
-    seed: int = 0
-    cache: RequestCache | None = None    # None while waiting (or after preemption)
+    seed: int = 0                          # of this request's random stream
+    num_drawn: int = 0                     # position in that stream: tokens sampled so far
+    cache: RequestCache | None = None
     status: Status = Status.WAITING
     finish_reason: str | None = None
-    num_drawn: int = 0                   # tokens sampled so far = position in its random stream
-    pending: bool = False                # the last entry of token_ids is a stand-in for a token in flight
+    # True while the last entry of token_ids stands in for a token the GPU has not delivered yet
+    pending: bool = False
     num_preemptions: int = 0
+
+    # -- derived -------------------------------------------------------------------------------------
+    @property
+    def finished(self) -> bool:
+        return self.status is Status.FINISHED
 
     @property
     def num_computed(self) -> int:
-        return 0 if self.cache is None else self.cache.num_tokens
+        """Tokens whose keys and values are in the cache."""
+        return self.cache.num_tokens if self.cache is not None else 0
 
     @property
     def num_uncomputed(self) -> int:
+        """Tokens still to run: 1 for a request that decodes, more in the middle of a prompt (or of
+        a recompute after preemption)."""
         return len(self.token_ids) - self.num_computed
 
     @property
-    def num_output(self) -> int:
-        return len(self.token_ids) - self.num_prompt_tokens
+    def decoding(self) -> bool:
+        return self.num_uncomputed == 1
 
     @property
     def output_ids(self) -> list[int]:
         return self.token_ids[self.num_prompt_tokens:]
 
     @property
-    def finished(self) -> bool:
-        return self.status == Status.FINISHED
-
-
-@dataclass
-class Scheduled:
-    request: Request
-    num_tokens: int
-    samples: bool                        # the portion reaches the end of token_ids
-
-
-@dataclass
-class BatchPlan:
-    items: list[Scheduled] = field(default_factory=list)
-    num_decode: int = 0
-    num_tokens: int = 0
-    preempted: list[Request] = field(default_factory=list)
-    failed: list[Request] = field(default_factory=list)      # can never fit: to be finished with "error"
+    def num_output(self) -> int:
+        return len(self.token_ids) - self.num_prompt_tokens
 
 
 @dataclass
 class RequestOutput:
+    """One step's news about a request: the tokens it gained and, when it ended, why."""
+
     request_id: str
     delta_token_ids: list[int]
     finished: bool

@@ -57,7 +57,7 @@ class Deferred:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 3
+    ABI = 4
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -87,9 +87,11 @@ class CudaOps:
             "ts_linear_tc_ex": [P, P, P, P, P, I, I, I, I, I, I, P, P],
             "ts_reduce_rmsnorm": [P, P, I, P, P, P, F, I, I, I, P],
             "ts_feed_tokens": [P, P, P, P, I, I, P],
-            "ts_sample": [P, P, P, P, I, I, P],
+            "ts_sample": [P, P, P, P, I, I, P, P],
             "ts_penalize": [P, P, P, P, I, I, P],
-            "ts_sample_greedy": [P, P, I, I, P, P, P],
+            "ts_sample_greedy": [P, P, I, I, P, P, P, P],
+            "ts_clear_status": [P],
+            "ts_poke_status": [I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -138,14 +140,11 @@ class CudaOps:
         self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self._device_index = torch.cuda.current_device()
         self.num_sms = torch.cuda.get_device_properties(self._device_index).multi_processor_count
-        self._scratch: torch.Tensor | None = None
-        self._counters: torch.Tensor | None = None
-        self._partials: torch.Tensor | None = None
+        # work buffers by name; one that was outgrown is kept, not freed: a captured graph may still
+        # hold its address
+        self._buffers: dict[str, torch.Tensor] = {}
+        self._outgrown: list[torch.Tensor] = []
         self._decode_slots: dict = {}
-        self._greedy_scratch: torch.Tensor | None = None
-        self._qkv_part: torch.Tensor | None = None
-        self._qkv_counters: torch.Tensor | None = None
-        self._greedy_counters: torch.Tensor | None = None
         self.use_fast_attention = True
         self.use_library_gemm = True
         self.max_splits = 10        # (the fused reduce kernels load up to 16 partial sums in one go)
@@ -156,6 +155,21 @@ class CudaOps:
         # the raw handle of the current stream: a tenth of the cost of building a torch.cuda.Stream
         # object for it, and every kernel launch asks
         return torch._C._cuda_getCurrentRawStream(self._device_index)
+
+    def _buffer(self, name: str, numel: int, dtype: torch.dtype, device, floor: int = 0, zero: bool = False) -> torch.Tensor:
+        """A work buffer of at least ``numel`` elements that lives as long as this object.  When a
+        larger one is needed the old one is set aside, never freed: decode graphs captured earlier
+        read and write it at its address on every replay."""
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        buf = self._buffers.get(name)
+        if buf is None or buf.numel() < numel or buf.device != device:
+            if buf is not None:
+                self._outgrown.append(buf)
+            make = torch.zeros if zero else torch.empty
+            buf = self._buffers[name] = make(max(int(numel), floor), dtype=dtype, device=device)
+        return buf
 
     def _check(self, rc: int, what: str) -> None:
         self.launches += 1
@@ -261,12 +275,11 @@ class CudaOps:
                 and self.lib.ts_linear_tc_supported(T, (H + 2 * KVH) * D, K)):
             splits = self.tc_splits(T, (H + 2 * KVH) * D, K)
             need = self.lib.ts_linear_tc_qkv_rope_scratch_floats(T, H + 2 * KVH, splits)
-            if self._qkv_part is None or self._qkv_part.numel() < need or self._qkv_part.device != x.device:
-                self._qkv_part = torch.empty(max(int(need), 1 << 18), dtype=torch.float32, device=x.device)
-                self._qkv_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
-            if (H + 2 * KVH) * -(-T // 16) <= self._qkv_counters.numel():
+            qkv_part = self._buffer("qkv_part", need, torch.float32, x.device, floor=1 << 18)
+            qkv_counters = self._buffer("qkv_counters", 4096, torch.int32, x.device, zero=True)
+            if (H + 2 * KVH) * -(-T // 16) <= qkv_counters.numel():
                 rc = self.lib.ts_linear_tc_qkv_rope(
-                    _ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(self._qkv_part), _ptr(self._qkv_counters),
+                    _ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(qkv_part), _ptr(qkv_counters),
                     _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), T, H, KVH,
                     page_size, K, splits, self._stream())
                 if rc != self.UNSUPPORTED:
@@ -277,9 +290,7 @@ class CudaOps:
 
     def scratch(self, floats: int, device) -> torch.Tensor:
         """A float32 work buffer of at least ``floats`` elements, kept between calls."""
-        if self._scratch is None or self._scratch.numel() < floats or self._scratch.device != device:
-            self._scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
-        return self._scratch
+        return self._buffer("scratch", floats, torch.float32, device, floor=1 << 20)
 
     def decode_splits(self, num_requests: int, KVH: int, max_seq_len: int) -> int:
         """How many pieces each request's keys are cut into so that the launch fills the GPU
@@ -303,9 +314,7 @@ class CudaOps:
         if nsplit <= 1:
             return None, None
         scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), device)
-        if self._counters is None or self._counters.numel() < nd * KVH or self._counters.device != device:
-            self._counters = torch.zeros(max(nd * KVH, 1 << 16), dtype=torch.int32, device=device)
-        return scratch, self._counters
+        return scratch, self._buffer("counters", nd * KVH, torch.int32, device, floor=1 << 16, zero=True)
 
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window) -> None:
@@ -406,9 +415,7 @@ class CudaOps:
 
     def partial_scratch(self, floats: int, device) -> torch.Tensor:
         """The buffer deferred products leave their partial sums in (one deferred product at a time)."""
-        if self._partials is None or self._partials.numel() < floats or self._partials.device != device:
-            self._partials = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
-        return self._partials
+        return self._buffer("partials", floats, torch.float32, device, floor=1 << 20)
 
     def tc_splits(self, M: int, N: int, K: int) -> int:
         """Pieces K is cut into for a few-token product, so that about one tile lands on every SM."""
@@ -430,26 +437,43 @@ class CudaOps:
         return (int(self.lib.ts_linear_tc_status()) or int(self.lib.ts_attention_prefill_tc_status())
                 or int(self.lib.ts_attention_decode_tma_status()))
 
+    STATUS_WORDS = 4            # what ts_sample* report beside the tokens: GEMM, prompt attention, TMA decode attention, spare
+
+    def fault_reported(self, status) -> str:
+        """The engine found non-zero status words beside a step's tokens: a block of one of the
+        kernels with bounded waits gave up, so the step's output cannot be trusted.  Takes the kernel
+        concerned off the product path (its slower counterpart runs from the next step on), clears
+        the words, and says what happened."""
+        names = ("tensor-core product", "tensor-core prompt attention", "TMA decode attention", "spare")
+        hit = [f"{names[i]} (wait {int(v)})" for i, v in enumerate(status) if int(v)]
+        if int(status[0]):
+            self.gemm_mode = "library"
+        if int(status[1]):
+            self.use_tc_attention = False
+        if int(status[2]):
+            self.decode_kernel = "cp"
+        self.lib.ts_clear_status(self._stream())
+        return "a kernel gave up on a bounded wait: " + ", ".join(hit) + "; its fallback runs from now on"
+
     def feed_tokens(self, ids, rows, src, tokens, vocab: int) -> None:
         """ids[rows[i]] = tokens[src[i]] on the device (all int32)."""
         self._check(self.lib.ts_feed_tokens(_ptr(ids), _ptr(rows), _ptr(src), _ptr(tokens), rows.shape[0], vocab,
                                             self._stream()), "feed_tokens")
 
-    def sample(self, out, logits, fparams, iparams) -> None:
+    def sample(self, out, logits, fparams, iparams, status_out=None) -> None:
+        """``status_out``: STATUS_WORDS int32 that receive the kernels' status words (see fault_reported)."""
         S, V = logits.shape
         self._check(self.lib.ts_sample(_ptr(out), _ptr(logits), _ptr(fparams), _ptr(iparams), S, V,
-                                       self._stream()), "sample")
+                                       _ptr(status_out), self._stream()), "sample")
 
-    def sample_greedy(self, out, logits) -> None:
+    def sample_greedy(self, out, logits, status_out=None) -> None:
         """Every row greedy: the draw without parameters, each row spread over many blocks."""
         S, V = logits.shape
         need = 2 * S * self.lib.ts_sample_greedy_parts(V)
-        if self._greedy_scratch is None or self._greedy_scratch.numel() < need or self._greedy_scratch.device != logits.device:
-            self._greedy_scratch = torch.empty(max(need, 2 * 256 * 64), dtype=torch.int32, device=logits.device)
-        if self._greedy_counters is None or self._greedy_counters.numel() < S or self._greedy_counters.device != logits.device:
-            self._greedy_counters = torch.zeros(max(S, 1024), dtype=torch.int32, device=logits.device)
-        self._check(self.lib.ts_sample_greedy(_ptr(out), _ptr(logits), S, V, _ptr(self._greedy_scratch),
-                                              _ptr(self._greedy_counters), self._stream()), "sample_greedy")
+        scratch = self._buffer("greedy_scratch", need, torch.int32, logits.device, floor=2 * 256 * 64)
+        counters = self._buffer("greedy_counters", S, torch.int32, logits.device, floor=1024, zero=True)
+        self._check(self.lib.ts_sample_greedy(_ptr(out), _ptr(logits), S, V, _ptr(scratch), _ptr(counters),
+                                              _ptr(status_out), self._stream()), "sample_greedy")
 
     def penalize(self, logits, ids, meta, pen) -> None:
         S, V = logits.shape

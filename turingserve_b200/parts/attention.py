@@ -15,11 +15,15 @@ from turingserve_b200.parts.base import BuildContext, CacheNeed, Mixer, ParamSpe
 
 
 class Attention(Mixer):
+    MAX_HEAD_DIM = 256          # the any-size attention kernel's limit; the faster ones take 64 and 128
+
     def __init__(self, spec, ctx: BuildContext) -> None:
         self.hidden = ctx.hidden_size
         self.H, self.KVH, self.D = int(spec.num_heads), int(spec.num_kv_heads), int(spec.head_dim)
         if self.H % self.KVH:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if not 0 < self.D <= self.MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {self.D}: the attention kernels take head sizes up to {self.MAX_HEAD_DIM}")
         self.scale = float(spec.scale)
         self.window = None if spec.window is None else int(spec.window)
         self.qkv_bias, self.out_bias = bool(spec.qkv_bias), bool(spec.out_bias)

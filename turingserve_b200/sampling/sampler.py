@@ -51,6 +51,13 @@ class PendingSample:
     host_out: torch.Tensor          # the same, in pinned host memory (valid after ``event``)
     event: object
     count: int
+    host_status: torch.Tensor | None = None     # the kernels' status words, copied with the tokens
+
+    def status(self):
+        """The status words of the kernels with bounded waits as the draw saw them (all zero: every
+        block of the step ran to its end); None when the kernel object reports none.  Valid after
+        ``Sampler.finish``."""
+        return None if self.host_status is None else self.host_status.numpy()
 
 
 class Sampler:
@@ -100,17 +107,17 @@ class Sampler:
         self._param_ring[k] = (fh, ih, ev)
         self._param_turn += 1
 
-    def _host_buffer(self, S: int) -> torch.Tensor:
-        """A contiguous pinned [2, S] int32 buffer (contiguous, so that the copy into it is one
-        asynchronous transfer)."""
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        """A contiguous pinned int32 buffer of ``n`` elements (contiguous, so that the copy into it
+        is one asynchronous transfer)."""
         if len(self._host_ring) < 4:
             pin = self.device.type == "cuda"
-            self._host_ring.append(torch.empty(2 * max(S, 256), dtype=torch.int32, pin_memory=pin))
+            self._host_ring.append(torch.empty(max(n, 516), dtype=torch.int32, pin_memory=pin))
         k = self._turn % len(self._host_ring)
-        if self._host_ring[k].numel() < 2 * S:
-            self._host_ring[k] = torch.empty(2 * S, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        if self._host_ring[k].numel() < n:
+            self._host_ring[k] = torch.empty(n, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self._turn += 1
-        return self._host_ring[k][: 2 * S].view(2, S)
+        return self._host_ring[k][:n]
 
     @torch.inference_mode()
     def launch(self, logits: torch.Tensor, rows: list[SampleRow]) -> PendingSample:
@@ -122,11 +129,16 @@ class Sampler:
         if any(r.params.uses_penalties or len(r.output_ids) < r.params.min_tokens for r in rows):
             logits = logits.clone()
             self._edit_logits(ops, logits, rows)
+        # tokens, flags and (where the kernel object reports them) the kernels' status words leave in
+        # one buffer and one copy
+        W = int(getattr(ops, "STATUS_WORDS", 0))
+        buf = torch.empty(2 * S + W, dtype=torch.int32, device=dev)
+        out, status = buf[: 2 * S].view(2, S), (buf[2 * S:] if W else None)
+        extra = (status,) if W else ()
         if all(r.params.greedy for r in rows) and hasattr(ops, "sample_greedy"):
             # no parameters to send, and the rows spread over many blocks instead of one each
-            out = torch.empty((2, S), dtype=torch.int32, device=dev)
-            ops.sample_greedy(out, logits)
-            return self._copy_out(out, S)
+            ops.sample_greedy(out, logits, *extra)
+            return self._copy_out(buf, S, W)
         fh, ih = self._param_buffers(S)
         f, i = fh.numpy()[:S], ih.numpy()[:S]
         f[:] = 0
@@ -141,18 +153,18 @@ class Sampler:
         fp = fh[:S].to(dev, non_blocking=True)
         ip = ih[:S].to(dev, non_blocking=True)
         self._param_copied()
-        out = torch.empty((2, S), dtype=torch.int32, device=dev)
-        ops.sample(out, logits, fp, ip)
-        return self._copy_out(out, S)
+        ops.sample(out, logits, fp, ip, *extra)
+        return self._copy_out(buf, S, W)
 
-    def _copy_out(self, out: torch.Tensor, S: int) -> PendingSample:
-        host = self._host_buffer(S)
-        host.copy_(out, non_blocking=True)             # the one device-to-host copy of the step
+    def _copy_out(self, buf: torch.Tensor, S: int, W: int) -> PendingSample:
+        host = self._host_buffer(2 * S + W)
+        host.copy_(buf, non_blocking=True)             # the one device-to-host copy of the step
         event = None
         if self.device.type == "cuda":
             event = torch.cuda.Event()
             event.record()
-        return PendingSample(out, host, event, S)
+        return PendingSample(buf[: 2 * S].view(2, S), host[: 2 * S].view(2, S), event, S,
+                             host[2 * S:] if W else None)
 
     def _edit_logits(self, ops, logits: torch.Tensor, rows: list[SampleRow]) -> None:
         """Penalties (penalties.py:20-45), then stop tokens masked to -inf while fewer than
