@@ -3,6 +3,13 @@
 fractions for a Qwen2.5-shaped model with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--model qwen2.5-1.5b|qwen2.5-7b|qwen2.5-14b] [--batch 8] [--kv-block 16] [--phases ...]
+
+One JSON line.  Beside the contract's keys: ``prefill``, ``roofline`` (the whole decode step against
+the copy bandwidth), ``points`` (batch 1 and 64, and the headline batch with pages of 64 tokens),
+``kernels`` (each dominant kernel alone against its roofline), ``graph_check`` (the captured decode
+step against the same step launched kernel by kernel) and ``mixed`` (the Qwen2.5-14B shape with 32
+decodes beside a 2,048-token prompt in portions of 512).
 
 A "step" is one decode step of the whole batch.  ``value`` times K decode steps of the engine's
 step function with CUDA events (inputs built on the host, copied to the device each step);
@@ -34,8 +41,17 @@ SHAPES = {
     "qwen2.5-7b": dict(hidden_size=3584, intermediate_size=18944, num_layers=28, num_heads=28, num_kv_heads=4,
                        head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
                        tie_word_embeddings=False, max_position_embeddings=32768),
+    "qwen2.5-14b": dict(hidden_size=5120, intermediate_size=13824, num_layers=48, num_heads=40, num_kv_heads=8,
+                        head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
+                        tie_word_embeddings=False, max_position_embeddings=32768),
 }
-SHAPE_NAMES = {"qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B"}
+SHAPE_NAMES = {"qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B", "qwen2.5-14b": "Qwen2.5-14B"}
+
+
+def metric_name(a) -> str:
+    """The same words in both arms: the driver divides two lines only when their metrics read alike.
+    The precision each arm computes in is in its ``dtype``."""
+    return f"decode tok/s at batch {a.batch} ({SHAPE_NAMES[a.model]} shape, {a.prompt_len:,}-token prompts)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -118,11 +134,77 @@ def make_model(shape: str, layers: int, tmp: str) -> str:
     return folder
 
 
+def build_engine_on_device(shape: str, layers: int, *, ctx_len: int, page: int, max_seqs: int, max_tokens: int,
+                           graph_sizes: tuple[int, ...], model=None):
+    """An engine around a model whose N(0, 0.02) weights are drawn on the device (no checkpoint file:
+    the 14B shape would be 30 GB of it); everything else as ``LLMEngine.from_config`` builds it."""
+    import torch
+
+    from turingserve_b200 import EngineConfig, LLMEngine
+    from turingserve_b200.cache.manager import CacheManager
+    from turingserve_b200.engine.runner import ModelRunner, run_needs
+    from turingserve_b200.engine.scheduler import Scheduler
+    from turingserve_b200.models.qwen2 import make_config
+    from turingserve_b200.sampling.sampler import Sampler
+    from turingserve_b200.weights.random_init import random_model_on_device
+
+    kw = dict(SHAPES[shape])
+    kw["num_layers"] = layers
+    mcfg = make_config(**kw)
+    device = torch.device("cuda", 0)
+    if model is None:
+        t0 = time.time()
+        model = random_model_on_device(mcfg, torch.bfloat16, device, seed=0, max_positions=ctx_len)
+        torch.cuda.synchronize()
+        print(f"[bench] random {shape} ({layers} layers) on the device in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    cfg = EngineConfig(model=f"<random {shape}>", dtype="bfloat16", max_model_len=ctx_len, block_size=page,
+                       num_blocks=max_seqs * (-(-ctx_len // page)) + 8, max_num_seqs=max_seqs,
+                       max_num_batched_tokens=max_tokens, graph_batch_sizes=graph_sizes, watermark=0.0)
+    cfg.validate(mcfg.max_position_embeddings)
+    cache = CacheManager(run_needs(model), page, cfg.num_blocks, max_seqs, torch.bfloat16, device)
+    runner = ModelRunner(model, cache, max(max_tokens, max_seqs), max_seqs, ctx_len, cfg.graph_batch_sizes)
+    sched = Scheduler(cache, max_tokens, max_seqs, 0.0)
+    return LLMEngine(cfg, runner, cache, sched, Sampler(device), mcfg.eos_token_ids, ctx_len, mcfg.vocab_size)
+
+
+def graph_check(runner, cache, rcs, tokens) -> dict:
+    """One decode step replayed from its captured graph, then the same tokens at the same positions
+    launched kernel by kernel (the cache is told to forget the step, whose keys and values are simply
+    written again): the logits must agree to within bfloat16 rounding of a step's different split of
+    the keys.  A wrong-but-finite output head or a stale graph input would show here."""
+    import torch
+
+    from turingserve_b200.engine.batch import StepEntry
+    entries = [StepEntry(rc, [int(t)], [0]) for rc, t in zip(rcs, tokens)]
+    with_graph = runner.step(entries).clone()
+    for rc in rcs:
+        rc.num_tokens -= 1
+    sizes, runner.graph_batch_sizes = runner.graph_batch_sizes, ()
+    try:
+        without = runner.step([StepEntry(rc, [int(t)], [0]) for rc, t in zip(rcs, tokens)])
+    finally:
+        runner.graph_batch_sizes = sizes
+    err = float((with_graph - without).abs().max())
+    top = float(without.abs().max())
+    rel = float((with_graph - without).norm() / without.norm())
+    same = int((with_graph.argmax(-1) == without.argmax(-1)).sum())
+    # The two runs split the keys differently (a captured step sizes its launch for the longest context),
+    # so they differ by bfloat16 roundings carried through every layer: a few percent of the largest logit
+    # at the worst of a million entries and about 3 % in the root mean square after 28 layers (some 200
+    # roundings of 2^-9 each, added like a random walk).  A stale graph input or a wrong head gives
+    # unrelated rows: a relative difference near 1.4.
+    if not (rel <= 0.15):
+        raise RuntimeError(f"the captured decode step disagrees with the same step launched kernel by kernel: "
+                           f"relative difference {rel:.4g} (largest {err:.4g} against a largest logit of {top:.4g})")
+    return {"rel_l2_diff": round(rel, 5), "max_abs_diff": round(err, 5), "max_logit": round(top, 3),
+            "same_argmax": same, "rows": len(rcs)}
+
+
 def run_ours(a) -> dict:
     import numpy as np
     import torch
 
-    from turingserve_b200 import EngineConfig, LLMEngine, SamplingParams, kernels
+    from turingserve_b200 import SamplingParams, kernels
     from turingserve_b200.engine.batch import StepEntry
 
     torch.cuda.set_device(0)
@@ -135,14 +217,9 @@ def run_ours(a) -> dict:
     rng = np.random.default_rng(0)
     V = kw["vocab_size"]
 
-    with tempfile.TemporaryDirectory() as tmp:
-        folder = make_model(a.model, layers, tmp)
-        max_b = max(B, 64)
-        pages = max_b * (-(-ctx_len // a.kv_block)) + 8
-        eng = LLMEngine.from_config(EngineConfig(
-            model=folder, dtype="bfloat16", max_model_len=ctx_len, block_size=a.kv_block, num_blocks=pages,
-            max_num_seqs=max_b, max_num_batched_tokens=max(2048, max_b), graph_batch_sizes=(1, 8, 64, B),
-            watermark=0.0))
+    max_b = max(B, 64)
+    eng = build_engine_on_device(a.model, layers, ctx_len=ctx_len, page=a.kv_block, max_seqs=max_b,
+                                 max_tokens=max(2048, max_b), graph_sizes=(1, 8, 64, B))
     runner, cache = eng.runner, eng.cache
 
     def ev():
@@ -178,6 +255,8 @@ def run_ours(a) -> dict:
         for rc in rcs:                                           # prompts, one request per step
             runner.step([StepEntry(rc, rng.integers(0, V, size=prompt_len).tolist(), [])])
         toks = rng.integers(0, V, size=(warmup + steps, batch))
+        if batch == B and not checks:
+            checks.update(graph_check(runner, cache, rcs, rng.integers(0, V, size=batch)))
         for s in range(warmup):
             runner.step([StepEntry(rc, [int(toks[s, i])], [0]) for i, rc in enumerate(rcs)])
         torch.cuda.synchronize()
@@ -196,6 +275,7 @@ def run_ours(a) -> dict:
         return ms, launches, ctx_mid
 
     steps, warmup = a.steps, max(3, a.warmup)
+    checks: dict = {}
     with ClockSampler() as clocks:
         ms, launches, ctx_mid = decode_run(B, steps, warmup)
     value = B / (ms / 1e3)
@@ -235,12 +315,34 @@ def run_ours(a) -> dict:
         # map, block tables) goes up (greedy rows need no sampler parameters); tokens and flags come back
         width = runner.max_pages
         h2d = 4 * (4 * B + (B + 1) + 3 * B + B * width)
-        d2h = 2 * B * 4
+        d2h = (2 * B + ops.STATUS_WORDS) * 4
         e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": round(1e3 * e2e_s / steps, 4)}
 
+    kernel_points = None
+    if "kernels" in phases:
+        kernel_points = per_kernel(ops, kw, B, prompt_len + warmup + steps // 2, a.kv_block, a.prefill_tokens, pk)
+    if "points" in phases and a.kv_block != 64:
+        # the same decode step with pages of 64 tokens (one TMA box of the attention kernels a page)
+        model = runner.model
+        del eng, runner, cache
+        torch.cuda.empty_cache()
+        eng = build_engine_on_device(a.model, layers, ctx_len=ctx_len, page=64, max_seqs=B, max_tokens=max(2048, B),
+                                     graph_sizes=(B,), model=model)
+        runner, cache = eng.runner, eng.cache
+        pms_, _, _ = decode_run(B, min(steps, 64), 3)
+        points[f"decode_b{B}_page64"] = round(B / (pms_ / 1e3), 1)
+    mixed = None
+    if "mixed" in phases:
+        del eng, runner, cache
+        torch.cuda.empty_cache()
+        try:
+            mixed = run_mixed(a, pk)
+        except Exception as e:                              # the 14B point must not take the headline down
+            mixed = {"error": f"{type(e).__name__}: {str(e).splitlines()[0][:160] if str(e) else ''}"}
+
     return {
-        "metric": f"decode tok/s at batch {B} ({SHAPE_NAMES[a.model]} shape, {prompt_len:,}-token prompts, bf16)",
+        "metric": metric_name(a),
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, N(0,0.02) random weights", "impl": "ours",
@@ -258,7 +360,201 @@ def run_ours(a) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
         "points": points,
+        "graph_check": checks,
+        "kernels": kernel_points,
+        "mixed": mixed,
     }
+
+
+def per_kernel(ops, kw: dict, B: int, ctx: int, page: int, prefill_tokens: int, pk: dict) -> dict:
+    """Each dominant kernel alone at the step's shapes: mean time per launch with CUDA events around a
+    CUDA graph of launches that rotate over enough copies of the weights (or caches) that they come from
+    DRAM, the bytes (or FLOPs) the launch must move, and that rate over the measured peak (copy bandwidth;
+    burst cuBLAS rate for the prompt attention, which is timed in isolation).  Inside a step the same
+    kernels overlap their neighbours through programmatic dependent launch, so these times do not add up
+    to the step; they say how far each is from its own roofline."""
+    import torch
+
+    from turingserve_b200.engine.batch import streaming_decode
+
+    h, I, H, KVH, D, V = (kw["hidden_size"], kw["intermediate_size"], kw["num_heads"], kw["num_kv_heads"],
+                          kw["head_dim"], kw["vocab_size"])
+    dev, bf = "cuda", torch.bfloat16
+    out: dict = {"method": "CUDA events around a graph of rotating launches, each kernel alone"}
+
+    def timed_graph(fn, copies: int) -> float:
+        for i in range(copies):
+            fn(i)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(copies):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * copies) * 1e3            # us per launch
+
+    def record(name: str, us: float, nbytes: float = 0.0, flops: float = 0.0) -> None:
+        r = {"us": round(us, 2)}
+        if nbytes:
+            r["GBps"] = round(nbytes / us / 1e3, 1)
+            r["frac_hbm"] = round(nbytes / us / 1e3 / pk["hbm_gbs"], 4)
+        if flops:
+            r["TFLOPs"] = round(flops / us / 1e6, 1)
+            r["frac_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = r
+
+    def weights(n: int, k: int):
+        copies = max(2, int(300e6 // (n * k * 2)) + 1)
+        return [torch.randn(n, k, device=dev, dtype=bf) * 0.02 for _ in range(copies)]
+
+    x = torch.randn(B, h, device=dev, dtype=bf)
+    positions = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    half = D // 2
+    cos, sin = torch.ones(ctx + 8, half, device=dev), torch.zeros(ctx + 8, half, device=dev)
+    slots = torch.full((B,), -1, dtype=torch.int32, device=dev)
+    # K3: q/k/v product with bias, rotation and cache write (slots -1: nothing is written)
+    nqkv = (H + 2 * KVH) * D
+    ws, bias = weights(nqkv, h), torch.zeros(nqkv, device=dev, dtype=bf)
+    qkv = torch.empty(B, nqkv, device=dev, dtype=bf)
+    kc1 = torch.zeros(2, KVH, page, D, device=dev, dtype=bf)
+    us = timed_graph(lambda i: ops.qkv_rope(qkv, x, ws[i % len(ws)], bias, positions, cos, sin, H, KVH, D, D, kc1, kc1,
+                                            slots, page), len(ws))
+    record("qkv_rope", us, nqkv * h * 2)
+    del ws
+    # K7, K10: output and down projections, left unreduced as the step leaves them (the norm finishes them)
+    for name, n, k in (("o_proj", h, H * D), ("down_proj", h, I)):
+        ws = weights(n, k)
+        xin = torch.randn(B, k, device=dev, dtype=bf)
+        o = torch.empty(B, n, device=dev, dtype=bf)
+        record(name, timed_graph(lambda i: ops.linear(o, xin, ws[i % len(ws)], None, may_defer=True), len(ws)), n * k * 2)
+        del ws
+    # K8: gate/up product with the activation in its epilogue
+    ws = weights(2 * I, h)
+    act = torch.empty(B, I, device=dev, dtype=bf)
+    group = 64 if I % 64 == 0 else 0
+    record("gate_up_silu", timed_graph(lambda i: ops.gated_linear(act, x, ws[i % len(ws)], None, group), len(ws)), 2 * I * h * 2)
+    del ws
+    # K11: output head, 32-bit logits
+    ws = weights(V, h)
+    logits = torch.empty(B, V, device=dev, dtype=torch.float32)
+    record("lm_head", timed_graph(lambda i: ops.linear(logits, x, ws[i % len(ws)], None), len(ws)), V * h * 2)
+    del ws
+    torch.cuda.empty_cache()
+
+    class Step:
+        pass
+
+    def caches(batch: int, tokens: int, copies: int):
+        per = -(-tokens // page)
+        pages = batch * per + 1
+        kv = [(torch.randn(pages, KVH, page, D, device=dev, dtype=bf), torch.randn(pages, KVH, page, D, device=dev, dtype=bf))
+              for _ in range(copies)]
+        table = (torch.randperm(pages - 1, device=dev).to(torch.int32) + 1).view(batch, per)
+        return kv, table
+
+    # K5: decode attention over the cache
+    kv_bytes = B * (ctx + 1) * KVH * D * 2 * 2
+    copies = max(2, min(28, int(300e6 // kv_bytes) + 1))
+    kv, table = caches(B, ctx + 1, copies)
+    st = Step()
+    st.q_start = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    st.seq_lens = torch.full((B,), ctx + 1, dtype=torch.int32, device=dev)
+    st.num_requests, st.max_q_len, st.max_seq_len, st.num_decode = B, 1, max(4096, ctx + 1), B
+    st.streaming_decode = streaming_decode(B, ctx + 1)
+    ao = torch.empty(B, H * D, device=dev, dtype=bf)
+    record("decode_attention", timed_graph(lambda i: ops.attention(ao, qkv, kv[i % copies][0], kv[i % copies][1], table, st,
+                                                                   H, KVH, D, page, D ** -0.5, None), copies), kv_bytes)
+    del kv
+    # K6: prompt attention, one prompt
+    T = prefill_tokens
+    kv, table = caches(1, T, 4)
+    pq = torch.randn(T, nqkv, device=dev, dtype=bf)
+    st = Step()
+    st.q_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    st.seq_lens = torch.tensor([T], dtype=torch.int32, device=dev)
+    st.num_requests, st.max_q_len, st.max_seq_len, st.num_decode, st.streaming_decode = 1, T, T, 0, False
+    po = torch.empty(T, H * D, device=dev, dtype=bf)
+    record("prefill_attention", timed_graph(lambda i: ops.attention(po, pq, kv[i % 4][0], kv[i % 4][1], table, st, H, KVH, D,
+                                                                    page, D ** -0.5, None), 4), flops=2.0 * T * T * D * H)
+    return out
+
+
+def run_mixed(a, pk: dict) -> dict:
+    """The Qwen2.5-14B shape under a mixed step: 32 requests decode at about 2,048 tokens of context
+    while a 2,048-token prompt arrives in portions of 512 (four steps a prompt).  Times the steps with
+    CUDA events through the step function, and the same through ``LLMEngine.step`` with its scheduler
+    (token budget 544: the decodes first, then the portion)."""
+    import numpy as np
+    import torch
+
+    from turingserve_b200 import SamplingParams
+    from turingserve_b200.engine.batch import StepEntry
+
+    shape, nd, plen, chunk, ctx_len = "qwen2.5-14b", 32, 2048, 512, 4096
+    kw = SHAPES[shape]
+    layers = kw["num_layers"]
+    V = kw["vocab_size"]
+    rng = np.random.default_rng(1)
+    eng = build_engine_on_device(shape, layers, ctx_len=ctx_len, page=a.kv_block, max_seqs=nd + 2, max_tokens=nd + chunk,
+                                 graph_sizes=())
+    runner, cache = eng.runner, eng.cache
+    rcs = [cache.admit(f"d{i}") for i in range(nd)]
+    for rc in rcs:
+        for at in range(0, plen, 1024):
+            runner.step([StepEntry(rc, rng.integers(0, V, size=1024).tolist(), [])])
+
+    def prompt_round(tag: str) -> float:
+        rc = cache.admit(tag)
+        ptoks = rng.integers(0, V, size=plen).tolist()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for at in range(0, plen, chunk):
+            entries = [StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rcs]
+            entries.append(StepEntry(rc, ptoks[at:at + chunk], [chunk - 1] if at + chunk == plen else []))
+            runner.step(entries)
+        e1.record()
+        torch.cuda.synchronize()
+        cache.release(rc)
+        return e0.elapsed_time(e1) / (plen // chunk)
+
+    prompt_round("w0")
+    prompt_round("w1")
+    ms = sorted(prompt_round(f"p{i}") for i in range(3))[1]
+    for rc in rcs:
+        cache.release(rc)
+    # the same through the engine: 32 running requests, prompts arriving one after the other
+    params = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    for i in range(nd):
+        eng.add_request(f"e{i}", rng.integers(0, V, size=plen).tolist(), params)
+    while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
+        eng.step()
+    eng.add_request("x0", rng.integers(0, V, size=plen).tolist(), SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+    for _ in range(4):
+        eng.step()
+    eng.add_request("x1", rng.integers(0, V, size=plen).tolist(), SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_tok = 0
+    for _ in range(4):
+        n_tok += sum(len(o.delta_token_ids) for o in eng.step())
+    torch.cuda.synchronize()
+    wall_ms = 1e3 * (time.perf_counter() - t0) / 4
+    for rid in list(eng.requests):
+        eng.abort(rid)
+    eng.step()
+    nums = model_numbers(kw, layers)
+    flops = 2.0 * (nd + chunk) * (nums["linear_params"] + 0) + 2.0 * (nd + 1) * nums["head_params"]
+    return {"model": shape, "layers": layers, "decodes": nd, "prompt_tokens": plen, "portion": chunk,
+            "ms_per_step": round(ms, 3), "tok_per_s": round((nd + chunk) / (ms / 1e3), 1),
+            "e2e_ms_per_step": round(wall_ms, 3), "e2e_tokens_out": n_tok,
+            "frac_bf16_products": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
 
 
 class _StubTokenizer:
@@ -313,7 +609,14 @@ def run_reference(a) -> dict:
             torch.cuda.synchronize()
             wall = time.perf_counter() - t0
         ms = e0.elapsed_time(e1) / steps
-        return {"metric": f"decode tok/s at batch {B} ({SHAPE_NAMES[a.model]} shape, {prompt_len:,}-token prompts)",
+        # per step its input builder copies ids, positions, slots and sample rows (int64), query starts and
+        # lengths (int32), the block table at its live width, and the all-greedy flag; tokens and bad flags
+        # (int64) and that flag's answer come back (turingserve/runner/input_builder.py:138-144,
+        # turingserve/sampling/sampler.py:88-89,105-106)
+        width = -(-(prompt_len + warmup + steps) // 16)
+        h2d = 8 * 4 * B + 4 * (B + 1) + 4 * B + 4 * B * width + B
+        d2h = 2 * 8 * B + 1
+        return {"metric": metric_name(a),
                 "value": round(n_tok / (ms * steps / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
                 "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "fp16", "data": "synthetic: uniform random token ids, N(0,0.02) random weights",
@@ -322,7 +625,8 @@ def run_reference(a) -> dict:
                            "prompt_len": prompt_len, "parallelism": "single GPU", "cuda_graphs": True,
                            "kernels": "triton"},
                 "clocks": clocks.summary(),
-                "e2e": {"value": round(n_tok / wall, 1), "unit": "tok/s"}}
+                "e2e": {"value": round(n_tok / wall, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h}}
     except Exception as e:                                   # the reference targets Turing + torch 2.6/triton 3.2
         return {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e).splitlines()[0][:200] if str(e) else ''}"}
 
@@ -336,11 +640,11 @@ def main() -> int:
     ap.add_argument("--model", default="qwen2.5-1.5b", choices=sorted(SHAPES))
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--kv-block", type=int, default=64, help="tokens per cache page")
+    ap.add_argument("--kv-block", type=int, default=16, help="tokens per cache page (the reference's 16)")
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--phases", default="prefill,decode,points,e2e",
+    ap.add_argument("--phases", default="prefill,decode,points,e2e,kernels,mixed",
                     help="which measurements to run (decode always runs); fewer for a profiler capture")
     a = ap.parse_args()
     if a.gpus != 1:

@@ -1,10 +1,12 @@
-"""Single-kernel workloads at the sizes of a Qwen2.5-1.5B-shaped step, small enough for a profiler
-capture that ends by itself (a few hundred MB on the device, a few dozen launches).
+#!/usr/bin/env python3
+"""Single-kernel workloads at the layer sizes of one of bench.py's model shapes (--model), small
+enough for a profiler capture that ends by itself (a few hundred MB on the device, a few dozen
+launches), and the kernel-by-kernel timeline of one captured decode step.
 
-    python -m turingserve_b200.profiling decode_attention [--batch 8] [--context 2048] [--page 16] [--graph]
-    python -m turingserve_b200.profiling prefill_attention [--tokens 2048] [--page 16]
-    python -m turingserve_b200.profiling gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated] [--graph]
-    python -m turingserve_b200.profiling timeline [--batch 8] [--context 2048] [--layers 28]
+    python profile_kernels.py decode_attention [--model qwen2.5-1.5b] [--batch 8] [--context 2048] [--page 16] [--graph]
+    python profile_kernels.py prefill_attention [--tokens 2048] [--page 16]
+    python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated] [--graph]
+    python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
 
 Each prints the launches it made and, timed with CUDA events, the mean time per launch.
 """
@@ -13,13 +15,20 @@ from __future__ import annotations
 
 import argparse
 import dataclasses
+import os
+import sys
 
 import torch
 
-from turingserve_b200 import kernels
-from turingserve_b200.engine.batch import streaming_decode
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-H, KVH, D, PAGE, LAYERS = 12, 2, 128, 16, 28
+from bench import SHAPES                                    # noqa: E402
+from turingserve_b200 import kernels                        # noqa: E402
+from turingserve_b200.engine.batch import streaming_decode  # noqa: E402
+
+PAGE = 16
+H = KVH = D = LAYERS = 0            # set from --model in main()
+SHAPE: dict = {}
 
 
 @dataclasses.dataclass
@@ -160,16 +169,16 @@ def timeline(a) -> None:
 
     B, ctx = a.batch, a.context
     with tempfile.TemporaryDirectory() as tmp:
-        write_random_model(tmp, make_config(hidden_size=1536, intermediate_size=8960, num_layers=a.layers, num_heads=H,
-                                            num_kv_heads=KVH, head_dim=D, vocab_size=151936, rope_theta=1e6,
-                                            rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768), seed=0)
-        eng = LLMEngine.from_config(EngineConfig(model=tmp, dtype="bfloat16", max_model_len=2 * ctx,
-                                                 num_blocks=B * (2 * ctx // 64) + 8, max_num_seqs=B,
+        kw = dict(SHAPE)
+        kw["num_layers"] = a.layers or LAYERS
+        write_random_model(tmp, make_config(**kw), seed=0)
+        eng = LLMEngine.from_config(EngineConfig(model=tmp, dtype="bfloat16", max_model_len=2 * ctx, block_size=a.page,
+                                                 num_blocks=B * (2 * ctx // a.page) + 8, max_num_seqs=B,
                                                  max_num_batched_tokens=max(2048, B), graph_batch_sizes=(B,), watermark=0.0))
     rng = np.random.default_rng(0)
     params = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
     for i in range(B):
-        eng.add_request(f"r{i}", rng.integers(0, 151936, size=ctx).tolist(), params)
+        eng.add_request(f"r{i}", rng.integers(0, SHAPE["vocab_size"], size=ctx).tolist(), params)
     while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
         eng.step()
     for _ in range(8):
@@ -200,18 +209,19 @@ def timeline(a) -> None:
         share[n][0] += 1
         share[n][1] += d
         rows.append((e.time_range.start - t0, e.time_range.end - t0, d, n))
-    print(f"timeline batch {B} context {ctx} layers {a.layers}: one step = {prev - t0:.1f} us, {len(step)} kernels and copies")
+    print(f"timeline batch {B} context {ctx} layers {a.layers or LAYERS} page {a.page}: one step = {prev - t0:.1f} us, {len(step)} kernels and copies")
     print("end-time increments, summed per kernel:")
     for n, (c, d) in sorted(share.items(), key=lambda kv: -kv[1][1]):
         print(f"  {d:8.1f} us  {c:4d} x {d / c:6.2f}  {n}")
     print("second layer (start, end, increment):")
-    per_layer = (len(step) - 10) // max(a.layers, 1)
+    per_layer = (len(step) - 10) // max(a.layers or LAYERS, 1)
     for r in rows[3 + per_layer: 3 + 2 * per_layer]:
         print(f"  {r[0]:8.2f} {r[1]:8.2f}  +{r[2]:5.2f}  {r[3]}")
 
 
 def main() -> int:
-    ap = argparse.ArgumentParser(prog="python -m turingserve_b200.profiling")
+    ap = argparse.ArgumentParser(prog="python profile_kernels.py")
+    ap.add_argument("--model", default="qwen2.5-1.5b", choices=sorted(SHAPES), help="whose layer sizes to use")
     sub = ap.add_subparsers(dest="workload", required=True)
     s = sub.add_parser("decode_attention")
     s.add_argument("--batch", type=int, default=8)
@@ -232,8 +242,12 @@ def main() -> int:
     s = sub.add_parser("timeline")
     s.add_argument("--batch", type=int, default=8)
     s.add_argument("--context", type=int, default=2048)
-    s.add_argument("--layers", type=int, default=28)
+    s.add_argument("--layers", type=int, default=0, help="0: as many as the model has")
+    s.add_argument("--page", type=int, default=PAGE)
     a = ap.parse_args()
+    global H, KVH, D, LAYERS, SHAPE
+    SHAPE = SHAPES[a.model]
+    H, KVH, D, LAYERS = SHAPE["num_heads"], SHAPE["num_kv_heads"], SHAPE["head_dim"], SHAPE["num_layers"]
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm": gemm,
      "timeline": timeline}[a.workload](a)
     return 0

@@ -552,7 +552,7 @@ def test_work_buffers_outlive_the_graphs_that_captured_them(ops):
     g.replay()
     torch.cuda.synchronize()
     want = torch.empty((M, N), dtype=torch.bfloat16)
-    TwinOps().rmsnorm(want, ref.to(torch.bfloat16), nw.cpu(), 1e-6)
+    TwinOps().rmsnorm(want, ref.cpu().to(torch.bfloat16), nw.cpu(), 1e-6)
     torch.testing.assert_close(normed.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
     assert all(torch.isnan(j).all() for j in junk)
     assert ops.tc_status() == 0

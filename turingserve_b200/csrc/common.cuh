@@ -114,7 +114,7 @@ __device__ __forceinline__ float4 ld_peer_v4(unsigned addr) {
 }
 
 // Status words of the kernels whose waits are bounded (0 = fine; otherwise which wait ran out):
-// the tcgen05 product, the tcgen05 prompt attention, the TMA decode attention.  Device addresses,
+// the tcgen05 product, the tcgen05 prompt attention, the TMA decode attention, the fused decode step.  Device addresses,
 // null when a word could not be found.  ts_sample / ts_sample_greedy copy them out beside the tokens.
 constexpr int TS_STATUS_WORDS = 4;
 struct TsStatusPtrs {
@@ -123,6 +123,7 @@ struct TsStatusPtrs {
 int* ts_gemm_status_word();
 int* ts_attn_status_word();
 int* ts_dec_status_word();
+int* ts_step_status_word();
 TsStatusPtrs ts_status_ptrs();
 
 bool ts_pdl_enabled();

@@ -1,0 +1,1082 @@
+// One whole decode step of a pre-norm decoder (RMSNorm, rotary grouped-query attention over the paged
+// cache, gated SiLU feed-forward, output head) for up to 16 single-token requests, as ONE persistent
+// kernel: one block per SM, every weight streamed exactly once through a ring of shared-memory stages
+// that never drains between the products of a layer or between layers.
+//
+// The same step out of separate kernels (turingserve/model/qwen2.py:38-61 is the recipe; this
+// library's q/k/v, attention, output, gate/up and down kernels are the separate form) pays, per
+// kernel, a grid drain, a pipeline fill and a memory round trip during which no weight moves: seven
+// links of 3 to 12 microseconds a layer where the layer's weights need 14.  Here the phases of a
+// layer are separated by grid-wide barriers (a counter in global memory), and while a block waits at
+// one, its producer warp keeps fetching the weights of the phases to come: weights depend on nothing.
+//
+// Block = 7 warps:
+//   warp 0     weight producer: one lane walks the block's whole list of (tile, k-block) units, layer
+//              after layer, and issues the TMA loads into the ring as stages free up; further ahead
+//              it asks for the weights to be brought into L2 (cp.async.bulk.prefetch).
+//   warp 1     issues tcgen05.mma (one lane): tile rows are weight rows (outputs), the 16 columns are
+//              the tokens; accumulators in tensor memory, two of them, so one is filled while the
+//              other is read back.
+//   warp 2     activation loader: for products whose input another phase wrote (attention output,
+//              activation), copies the unit's [16 tokens x 64] slices into the stage with cp.async.
+//   warps 3-6  everything else: the norm that opens a phase (written straight into the MMA operand
+//              layout), reading accumulators back, split-K partial sums to scratch and the finish by
+//              the block that comes last for a tile (a ticket, nobody waits): bias + rotary + cache
+//              write, residual add, SiLU*mul, logits; the decode attention (mma.sync over cp.async
+//              tiles, the four warps on disjoint keys); the grid barriers.
+//
+// Every wait (mbarrier, shared-memory flag, grid barrier) is bounded: when one runs out the block
+// records where in the status word, raises the step's abort flag so that the other blocks stop
+// waiting too, and leaves through the common exit, which frees its tensor memory.
+//
+// Rounding points are those of the separate kernels: a product is rounded to bfloat16 before the
+// residual add, the sum again; the norm's x * rstd is rounded before the scale; SiLU and the
+// product with `up` round as the activation kernel does; probabilities are rounded to bfloat16 for
+// the second attention product; logits leave the accumulator unrounded.
+#include <string.h>
+
+#include "common.cuh"
+#include "decode_step.h"
+#include "mma_utils.cuh"
+#include "tc_utils.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;                    // tile rows (weight rows) = TMEM lanes
+constexpr int BN = TS_STEP_MAX_TOKENS;     // tile columns = tokens
+constexpr int W_BYTES = BM * BK * 2;       // 16 KB of weights per k-block
+constexpr int X_BYTES = BN * BK * 2;       // 2 KB of activations per k-block
+constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+constexpr int NUM_WARPS = 7;
+constexpr int NUM_THREADS = NUM_WARPS * 32;
+constexpr int CW0 = 3;                     // first compute warp
+constexpr int CT = 128;                    // compute threads
+constexpr int UMMA_K = 16;
+constexpr int ATT_TILE = 64;
+constexpr int ATT_STAGES = 3;
+constexpr int D = 128;                     // head size this kernel is written for
+constexpr int PAGES_S = 256;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int FULL_COUNT = 33;             // arrivals a stage needs: the producer's expect_tx + 32 loader lanes
+
+enum Kind : int { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_HEAD = 4 };
+
+struct Unit {
+  int kind, layer, tile, part, kb0, kb1;
+};
+
+// Walks a block's units in the order every role of the block agrees on: layer by layer the q/k/v,
+// output, gate/up and down products, then the head.  Unit u of a product is (tile u / S, part u % S);
+// block c takes units (c + rot) % blocks, + blocks, ...
+struct Walker {
+  int layer, kind, u;
+  __device__ void start() {
+    layer = 0;
+    kind = K_QKV;
+    u = -1;
+  }
+  __device__ bool next(const TsStepArgs& a, int cta, int nb, Unit& out) {
+    while (true) {
+      if (layer > a.L) return false;
+      const TsStepShape& sh = a.shape[kind];
+      if (u < 0) u = (cta + sh.rot) % nb;
+      if (u < sh.R * sh.S) {
+        out.kind = kind;
+        out.layer = layer;
+        out.tile = u / sh.S;
+        out.part = u % sh.S;
+        out.kb0 = out.part * sh.per;
+        out.kb1 = min(sh.KB, out.kb0 + sh.per);
+        u += nb;
+        return true;
+      }
+      u = -1;
+      if (layer == a.L) {
+        layer = a.L + 1;
+        continue;
+      }
+      if (++kind == K_HEAD) {
+        kind = K_QKV;
+        if (++layer == a.L) kind = K_HEAD;
+      }
+    }
+  }
+};
+
+// Does block `cta` own a unit of product `kind`?
+__device__ __forceinline__ bool has_units(const TsStepArgs& a, int kind, int cta, int nb) {
+  const TsStepShape& sh = a.shape[kind];
+  return (cta + sh.rot) % nb < sh.R * sh.S;
+}
+
+__device__ __forceinline__ const CUtensorMap* map_of(const TsStepArgs& a, int kind, int layer) {
+  return reinterpret_cast<const CUtensorMap*>(a.maps) + (kind == K_HEAD ? 4 * a.L : 4 * layer + kind);
+}
+
+// ---- bounded waits on plain flags ---------------------------------------------------------------
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_cta(const volatile int* p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32((const void*)p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta(volatile int* p, int v) {
+  asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32((const void*)p)), "r"(v) : "memory");
+}
+
+struct Abort {
+  volatile int* flag;      // shared: this block gives up
+  int* status;             // global status word
+  int* step_abort;         // global: the step gives up (other blocks stop waiting)
+  __device__ __forceinline__ bool raised() const { return *flag != 0; }
+  __device__ __forceinline__ void raise(int code) const {
+    atomicCAS(status, 0, code);
+    atomicExch(step_abort, 1);
+    *flag = 1;
+  }
+};
+
+// Waits until the shared counter *p reaches `target`.
+__device__ __forceinline__ bool wait_shared_ge(volatile int* p, int target, const Abort& ab, int code) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (ld_acquire_cta(p) >= target) return true;
+    if ((i & 63u) == 63u) {
+      if (ab.raised()) return false;
+      if (clock64() - t0 > 2 * WAIT_LIMIT_CYCLES) break;
+    }
+  }
+  ab.raise(code);
+  return false;
+}
+
+__device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abort& ab, int code) {
+  if (mbar_wait(bar, parity, ab.status, code, ab.flag)) return true;
+  atomicExch(ab.step_abort, 1);
+  return false;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// True when `ok` holds in all 128 compute threads (a barrier among them as well).
+__device__ __forceinline__ bool compute_all(bool ok) {
+  int r;
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.b32 p, %1, 0;\n bar.red.and.pred q, 1, 128, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+      : "=r"(r) : "r"((int)ok) : "memory");
+  return r != 0;
+}
+
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+// Shared memory of a block.
+struct Smem {
+  unsigned char* ring;       // [stages][STAGE_BYTES]
+  unsigned char* work;       // the norm's output (MMA operand, [k-blocks][16][64] swizzled) or the attention's stages
+  float* ex;                 // [64][16] exchange of the gated epilogue
+  uint64_t* full;            // [stages]
+  uint64_t* empty;           // [stages]
+  uint64_t* acc_full;        // [2]
+  uint64_t* acc_empty;       // [2]
+  uint64_t* x_ready;         // [1]
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  volatile int* w_issued;    // k-blocks whose weights the producer has asked for
+  volatile int* phase_open;  // grid barriers this block has passed
+  volatile int* flag;        // compute warps' broadcast word (ticket results)
+  int* pages;                // [PAGES_S]
+};
+
+// ---- the grid barrier ---------------------------------------------------------------------------
+// All compute threads of all blocks.  `seq` counts the barriers of the step from 1; the counter in
+// global memory starts the step at 0 (cleared by the host in stream order).
+__device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm, int seq, int nb, int ct, const Abort& ab) {
+  compute_sync();
+  if (ct == 0) {
+    bool ok = !ab.raised();
+    if (ok) {
+      __threadfence();
+      atomicAdd(a.ctrl, 1);
+      const int target = seq * nb;
+      const long long t0 = clock64();
+      for (uint32_t i = 0;; ++i) {
+        if (ld_acquire_gpu(a.ctrl) >= target) break;
+        if ((i & 15u) == 15u) {
+          if (ab.raised() || ld_acquire_gpu(a.ctrl + 1) != 0) {
+            ok = false;
+            break;
+          }
+          if (clock64() - t0 > 4 * WAIT_LIMIT_CYCLES) {
+            ab.raise(40);
+            ok = false;
+            break;
+          }
+        }
+      }
+    }
+    if (!ok) *ab.flag = 1;
+    st_release_cta(sm.phase_open, ok ? seq : (1 << 30));          // a block that gives up lets its loader through
+  }
+  compute_sync();
+  return !ab.raised();
+}
+
+// ---- the norm that opens a phase ------------------------------------------------------------------
+// x[t, :] = w * bf16(r * rsqrt(mean(r^2) + eps)) for the step's tokens, r = resid[t, :] (32-bit
+// statistics, turingserve/ops/reference.py:13-23), written as the B operand of the products that
+// follow: k-block kb is a [16 tokens][64] tile of 128-byte rows with the 128-byte swizzle.
+template <typename WT>
+__device__ void norm_to_operand(const TsStepArgs& a, const Smem& sm, const WT* __restrict__ w, int ct) {
+  const int warp = ct >> 5, lane = ct & 31;
+  const int chunks = a.hidden / 8;                     // 16-byte chunks a row
+  // rows of tokens that do not exist are zero
+  for (int idx = ct; idx < (BN - a.T) * chunks; idx += CT) {
+    const int t = a.T + idx / chunks, c = idx % chunks;
+    *reinterpret_cast<uint4*>(sm.work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  constexpr int KEEP = 8;                              // chunks a lane keeps in registers (rows up to 2,048 wide)
+  for (int t = warp; t < a.T; t += 4) {
+    const bf16* row = reinterpret_cast<const bf16*>(a.resid) + (size_t)t * a.hidden;
+    uint4 kept[KEEP];
+    float ss = 0.f;
+    int j = 0;
+    for (int c = lane; c < chunks; c += 32, ++j) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
+      if (j < KEEP) kept[j] = v;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
+    j = 0;
+    for (int c = lane; c < chunks; c += 32, ++j) {
+      const uint4 v = j < KEEP ? kept[j < KEEP ? j : 0] : __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
+      const bf16* e = reinterpret_cast<const bf16*>(&v);
+      uint4 o;
+      bf16* oe = reinterpret_cast<bf16*>(&o);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        oe[k] = __float2bfloat16_rn(to_f(w[c * 8 + k]) * round_to<bf16>(to_f(e[k]) * rstd));
+      *reinterpret_cast<uint4*>(sm.work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = o;
+    }
+  }
+  fence_async_smem();                                  // ordinary stores, read by the tensor core
+  mbar_arrive(sm.x_ready);
+}
+
+// ---- accumulator read-back ----------------------------------------------------------------------
+// Row r = quadrant * 32 + lane of accumulator `acc`: the 16 token columns.
+__device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_base, int v, int quad, float (&x)[BN],
+                                                 const Abort& ab) {
+  const int acc = v & 1;
+  bool ok = mwait(&sm.acc_full[acc], (uint32_t)(v >> 1) & 1u, ab, 31);
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) return false;
+  tc_fence_after();
+  uint32_t raw[16];
+  tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN), raw);
+  tmem_wait_ld();
+  tc_fence_before();
+  mbar_arrive(&sm.acc_empty[acc]);
+#pragma unroll
+  for (int i = 0; i < BN; ++i) x[i] = __uint_as_float(raw[i]);
+  return true;
+}
+
+// Leaves this unit's partial sums in scratch and takes a ticket for its tile; true for the block that
+// comes last (it then sees every part).  Slot of (tile, part): [tile * S + part][token][row].
+__device__ __forceinline__ bool leave_partial(const TsStepArgs& a, const Smem& sm, const Unit& u, int S, int* tickets,
+                                              const float (&x)[BN], int r, int ct) {
+  float* mine = a.part + ((size_t)(u.tile * S + u.part) * BN) * BM;
+#pragma unroll
+  for (int c = 0; c < BN; ++c)
+    if (c < a.T) mine[c * BM + r] = x[c];
+  __threadfence();
+  compute_sync();
+  if (ct == 0) {
+    const int ticket = atomicAdd(&tickets[u.tile], 1);
+    const int last = ticket == S - 1;
+    if (last) tickets[u.tile] = 0;                     // ready for the next layer
+    *sm.flag = last;
+  }
+  compute_sync();
+  const bool last = *sm.flag != 0;
+  if (last) __threadfence();
+  return last;
+}
+
+// Sum over the parts of a tile, in part order, of token `tok`, row `row`.
+__device__ __forceinline__ float sum_parts(const TsStepArgs& a, int tile, int S, int tok, int row) {
+  const float* base = a.part + ((size_t)tile * S * BN + tok) * BM + row;
+  float v[16];
+  float acc = 0.f;
+  if (S <= 16) {
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp)
+      if (sp < S) v[sp] = __ldcg(base + (size_t)sp * BN * BM);
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp)
+      if (sp < S) acc += v[sp];
+  } else {
+    for (int sp = 0; sp < S; ++sp) acc += __ldcg(base + (size_t)sp * BN * BM);
+  }
+  return acc;
+}
+
+// The last block of a q/k/v tile (= one head of 128): bias, rotation of q and k, q/k/v out, new keys
+// and values into the cache (what ts_rope_kv_write does to a finished product).
+__device__ void finish_qkv(const TsStepArgs& a, const TsStepLayer& ly, int tile, int S, int r) {
+  const int head = tile, p = r & 63, tg = r >> 6;
+  const int N = (a.H + 2 * a.KVH) * D;
+  const bf16* bias = reinterpret_cast<const bf16*>(ly.qkv_bias);
+  bf16* qkv = reinterpret_cast<bf16*>(a.qkv);
+  const float b1 = bias != nullptr ? to_f(bias[head * D + p]) : 0.f;
+  const float b2 = bias != nullptr ? to_f(bias[head * D + p + 64]) : 0.f;
+  const int* slots = a.slot_mapping[ly.group];
+  for (int tok = tg; tok < a.T; tok += 2) {
+    float x1 = round_to<bf16>(sum_parts(a, tile, S, tok, p) + b1);
+    float x2 = round_to<bf16>(sum_parts(a, tile, S, tok, p + 64) + b2);
+    float o1 = x1, o2 = x2;
+    if (head < a.H + a.KVH && ly.cos_t != nullptr) {
+      const int pos = a.positions[tok];
+      const float cs = round_to<bf16>(ly.cos_t[(size_t)pos * 64 + p]);
+      const float sn = round_to<bf16>(ly.sin_t[(size_t)pos * 64 + p]);
+      o1 = x1 * cs - x2 * sn;
+      o2 = x2 * cs + x1 * sn;
+    }
+    const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
+    qkv[(size_t)tok * N + head * D + p] = w1;
+    qkv[(size_t)tok * N + head * D + p + 64] = w2;
+    if (head >= a.H) {
+      const int slot = slots[tok];
+      if (slot >= 0) {
+        const bool is_k = head < a.H + a.KVH;
+        const int kvh = head - a.H - (is_k ? 0 : a.KVH);
+        bf16* dst = reinterpret_cast<bf16*>(is_k ? ly.k_cache : ly.v_cache) +
+                    (((size_t)(slot / a.page) * a.KVH + kvh) * a.page + (size_t)(slot % a.page)) * D;
+        dst[p] = w1;
+        dst[p + 64] = w2;
+      }
+    }
+  }
+}
+
+// The last block of an output- or down-projection tile: resid = bf16(bf16(product) + resid).
+__device__ void finish_residual(const TsStepArgs& a, int tile, int S, int r) {
+  const int n = tile * BM + r;
+  if (n >= a.hidden) return;
+  for (int tok = 0; tok < a.T; ++tok) {
+    const float o = round_to<bf16>(sum_parts(a, tile, S, tok, r));
+    bf16* dst = reinterpret_cast<bf16*>(a.resid) + (size_t)tok * a.hidden + n;
+    const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(dst));
+    *dst = __float2bfloat16_rn(o + __bfloat162float(__ushort_as_bfloat16(raw)));
+  }
+}
+
+// ---- decode attention for one (request, kv head, key split) -----------------------------------------
+// The four compute warps on disjoint 16-key slices of every 64-key tile (as ts_attention_decode).
+__device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct) {
+  constexpr int CH = D / 8, KS = D / 16, NT = D / 8;
+  const int NS = a.attn_splits;
+  const int b = unit / (a.KVH * NS), kvh = (unit / NS) % a.KVH, split = unit % NS;
+  const int H = a.H, KVH = a.KVH, G = H / KVH, page = a.page;
+  const int lane = ct & 31, warp = ct >> 5;
+  const int seq_len = a.seq_lens[b];
+  const int lo = ly.window > 0 ? max(0, seq_len - ly.window) : 0;
+  const int span = max(seq_len - lo, 0);
+  int chunk = (span + NS - 1) / NS;
+  chunk = (chunk + ATT_TILE - 1) / ATT_TILE * ATT_TILE;
+  const int k_begin = lo + split * chunk;
+  const int k_end = min(seq_len, k_begin + chunk);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + ATT_TILE - 1) / ATT_TILE : 0;
+  const int* table = a.block_tables[ly.group] + (size_t)b * a.table_width[ly.group];
+  unsigned char* k_s = sm.work;
+  unsigned char* v_s = sm.work + ATT_STAGES * ATT_TILE * D * 2;
+
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+  const int page_first = k_begin / page;
+  const int n_pages = k_end > k_begin ? (k_end - 1) / page - page_first + 1 : 0;
+  const bool staged = n_pages <= PAGES_S;
+  if (staged)
+    for (int i = ct; i < n_pages; i += CT) sm.pages[i] = table[page_first + i];
+  compute_sync();
+
+  auto load_tile = [&](int tile, int stage) {
+    const int j0 = k_begin + tile * ATT_TILE;
+    unsigned char* ks_ = k_s + stage * ATT_TILE * D * 2;
+    unsigned char* vs_ = v_s + stage * ATT_TILE * D * 2;
+    for (int idx = ct; idx < ATT_TILE * CH; idx += CT) {
+      const int key = idx / CH, c = idx % CH;
+      const int j = j0 + key;
+      const bool ok = j < k_end;
+      size_t off = 0;
+      if (ok) {
+        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+        const int pg = staged ? sm.pages[lp - page_first] : table[lp];
+        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
+      }
+      cp_async_16(ks_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.k_cache) + off, ok);
+      cp_async_16(vs_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.v_cache) + off, ok);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < ATT_STAGES - 1; ++s) {
+    if (s < n_tiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  unsigned qf[KS][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
+    const bf16* qbase = reinterpret_cast<const bf16*>(a.qkv) + (size_t)b * (H + 2 * KVH) * D + (size_t)kvh * G * D;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k = ks * 16 + kc;
+      qf[ks][0] = r0 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r0 * D + k)) : 0u;
+      qf[ks][1] = r1 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r1 * D + k)) : 0u;
+      qf[ks][2] = r0 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r0 * D + k + 8)) : 0u;
+      qf[ks][3] = r1 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r1 * D + k + 8)) : 0u;
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sc = a.scale * LOG2E;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    if (t + ATT_STAGES - 1 < n_tiles) load_tile(t + ATT_STAGES - 1, (t + ATT_STAGES - 1) % ATT_STAGES);
+    cp_async_commit();
+    cp_async_wait<ATT_STAGES - 1>();
+    compute_sync();
+    const unsigned char* ks_ = k_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
+    const unsigned char* vs_ = v_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
+    const int key0 = warp * 16;
+    const int j_base = k_begin + t * ATT_TILE + key0;
+    if (j_base < k_end) {
+      float s_acc[2][4] = {};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int mat = lane >> 3, r = lane & 7;
+        const int key = key0 + (mat >> 1) * 8 + r;
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, ks_ + swz<D>(key, ks * 2 + (mat & 1)));
+        mma_bf16(s_acc[0], qf[ks], b0, b1);
+        mma_bf16(s_acc[1], qf[ks], b2, b3);
+      }
+      float p[2][4];
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j_base + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const float v = j < k_end ? s_acc[nt][e] * sc : -INFINITY;
+          s_acc[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        corr[r] = exp2f(m_run[r] - m_new);
+        m_run[r] = m_new;
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[nt][e] = exp2f(s_acc[nt][e] - m_run[e >> 1]);
+          rs[e >> 1] += p[nt][e];
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        l_run[r] = l_run[r] * corr[r] + rs[r];
+      }
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      unsigned pf[4];
+      pf[0] = pack_bf16(p[0][0], p[0][1]);
+      pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]);
+      pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+      for (int i = 0; i < NT; i += 2) {
+        const int mat = lane >> 3, r = lane & 7;
+        const int key = key0 + (mat & 1) * 8 + r;
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + swz<D>(key, i + (mat >> 1)));
+        mma_bf16(o[i], pf, b0, b1);
+        mma_bf16(o[i + 1], pf, b2, b3);
+      }
+    }
+    compute_sync();
+  }
+  cp_async_wait<0>();
+  compute_sync();
+
+  // merge the four warps' states (the stage buffers are free now)
+  float* m_s = reinterpret_cast<float*>(sm.work);
+  float* l_s = m_s + 4 * 16;
+  float* o_s = l_s + 4 * 16;                                       // [4][16][D]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    if ((lane & 3) == 0) {
+      m_s[warp * 16 + r0] = m_run[0];
+      m_s[warp * 16 + r1] = m_run[1];
+      l_s[warp * 16 + r0] = l_run[0];
+      l_s[warp * 16 + r1] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      float* x = o_s + ((size_t)warp * 16 + r0) * D + d;
+      float* y = o_s + ((size_t)warp * 16 + r1) * D + d;
+      x[0] = o[i][0];
+      x[1] = o[i][1];
+      y[0] = o[i][2];
+      y[1] = o[i][3];
+    }
+  }
+  compute_sync();
+  float* f_s = o_s + 4 * 16 * D;                                   // [4][16]
+  float* M_s = f_s + 4 * 16;
+  float* L_s = M_s + 16;
+  if (ct < 4 * G) {
+    const int v = ct / G, g = ct % G;
+    float M = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) M = fmaxf(M, m_s[u * 16 + g]);
+    const float mv = m_s[v * 16 + g];
+    f_s[v * 16 + g] = (mv == -INFINITY) ? 0.f : exp2f(mv - M);
+    if (v == 0) {
+      float L = 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float mu = m_s[u * 16 + g];
+        if (mu != -INFINITY) L += l_s[u * 16 + g] * exp2f(mu - M);
+      }
+      M_s[g] = M;
+      L_s[g] = L;
+    }
+  }
+  compute_sync();
+  float* part_acc = a.attn_part;
+  float* part_ml = a.attn_part + (size_t)a.T * H * NS * D;
+  for (int idx = ct; idx < G * (D / 4); idx += CT) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const float f = f_s[v * 16 + g];
+      const float4 x = *reinterpret_cast<const float4*>(o_s + ((size_t)v * 16 + g) * D + d);
+      acc.x += x.x * f; acc.y += x.y * f; acc.z += x.z * f; acc.w += x.w * f;
+    }
+    const int h = kvh * G + g;
+    if (NS == 1) {
+      const float L = L_s[g], inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* op = reinterpret_cast<bf16*>(a.attn) + (size_t)b * H * D + (size_t)h * D + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    } else {
+      const size_t pi = ((size_t)b * H + h) * NS + split;
+      *reinterpret_cast<float4*>(part_acc + pi * D + d) = acc;
+      if (d == 0) *reinterpret_cast<float2*>(part_ml + pi * 2) = make_float2(M_s[g], L_s[g]);
+    }
+  }
+  if (NS == 1) {
+    compute_sync();
+    return;
+  }
+  __threadfence();
+  compute_sync();
+  if (ct == 0) {
+    int* counter = a.tickets + TS_STEP_TICKETS_ATTN + b * KVH + kvh;
+    const int ticket = atomicAdd(counter, 1);
+    const int last = ticket == NS - 1;
+    if (last) *counter = 0;
+    *sm.flag = last;
+  }
+  compute_sync();
+  if (*sm.flag == 0) {
+    compute_sync();
+    return;
+  }
+  __threadfence();
+  float* w_s = reinterpret_cast<float*>(sm.work);                  // [G][NS]
+  float* m_all = w_s + G * NS;
+  float* l_all = m_all + G * NS;
+  for (int idx = ct; idx < G * NS; idx += CT) {
+    const int g = idx / NS, s2 = idx % NS;
+    const size_t pi = ((size_t)b * H + kvh * G + g) * NS + s2;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + pi * 2));
+    m_all[idx] = ml.x;
+    l_all[idx] = ml.y;
+  }
+  compute_sync();
+  for (int idx = ct; idx < G * NS; idx += CT) {
+    const int g = idx / NS;
+    float M = -INFINITY, L = 0.f;
+    for (int s2 = 0; s2 < NS; ++s2) M = fmaxf(M, m_all[g * NS + s2]);
+    if (M > -INFINITY)
+      for (int s2 = 0; s2 < NS; ++s2) {
+        const float ms = m_all[g * NS + s2];
+        if (ms != -INFINITY) L += l_all[g * NS + s2] * exp2f(ms - M);
+      }
+    const float mi = m_all[idx];
+    w_s[idx] = (L > 0.f && mi != -INFINITY) ? exp2f(mi - M) / L : 0.f;
+  }
+  compute_sync();
+  for (int idx = ct; idx < G * (D / 4); idx += CT) {
+    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    const int h = kvh * G + g;
+    const float* src = part_acc + (((size_t)b * H + h) * NS) * D + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s2 = 0; s2 < NS; ++s2) {
+      const float w = w_s[g * NS + s2];
+      if (w != 0.f) {                                               // a split without keys left nothing to read
+        const float4 v = ldcg4(src + (size_t)s2 * D);
+        acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+      }
+    }
+    bf16* op = reinterpret_cast<bf16*>(a.attn) + (size_t)b * H * D + (size_t)h * D + d;
+    *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x, acc.y);
+    *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+  }
+  compute_sync();
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __grid_constant__ TsStepArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int NST = a.stages;
+  Smem sm;
+  sm.ring = base;
+  sm.work = base + (size_t)NST * STAGE_BYTES;
+  sm.ex = reinterpret_cast<float*>(sm.work + a.work_bytes);
+  sm.full = reinterpret_cast<uint64_t*>(sm.ex + 64 * BN);
+  sm.empty = sm.full + NST;
+  sm.acc_full = sm.empty + NST;
+  sm.acc_empty = sm.acc_full + 2;
+  sm.x_ready = sm.acc_empty + 2;
+  sm.tmem_slot = reinterpret_cast<uint32_t*>(sm.x_ready + 1);
+  sm.abort_flag = reinterpret_cast<volatile int*>(sm.tmem_slot + 1);
+  sm.w_issued = sm.abort_flag + 1;
+  sm.phase_open = sm.abort_flag + 2;
+  sm.flag = sm.abort_flag + 3;
+  sm.pages = const_cast<int*>(reinterpret_cast<volatile int*>(sm.abort_flag + 4));
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, nb = gridDim.x;
+  const Abort ab{sm.abort_flag, a.status, a.ctrl + 1};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&sm.full[s], FULL_COUNT);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.acc_full[0], 1);
+    mbar_init(&sm.acc_full[1], 1);
+    mbar_init(&sm.acc_empty[0], CT);
+    mbar_init(&sm.acc_empty[1], CT);
+    mbar_init(sm.x_ready, CT);
+    *sm.abort_flag = 0;
+    *sm.w_issued = 0;
+    *sm.phase_open = 0;
+    *sm.flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // the activation part of every stage starts as zeros: rows of tokens that do not exist are never written
+  for (int i = threadIdx.x; i < NST * (X_BYTES / 16); i += NUM_THREADS)
+    *reinterpret_cast<uint4*>(sm.ring + (size_t)(i / (X_BYTES / 16)) * STAGE_BYTES + W_BYTES + (i % (X_BYTES / 16)) * 16) =
+        make_uint4(0u, 0u, 0u, 0u);
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(32) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm.tmem_slot;
+
+  if (warp == 0) {
+    // ---- weight producer ------------------------------------------------------------------------
+    if (lane == 0) {
+      Walker w, ahead;
+      w.start();
+      ahead.start();
+      Unit u, ua;
+      int q = 0;
+      int a_kb = 0, a_left = 0;                       // the look-ahead cursor: k-block within `ua`, units still valid
+      bool a_more = ahead.next(a, cta, nb, ua);
+      if (a_more) a_kb = ua.kb0;
+      int a_q = 0;                                    // k-blocks the look-ahead has asked L2 for
+      (void)a_left;
+      bool ok = true;
+      while (ok && w.next(a, cta, nb, u)) {
+        const CUtensorMap* map = map_of(a, u.kind, u.layer);
+        for (int kb = u.kb0; kb < u.kb1 && ok; ++kb, ++q) {
+          // keep L2 `lookahead` k-blocks ahead of the ring
+          while (a_more && a_q < q + NST + a.lookahead) {
+            if (a_q >= q + NST)
+              asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_of(a, ua.kind, ua.layer)),
+                           "r"(a_kb * BK), "r"(ua.tile * BM) : "memory");
+            ++a_q;
+            if (++a_kb >= ua.kb1) {
+              a_more = ahead.next(a, cta, nb, ua);
+              if (a_more) a_kb = ua.kb0;
+            }
+          }
+          const int s = q % NST;
+          if (q >= NST) ok = mwait(&sm.empty[s], (uint32_t)((q / NST) - 1) & 1u, ab, 11);
+          if (!ok) break;
+          mbar_expect_tx(&sm.full[s], W_BYTES);
+          tma_load_2d(sm.ring + (size_t)s * STAGE_BYTES, map, kb * BK, u.tile * BM, &sm.full[s]);
+          st_release_cta(sm.w_issued, q + 1);
+        }
+      }
+      if (!ok) {
+        st_release_cta(sm.w_issued, 1 << 30);         // the loader must not wait for weights that will not come
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {}            // copies already asked for land in shared memory before the block leaves
+      }
+    }
+  } else if (warp == 1) {
+    // ---- tensor-core issue ----------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      Walker w;
+      w.start();
+      Unit u;
+      int q = 0, v = 0, xr = 0, cur_phase = -1;
+      bool ok = true;
+      while (ok && w.next(a, cta, nb, u)) {
+        const bool from_norm = u.kind == K_QKV || u.kind == K_GU || u.kind == K_HEAD;
+        const int phase = u.layer * 4 + u.kind;
+        if (from_norm && phase != cur_phase) {          // this phase's norm output must be in place
+          ok = mwait(sm.x_ready, (uint32_t)xr & 1u, ab, 21);
+          ++xr;
+          if (!ok) break;
+        }
+        cur_phase = phase;
+        const int acc = v & 1;
+        if (v >= 2) ok = mwait(&sm.acc_empty[acc], (uint32_t)((v >> 1) - 1) & 1u, ab, 22);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = u.kb0; kb < u.kb1; ++kb, ++q) {
+          const int s = q % NST;
+          ok = mwait(&sm.full[s], (uint32_t)(q / NST) & 1u, ab, 23);
+          if (!ok) break;
+          tc_fence_after();
+          fence_async_smem();                           // activations arrived by cp.async, an ordinary-proxy write
+          const uint64_t da = smem_desc(smem_u32(sm.ring + (size_t)s * STAGE_BYTES));
+          const uint64_t db = smem_desc(smem_u32(from_norm ? sm.work + (size_t)kb * X_BYTES
+                                                            : sm.ring + (size_t)s * STAGE_BYTES + W_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem_base + (uint32_t)(acc * BN), da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16),
+                 idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
+          umma_commit(&sm.empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&sm.acc_full[acc]);
+        ++v;
+      }
+    }
+  } else if (warp == 2) {
+    // ---- activation loader ----------------------------------------------------------------------
+    Walker w;
+    w.start();
+    Unit u;
+    int q = 0;
+    bool ok = true;
+    while (ok && w.next(a, cta, nb, u)) {
+      const bool stream = u.kind == K_O || u.kind == K_DOWN;
+      const bf16* src = reinterpret_cast<const bf16*>(u.kind == K_O ? a.attn : a.act);
+      const int K = u.kind == K_O ? a.H * D : a.inter;
+      if (stream) {
+        // the output projection of layer l opens after barrier 5 l + 3, the down projection after 5 l + 5
+        ok = wait_shared_ge(sm.phase_open, 5 * u.layer + (u.kind == K_O ? 3 : 5), ab, 51);
+        ok = __all_sync(0xffffffffu, ok) && !ab.raised();
+        if (!ok) break;
+      }
+      for (int kb = u.kb0; kb < u.kb1; ++kb, ++q) {
+        const int s = q % NST;
+        ok = wait_shared_ge(sm.w_issued, q + 1, ab, 52);
+        ok = __all_sync(0xffffffffu, ok) && !ab.raised();
+        if (!ok) break;
+        if (stream) {
+          unsigned char* xs = sm.ring + (size_t)s * STAGE_BYTES + W_BYTES;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j, t = i >> 3, c = i & 7;
+            if (t < a.T) cp_async_16(xs + t * 128 + ((c ^ (t & 7)) << 4), src + (size_t)t * K + kb * BK + c * 8, true);
+          }
+          cp_async_arrive_noinc(&sm.full[s]);
+        } else {
+          mbar_arrive(&sm.full[s]);
+        }
+      }
+    }
+    cp_async_wait_all();
+  } else {
+    // ---- compute warps ----------------------------------------------------------------------------
+    const int ct = threadIdx.x - CW0 * 32;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    int v = 0, seq = 0;
+    bool ok = true;
+    pdl_wait();                                        // the step's ids, positions and tables are in place
+    // embedding rows into the residual stream (the first norm adds nothing to them)
+    if (cta < a.T) {
+      const int id = a.ids[cta];
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.embedding) + (size_t)id * a.hidden);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(a.resid) + (size_t)cta * a.hidden);
+      for (int i = ct; i < a.hidden / 8; i += CT) dst[i] = src[i];
+    }
+    ok = grid_barrier(a, sm, ++seq, nb, ct, ab);
+
+    auto run_units = [&](int kind, int layer, auto&& finish) {
+      const TsStepShape& sh = a.shape[kind];
+      const int S = (sh.KB + sh.per - 1) / sh.per;
+      for (int un = (cta + sh.rot) % nb; ok && un < sh.R * sh.S; un += nb) {
+        Unit u{kind, layer, un / sh.S, un % sh.S, 0, 0};
+        float x[BN];
+        ok = compute_all(read_accumulator(sm, tmem_base, v, quad, x, ab));
+        ++v;
+        if (ok) finish(u, S, x);
+      }
+    };
+    auto open_with_norm = [&](int kind, const void* w) {
+      if (!ok || !has_units(a, kind, cta, nb)) return;
+      if (a.norm_w_is_f32) norm_to_operand<float>(a, sm, reinterpret_cast<const float*>(w), ct);
+      else norm_to_operand<bf16>(a, sm, reinterpret_cast<const bf16*>(w), ct);
+    };
+
+    for (int layer = 0; layer < a.L && ok; ++layer) {
+      const TsStepLayer& ly = a.layers[layer];
+      // q/k/v
+      open_with_norm(K_QKV, ly.ln1_w);
+      run_units(K_QKV, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
+        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_QKV, x, r, ct)) finish_qkv(a, ly, u.tile, S, r);
+      });
+      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+      // attention
+      if (ok && cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct);
+      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+      // output projection, residual add
+      run_units(K_O, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
+        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_O, x, r, ct)) finish_residual(a, u.tile, S, r);
+      });
+      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+      // gate/up with SiLU * mul: rows 0..63 of a tile are gates, 64..127 their ups
+      open_with_norm(K_GU, ly.ln2_w);
+      run_units(K_GU, layer, [&](const Unit& u, int, const float (&x)[BN]) {
+        if (quad >= 2) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) sm.ex[(r - 64) * BN + c] = x[c];
+        }
+        compute_sync();
+        if (quad < 2) {
+          const int n = u.tile * 64 + r;
+          if (n < a.inter)
+            for (int c = 0; c < a.T; ++c) {
+              const float g = round_to<bf16>(x[c]);
+              const float up = round_to<bf16>(sm.ex[r * BN + c]);
+              const float sl = round_to<bf16>(silu_for<bf16>(g));
+              reinterpret_cast<bf16*>(a.act)[(size_t)c * a.inter + n] = __float2bfloat16_rn(sl * up);
+            }
+        }
+        compute_sync();
+      });
+      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+      // down projection, residual add
+      run_units(K_DOWN, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
+        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_DOWN, x, r, ct)) finish_residual(a, u.tile, S, r);
+      });
+      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+    }
+    // final norm and output head: 32-bit logits
+    open_with_norm(K_HEAD, a.final_norm_w);
+    run_units(K_HEAD, a.L, [&](const Unit& u, int, const float (&x)[BN]) {
+      const int n = u.tile * BM + r;
+      if (n < a.V)
+        for (int c = 0; c < a.T; ++c) a.logits[(size_t)c * a.V + n] = x[c];
+    });
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(32) : "memory");
+  }
+}
+
+__device__ int g_step_status = 0;
+
+int* step_status_word() {
+  static int* p = nullptr;
+  if (p == nullptr && cudaGetSymbolAddress((void**)&p, g_step_status) != cudaSuccess) p = nullptr;
+  return p;
+}
+
+}  // namespace
+
+int* ts_step_status_word() { return step_status_word(); }
+
+TS_API int ts_decode_step_status() {
+  int* p = step_status_word();
+  int v = -1;
+  if (p != nullptr) cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+// Encodes the tensor map of one weight matrix [rows, K] (bfloat16, row-major) as the kernel reads it:
+// boxes of 128 rows x 64 columns, 128-byte swizzle, zeros outside.  `out` is 128 bytes of HOST memory
+// (the caller copies the maps of all matrices to the device in one piece).
+TS_API int ts_decode_step_encode_map(void* out, const void* weights, int rows, int K) {
+  if (((uintptr_t)weights & 15) || K % 8) TS_REFUSE(TS_ERR_ALIGN, "ts_decode_step_encode_map: weights must be 16-byte aligned, K a multiple of 8");
+  CUtensorMap m;
+  if (!tc::tensor_map(&m, weights, rows, K, BM)) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step_encode_map: cuTensorMapEncodeTiled failed");
+  memcpy(out, &m, sizeof(m));
+  return 0;
+}
+
+TS_API int ts_decode_step_sizes(int* args_bytes, int* layer_bytes, int* map_bytes) {
+  *args_bytes = (int)sizeof(TsStepArgs);
+  *layer_bytes = (int)sizeof(TsStepLayer);
+  *map_bytes = (int)sizeof(CUtensorMap);
+  return 0;
+}
+
+// Shared memory the kernel needs for `stages` ring stages and a work area of `work_bytes`.
+static size_t step_smem(int stages, int work_bytes) {
+  return 1024 + (size_t)stages * STAGE_BYTES + (size_t)work_bytes + 64 * BN * 4 + (size_t)(2 * stages + 5) * 8 + 32 + PAGES_S * 4;
+}
+
+// The work area: the norm's output for `hidden` columns, or the attention's stages and merge space.
+TS_API int ts_decode_step_work_bytes(int hidden) {
+  const int x = (hidden / BK) * X_BYTES;
+  const int att = 2 * ATT_STAGES * ATT_TILE * D * 2;
+  const int merge = 4 * (3 * 4 * 16 + 32 + 5 * 16 * D);
+  int m = x > att ? x : att;
+  m = m > merge ? m : merge;
+  return (m + 1023) / 1024 * 1024;
+}
+
+// The most ring stages that fit beside the work area (0: the shape does not fit at all).
+TS_API int ts_decode_step_max_stages(int hidden) {
+  int dev = 0, limit = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
+  const int work = ts_decode_step_work_bytes(hidden);
+  int st = 0;
+  while (st < 16 && step_smem(st + 1, work) <= (size_t)limit) ++st;
+  return st >= 3 ? st : 0;
+}
+
+// Blocks of the kernel that run at once on the current device (one per SM when the shape fits).
+TS_API int ts_decode_step_blocks(int stages, int hidden) {
+  int dev = 0, sms = 0, per = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  const size_t smem = step_smem(stages, ts_decode_step_work_bytes(hidden));
+  if (cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, decode_step_kernel, NUM_THREADS, smem) != cudaSuccess || per < 1) {
+    cudaGetLastError();
+    return 0;
+  }
+  return sms;
+}
+
+// Runs one decode step.  `args` is a TsStepArgs in HOST memory, filled by the caller (see
+// decode_step.h); its `status` is set here.  The control words (barrier counter, abort flag) are
+// cleared in stream order before the launch.  The launch is cooperative where the driver allows it
+// (all blocks are then guaranteed to be resident together, which the grid barriers need); where it
+// does not (inside some stream captures), an ordinary launch of one block per SM is the same thing as
+// long as nothing else occupies the device, and the barriers are bounded either way.
+TS_API int ts_decode_step(const void* args_host, int blocks, void* stream) {
+  TsStepArgs a;
+  memcpy(&a, args_host, sizeof(a));
+  if (a.T < 1 || a.T > BN) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: %d tokens (1..%d)", a.T, BN);
+  if (a.hidden % BK || a.inter % BK || a.H % a.KVH || a.H / a.KVH > 16 || a.L < 1)
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: hidden %d, inner %d, heads %d/%d are not taken by this kernel", a.hidden, a.inter, a.H, a.KVH);
+  if (a.stages < 3 || a.work_bytes < ts_decode_step_work_bytes(a.hidden)) TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: stages %d, work area %d", a.stages, a.work_bytes);
+  if (a.T * a.KVH * a.attn_splits > blocks || a.attn_splits < 1) TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: %d attention units on %d blocks", a.T * a.KVH * a.attn_splits, blocks);
+  for (int k = 0; k < 5; ++k) {
+    const TsStepShape& sh = a.shape[k];
+    if (sh.R < 1 || sh.KB < 1 || sh.S < 1 || sh.per < 1 || sh.S * sh.per < sh.KB || (sh.S - 1) * sh.per >= sh.KB)
+      TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: product %d is cut badly (R %d, KB %d, S %d, per %d)", k, sh.R, sh.KB, sh.S, sh.per);
+    if ((k == K_GU || k == K_HEAD) && sh.S != 1) TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: product %d cannot be split over K", k);
+    if (k != K_GU && k != K_HEAD && sh.R * sh.S > TS_STEP_MAX_UNITS) TS_REFUSE(TS_ERR_LIMIT, "ts_decode_step: product %d has too many units", k);
+    if (k != K_GU && k != K_HEAD && sh.R > TS_STEP_TICKETS_EACH) TS_REFUSE(TS_ERR_LIMIT, "ts_decode_step: product %d has too many tiles", k);
+  }
+  if (a.T * a.KVH > TS_STEP_TICKETS_EACH) TS_REFUSE(TS_ERR_LIMIT, "ts_decode_step: too many (request, kv head) pairs");
+  a.status = step_status_word();
+  if (a.status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_decode_step: no status word");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = step_smem(a.stages, a.work_bytes);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_decode_step: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  cudaError_t e = cudaMemsetAsync(a.ctrl, 0, 2 * sizeof(int), s);
+  if (e != cudaSuccess) TS_REFUSE((int)e, "ts_decode_step: clearing the control words: %s", cudaGetErrorString(e));
+  // 0: cooperative, 1: ordinary; remembered once one of them has worked
+  static int mode = 0;
+  for (; mode < 2; ++mode) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (mode == 0) {
+      attr[n].id = cudaLaunchAttributeCooperative;
+      attr[n].val.cooperative = 1;
+      ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    e = cudaLaunchKernelEx(&cfg, decode_step_kernel, a);
+    if (e == cudaSuccess) return 0;
+    cudaGetLastError();
+  }
+  mode = 0;
+  ts_set_error("ts_decode_step: launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}

@@ -16,7 +16,7 @@ void ts_set_error(const char* fmt, ...) {
 TS_API const char* ts_last_error() { return g_error; }
 
 // Compiled-for architecture and ABI version, so the Python side can refuse a stale library.
-TS_API int ts_abi_version() { return 4; }
+TS_API int ts_abi_version() { return 5; }
 
 // Programmatic dependent launch for this library's kernels (on by default).
 static bool g_pdl = true;
@@ -36,7 +36,7 @@ TsStatusPtrs ts_status_ptrs() {
   s.p[0] = ts_gemm_status_word();
   s.p[1] = ts_attn_status_word();
   s.p[2] = ts_dec_status_word();
-  s.p[3] = nullptr;
+  s.p[3] = ts_step_status_word();
   return s;
 }
 
