@@ -147,6 +147,7 @@ __device__ __forceinline__ bool wait_shared_ge(volatile int* p, int target, cons
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (ld_acquire_cta(p) >= target) return true;
+    __nanosleep(40);                                   // a polling warp must not take issue slots from the working ones
     if ((i & 63u) == 63u) {
       if (ab.raised()) return false;
       if (clock64() - t0 > 2 * WAIT_LIMIT_CYCLES) break;
@@ -154,6 +155,12 @@ __device__ __forceinline__ bool wait_shared_ge(volatile int* p, int target, cons
   }
   ab.raise(code);
   return false;
+}
+// The same for a whole warp: one lane polls.
+__device__ __forceinline__ bool warp_wait_shared_ge(volatile int* p, int target, const Abort& ab, int code, int lane) {
+  bool ok = true;
+  if (lane == 0) ok = wait_shared_ge(p, target, ab, code);
+  return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
 }
 
 __device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abort& ab, int code) {
@@ -164,6 +171,9 @@ __device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abor
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, int n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -181,23 +191,65 @@ __device__ __forceinline__ bool compute_all(bool ok) {
 
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
 
-// Shared memory of a block.
+// Shared memory of a block: one base address, the rest by offset (a pointer per field would keep two
+// dozen registers busy through every phase).
 struct Smem {
-  unsigned char* ring;       // [stages][STAGE_BYTES]
-  unsigned char* work;       // the norm's output (MMA operand, [k-blocks][16][64] swizzled) or the attention's stages
-  float* ex;                 // [64][16] exchange of the gated epilogue
-  uint64_t* full;            // [stages]
-  uint64_t* empty;           // [stages]
-  uint64_t* acc_full;        // [2]
-  uint64_t* acc_empty;       // [2]
-  uint64_t* x_ready;         // [1]
-  uint32_t* tmem_slot;
-  volatile int* abort_flag;
-  volatile int* w_issued;    // k-blocks whose weights the producer has asked for
-  volatile int* phase_open;  // grid barriers this block has passed
-  volatile int* flag;        // compute warps' broadcast word (ticket results)
-  int* pages;                // [PAGES_S]
+  unsigned char* base;       // 1024-byte aligned
+  int nst;                   // ring stages
+  int work_bytes;
+  __device__ __forceinline__ unsigned char* ring_() const { return base; }                       // [stages][STAGE_BYTES]
+  // the norm's output (MMA operand, [k-blocks][16][64] swizzled) or the attention's stages
+  __device__ __forceinline__ unsigned char* work_() const { return base + (size_t)nst * STAGE_BYTES; }
+  __device__ __forceinline__ float* ex_() const { return reinterpret_cast<float*>(work_() + work_bytes); }   // [64][16] exchange of the gated epilogue
+  __device__ __forceinline__ uint64_t* full_() const { return reinterpret_cast<uint64_t*>(ex_() + 64 * BN); }  // [stages]
+  __device__ __forceinline__ uint64_t* empty_() const { return full_() + nst; }                    // [stages]
+  __device__ __forceinline__ uint64_t* acc_full_() const { return empty_() + nst; }                // [2]
+  __device__ __forceinline__ uint64_t* acc_empty_() const { return acc_full_() + 2; }              // [2]
+  __device__ __forceinline__ uint64_t* x_ready_() const { return acc_empty_() + 2; }               // [1]
+  __device__ __forceinline__ uint32_t* tmem_slot_() const { return reinterpret_cast<uint32_t*>(x_ready_() + 1); }
+  // (the barriers end 8 bytes past a multiple of 16: two words further the integers start 16-byte aligned,
+  // which the cp.async copies into the scale slots behind them need)
+  __device__ __forceinline__ volatile int* ints_() const { return reinterpret_cast<volatile int*>(tmem_slot_() + 2); }
+  __device__ __forceinline__ volatile int* abort_flag_() const { return ints_(); }
+  __device__ __forceinline__ volatile int* w_issued_() const { return ints_() + 1; }   // k-blocks whose weights the producer has asked for
+  __device__ __forceinline__ volatile int* phase_open_() const { return ints_() + 2; } // grid barriers this block has passed
+  __device__ __forceinline__ volatile int* flag_() const { return ints_() + 3; }       // compute warps' broadcast word (ticket results)
+  __device__ __forceinline__ int* pos_() const { return const_cast<int*>(ints_()) + 4; }           // [16] the step's positions
+  __device__ __forceinline__ int* seq_() const { return pos_() + BN; }                             // [16] context lengths
+  __device__ __forceinline__ int* slot_() const { return seq_() + BN; }                            // [groups][16] cache slots of the new tokens
+  // [groups][PAGES_S] pages of this block's share of the keys (the same in every layer of a group)
+  __device__ __forceinline__ int* pages_() const { return slot_() + TS_STEP_MAX_GROUPS * BN; }
+  // [2][hidden] scale of the norm in use and of the next one (brought in while the phases between them run)
+  __device__ __forceinline__ unsigned char* scale_(int slot, int bytes) const {
+    return reinterpret_cast<unsigned char*>(pages_() + TS_STEP_MAX_GROUPS * PAGES_S) + (size_t)slot * bytes;
+  }
 };
+
+// This block's share of the keys of its attention unit, for a group whose layers see `window` keys.
+struct KeyRange {
+  int b, kvh, split, k_begin, k_end, page_first, n_pages;
+};
+__device__ __forceinline__ KeyRange key_range(const TsStepArgs& a, int unit, int seq_len, int window) {
+  KeyRange k;
+  const int NS = a.attn_splits;
+  k.b = unit / (a.KVH * NS);
+  k.kvh = (unit / NS) % a.KVH;
+  k.split = unit % NS;
+  const int lo = window > 0 ? max(0, seq_len - window) : 0;
+  const int span = max(seq_len - lo, 0);
+  int chunk = (span + NS - 1) / NS;
+  chunk = (chunk + ATT_TILE - 1) / ATT_TILE * ATT_TILE;
+  k.k_begin = lo + k.split * chunk;
+  k.k_end = min(seq_len, k.k_begin + chunk);
+  k.page_first = k.k_begin / a.page;
+  k.n_pages = k.k_end > k.k_begin ? (k.k_end - 1) / a.page - k.page_first + 1 : 0;
+  return k;
+}
+
+// A time stamp for the timeline: slot k (2..7) of the interval that ends at barrier `seq`.
+__device__ __forceinline__ void mark(const TsStepArgs& a, int seq, int k, int ct) {
+  if (a.trace != nullptr && ct == 0) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8 + k] = clock64();
+}
 
 // ---- the grid barrier ---------------------------------------------------------------------------
 // All compute threads of all blocks.  `seq` counts the barriers of the step from 1; the counter in
@@ -207,6 +259,7 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
   if (ct == 0) {
     bool ok = !ab.raised();
     if (ok) {
+      if (a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8] = clock64();
       __threadfence();
       atomicAdd(a.ctrl, 1);
       const int target = seq * nb;
@@ -226,8 +279,9 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
         }
       }
     }
+    if (ok && a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8 + 1] = clock64();
     if (!ok) *ab.flag = 1;
-    st_release_cta(sm.phase_open, ok ? seq : (1 << 30));          // a block that gives up lets its loader through
+    st_release_cta(sm.phase_open_(), ok ? seq : (1 << 30));          // a block that gives up lets its loader through
   }
   compute_sync();
   return !ab.raised();
@@ -237,47 +291,87 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
 // x[t, :] = w * bf16(r * rsqrt(mean(r^2) + eps)) for the step's tokens, r = resid[t, :] (32-bit
 // statistics, turingserve/ops/reference.py:13-23), written as the B operand of the products that
 // follow: k-block kb is a [16 tokens][64] tile of 128-byte rows with the 128-byte swizzle.
-template <typename WT>
-__device__ void norm_to_operand(const TsStepArgs& a, const Smem& sm, const WT* __restrict__ w, int ct) {
-  const int warp = ct >> 5, lane = ct & 31;
+// Half a warp per token (eight tokens a pass), 16 chunks of 8 values a lane kept in registers between
+// the two passes (rows up to 2,048 wide; wider rows are read twice).  The scale `ws` is in shared
+// memory, 32-bit or bfloat16.  One copy of this code in the kernel: the phases of a layer run seldom
+// enough that what they execute comes from the instruction cache only if it is small.
+__device__ void norm_to_operand(const TsStepArgs& a, unsigned char* work, uint64_t* x_ready, const unsigned char* ws, int ct,
+                                long long* tr) {
+  const int half = ct >> 4, hl = ct & 15;
   const int chunks = a.hidden / 8;                     // 16-byte chunks a row
-  // rows of tokens that do not exist are zero
-  for (int idx = ct; idx < (BN - a.T) * chunks; idx += CT) {
-    const int t = a.T + idx / chunks, c = idx % chunks;
-    *reinterpret_cast<uint4*>(sm.work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-  }
-  constexpr int KEEP = 8;                              // chunks a lane keeps in registers (rows up to 2,048 wide)
-  for (int t = warp; t < a.T; t += 4) {
+  constexpr int KEEP = 16;
+  const bool fits = chunks <= 16 * KEEP;
+  const bool f32 = a.norm_w_is_f32 != 0;
+#pragma unroll 1
+  for (int t0 = 0; t0 < a.T; t0 += 8) {
+    const int t = t0 + half;
+    const bool live = t < a.T;
     const bf16* row = reinterpret_cast<const bf16*>(a.resid) + (size_t)t * a.hidden;
     uint4 kept[KEEP];
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int c = hl + 16 * j;
+      kept[j] = (live && c < chunks) ? __ldcg(reinterpret_cast<const uint4*>(row + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (t0 == 0)                                       // rows of tokens that do not exist are zero (while the loads travel)
+      for (int tz = a.T + half; tz < BN; tz += 8)
+        for (int c = hl; c < chunks; c += 16)
+          *reinterpret_cast<uint4*>(work + (c >> 3) * X_BYTES + tz * 128 + (((c & 7) ^ (tz & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
     float ss = 0.f;
-    int j = 0;
-    for (int c = lane; c < chunks; c += 32, ++j) {
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
-      if (j < KEEP) kept[j] = v;
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&kept[j]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(h[k]);
+        const float2 f = __bfloat1622float2(e[k]);
         ss += f.x * f.x + f.y * f.y;
       }
     }
-    ss = warp_sum(ss);
+    if (!fits && live)
+      for (int c = hl + 16 * KEEP; c < chunks; c += 16) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
+        const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(e[k]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // over the 16 lanes of the token
     const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
-    j = 0;
-    for (int c = lane; c < chunks; c += 32, ++j) {
-      const uint4 v = j < KEEP ? kept[j < KEEP ? j : 0] : __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
+    if (tr != nullptr && ct == 0) tr[6] = clock64();
+    auto put = [&](int c, const uint4& v) {
       const bf16* e = reinterpret_cast<const bf16*>(&v);
+      float wv[8];
+      if (f32) {
+        const float4 w0 = *reinterpret_cast<const float4*>(ws + (size_t)c * 32), w1 = *reinterpret_cast<const float4*>(ws + (size_t)c * 32 + 16);
+        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+      } else {
+        const uint4 wq = *reinterpret_cast<const uint4*>(ws + (size_t)c * 16);
+        const bf16* we = reinterpret_cast<const bf16*>(&wq);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) wv[k] = to_f(we[k]);
+      }
       uint4 o;
       bf16* oe = reinterpret_cast<bf16*>(&o);
 #pragma unroll
-      for (int k = 0; k < 8; ++k)
-        oe[k] = __float2bfloat16_rn(to_f(w[c * 8 + k]) * round_to<bf16>(to_f(e[k]) * rstd));
-      *reinterpret_cast<uint4*>(sm.work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = o;
+      for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16_rn(wv[k] * round_to<bf16>(to_f(e[k]) * rstd));
+      *reinterpret_cast<uint4*>(work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = o;
+    };
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < KEEP; ++j) {
+        const int c = hl + 16 * j;
+        if (c < chunks) put(c, kept[j]);
+      }
+      if (!fits)
+        for (int c = hl + 16 * KEEP; c < chunks; c += 16) put(c, __ldcg(reinterpret_cast<const uint4*>(row + c * 8)));
     }
   }
+  if (tr != nullptr && ct == 0) tr[7] = clock64();
   fence_async_smem();                                  // ordinary stores, read by the tensor core
-  mbar_arrive(sm.x_ready);
+  mbar_arrive(x_ready);
 }
 
 // ---- accumulator read-back ----------------------------------------------------------------------
@@ -285,7 +379,7 @@ __device__ void norm_to_operand(const TsStepArgs& a, const Smem& sm, const WT* _
 __device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_base, int v, int quad, float (&x)[BN],
                                                  const Abort& ab) {
   const int acc = v & 1;
-  bool ok = mwait(&sm.acc_full[acc], (uint32_t)(v >> 1) & 1u, ab, 31);
+  bool ok = mwait(&sm.acc_full_()[acc], (uint32_t)(v >> 1) & 1u, ab, 31);
   ok = __all_sync(0xffffffffu, ok);
   if (!ok) return false;
   tc_fence_after();
@@ -293,7 +387,7 @@ __device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_b
   tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN), raw);
   tmem_wait_ld();
   tc_fence_before();
-  mbar_arrive(&sm.acc_empty[acc]);
+  mbar_arrive(&sm.acc_empty_()[acc]);
 #pragma unroll
   for (int i = 0; i < BN; ++i) x[i] = __uint_as_float(raw[i]);
   return true;
@@ -307,71 +401,92 @@ __device__ __forceinline__ bool leave_partial(const TsStepArgs& a, const Smem& s
 #pragma unroll
   for (int c = 0; c < BN; ++c)
     if (c < a.T) mine[c * BM + r] = x[c];
-  __threadfence();
-  compute_sync();
+  compute_sync();                                      // every thread's stores precede thread 0's fence
   if (ct == 0) {
+    __threadfence();
     const int ticket = atomicAdd(&tickets[u.tile], 1);
     const int last = ticket == S - 1;
-    if (last) tickets[u.tile] = 0;                     // ready for the next layer
-    *sm.flag = last;
+    if (last) {
+      tickets[u.tile] = 0;                             // ready for the next layer
+      __threadfence();                                 // the other parts' sums are visible from here on
+    }
+    *sm.flag_() = last;
   }
   compute_sync();
-  const bool last = *sm.flag != 0;
-  if (last) __threadfence();
-  return last;
+  return *sm.flag_() != 0;
 }
 
-// Sum over the parts of a tile, in part order, of token `tok`, row `row`.
-__device__ __forceinline__ float sum_parts(const TsStepArgs& a, int tile, int S, int tok, int row) {
-  const float* base = a.part + ((size_t)tile * S * BN + tok) * BM + row;
-  float v[16];
-  float acc = 0.f;
-  if (S <= 16) {
+// Sums over the parts of a tile, in part order, for up to NT tokens at once (tokens tok0, tok0 + stride,
+// ...; NT * S independent loads in flight, one round trip to L2): out[i] = sum_sp part[tile, sp, tok_i, row].
+template <int NT>
+__device__ __forceinline__ void sum_parts(const TsStepArgs& a, int tile, int S, int tok0, int stride, int row, float (&out)[NT]) {
+  const float* base = a.part + ((size_t)tile * S * BN) * BM + row;
 #pragma unroll
-    for (int sp = 0; sp < 16; ++sp)
-      if (sp < S) v[sp] = __ldcg(base + (size_t)sp * BN * BM);
+  for (int i = 0; i < NT; ++i) out[i] = 0.f;
+  for (int sp0 = 0; sp0 < S; sp0 += 8) {               // eight parts a round trip
+    float v[NT][8];
 #pragma unroll
-    for (int sp = 0; sp < 16; ++sp)
-      if (sp < S) acc += v[sp];
-  } else {
-    for (int sp = 0; sp < S; ++sp) acc += __ldcg(base + (size_t)sp * BN * BM);
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp)
+        v[i][sp] = (sp0 + sp < S && tok0 + i * stride < a.T) ? __ldcg(base + ((size_t)(sp0 + sp) * BN + tok0 + i * stride) * BM) : 0.f;
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) out[i] += v[i][sp];
   }
-  return acc;
 }
 
 // The last block of a q/k/v tile (= one head of 128): bias, rotation of q and k, q/k/v out, new keys
-// and values into the cache (what ts_rope_kv_write does to a finished product).
-__device__ void finish_qkv(const TsStepArgs& a, const TsStepLayer& ly, int tile, int S, int r) {
+// and values into the cache (what ts_rope_kv_write does to a finished product).  Everything it reads
+// from global memory is asked for at once: one round trip.
+__device__ void finish_qkv(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int tile, int S, int r) {
   const int head = tile, p = r & 63, tg = r >> 6;
   const int N = (a.H + 2 * a.KVH) * D;
   const bf16* bias = reinterpret_cast<const bf16*>(ly.qkv_bias);
   bf16* qkv = reinterpret_cast<bf16*>(a.qkv);
-  const float b1 = bias != nullptr ? to_f(bias[head * D + p]) : 0.f;
-  const float b2 = bias != nullptr ? to_f(bias[head * D + p + 64]) : 0.f;
-  const int* slots = a.slot_mapping[ly.group];
-  for (int tok = tg; tok < a.T; tok += 2) {
-    float x1 = round_to<bf16>(sum_parts(a, tile, S, tok, p) + b1);
-    float x2 = round_to<bf16>(sum_parts(a, tile, S, tok, p + 64) + b2);
-    float o1 = x1, o2 = x2;
-    if (head < a.H + a.KVH && ly.cos_t != nullptr) {
-      const int pos = a.positions[tok];
-      const float cs = round_to<bf16>(ly.cos_t[(size_t)pos * 64 + p]);
-      const float sn = round_to<bf16>(ly.sin_t[(size_t)pos * 64 + p]);
-      o1 = x1 * cs - x2 * sn;
-      o2 = x2 * cs + x1 * sn;
+  const bool rotate = head < a.H + a.KVH && ly.cos_t != nullptr;
+  for (int tok0 = tg; tok0 < a.T; tok0 += 8) {          // four tokens of this thread's parity a pass
+    float lo[4], hi[4], cs[4], sn[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int tok = tok0 + 2 * i;
+      cs[i] = 1.f;
+      sn[i] = 0.f;
+      if (rotate && tok < a.T) {
+        const int pos = sm.pos_()[tok];
+        cs[i] = ly.cos_t[(size_t)pos * 64 + p];
+        sn[i] = ly.sin_t[(size_t)pos * 64 + p];
+      }
     }
-    const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
-    qkv[(size_t)tok * N + head * D + p] = w1;
-    qkv[(size_t)tok * N + head * D + p + 64] = w2;
-    if (head >= a.H) {
-      const int slot = slots[tok];
-      if (slot >= 0) {
-        const bool is_k = head < a.H + a.KVH;
-        const int kvh = head - a.H - (is_k ? 0 : a.KVH);
-        bf16* dst = reinterpret_cast<bf16*>(is_k ? ly.k_cache : ly.v_cache) +
-                    (((size_t)(slot / a.page) * a.KVH + kvh) * a.page + (size_t)(slot % a.page)) * D;
-        dst[p] = w1;
-        dst[p + 64] = w2;
+    const float b1 = bias != nullptr ? to_f(bias[head * D + p]) : 0.f;
+    const float b2 = bias != nullptr ? to_f(bias[head * D + p + 64]) : 0.f;
+    sum_parts<4>(a, tile, S, tok0, 2, p, lo);
+    sum_parts<4>(a, tile, S, tok0, 2, p + 64, hi);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int tok = tok0 + 2 * i;
+      if (tok >= a.T) continue;
+      const float x1 = round_to<bf16>(lo[i] + b1), x2 = round_to<bf16>(hi[i] + b2);
+      float o1 = x1, o2 = x2;
+      if (rotate) {
+        const float c1 = round_to<bf16>(cs[i]), s1 = round_to<bf16>(sn[i]);
+        o1 = x1 * c1 - x2 * s1;
+        o2 = x2 * c1 + x1 * s1;
+      }
+      const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
+      qkv[(size_t)tok * N + head * D + p] = w1;
+      qkv[(size_t)tok * N + head * D + p + 64] = w2;
+      if (head >= a.H) {
+        const int slot = sm.slot_()[ly.group * BN + tok];
+        if (slot >= 0) {
+          const bool is_k = head < a.H + a.KVH;
+          const int kvh = head - a.H - (is_k ? 0 : a.KVH);
+          bf16* dst = reinterpret_cast<bf16*>(is_k ? ly.k_cache : ly.v_cache) +
+                      (((size_t)(slot / a.page) * a.KVH + kvh) * a.page + (size_t)(slot % a.page)) * D;
+          dst[p] = w1;
+          dst[p + 64] = w2;
+        }
       }
     }
   }
@@ -381,11 +496,19 @@ __device__ void finish_qkv(const TsStepArgs& a, const TsStepLayer& ly, int tile,
 __device__ void finish_residual(const TsStepArgs& a, int tile, int S, int r) {
   const int n = tile * BM + r;
   if (n >= a.hidden) return;
-  for (int tok = 0; tok < a.T; ++tok) {
-    const float o = round_to<bf16>(sum_parts(a, tile, S, tok, r));
-    bf16* dst = reinterpret_cast<bf16*>(a.resid) + (size_t)tok * a.hidden + n;
-    const unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(dst));
-    *dst = __float2bfloat16_rn(o + __bfloat162float(__ushort_as_bfloat16(raw)));
+  bf16* resid = reinterpret_cast<bf16*>(a.resid);
+  for (int tok0 = 0; tok0 < a.T; tok0 += 8) {
+    float sum[8];
+    unsigned short old[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      old[i] = tok0 + i < a.T ? __ldcg(reinterpret_cast<const unsigned short*>(resid + (size_t)(tok0 + i) * a.hidden + n)) : (unsigned short)0;
+    sum_parts<8>(a, tile, S, tok0, 1, r, sum);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (tok0 + i < a.T)
+        resid[(size_t)(tok0 + i) * a.hidden + n] =
+            __float2bfloat16_rn(round_to<bf16>(sum[i]) + __bfloat162float(__ushort_as_bfloat16(old[i])));
   }
 }
 
@@ -394,28 +517,20 @@ __device__ void finish_residual(const TsStepArgs& a, int tile, int S, int r) {
 __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct) {
   constexpr int CH = D / 8, KS = D / 16, NT = D / 8;
   const int NS = a.attn_splits;
-  const int b = unit / (a.KVH * NS), kvh = (unit / NS) % a.KVH, split = unit % NS;
   const int H = a.H, KVH = a.KVH, G = H / KVH, page = a.page;
   const int lane = ct & 31, warp = ct >> 5;
-  const int seq_len = a.seq_lens[b];
-  const int lo = ly.window > 0 ? max(0, seq_len - ly.window) : 0;
-  const int span = max(seq_len - lo, 0);
-  int chunk = (span + NS - 1) / NS;
-  chunk = (chunk + ATT_TILE - 1) / ATT_TILE * ATT_TILE;
-  const int k_begin = lo + split * chunk;
-  const int k_end = min(seq_len, k_begin + chunk);
+  const KeyRange kr = key_range(a, unit, sm.seq_()[unit / (KVH * NS)], ly.window);
+  const int b = kr.b, kvh = kr.kvh, split = kr.split, k_begin = kr.k_begin, k_end = kr.k_end;
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + ATT_TILE - 1) / ATT_TILE : 0;
   const int* table = a.block_tables[ly.group] + (size_t)b * a.table_width[ly.group];
-  unsigned char* k_s = sm.work;
-  unsigned char* v_s = sm.work + ATT_STAGES * ATT_TILE * D * 2;
-
+  unsigned char* work = sm.work_();
+  volatile int* flag = sm.flag_();
+  unsigned char* k_s = work;
+  unsigned char* v_s = work + ATT_STAGES * ATT_TILE * D * 2;
   const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
-  const int page_first = k_begin / page;
-  const int n_pages = k_end > k_begin ? (k_end - 1) / page - page_first + 1 : 0;
-  const bool staged = n_pages <= PAGES_S;
-  if (staged)
-    for (int i = ct; i < n_pages; i += CT) sm.pages[i] = table[page_first + i];
-  compute_sync();
+  const int page_first = kr.page_first;
+  const bool staged = kr.n_pages <= PAGES_S;           // then the pages were put in shared memory when the step began
+  const int* pages = sm.pages_() + ly.group * PAGES_S;
 
   auto load_tile = [&](int tile, int stage) {
     const int j0 = k_begin + tile * ATT_TILE;
@@ -428,7 +543,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
       size_t off = 0;
       if (ok) {
         const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
-        const int pg = staged ? sm.pages[lp - page_first] : table[lp];
+        const int pg = staged ? pages[lp - page_first] : table[lp];
         off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
       }
       cp_async_16(ks_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.k_cache) + off, ok);
@@ -541,7 +656,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   compute_sync();
 
   // merge the four warps' states (the stage buffers are free now)
-  float* m_s = reinterpret_cast<float*>(sm.work);
+  float* m_s = reinterpret_cast<float*>(work);
   float* l_s = m_s + 4 * 16;
   float* o_s = l_s + 4 * 16;                                       // [4][16][D]
   {
@@ -620,15 +735,15 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
     const int ticket = atomicAdd(counter, 1);
     const int last = ticket == NS - 1;
     if (last) *counter = 0;
-    *sm.flag = last;
+    *flag = last;
   }
   compute_sync();
-  if (*sm.flag == 0) {
+  if (*flag == 0) {
     compute_sync();
     return;
   }
   __threadfence();
-  float* w_s = reinterpret_cast<float*>(sm.work);                  // [G][NS]
+  float* w_s = reinterpret_cast<float*>(work);                  // [G][NS]
   float* m_all = w_s + G * NS;
   float* l_all = m_all + G * NS;
   for (int idx = ct; idx < G * NS; idx += CT) {
@@ -677,56 +792,42 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int NST = a.stages;
-  Smem sm;
-  sm.ring = base;
-  sm.work = base + (size_t)NST * STAGE_BYTES;
-  sm.ex = reinterpret_cast<float*>(sm.work + a.work_bytes);
-  sm.full = reinterpret_cast<uint64_t*>(sm.ex + 64 * BN);
-  sm.empty = sm.full + NST;
-  sm.acc_full = sm.empty + NST;
-  sm.acc_empty = sm.acc_full + 2;
-  sm.x_ready = sm.acc_empty + 2;
-  sm.tmem_slot = reinterpret_cast<uint32_t*>(sm.x_ready + 1);
-  sm.abort_flag = reinterpret_cast<volatile int*>(sm.tmem_slot + 1);
-  sm.w_issued = sm.abort_flag + 1;
-  sm.phase_open = sm.abort_flag + 2;
-  sm.flag = sm.abort_flag + 3;
-  sm.pages = const_cast<int*>(reinterpret_cast<volatile int*>(sm.abort_flag + 4));
+  const Smem sm{base, a.stages, a.work_bytes};
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, nb = gridDim.x;
-  const Abort ab{sm.abort_flag, a.status, a.ctrl + 1};
+  const Abort ab{sm.abort_flag_(), a.status, a.ctrl + 1};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
-      mbar_init(&sm.full[s], FULL_COUNT);
-      mbar_init(&sm.empty[s], 1);
+      mbar_init(&sm.full_()[s], FULL_COUNT);
+      mbar_init(&sm.empty_()[s], 1);
     }
-    mbar_init(&sm.acc_full[0], 1);
-    mbar_init(&sm.acc_full[1], 1);
-    mbar_init(&sm.acc_empty[0], CT);
-    mbar_init(&sm.acc_empty[1], CT);
-    mbar_init(sm.x_ready, CT);
-    *sm.abort_flag = 0;
-    *sm.w_issued = 0;
-    *sm.phase_open = 0;
-    *sm.flag = 0;
+    mbar_init(&sm.acc_full_()[0], 1);
+    mbar_init(&sm.acc_full_()[1], 1);
+    mbar_init(&sm.acc_empty_()[0], CT);
+    mbar_init(&sm.acc_empty_()[1], CT);
+    mbar_init(sm.x_ready_(), CT);
+    *sm.abort_flag_() = 0;
+    *sm.w_issued_() = 0;
+    *sm.phase_open_() = 0;
+    *sm.flag_() = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // the activation part of every stage starts as zeros: rows of tokens that do not exist are never written
   for (int i = threadIdx.x; i < NST * (X_BYTES / 16); i += NUM_THREADS)
-    *reinterpret_cast<uint4*>(sm.ring + (size_t)(i / (X_BYTES / 16)) * STAGE_BYTES + W_BYTES + (i % (X_BYTES / 16)) * 16) =
+    *reinterpret_cast<uint4*>(sm.ring_() + (size_t)(i / (X_BYTES / 16)) * STAGE_BYTES + W_BYTES + (i % (X_BYTES / 16)) * 16) =
         make_uint4(0u, 0u, 0u, 0u);
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(32) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot_())), "r"(32) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *sm.tmem_slot;
+  const uint32_t tmem_base = *sm.tmem_slot_();
 
   if (warp == 0) {
     // ---- weight producer ------------------------------------------------------------------------
@@ -736,14 +837,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
       ahead.start();
       Unit u, ua;
       int q = 0;
-      int a_kb = 0, a_left = 0;                       // the look-ahead cursor: k-block within `ua`, units still valid
+      int a_kb = 0;                                   // the look-ahead cursor: k-block within `ua`
       bool a_more = ahead.next(a, cta, nb, ua);
       if (a_more) a_kb = ua.kb0;
       int a_q = 0;                                    // k-blocks the look-ahead has asked L2 for
-      (void)a_left;
       bool ok = true;
       while (ok && w.next(a, cta, nb, u)) {
         const CUtensorMap* map = map_of(a, u.kind, u.layer);
+        const bool streamed = u.kind == K_O || u.kind == K_DOWN;
         for (int kb = u.kb0; kb < u.kb1 && ok; ++kb, ++q) {
           // keep L2 `lookahead` k-blocks ahead of the ring
           while (a_more && a_q < q + NST + a.lookahead) {
@@ -757,15 +858,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
             }
           }
           const int s = q % NST;
-          if (q >= NST) ok = mwait(&sm.empty[s], (uint32_t)((q / NST) - 1) & 1u, ab, 11);
+          if (q >= NST) ok = mwait(&sm.empty_()[s], (uint32_t)((q / NST) - 1) & 1u, ab, 11);
           if (!ok) break;
-          mbar_expect_tx(&sm.full[s], W_BYTES);
-          tma_load_2d(sm.ring + (size_t)s * STAGE_BYTES, map, kb * BK, u.tile * BM, &sm.full[s]);
-          st_release_cta(sm.w_issued, q + 1);
+          mbar_expect_tx(&sm.full_()[s], W_BYTES);
+          tma_load_2d(sm.ring_() + (size_t)s * STAGE_BYTES, map, kb * BK, u.tile * BM, &sm.full_()[s]);
+          if (streamed) st_release_cta(sm.w_issued_(), q + 1);        // the loader adds this k-block's activations
+          else mbar_arrive_n(&sm.full_()[s], 32);                     // the norm's output is the operand: nothing to add
         }
       }
       if (!ok) {
-        st_release_cta(sm.w_issued, 1 << 30);         // the loader must not wait for weights that will not come
+        st_release_cta(sm.w_issued_(), 1 << 30);         // the loader must not wait for weights that will not come
         const long long t0 = clock64();
         while (clock64() - t0 < 200000) {}            // copies already asked for land in shared memory before the block leaves
       }
@@ -783,32 +885,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
         const bool from_norm = u.kind == K_QKV || u.kind == K_GU || u.kind == K_HEAD;
         const int phase = u.layer * 4 + u.kind;
         if (from_norm && phase != cur_phase) {          // this phase's norm output must be in place
-          ok = mwait(sm.x_ready, (uint32_t)xr & 1u, ab, 21);
+          ok = mwait(sm.x_ready_(), (uint32_t)xr & 1u, ab, 21);
           ++xr;
           if (!ok) break;
         }
         cur_phase = phase;
         const int acc = v & 1;
-        if (v >= 2) ok = mwait(&sm.acc_empty[acc], (uint32_t)((v >> 1) - 1) & 1u, ab, 22);
+        if (v >= 2) ok = mwait(&sm.acc_empty_()[acc], (uint32_t)((v >> 1) - 1) & 1u, ab, 22);
         if (!ok) break;
         tc_fence_after();
         for (int kb = u.kb0; kb < u.kb1; ++kb, ++q) {
           const int s = q % NST;
-          ok = mwait(&sm.full[s], (uint32_t)(q / NST) & 1u, ab, 23);
+          ok = mwait(&sm.full_()[s], (uint32_t)(q / NST) & 1u, ab, 23);
           if (!ok) break;
           tc_fence_after();
           fence_async_smem();                           // activations arrived by cp.async, an ordinary-proxy write
-          const uint64_t da = smem_desc(smem_u32(sm.ring + (size_t)s * STAGE_BYTES));
-          const uint64_t db = smem_desc(smem_u32(from_norm ? sm.work + (size_t)kb * X_BYTES
-                                                            : sm.ring + (size_t)s * STAGE_BYTES + W_BYTES));
+          const uint64_t da = smem_desc(smem_u32(sm.ring_() + (size_t)s * STAGE_BYTES));
+          const uint64_t db = smem_desc(smem_u32(from_norm ? sm.work_() + (size_t)kb * X_BYTES
+                                                            : sm.ring_() + (size_t)s * STAGE_BYTES + W_BYTES));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma(tmem_base + (uint32_t)(acc * BN), da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16),
                  idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
-          umma_commit(&sm.empty[s]);
+          umma_commit(&sm.empty_()[s]);
         }
         if (!ok) break;
-        umma_commit(&sm.acc_full[acc]);
+        umma_commit(&sm.acc_full_()[acc]);
         ++v;
       }
     }
@@ -821,30 +923,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     bool ok = true;
     while (ok && w.next(a, cta, nb, u)) {
       const bool stream = u.kind == K_O || u.kind == K_DOWN;
+      if (!stream) {                                   // the producer arrives for this warp's lanes
+        q += u.kb1 - u.kb0;
+        continue;
+      }
       const bf16* src = reinterpret_cast<const bf16*>(u.kind == K_O ? a.attn : a.act);
       const int K = u.kind == K_O ? a.H * D : a.inter;
-      if (stream) {
-        // the output projection of layer l opens after barrier 5 l + 3, the down projection after 5 l + 5
-        ok = wait_shared_ge(sm.phase_open, 5 * u.layer + (u.kind == K_O ? 3 : 5), ab, 51);
-        ok = __all_sync(0xffffffffu, ok) && !ab.raised();
-        if (!ok) break;
-      }
+      // the output projection of layer l opens after barrier 5 l + 3, the down projection after 5 l + 5
+      ok = warp_wait_shared_ge(sm.phase_open_(), 5 * u.layer + (u.kind == K_O ? 3 : 5), ab, 51, lane) && !ab.raised();
+      if (!ok) break;
       for (int kb = u.kb0; kb < u.kb1; ++kb, ++q) {
         const int s = q % NST;
-        ok = wait_shared_ge(sm.w_issued, q + 1, ab, 52);
-        ok = __all_sync(0xffffffffu, ok) && !ab.raised();
+        ok = warp_wait_shared_ge(sm.w_issued_(), q + 1, ab, 52, lane) && !ab.raised();
         if (!ok) break;
-        if (stream) {
-          unsigned char* xs = sm.ring + (size_t)s * STAGE_BYTES + W_BYTES;
+        unsigned char* xs = sm.ring_() + (size_t)s * STAGE_BYTES + W_BYTES;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int i = lane + 32 * j, t = i >> 3, c = i & 7;
-            if (t < a.T) cp_async_16(xs + t * 128 + ((c ^ (t & 7)) << 4), src + (size_t)t * K + kb * BK + c * 8, true);
-          }
-          cp_async_arrive_noinc(&sm.full[s]);
-        } else {
-          mbar_arrive(&sm.full[s]);
+        for (int j = 0; j < 4; ++j) {
+          const int i = lane + 32 * j, t = i >> 3, c = i & 7;
+          if (t < a.T) cp_async_16(xs + t * 128 + ((c ^ (t & 7)) << 4), src + (size_t)t * K + kb * BK + c * 8, true);
         }
+        cp_async_arrive_noinc(&sm.full_()[s]);
       }
     }
     cp_async_wait_all();
@@ -855,7 +953,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     const int r = quad * 32 + lane;
     int v = 0, seq = 0;
     bool ok = true;
+    {                                                  // the first norm's scale: a weight, it need not wait for anything
+      const int sb = a.hidden * (a.norm_w_is_f32 ? 4 : 2);
+      unsigned char* dst = sm.scale_(0, sb);
+      for (int i = ct * 16; i < sb; i += CT * 16) cp_async_16(dst + i, reinterpret_cast<const unsigned char*>(a.layers[0].ln1_w) + i, true);
+    }
     pdl_wait();                                        // the step's ids, positions and tables are in place
+    // What the step's index arrays say about this block's work goes to shared memory once: positions,
+    // context lengths, cache slots, and the pages of this block's share of the keys (the same in every
+    // layer of a cache group).
+    if (ct < BN) {
+      sm.pos_()[ct] = ct < a.T ? a.positions[ct] : 0;
+      sm.seq_()[ct] = ct < a.T ? a.seq_lens[ct] : 0;
+      for (int g = 0; g < a.num_groups; ++g) sm.slot_()[g * BN + ct] = ct < a.T ? a.slot_mapping[g][ct] : -1;
+    }
+    compute_sync();
+    if (cta < a.T * a.KVH * a.attn_splits)
+      for (int g = 0; g < a.num_groups; ++g) {
+        const KeyRange kr = key_range(a, cta, sm.seq_()[cta / (a.KVH * a.attn_splits)], a.group_window[g]);
+        if (kr.n_pages <= PAGES_S) {
+          const int* table = a.block_tables[g] + (size_t)kr.b * a.table_width[g];
+          for (int i = ct; i < kr.n_pages; i += CT) sm.pages_()[g * PAGES_S + i] = table[kr.page_first + i];
+        }
+      }
     // embedding rows into the residual stream (the first norm adds nothing to them)
     if (cta < a.T) {
       const int id = a.ids[cta];
@@ -865,73 +985,92 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     }
     ok = grid_barrier(a, sm, ++seq, nb, ct, ab);
 
-    auto run_units = [&](int kind, int layer, auto&& finish) {
-      const TsStepShape& sh = a.shape[kind];
-      const int S = (sh.KB + sh.per - 1) / sh.per;
-      for (int un = (cta + sh.rot) % nb; ok && un < sh.R * sh.S; un += nb) {
-        Unit u{kind, layer, un / sh.S, un % sh.S, 0, 0};
-        float x[BN];
-        ok = compute_all(read_accumulator(sm, tmem_base, v, quad, x, ab));
-        ++v;
-        if (ok) finish(u, S, x);
+    // The phases of the step, one loop so that every piece of code exists once: phase p of layer p / 5
+    // is 0 q/k/v, 1 attention, 2 output projection, 3 gate/up, 4 down; after the last layer, the head.
+    const int scale_bytes = a.hidden * (a.norm_w_is_f32 ? 4 : 2);
+    const int n_phases = 5 * a.L + 1;
+    TsStepLayer ly = a.layers[0], next_ly = ly;
+#pragma unroll 1
+    for (int p = 0; p < n_phases && ok; ++p) {
+      const int layer = p / 5, k = p % 5;
+      const bool head = p == 5 * a.L;
+      const int kind = head ? K_HEAD : (k == 0 ? K_QKV : k == 2 ? K_O : k == 3 ? K_GU : k == 4 ? K_DOWN : -1);
+      if (k == 0 && !head) {
+        if (layer > 0) ly = next_ly;
+        // the next layer's table entry is asked for a layer ahead: nothing waits for it until then
+        next_ly = a.layers[layer + 1 < a.L ? layer + 1 : layer];
       }
-    };
-    auto open_with_norm = [&](int kind, const void* w) {
-      if (!ok || !has_units(a, kind, cta, nb)) return;
-      if (a.norm_w_is_f32) norm_to_operand<float>(a, sm, reinterpret_cast<const float*>(w), ct);
-      else norm_to_operand<bf16>(a, sm, reinterpret_cast<const bf16*>(w), ct);
-    };
-
-    for (int layer = 0; layer < a.L && ok; ++layer) {
-      const TsStepLayer& ly = a.layers[layer];
-      // q/k/v
-      open_with_norm(K_QKV, ly.ln1_w);
-      run_units(K_QKV, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
-        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_QKV, x, r, ct)) finish_qkv(a, ly, u.tile, S, r);
-      });
-      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
-      // attention
-      if (ok && cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct);
-      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
-      // output projection, residual add
-      run_units(K_O, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
-        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_O, x, r, ct)) finish_residual(a, u.tile, S, r);
-      });
-      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
-      // gate/up with SiLU * mul: rows 0..63 of a tile are gates, 64..127 their ups
-      open_with_norm(K_GU, ly.ln2_w);
-      run_units(K_GU, layer, [&](const Unit& u, int, const float (&x)[BN]) {
-        if (quad >= 2) {
+      if (kind == K_QKV || kind == K_GU || kind == K_HEAD) {
+        // Norm n of the step (0, 1: layer 0's two; ...; 2 L: the final one) finds its scale in shared
+        // memory slot n & 1, brought there with cp.async while the phases before it ran.
+        const int n = head ? 2 * a.L : 2 * layer + (kind == K_GU ? 1 : 0);
+        cp_async_wait_all();
+        compute_sync();                                // scale n is in its slot; everyone is done with slot (n + 1) & 1
+        if (has_units(a, kind, cta, nb)) {
+          long long* tr = a.trace == nullptr ? nullptr : a.trace + ((size_t)blockIdx.x * (5 * a.L + 1) + seq) * 8;
+          norm_to_operand(a, sm.work_(), sm.x_ready_(), sm.scale_(n & 1, scale_bytes), ct, tr);
+          mark(a, seq + 1, 2, ct);
+        }
+        if (n + 1 <= 2 * a.L) {                        // the next norm's scale sets out now
+          const int m = n + 1;
+          const void* w = m == 2 * a.L ? a.final_norm_w : (m & 1 ? ly.ln2_w : next_ly.ln1_w);
+          unsigned char* dst = sm.scale_(m & 1, scale_bytes);
+          for (int i = ct * 16; i < scale_bytes; i += CT * 16) cp_async_16(dst + i, reinterpret_cast<const unsigned char*>(w) + i, true);
+        }
+      }
+      if (kind < 0) {
+        if (cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct);
+      } else {
+        const TsStepShape& sh = a.shape[kind];
+        const int S = sh.S;
+#pragma unroll 1
+        for (int un = (cta + sh.rot) % nb; ok && un < sh.R * sh.S; un += nb) {
+          const Unit u{kind, layer, un / sh.S, un % sh.S, 0, 0};
+          float x[BN];
+          ok = compute_all(read_accumulator(sm, tmem_base, v, quad, x, ab));
+          ++v;
+          mark(a, seq + 1, 3, ct);
+          if (!ok) break;
+          if (kind == K_GU) {
+            // SiLU * mul: rows 0..63 of a tile are gates, 64..127 their ups
+            if (quad >= 2) {
 #pragma unroll
-          for (int c = 0; c < BN; ++c) sm.ex[(r - 64) * BN + c] = x[c];
-        }
-        compute_sync();
-        if (quad < 2) {
-          const int n = u.tile * 64 + r;
-          if (n < a.inter)
-            for (int c = 0; c < a.T; ++c) {
-              const float g = round_to<bf16>(x[c]);
-              const float up = round_to<bf16>(sm.ex[r * BN + c]);
-              const float sl = round_to<bf16>(silu_for<bf16>(g));
-              reinterpret_cast<bf16*>(a.act)[(size_t)c * a.inter + n] = __float2bfloat16_rn(sl * up);
+              for (int c = 0; c < BN; ++c) sm.ex_()[(r - 64) * BN + c] = x[c];
             }
+            compute_sync();
+            if (quad < 2) {
+              const int n = u.tile * 64 + r;
+              if (n < a.inter)
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                  if (c >= a.T) break;
+                  const float g = round_to<bf16>(x[c]);
+                  const float up = round_to<bf16>(sm.ex_()[r * BN + c]);
+                  const float sl = round_to<bf16>(silu_for<bf16>(g));
+                  reinterpret_cast<bf16*>(a.act)[(size_t)c * a.inter + n] = __float2bfloat16_rn(sl * up);
+                }
+            }
+            compute_sync();
+          } else if (kind == K_HEAD) {
+            const int n = u.tile * BM + r;
+            if (n < a.V)
+#pragma unroll
+              for (int c = 0; c < BN; ++c)
+                if (c < a.T) a.logits[(size_t)c * a.V + n] = x[c];
+          } else {
+            int* tickets = a.tickets + (kind == K_QKV ? TS_STEP_TICKETS_QKV : kind == K_O ? TS_STEP_TICKETS_O : TS_STEP_TICKETS_DOWN);
+            const bool last = leave_partial(a, sm, u, S, tickets, x, r, ct);
+            mark(a, seq + 1, 4, ct);
+            if (last) {
+              if (kind == K_QKV) finish_qkv(a, ly, sm, u.tile, S, r);
+              else finish_residual(a, u.tile, S, r);
+            }
+          }
+          mark(a, seq + 1, 5, ct);
         }
-        compute_sync();
-      });
-      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
-      // down projection, residual add
-      run_units(K_DOWN, layer, [&](const Unit& u, int S, const float (&x)[BN]) {
-        if (leave_partial(a, sm, u, S, a.tickets + TS_STEP_TICKETS_DOWN, x, r, ct)) finish_residual(a, u.tile, S, r);
-      });
-      ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
+      }
+      if (!head) ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
     }
-    // final norm and output head: 32-bit logits
-    open_with_norm(K_HEAD, a.final_norm_w);
-    run_units(K_HEAD, a.L, [&](const Unit& u, int, const float (&x)[BN]) {
-      const int n = u.tile * BM + r;
-      if (n < a.V)
-        for (int c = 0; c < a.T; ++c) a.logits[(size_t)c * a.V + n] = x[c];
-    });
   }
   tc_fence_before();
   __syncthreads();
@@ -978,8 +1117,9 @@ TS_API int ts_decode_step_sizes(int* args_bytes, int* layer_bytes, int* map_byte
 }
 
 // Shared memory the kernel needs for `stages` ring stages and a work area of `work_bytes`.
-static size_t step_smem(int stages, int work_bytes) {
-  return 1024 + (size_t)stages * STAGE_BYTES + (size_t)work_bytes + 64 * BN * 4 + (size_t)(2 * stages + 5) * 8 + 32 + PAGES_S * 4;
+static size_t step_smem(int stages, int work_bytes, int hidden) {
+  return 1024 + (size_t)stages * STAGE_BYTES + (size_t)work_bytes + 64 * BN * 4 + (size_t)(2 * stages + 5) * 8 + 32 +
+         (size_t)(2 * BN + TS_STEP_MAX_GROUPS * (BN + PAGES_S)) * 4 + 2 * (size_t)hidden * 4;
 }
 
 // The work area: the norm's output for `hidden` columns, or the attention's stages and merge space.
@@ -999,7 +1139,7 @@ TS_API int ts_decode_step_max_stages(int hidden) {
   if (cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
   const int work = ts_decode_step_work_bytes(hidden);
   int st = 0;
-  while (st < 16 && step_smem(st + 1, work) <= (size_t)limit) ++st;
+  while (st < 16 && step_smem(st + 1, work, hidden) <= (size_t)limit) ++st;
   return st >= 3 ? st : 0;
 }
 
@@ -1008,7 +1148,7 @@ TS_API int ts_decode_step_blocks(int stages, int hidden) {
   int dev = 0, sms = 0, per = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  const size_t smem = step_smem(stages, ts_decode_step_work_bytes(hidden));
+  const size_t smem = step_smem(stages, ts_decode_step_work_bytes(hidden), hidden);
   if (cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
     return 0;
@@ -1026,7 +1166,7 @@ TS_API int ts_decode_step_blocks(int stages, int hidden) {
 // (all blocks are then guaranteed to be resident together, which the grid barriers need); where it
 // does not (inside some stream captures), an ordinary launch of one block per SM is the same thing as
 // long as nothing else occupies the device, and the barriers are bounded either way.
-TS_API int ts_decode_step(const void* args_host, int blocks, void* stream) {
+TS_API int ts_decode_step(const void* args_host, int blocks, int cooperative, void* stream) {
   TsStepArgs a;
   memcpy(&a, args_host, sizeof(a));
   if (a.T < 1 || a.T > BN) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: %d tokens (1..%d)", a.T, BN);
@@ -1046,7 +1186,7 @@ TS_API int ts_decode_step(const void* args_host, int blocks, void* stream) {
   a.status = step_status_word();
   if (a.status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_decode_step: no status word");
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = step_smem(a.stages, a.work_bytes);
+  const size_t smem = step_smem(a.stages, a.work_bytes, a.hidden);
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1057,6 +1197,7 @@ TS_API int ts_decode_step(const void* args_host, int blocks, void* stream) {
   if (e != cudaSuccess) TS_REFUSE((int)e, "ts_decode_step: clearing the control words: %s", cudaGetErrorString(e));
   // 0: cooperative, 1: ordinary; remembered once one of them has worked
   static int mode = 0;
+  if (!cooperative && mode == 0) mode = 1;
   for (; mode < 2; ++mode) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);

@@ -51,6 +51,9 @@ typedef struct {
   const int* block_tables[TS_STEP_MAX_GROUPS];
   const int* slot_mapping[TS_STEP_MAX_GROUPS];
   int table_width[TS_STEP_MAX_GROUPS];
+  int group_window[TS_STEP_MAX_GROUPS];   // the window of the layers of each group (<= 0: none)
+  int num_groups;
+  int pad0;
   const void* embedding;      // bfloat16 [vocabulary, hidden]
   const void* final_norm_w;
   // work buffers (device)
@@ -64,4 +67,5 @@ typedef struct {
   int* ctrl;                  // [0] barrier counter, [1] abort flag: cleared by ts_decode_step
   int* tickets;               // [TS_STEP_TICKETS], zero
   int* status;                // set by ts_decode_step
+  long long* trace;           // null, or [blocks][barriers of the step][8] clock64: arrival at and exit from every grid barrier, marks within the phase before it
 } TsStepArgs;

@@ -65,6 +65,8 @@ class StepInputs:
     # kernel built for streaming, not the one built for the shortest chain.  Set from the real
     # lengths; a captured step keeps one graph for each value.
     streaming_decode: bool = False
+    # every row of the batch is wanted, in batch order (a captured decode step)
+    all_rows_sampled: bool = False
 
 
 # From about this many keys under the decode rows of a step (requests x longest context), reading them

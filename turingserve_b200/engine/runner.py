@@ -41,6 +41,9 @@ class ModelRunner:
         self.builder = StepInputBuilder(cache, max_tokens, max_requests, self.max_pages, model.device)
         self.views = cache.views()
         self.graph_batch_sizes = tuple(sorted(graph_batch_sizes))
+        # a step of a few single tokens as ONE kernel, where the model's parts are the ones it is written for
+        from turingserve_b200.parts.fused_decode import FusedDecodeStep
+        self.fused = FusedDecodeStep.try_build(model, self.views) if hasattr(model, "blocks") else None
         self._graphs: dict[tuple[int, bool], _DecodeGraph] = {}
 
     # -- the step ---------------------------------------------------------------------------------
@@ -71,6 +74,15 @@ class ModelRunner:
                                       self.model.cfg.vocab_size)
 
     def forward(self, step: StepInputs) -> torch.Tensor | None:
+        if self.fused is not None and getattr(kernels.ops(), "use_fused_step", False) and self.fused.takes(step):
+            logits = self.fused.run(step)
+            if step.all_rows_sampled:
+                return logits
+            if step.sample_rows.shape[0] == 0:
+                return None
+            wanted = torch.empty((step.sample_rows.shape[0], logits.shape[1]), dtype=logits.dtype, device=logits.device)
+            kernels.ops().gather_rows(wanted, logits, step.sample_rows)
+            return wanted
         hidden = self.model.forward(step, self.views, self.cache.states)
         if step.sample_rows.shape[0] == 0:
             return None
@@ -134,7 +146,7 @@ class _DecodeGraph:
                                arena=self.arena)
         # launch geometry must not depend on this step's lengths: size it for the longest context
         return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len,
-                                   streaming_decode=self.streaming)
+                                   streaming_decode=self.streaming, all_rows_sampled=True)
 
     def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
         step = self._build(entries)

@@ -57,7 +57,7 @@ class Deferred:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 4
+    ABI = 5
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -91,6 +91,8 @@ class CudaOps:
             "ts_penalize": [P, P, P, P, I, I, P],
             "ts_sample_greedy": [P, P, I, I, P, P, P, P],
             "ts_clear_status": [P],
+            "ts_decode_step": [P, I, I, P],
+            "ts_decode_step_encode_map": [P, P, I, I],
             "ts_poke_status": [I, I, P],
         }
         for name, args in sigs.items():
@@ -136,6 +138,10 @@ class CudaOps:
         self.use_tc_attention = os.environ.get("TURINGSERVE_B200_ATTENTION", "tc") == "tc"
         self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_prefill_supported.restype = c_int
+        for name, args in (("ts_decode_step_max_stages", [I]), ("ts_decode_step_blocks", [I, I]),
+                           ("ts_decode_step_work_bytes", [I]), ("ts_decode_step_status", [])):
+            getattr(self.lib, name).argtypes = args
+            getattr(self.lib, name).restype = c_int
         self.lib.ts_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self._device_index = torch.cuda.current_device()
@@ -146,6 +152,7 @@ class CudaOps:
         self._outgrown: list[torch.Tensor] = []
         self._decode_slots: dict = {}
         self.use_fast_attention = True
+        self.use_fused_step = True          # a whole decode step as one kernel where the model allows it
         self.use_library_gemm = True
         self.max_splits = 10        # (the fused reduce kernels load up to 16 partial sums in one go)
         self.launches = 0           # kernels of this library launched (graph replays add their share)
@@ -435,16 +442,16 @@ class CudaOps:
     def tc_status(self) -> int:
         """0 when no tensor-core block (GEMM or attention) ever gave up on a wait (synchronises the device)."""
         return (int(self.lib.ts_linear_tc_status()) or int(self.lib.ts_attention_prefill_tc_status())
-                or int(self.lib.ts_attention_decode_tma_status()))
+                or int(self.lib.ts_attention_decode_tma_status()) or int(self.lib.ts_decode_step_status()))
 
-    STATUS_WORDS = 4            # what ts_sample* report beside the tokens: GEMM, prompt attention, TMA decode attention, spare
+    STATUS_WORDS = 4            # what ts_sample* report beside the tokens: GEMM, prompt attention, TMA decode attention, fused decode step
 
     def fault_reported(self, status) -> str:
         """The engine found non-zero status words beside a step's tokens: a block of one of the
         kernels with bounded waits gave up, so the step's output cannot be trusted.  Takes the kernel
         concerned off the product path (its slower counterpart runs from the next step on), clears
         the words, and says what happened."""
-        names = ("tensor-core product", "tensor-core prompt attention", "TMA decode attention", "spare")
+        names = ("tensor-core product", "tensor-core prompt attention", "TMA decode attention", "fused decode step")
         hit = [f"{names[i]} (wait {int(v)})" for i, v in enumerate(status) if int(v)]
         if int(status[0]):
             self.gemm_mode = "library"
@@ -452,6 +459,8 @@ class CudaOps:
             self.use_tc_attention = False
         if int(status[2]):
             self.decode_kernel = "cp"
+        if int(status[3]):
+            self.use_fused_step = False
         self.lib.ts_clear_status(self._stream())
         return "a kernel gave up on a bounded wait: " + ", ".join(hit) + "; its fallback runs from now on"
 
