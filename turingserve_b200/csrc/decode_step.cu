@@ -59,6 +59,7 @@ constexpr int ATT_STAGES = 3;
 constexpr int D = 128;                     // head size this kernel is written for
 constexpr int PAGES_S = 256;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int EX_BYTES = 5120;               // the gated epilogue's exchange [64][16] floats; the attention's q rows and new key/value
 constexpr int FULL_COUNT = 33;             // arrivals a stage needs: the producer's expect_tx + 32 loader lanes
 
 enum Kind : int { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_HEAD = 4 };
@@ -168,6 +169,13 @@ __device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abor
   atomicExch(ab.step_abort, 1);
   return false;
 }
+// The same without the hardware's suspend between polls: for the hand-overs a phase's length hangs on
+// (norm -> products -> accumulator read-back), where the waiter's reaction time counts.
+__device__ __forceinline__ bool mwait_now(uint64_t* bar, uint32_t parity, const Abort& ab, int code) {
+  if (mbar_wait_spin(bar, parity, ab.status, code, ab.flag)) return true;
+  atomicExch(ab.step_abort, 1);
+  return false;
+}
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -201,7 +209,7 @@ struct Smem {
   // the norm's output (MMA operand, [k-blocks][16][64] swizzled) or the attention's stages
   __device__ __forceinline__ unsigned char* work_() const { return base + (size_t)nst * STAGE_BYTES; }
   __device__ __forceinline__ float* ex_() const { return reinterpret_cast<float*>(work_() + work_bytes); }   // [64][16] exchange of the gated epilogue
-  __device__ __forceinline__ uint64_t* full_() const { return reinterpret_cast<uint64_t*>(ex_() + 64 * BN); }  // [stages]
+  __device__ __forceinline__ uint64_t* full_() const { return reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ex_()) + EX_BYTES); }  // [stages]
   __device__ __forceinline__ uint64_t* empty_() const { return full_() + nst; }                    // [stages]
   __device__ __forceinline__ uint64_t* acc_full_() const { return empty_() + nst; }                // [2]
   __device__ __forceinline__ uint64_t* acc_empty_() const { return acc_full_() + 2; }              // [2]
@@ -221,7 +229,11 @@ struct Smem {
   __device__ __forceinline__ int* pages_() const { return slot_() + TS_STEP_MAX_GROUPS * BN; }
   // [2][hidden] scale of the norm in use and of the next one (brought in while the phases between them run)
   __device__ __forceinline__ unsigned char* scale_(int slot, int bytes) const {
-    return reinterpret_cast<unsigned char*>(pages_() + TS_STEP_MAX_GROUPS * PAGES_S) + (size_t)slot * bytes;
+    return reinterpret_cast<unsigned char*>(pages_() + TS_STEP_MAX_GROUPS * PAGES_S) + 2 * sizeof(TsStepLayer) + (size_t)slot * bytes;
+  }
+  // [2] the table entries of the layer in work and of the next one
+  __device__ __forceinline__ TsStepLayer* layer_(int slot) const {
+    return reinterpret_cast<TsStepLayer*>(pages_() + TS_STEP_MAX_GROUPS * PAGES_S) + slot;
   }
 };
 
@@ -248,7 +260,7 @@ __device__ __forceinline__ KeyRange key_range(const TsStepArgs& a, int unit, int
 
 // A time stamp for the timeline: slot k (2..7) of the interval that ends at barrier `seq`.
 __device__ __forceinline__ void mark(const TsStepArgs& a, int seq, int k, int ct) {
-  if (a.trace != nullptr && ct == 0) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8 + k] = clock64();
+  if (a.trace != nullptr && ct == 0) a.trace[((size_t)blockIdx.x * (5 * a.L + 2) + (seq - 1)) * 8 + k] = clock64();
 }
 
 // ---- the grid barrier ---------------------------------------------------------------------------
@@ -259,7 +271,7 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
   if (ct == 0) {
     bool ok = !ab.raised();
     if (ok) {
-      if (a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8] = clock64();
+      if (a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 2) + (seq - 1)) * 8] = clock64();
       __threadfence();
       atomicAdd(a.ctrl, 1);
       const int target = seq * nb;
@@ -279,7 +291,7 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
         }
       }
     }
-    if (ok && a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 1) + (seq - 1)) * 8 + 1] = clock64();
+    if (ok && a.trace != nullptr) a.trace[((size_t)blockIdx.x * (5 * a.L + 2) + (seq - 1)) * 8 + 1] = clock64();
     if (!ok) *ab.flag = 1;
     st_release_cta(sm.phase_open_(), ok ? seq : (1 << 30));          // a block that gives up lets its loader through
   }
@@ -291,82 +303,63 @@ __device__ __forceinline__ bool grid_barrier(const TsStepArgs& a, const Smem& sm
 // x[t, :] = w * bf16(r * rsqrt(mean(r^2) + eps)) for the step's tokens, r = resid[t, :] (32-bit
 // statistics, turingserve/ops/reference.py:13-23), written as the B operand of the products that
 // follow: k-block kb is a [16 tokens][64] tile of 128-byte rows with the 128-byte swizzle.
-// Half a warp per token (eight tokens a pass), 16 chunks of 8 values a lane kept in registers between
-// the two passes (rows up to 2,048 wide; wider rows are read twice).  The scale `ws` is in shared
-// memory, 32-bit or bfloat16.  One copy of this code in the kernel: the phases of a layer run seldom
-// enough that what they execute comes from the instruction cache only if it is small.
-__device__ void norm_to_operand(const TsStepArgs& a, unsigned char* work, uint64_t* x_ready, const unsigned char* ws, int ct,
-                                long long* tr) {
+// Half a warp per token (eight tokens a pass).  The residual stream is 32-bit (the products that feed
+// it add their parts into it with atomic adds); a row of up to 1,536 values stays in registers between
+// the two passes (12 chunks of 8 values a lane; the host sends wider models down the other path).  The
+// scale `ws` is in shared memory, 32-bit (the host converts the norms' scales once).  This code exists
+// once in the kernel and is kept short: the phases of a layer run so seldom that what they execute
+// comes from the instruction cache only if all of it fits there.
+__device__ void norm_to_operand(const TsStepArgs& a, unsigned char* work, uint64_t* x_ready, const float* ws, int ct, long long* tr) {
   const int half = ct >> 4, hl = ct & 15;
-  const int chunks = a.hidden / 8;                     // 16-byte chunks a row
-  constexpr int KEEP = 16;
-  const bool fits = chunks <= 16 * KEEP;
-  const bool f32 = a.norm_w_is_f32 != 0;
+  const int chunks = a.hidden / 8;                     // chunks of 8 values a row
+  constexpr int KEEP = TS_STEP_MAX_HIDDEN / 8 / 16;
 #pragma unroll 1
   for (int t0 = 0; t0 < a.T; t0 += 8) {
     const int t = t0 + half;
     const bool live = t < a.T;
-    const bf16* row = reinterpret_cast<const bf16*>(a.resid) + (size_t)t * a.hidden;
-    uint4 kept[KEEP];
+    const float* row = a.resid + (size_t)t * a.hidden;
+    float4 kept[KEEP][2];
 #pragma unroll
     for (int j = 0; j < KEEP; ++j) {
       const int c = hl + 16 * j;
-      kept[j] = (live && c < chunks) ? __ldcg(reinterpret_cast<const uint4*>(row + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+      const bool in = live && c < chunks;
+      kept[j][0] = in ? ldcg4(row + c * 8) : make_float4(0.f, 0.f, 0.f, 0.f);
+      kept[j][1] = in ? ldcg4(row + c * 8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (t0 == 0)                                       // rows of tokens that do not exist are zero (while the loads travel)
+#pragma unroll 1
       for (int tz = a.T + half; tz < BN; tz += 8)
+#pragma unroll 1
         for (int c = hl; c < chunks; c += 16)
           *reinterpret_cast<uint4*>(work + (c >> 3) * X_BYTES + tz * 128 + (((c & 7) ^ (tz & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < KEEP; ++j) {
-      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&kept[j]);
+    for (int j = 0; j < KEEP; ++j)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(e[k]);
-        ss += f.x * f.x + f.y * f.y;
-      }
-    }
-    if (!fits && live)
-      for (int c = hl + 16 * KEEP; c < chunks; c += 16) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row + c * 8));
-        const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 f = __bfloat1622float2(e[k]);
-          ss += f.x * f.x + f.y * f.y;
-        }
+      for (int q = 0; q < 2; ++q) {
+        const float4 f = kept[j][q];
+        ss += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
       }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // over the 16 lanes of the token
     const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
     if (tr != nullptr && ct == 0) tr[6] = clock64();
-    auto put = [&](int c, const uint4& v) {
-      const bf16* e = reinterpret_cast<const bf16*>(&v);
-      float wv[8];
-      if (f32) {
-        const float4 w0 = *reinterpret_cast<const float4*>(ws + (size_t)c * 32), w1 = *reinterpret_cast<const float4*>(ws + (size_t)c * 32 + 16);
-        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
-      } else {
-        const uint4 wq = *reinterpret_cast<const uint4*>(ws + (size_t)c * 16);
-        const bf16* we = reinterpret_cast<const bf16*>(&wq);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) wv[k] = to_f(we[k]);
-      }
-      uint4 o;
-      bf16* oe = reinterpret_cast<bf16*>(&o);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16_rn(wv[k] * round_to<bf16>(to_f(e[k]) * rstd));
-      *reinterpret_cast<uint4*>(work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = o;
-    };
     if (live) {
 #pragma unroll
       for (int j = 0; j < KEEP; ++j) {
         const int c = hl + 16 * j;
-        if (c < chunks) put(c, kept[j]);
+        if (c < chunks) {
+          const float4 w0 = *reinterpret_cast<const float4*>(ws + c * 8), w1 = *reinterpret_cast<const float4*>(ws + c * 8 + 4);
+          const float4 f0 = kept[j][0], f1 = kept[j][1];
+          uint4 o;
+          __nv_bfloat162* oe = reinterpret_cast<__nv_bfloat162*>(&o);
+          oe[0] = __floats2bfloat162_rn(w0.x * round_to<bf16>(f0.x * rstd), w0.y * round_to<bf16>(f0.y * rstd));
+          oe[1] = __floats2bfloat162_rn(w0.z * round_to<bf16>(f0.z * rstd), w0.w * round_to<bf16>(f0.w * rstd));
+          oe[2] = __floats2bfloat162_rn(w1.x * round_to<bf16>(f1.x * rstd), w1.y * round_to<bf16>(f1.y * rstd));
+          oe[3] = __floats2bfloat162_rn(w1.z * round_to<bf16>(f1.z * rstd), w1.w * round_to<bf16>(f1.w * rstd));
+          *reinterpret_cast<uint4*>(work + (c >> 3) * X_BYTES + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = o;
+        }
       }
-      if (!fits)
-        for (int c = hl + 16 * KEEP; c < chunks; c += 16) put(c, __ldcg(reinterpret_cast<const uint4*>(row + c * 8)));
     }
   }
   if (tr != nullptr && ct == 0) tr[7] = clock64();
@@ -379,7 +372,7 @@ __device__ void norm_to_operand(const TsStepArgs& a, unsigned char* work, uint64
 __device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_base, int v, int quad, float (&x)[BN],
                                                  const Abort& ab) {
   const int acc = v & 1;
-  bool ok = mwait(&sm.acc_full_()[acc], (uint32_t)(v >> 1) & 1u, ab, 31);
+  bool ok = mwait_now(&sm.acc_full_()[acc], (uint32_t)(v >> 1) & 1u, ab, 31);
   ok = __all_sync(0xffffffffu, ok);
   if (!ok) return false;
   tc_fence_after();
@@ -393,179 +386,156 @@ __device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_b
   return true;
 }
 
-// Leaves this unit's partial sums in scratch and takes a ticket for its tile; true for the block that
-// comes last (it then sees every part).  Slot of (tile, part): [tile * S + part][token][row].
-__device__ __forceinline__ bool leave_partial(const TsStepArgs& a, const Smem& sm, const Unit& u, int S, int* tickets,
-                                              const float (&x)[BN], int r, int ct) {
-  float* mine = a.part + ((size_t)(u.tile * S + u.part) * BN) * BM;
-#pragma unroll
-  for (int c = 0; c < BN; ++c)
-    if (c < a.T) mine[c * BM + r] = x[c];
-  compute_sync();                                      // every thread's stores precede thread 0's fence
-  if (ct == 0) {
-    __threadfence();
-    const int ticket = atomicAdd(&tickets[u.tile], 1);
-    const int last = ticket == S - 1;
-    if (last) {
-      tickets[u.tile] = 0;                             // ready for the next layer
-      __threadfence();                                 // the other parts' sums are visible from here on
-    }
-    *sm.flag_() = last;
-  }
-  compute_sync();
-  return *sm.flag_() != 0;
-}
-
-// Sums over the parts of a tile, in part order, for up to NT tokens at once (tokens tok0, tok0 + stride,
-// ...; NT * S independent loads in flight, one round trip to L2): out[i] = sum_sp part[tile, sp, tok_i, row].
-template <int NT>
-__device__ __forceinline__ void sum_parts(const TsStepArgs& a, int tile, int S, int tok0, int stride, int row, float (&out)[NT]) {
-  const float* base = a.part + ((size_t)tile * S * BN) * BM + row;
-#pragma unroll
-  for (int i = 0; i < NT; ++i) out[i] = 0.f;
-  for (int sp0 = 0; sp0 < S; sp0 += 8) {               // eight parts a round trip
-    float v[NT][8];
-#pragma unroll
-    for (int i = 0; i < NT; ++i)
-#pragma unroll
-      for (int sp = 0; sp < 8; ++sp)
-        v[i][sp] = (sp0 + sp < S && tok0 + i * stride < a.T) ? __ldcg(base + ((size_t)(sp0 + sp) * BN + tok0 + i * stride) * BM) : 0.f;
-#pragma unroll
-    for (int i = 0; i < NT; ++i)
-#pragma unroll
-      for (int sp = 0; sp < 8; ++sp) out[i] += v[i][sp];
-  }
-}
-
-// The last block of a q/k/v tile (= one head of 128): bias, rotation of q and k, q/k/v out, new keys
-// and values into the cache (what ts_rope_kv_write does to a finished product).  Everything it reads
-// from global memory is asked for at once: one round trip.
-__device__ void finish_qkv(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int tile, int S, int r) {
-  const int head = tile, p = r & 63, tg = r >> 6;
-  const int N = (a.H + 2 * a.KVH) * D;
-  const bf16* bias = reinterpret_cast<const bf16*>(ly.qkv_bias);
-  bf16* qkv = reinterpret_cast<bf16*>(a.qkv);
-  const bool rotate = head < a.H + a.KVH && ly.cos_t != nullptr;
-  for (int tok0 = tg; tok0 < a.T; tok0 += 8) {          // four tokens of this thread's parity a pass
-    float lo[4], hi[4], cs[4], sn[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int tok = tok0 + 2 * i;
-      cs[i] = 1.f;
-      sn[i] = 0.f;
-      if (rotate && tok < a.T) {
-        const int pos = sm.pos_()[tok];
-        cs[i] = ly.cos_t[(size_t)pos * 64 + p];
-        sn[i] = ly.sin_t[(size_t)pos * 64 + p];
-      }
-    }
-    const float b1 = bias != nullptr ? to_f(bias[head * D + p]) : 0.f;
-    const float b2 = bias != nullptr ? to_f(bias[head * D + p + 64]) : 0.f;
-    sum_parts<4>(a, tile, S, tok0, 2, p, lo);
-    sum_parts<4>(a, tile, S, tok0, 2, p + 64, hi);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int tok = tok0 + 2 * i;
-      if (tok >= a.T) continue;
-      const float x1 = round_to<bf16>(lo[i] + b1), x2 = round_to<bf16>(hi[i] + b2);
-      float o1 = x1, o2 = x2;
-      if (rotate) {
-        const float c1 = round_to<bf16>(cs[i]), s1 = round_to<bf16>(sn[i]);
-        o1 = x1 * c1 - x2 * s1;
-        o2 = x2 * c1 + x1 * s1;
-      }
-      const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
-      qkv[(size_t)tok * N + head * D + p] = w1;
-      qkv[(size_t)tok * N + head * D + p + 64] = w2;
-      if (head >= a.H) {
-        const int slot = sm.slot_()[ly.group * BN + tok];
-        if (slot >= 0) {
-          const bool is_k = head < a.H + a.KVH;
-          const int kvh = head - a.H - (is_k ? 0 : a.KVH);
-          bf16* dst = reinterpret_cast<bf16*>(is_k ? ly.k_cache : ly.v_cache) +
-                      (((size_t)(slot / a.page) * a.KVH + kvh) * a.page + (size_t)(slot % a.page)) * D;
-          dst[p] = w1;
-          dst[p + 64] = w2;
-        }
-      }
-    }
-  }
-}
-
-// The last block of an output- or down-projection tile: resid = bf16(bf16(product) + resid).
-__device__ void finish_residual(const TsStepArgs& a, int tile, int S, int r) {
-  const int n = tile * BM + r;
-  if (n >= a.hidden) return;
-  bf16* resid = reinterpret_cast<bf16*>(a.resid);
-  for (int tok0 = 0; tok0 < a.T; tok0 += 8) {
-    float sum[8];
-    unsigned short old[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      old[i] = tok0 + i < a.T ? __ldcg(reinterpret_cast<const unsigned short*>(resid + (size_t)(tok0 + i) * a.hidden + n)) : (unsigned short)0;
-    sum_parts<8>(a, tile, S, tok0, 1, r, sum);
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (tok0 + i < a.T)
-        resid[(size_t)(tok0 + i) * a.hidden + n] =
-            __float2bfloat16_rn(round_to<bf16>(sum[i]) + __bfloat162float(__ushort_as_bfloat16(old[i])));
-  }
-}
-
 // ---- decode attention for one (request, kv head, key split) -----------------------------------------
 // The four compute warps on disjoint 16-key slices of every 64-key tile (as ts_attention_decode).
-__device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct) {
-  constexpr int CH = D / 8, KS = D / 16, NT = D / 8;
+// What one attention unit (request b, kv head, key split) covers and where its tiles come from.
+struct AttentionGeometry {
+  int b, kvh, split, k_begin, k_end, n_tiles, page_first, skip_key;
+  bool staged;
+  const int* pages;
+  const int* table;
+};
+__device__ __forceinline__ AttentionGeometry attention_geometry(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit) {
+  AttentionGeometry g;
+  const KeyRange kr = key_range(a, unit, sm.seq_()[unit / (a.KVH * a.attn_splits)], ly.window);
+  g.b = kr.b; g.kvh = kr.kvh; g.split = kr.split; g.k_begin = kr.k_begin; g.k_end = kr.k_end;
+  g.n_tiles = kr.k_end > kr.k_begin ? (kr.k_end - kr.k_begin + ATT_TILE - 1) / ATT_TILE : 0;
+  g.page_first = kr.page_first;
+  g.staged = kr.n_pages <= PAGES_S;                    // then the pages were put in shared memory when the step began
+  g.pages = sm.pages_() + ly.group * PAGES_S;
+  g.table = a.block_tables[ly.group] + (size_t)kr.b * a.table_width[ly.group];
+  // the new token's row is made in this step (by the unit whose share ends there), not read
+  g.skip_key = (g.n_tiles > 0 && kr.k_end == sm.seq_()[kr.b]) ? kr.k_end - 1 : -1;
+  return g;
+}
+
+// Tile `tile` of the unit's keys and values into stage `stage` of the work area (cp.async, 16 bytes a copy).
+__device__ __noinline__ void attention_load_tile(const TsStepArgs& a, const TsStepLayer& ly, const AttentionGeometry& g,
+                                                    unsigned char* work, int tile, int stage, int ct) {
+  constexpr int CH = D / 8;
+  const int page = a.page, KVH = a.KVH;
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+  const int j0 = g.k_begin + tile * ATT_TILE;
+  unsigned char* ks_ = work + stage * ATT_TILE * D * 2;
+  unsigned char* vs_ = work + (ATT_STAGES + stage) * ATT_TILE * D * 2;
+#pragma unroll 2
+  for (int idx = ct; idx < ATT_TILE * CH; idx += CT) {
+    const int key = idx / CH, c = idx % CH;
+    const int j = j0 + key;
+    if (j == g.skip_key) continue;
+    const bool ok = j < g.k_end;
+    size_t off = 0;
+    if (ok) {
+      const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+      const int pg = g.staged ? g.pages[lp - g.page_first] : g.table[lp];
+      off = (((size_t)pg * KVH + g.kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
+    }
+    cp_async_16(ks_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.k_cache) + off, ok);
+    cp_async_16(vs_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.v_cache) + off, ok);
+  }
+}
+
+// The first tiles of the unit set out.  Called as soon as the work area is free (the q/k/v products of
+// this block have been read back), before the grid barrier that ends the q/k/v phase: keys and values
+// of earlier steps depend on nothing in this one.
+__device__ void attention_prefetch(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct) {
+  const AttentionGeometry g = attention_geometry(a, ly, sm, unit);
+#pragma unroll 1
+  for (int s = 0; s < ATT_STAGES - 1; ++s) {
+    if (s < g.n_tiles) attention_load_tile(a, ly, g, sm.work_(), s, s, ct);
+    cp_async_commit();
+  }
+}
+
+__device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct, int seq1) {
+  constexpr int KS = D / 16, NT = D / 8;
   const int NS = a.attn_splits;
   const int H = a.H, KVH = a.KVH, G = H / KVH, page = a.page;
   const int lane = ct & 31, warp = ct >> 5;
-  const KeyRange kr = key_range(a, unit, sm.seq_()[unit / (KVH * NS)], ly.window);
-  const int b = kr.b, kvh = kr.kvh, split = kr.split, k_begin = kr.k_begin, k_end = kr.k_end;
-  const int n_tiles = k_end > k_begin ? (k_end - k_begin + ATT_TILE - 1) / ATT_TILE : 0;
-  const int* table = a.block_tables[ly.group] + (size_t)b * a.table_width[ly.group];
+  const AttentionGeometry geo = attention_geometry(a, ly, sm, unit);
+  const int b = geo.b, kvh = geo.kvh, split = geo.split, k_begin = geo.k_begin, k_end = geo.k_end, n_tiles = geo.n_tiles;
   unsigned char* work = sm.work_();
   volatile int* flag = sm.flag_();
   unsigned char* k_s = work;
   unsigned char* v_s = work + ATT_STAGES * ATT_TILE * D * 2;
-  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
-  const int page_first = kr.page_first;
-  const bool staged = kr.n_pages <= PAGES_S;           // then the pages were put in shared memory when the step began
-  const int* pages = sm.pages_() + ly.group * PAGES_S;
-
-  auto load_tile = [&](int tile, int stage) {
-    const int j0 = k_begin + tile * ATT_TILE;
-    unsigned char* ks_ = k_s + stage * ATT_TILE * D * 2;
-    unsigned char* vs_ = v_s + stage * ATT_TILE * D * 2;
-    for (int idx = ct; idx < ATT_TILE * CH; idx += CT) {
-      const int key = idx / CH, c = idx % CH;
-      const int j = j0 + key;
-      const bool ok = j < k_end;
-      size_t off = 0;
-      if (ok) {
-        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
-        const int pg = staged ? pages[lp - page_first] : table[lp];
-        off = (((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
-      }
-      cp_async_16(ks_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.k_cache) + off, ok);
-      cp_async_16(vs_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.v_cache) + off, ok);
-    }
-  };
+  // (the first ATT_STAGES - 1 tiles were asked for by attention_prefetch)
+  // The q/k/v product left 32-bit sums (all its parts added up) in a.qkv: bias, rounding to bfloat16
+  // and rotation happen here, where they are used.  The group's G query heads go to shared memory as
+  // the A operand's rows; the block whose share ends at the new token also makes that token's key and
+  // value, writes them into the cache and into its place in the last tile.
+  const int N = (H + 2 * KVH) * D;
+  const int seq_len = sm.seq_()[b];
+  const bool has_new = n_tiles > 0 && k_end == seq_len;
+  const int new_tile = has_new ? (seq_len - 1 - k_begin) / ATT_TILE : -1;
+  const int new_key = has_new ? (seq_len - 1 - k_begin) % ATT_TILE : 0;
+  bf16* q_s = reinterpret_cast<bf16*>(sm.ex_());                       // [16][D]: rows >= G zero
+  bf16* kv_new = q_s + 16 * D;                                         // [2][D]
+  {
+    const float* acc = a.qkv + (size_t)b * N;
+    const bf16* bias = reinterpret_cast<const bf16*>(ly.qkv_bias);
+    const int pos = sm.pos_()[b];
+    const int items = (G + (has_new ? 2 : 0)) * 64;                   // pairs (p, p + 64) of the group's q heads, then k, then v
+    const bool rope = ly.cos_t != nullptr;
+#pragma unroll 1
+    for (int base = 0; base < items; base += 4 * CT) {                // four pairs a thread, all their loads in flight together
+      float x1[4], x2[4], cs[4], sn[4];
 #pragma unroll
-  for (int s = 0; s < ATT_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(s, s);
-    cp_async_commit();
+      for (int i = 0; i < 4; ++i) {
+        const int idx = base + i * CT + ct;
+        const bool live = idx < items;
+        const int hh = idx >> 6, p = idx & 63;
+        const int head = hh < G ? kvh * G + hh : (hh == G ? H + kvh : H + KVH + kvh);
+        x1[i] = live ? __ldcg(acc + head * D + p) : 0.f;
+        x2[i] = live ? __ldcg(acc + head * D + p + 64) : 0.f;
+        if (live && bias != nullptr) {
+          x1[i] += to_f(bias[head * D + p]);
+          x2[i] += to_f(bias[head * D + p + 64]);
+        }
+        const bool rot = live && rope && hh <= G;
+        cs[i] = rot ? ly.cos_t[(size_t)pos * 64 + p] : 1.f;
+        sn[i] = rot ? ly.sin_t[(size_t)pos * 64 + p] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = base + i * CT + ct;
+        if (idx >= items) continue;
+        const int hh = idx >> 6, p = idx & 63;
+        const float v1 = round_to<bf16>(x1[i]), v2 = round_to<bf16>(x2[i]);
+        float o1 = v1, o2 = v2;
+        if (rope && hh <= G) {
+          const float c1 = round_to<bf16>(cs[i]), s1 = round_to<bf16>(sn[i]);
+          o1 = v1 * c1 - v2 * s1;
+          o2 = v2 * c1 + v1 * s1;
+        }
+        bf16* dst = hh < G ? q_s + hh * D : kv_new + (hh - G) * D;
+        dst[p] = __float2bfloat16_rn(o1);
+        dst[p + 64] = __float2bfloat16_rn(o2);
+      }
+    }
+    for (int idx = ct; idx < (16 - G) * (D / 8); idx += CT)            // rows of heads that do not exist
+      reinterpret_cast<uint4*>(q_s + G * D)[idx] = make_uint4(0u, 0u, 0u, 0u);
   }
+  compute_sync();
+  if (has_new) {                                                        // the new key and value into the cache
+    const int slot = sm.slot_()[ly.group * BN + b];
+    if (slot >= 0 && ct < 2 * (D / 8)) {
+      const int which = ct / (D / 8), c = ct % (D / 8);
+      bf16* dst = reinterpret_cast<bf16*>(which == 0 ? ly.k_cache : ly.v_cache) +
+                  (((size_t)(slot / page) * KVH + kvh) * page + (size_t)(slot % page)) * D;
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(kv_new + which * D)[c];
+    }
+  }
+  mark(a, seq1, 2, ct);
   unsigned qf[KS][4];
   {
     const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
-    const bf16* qbase = reinterpret_cast<const bf16*>(a.qkv) + (size_t)b * (H + 2 * KVH) * D + (size_t)kvh * G * D;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
       const int k = ks * 16 + kc;
-      qf[ks][0] = r0 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r0 * D + k)) : 0u;
-      qf[ks][1] = r1 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r1 * D + k)) : 0u;
-      qf[ks][2] = r0 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r0 * D + k + 8)) : 0u;
-      qf[ks][3] = r1 < G ? __ldcg(reinterpret_cast<const unsigned*>(qbase + r1 * D + k + 8)) : 0u;
+      qf[ks][0] = *reinterpret_cast<const unsigned*>(q_s + r0 * D + k);
+      qf[ks][1] = *reinterpret_cast<const unsigned*>(q_s + r1 * D + k);
+      qf[ks][2] = *reinterpret_cast<const unsigned*>(q_s + r0 * D + k + 8);
+      qf[ks][3] = *reinterpret_cast<const unsigned*>(q_s + r1 * D + k + 8);
     }
   }
   float o[NT][4];
@@ -575,10 +545,18 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   const float sc = a.scale * LOG2E;
 
   for (int t = 0; t < n_tiles; ++t) {
-    if (t + ATT_STAGES - 1 < n_tiles) load_tile(t + ATT_STAGES - 1, (t + ATT_STAGES - 1) % ATT_STAGES);
+    if (t + ATT_STAGES - 1 < n_tiles) attention_load_tile(a, ly, geo, work, t + ATT_STAGES - 1, (t + ATT_STAGES - 1) % ATT_STAGES, ct);
     cp_async_commit();
     cp_async_wait<ATT_STAGES - 1>();
     compute_sync();
+    if (t == new_tile) {                               // the new token's key and value take their place in the tile
+      if (ct < 2 * (D / 8)) {
+        const int which = ct / (D / 8), c = ct % (D / 8);
+        unsigned char* dst = (which == 0 ? k_s : v_s) + (t % ATT_STAGES) * ATT_TILE * D * 2 + swz<D>(new_key, c);
+        *reinterpret_cast<uint4*>(dst) = reinterpret_cast<const uint4*>(kv_new + which * D)[c];
+      }
+      compute_sync();
+    }
     const unsigned char* ks_ = k_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
     const unsigned char* vs_ = v_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
     const int key0 = warp * 16;
@@ -654,6 +632,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   }
   cp_async_wait<0>();
   compute_sync();
+  mark(a, seq1, 3, ct);
 
   // merge the four warps' states (the stage buffers are free now)
   float* m_s = reinterpret_cast<float*>(work);
@@ -738,6 +717,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
     *flag = last;
   }
   compute_sync();
+  mark(a, seq1, 4, ct);
   if (*flag == 0) {
     compute_sync();
     return;
@@ -746,6 +726,8 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   float* w_s = reinterpret_cast<float*>(work);                  // [G][NS]
   float* m_all = w_s + G * NS;
   float* l_all = m_all + G * NS;
+  const int pieces = G * (D / 4);                                  // 16-byte pieces of the output
+#pragma unroll 1
   for (int idx = ct; idx < G * NS; idx += CT) {
     const int g = idx / NS, s2 = idx % NS;
     const size_t pi = ((size_t)b * H + kvh * G + g) * NS + s2;
@@ -754,11 +736,14 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
     l_all[idx] = ml.y;
   }
   compute_sync();
+#pragma unroll 1
   for (int idx = ct; idx < G * NS; idx += CT) {
     const int g = idx / NS;
     float M = -INFINITY, L = 0.f;
+#pragma unroll 1
     for (int s2 = 0; s2 < NS; ++s2) M = fmaxf(M, m_all[g * NS + s2]);
     if (M > -INFINITY)
+#pragma unroll 1
       for (int s2 = 0; s2 < NS; ++s2) {
         const float ms = m_all[g * NS + s2];
         if (ms != -INFINITY) L += l_all[g * NS + s2] * exp2f(ms - M);
@@ -767,17 +752,21 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
     w_s[idx] = (L > 0.f && mi != -INFINITY) ? exp2f(mi - M) / L : 0.f;
   }
   compute_sync();
-  for (int idx = ct; idx < G * (D / 4); idx += CT) {
+#pragma unroll 1
+  for (int idx = ct; idx < pieces; idx += CT) {
     const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
     const int h = kvh * G + g;
     const float* src = part_acc + (((size_t)b * H + h) * NS) * D + d;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int s2 = 0; s2 < NS; ++s2) {
-      const float w = w_s[g * NS + s2];
-      if (w != 0.f) {                                               // a split without keys left nothing to read
-        const float4 v = ldcg4(src + (size_t)s2 * D);
-        acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+#pragma unroll 1
+    for (int s0 = 0; s0 < NS; s0 += 16) {                           // sixteen splits' pieces in flight together
+      float4 v[16];
+#pragma unroll
+      for (int s2 = 0; s2 < 16; ++s2) v[s2] = s0 + s2 < NS ? ldcg4(src + (size_t)(s0 + s2) * D) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s2 = 0; s2 < 16; ++s2) {
+        const float w = s0 + s2 < NS ? w_s[g * NS + s0 + s2] : 0.f;
+        acc.x += v[s2].x * w; acc.y += v[s2].y * w; acc.z += v[s2].z * w; acc.w += v[s2].w * w;
       }
     }
     bf16* op = reinterpret_cast<bf16*>(a.attn) + (size_t)b * H * D + (size_t)h * D + d;
@@ -785,6 +774,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
     *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z, acc.w);
   }
   compute_sync();
+  mark(a, seq1, 5, ct);
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------
@@ -858,7 +848,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
             }
           }
           const int s = q % NST;
-          if (q >= NST) ok = mwait(&sm.empty_()[s], (uint32_t)((q / NST) - 1) & 1u, ab, 11);
+          if (q >= NST) ok = mwait_now(&sm.empty_()[s], (uint32_t)((q / NST) - 1) & 1u, ab, 11);
           if (!ok) break;
           mbar_expect_tx(&sm.full_()[s], W_BYTES);
           tma_load_2d(sm.ring_() + (size_t)s * STAGE_BYTES, map, kb * BK, u.tile * BM, &sm.full_()[s]);
@@ -885,26 +875,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
         const bool from_norm = u.kind == K_QKV || u.kind == K_GU || u.kind == K_HEAD;
         const int phase = u.layer * 4 + u.kind;
         if (from_norm && phase != cur_phase) {          // this phase's norm output must be in place
-          ok = mwait(sm.x_ready_(), (uint32_t)xr & 1u, ab, 21);
+          ok = mwait_now(sm.x_ready_(), (uint32_t)xr & 1u, ab, 21);
           ++xr;
           if (!ok) break;
         }
         cur_phase = phase;
         const int acc = v & 1;
-        if (v >= 2) ok = mwait(&sm.acc_empty_()[acc], (uint32_t)((v >> 1) - 1) & 1u, ab, 22);
+        if (v >= 2) ok = mwait_now(&sm.acc_empty_()[acc], (uint32_t)((v >> 1) - 1) & 1u, ab, 22);
         if (!ok) break;
         tc_fence_after();
         for (int kb = u.kb0; kb < u.kb1; ++kb, ++q) {
           const int s = q % NST;
-          ok = mwait(&sm.full_()[s], (uint32_t)(q / NST) & 1u, ab, 23);
+          ok = mwait_now(&sm.full_()[s], (uint32_t)(q / NST) & 1u, ab, 23);
           if (!ok) break;
           tc_fence_after();
-          fence_async_smem();                           // activations arrived by cp.async, an ordinary-proxy write
+          if (!from_norm) fence_async_smem();           // activations arrived by cp.async, an ordinary-proxy write
           const uint64_t da = smem_desc(smem_u32(sm.ring_() + (size_t)s * STAGE_BYTES));
           const uint64_t db = smem_desc(smem_u32(from_norm ? sm.work_() + (size_t)kb * X_BYTES
                                                             : sm.ring_() + (size_t)s * STAGE_BYTES + W_BYTES));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
+            if (k == 0 || !(a.lookahead & 1024))
             umma(tmem_base + (uint32_t)(acc * BN), da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16),
                  idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
           umma_commit(&sm.empty_()[s]);
@@ -919,9 +910,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     Walker w;
     w.start();
     Unit u;
-    int q = 0;
+    int q = 0, l2_layer = -1;
     bool ok = true;
     while (ok && w.next(a, cta, nb, u)) {
+      if (a.l2_ahead && u.layer != l2_layer && u.layer < a.L) {
+        // A layer begins (barrier 5 l + 1 is passed): its q/k/v, attention and output phases move little
+        // memory, so this block's gate/up and down weights set out for L2 now and are read from there
+        // when their turn comes.
+        l2_layer = u.layer;
+        ok = warp_wait_shared_ge(sm.phase_open_(), 5 * u.layer + 1, ab, 53, lane) && !ab.raised();
+        if (!ok) break;
+        for (int kind = K_GU; kind <= K_DOWN; ++kind) {
+          const TsStepShape& sh = a.shape[kind];
+          const CUtensorMap* map = map_of(a, kind, u.layer);
+          for (int un = (cta + sh.rot) % nb; un < sh.R * sh.S; un += nb) {
+            const int tile = un / sh.S, kb0 = (un % sh.S) * sh.per, kb1 = min(sh.KB, kb0 + sh.per);
+            for (int kb = kb0 + lane; kb < kb1; kb += 32)
+              asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(kb * BK), "r"(tile * BM) : "memory");
+          }
+        }
+      }
       const bool stream = u.kind == K_O || u.kind == K_DOWN;
       if (!stream) {                                   // the producer arrives for this warp's lanes
         q += u.kb1 - u.kb0;
@@ -953,8 +961,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     const int r = quad * 32 + lane;
     int v = 0, seq = 0;
     bool ok = true;
+    if (ct < (int)sizeof(TsStepLayer) / 16)            // the first layer's table entry
+      cp_async_16(reinterpret_cast<unsigned char*>(sm.layer_(0)) + 16 * ct, reinterpret_cast<const unsigned char*>(a.layers) + 16 * ct, true);
     {                                                  // the first norm's scale: a weight, it need not wait for anything
-      const int sb = a.hidden * (a.norm_w_is_f32 ? 4 : 2);
+      const int sb = a.hidden * 4;
       unsigned char* dst = sm.scale_(0, sb);
       for (int i = ct * 16; i < sb; i += CT * 16) cp_async_16(dst + i, reinterpret_cast<const unsigned char*>(a.layers[0].ln1_w) + i, true);
     }
@@ -976,30 +986,34 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
           for (int i = ct; i < kr.n_pages; i += CT) sm.pages_()[g * PAGES_S + i] = table[kr.page_first + i];
         }
       }
-    // embedding rows into the residual stream (the first norm adds nothing to them)
+    // embedding rows into the residual stream (32-bit from here on); the q/k/v accumulator starts at zero
     if (cta < a.T) {
       const int id = a.ids[cta];
-      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.embedding) + (size_t)id * a.hidden);
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(a.resid) + (size_t)cta * a.hidden);
-      for (int i = ct; i < a.hidden / 8; i += CT) dst[i] = src[i];
+      const bf16* src = reinterpret_cast<const bf16*>(a.embedding) + (size_t)id * a.hidden;
+      float* dst = a.resid + (size_t)cta * a.hidden;
+      for (int i = ct; i < a.hidden; i += CT) dst[i] = to_f(src[i]);
+    }
+    {
+      const int total = a.T * (a.H + 2 * a.KVH) * D;
+      for (int i = cta * CT + ct; i < total; i += nb * CT) a.qkv[i] = 0.f;
     }
     ok = grid_barrier(a, sm, ++seq, nb, ct, ab);
 
     // The phases of the step, one loop so that every piece of code exists once: phase p of layer p / 5
     // is 0 q/k/v, 1 attention, 2 output projection, 3 gate/up, 4 down; after the last layer, the head.
-    const int scale_bytes = a.hidden * (a.norm_w_is_f32 ? 4 : 2);
+    const int scale_bytes = a.hidden * 4;
     const int n_phases = 5 * a.L + 1;
-    TsStepLayer ly = a.layers[0], next_ly = ly;
 #pragma unroll 1
     for (int p = 0; p < n_phases && ok; ++p) {
       const int layer = p / 5, k = p % 5;
       const bool head = p == 5 * a.L;
       const int kind = head ? K_HEAD : (k == 0 ? K_QKV : k == 2 ? K_O : k == 3 ? K_GU : k == 4 ? K_DOWN : -1);
-      if (k == 0 && !head) {
-        if (layer > 0) ly = next_ly;
-        // the next layer's table entry is asked for a layer ahead: nothing waits for it until then
-        next_ly = a.layers[layer + 1 < a.L ? layer + 1 : layer];
-      }
+      // the table entries of this layer and of the next one sit in shared memory (slots layer & 1)
+      const TsStepLayer& ly = *sm.layer_(layer & 1);
+      const TsStepLayer& next_ly = *sm.layer_((layer + 1) & 1);
+      if (k == 0 && layer + 1 < a.L && ct < (int)sizeof(TsStepLayer) / 16)      // the next entry sets out (the slot's old one, layer - 1, is done)
+        cp_async_16(reinterpret_cast<unsigned char*>(sm.layer_((layer + 1) & 1)) + 16 * ct,
+                    reinterpret_cast<const unsigned char*>(a.layers + layer + 1) + 16 * ct, true);
       if (kind == K_QKV || kind == K_GU || kind == K_HEAD) {
         // Norm n of the step (0, 1: layer 0's two; ...; 2 L: the final one) finds its scale in shared
         // memory slot n & 1, brought there with cp.async while the phases before it ran.
@@ -1007,8 +1021,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
         cp_async_wait_all();
         compute_sync();                                // scale n is in its slot; everyone is done with slot (n + 1) & 1
         if (has_units(a, kind, cta, nb)) {
-          long long* tr = a.trace == nullptr ? nullptr : a.trace + ((size_t)blockIdx.x * (5 * a.L + 1) + seq) * 8;
-          norm_to_operand(a, sm.work_(), sm.x_ready_(), sm.scale_(n & 1, scale_bytes), ct, tr);
+          long long* tr = a.trace == nullptr ? nullptr : a.trace + ((size_t)blockIdx.x * (5 * a.L + 2) + seq) * 8;
+          norm_to_operand(a, sm.work_(), sm.x_ready_(), reinterpret_cast<const float*>(sm.scale_(n & 1, scale_bytes)), ct, tr);
           mark(a, seq + 1, 2, ct);
         }
         if (n + 1 <= 2 * a.L) {                        // the next norm's scale sets out now
@@ -1018,12 +1032,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
           for (int i = ct * 16; i < scale_bytes; i += CT * 16) cp_async_16(dst + i, reinterpret_cast<const unsigned char*>(w) + i, true);
         }
       }
+      if (kind == K_O) {
+        // the q/k/v accumulator has been read (attention is over): zero again for the next layer
+        const int total = a.T * (a.H + 2 * a.KVH) * D;
+        for (int i = cta * CT + ct; i < total; i += nb * CT) a.qkv[i] = 0.f;
+      }
       if (kind < 0) {
-        if (cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct);
+        if (cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct, seq + 1);
       } else {
         const TsStepShape& sh = a.shape[kind];
-        const int S = sh.S;
-#pragma unroll 1
+        #pragma unroll 1
         for (int un = (cta + sh.rot) % nb; ok && un < sh.R * sh.S; un += nb) {
           const Unit u{kind, layer, un / sh.S, un % sh.S, 0, 0};
           float x[BN];
@@ -1058,17 +1076,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
               for (int c = 0; c < BN; ++c)
                 if (c < a.T) a.logits[(size_t)c * a.V + n] = x[c];
           } else {
-            int* tickets = a.tickets + (kind == K_QKV ? TS_STEP_TICKETS_QKV : kind == K_O ? TS_STEP_TICKETS_O : TS_STEP_TICKETS_DOWN);
-            const bool last = leave_partial(a, sm, u, S, tickets, x, r, ct);
-            mark(a, seq + 1, 4, ct);
-            if (last) {
-              if (kind == K_QKV) finish_qkv(a, ly, sm, u.tile, S, r);
-              else finish_residual(a, u.tile, S, r);
-            }
+            // A part of a product that is split over K: its sums are added into the 32-bit q/k/v
+            // accumulator or straight into the residual stream (red.global.add: nobody waits for the
+            // result, no ticket, no second pass; the order of the additions is not fixed).
+            const int n = u.tile * BM + r;
+            float* dst = kind == K_QKV ? a.qkv + n : a.resid + n;
+            const int width = kind == K_QKV ? (a.H + 2 * a.KVH) * D : a.hidden;
+            if (n < width)
+#pragma unroll
+              for (int c = 0; c < BN; ++c)
+                if (c < a.T) atomicAdd(dst + (size_t)c * width, x[c]);
           }
           mark(a, seq + 1, 5, ct);
         }
       }
+      if (kind == K_QKV && ok && cta < a.T * a.KVH * a.attn_splits) attention_prefetch(a, ly, sm, cta, ct);
       if (!head) ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
     }
   }
@@ -1118,8 +1140,8 @@ TS_API int ts_decode_step_sizes(int* args_bytes, int* layer_bytes, int* map_byte
 
 // Shared memory the kernel needs for `stages` ring stages and a work area of `work_bytes`.
 static size_t step_smem(int stages, int work_bytes, int hidden) {
-  return 1024 + (size_t)stages * STAGE_BYTES + (size_t)work_bytes + 64 * BN * 4 + (size_t)(2 * stages + 5) * 8 + 32 +
-         (size_t)(2 * BN + TS_STEP_MAX_GROUPS * (BN + PAGES_S)) * 4 + 2 * (size_t)hidden * 4;
+  return 1024 + (size_t)stages * STAGE_BYTES + (size_t)work_bytes + EX_BYTES + (size_t)(2 * stages + 5) * 8 + 32 +
+         (size_t)(2 * BN + TS_STEP_MAX_GROUPS * (BN + PAGES_S)) * 4 + 2 * sizeof(TsStepLayer) + 2 * (size_t)hidden * 4;
 }
 
 // The work area: the norm's output for `hidden` columns, or the attention's stages and merge space.
@@ -1170,6 +1192,8 @@ TS_API int ts_decode_step(const void* args_host, int blocks, int cooperative, vo
   TsStepArgs a;
   memcpy(&a, args_host, sizeof(a));
   if (a.T < 1 || a.T > BN) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: %d tokens (1..%d)", a.T, BN);
+  if (a.hidden > TS_STEP_MAX_HIDDEN || !a.norm_w_is_f32)
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: hidden %d (at most %d), norm scales must be 32-bit", a.hidden, TS_STEP_MAX_HIDDEN);
   if (a.hidden % BK || a.inter % BK || a.H % a.KVH || a.H / a.KVH > 16 || a.L < 1)
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: hidden %d, inner %d, heads %d/%d are not taken by this kernel", a.hidden, a.inter, a.H, a.KVH);
   if (a.stages < 3 || a.work_bytes < ts_decode_step_work_bytes(a.hidden)) TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: stages %d, work area %d", a.stages, a.work_bytes);

@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #define TS_STEP_MAX_TOKENS 16        // requests (one token each) a step may hold
+#define TS_STEP_MAX_HIDDEN 1536     // widest residual stream the in-kernel norm keeps in registers
 #define TS_STEP_MAX_GROUPS 4         // cache groups (block table + slot mapping each)
 #define TS_STEP_MAX_UNITS 1024       // (tile, part) units of a product that is split over K: slots of partial sums
 #define TS_STEP_TICKETS_EACH 512     // ticket counters per kind
@@ -26,8 +27,8 @@ typedef struct {
 
 // One layer.  Device pointers.
 typedef struct {
-  const void* ln1_w;          // norm before the mixer [hidden]
-  const void* ln2_w;          // norm before the feed-forward [hidden]
+  const void* ln1_w;          // norm before the mixer [hidden], 32-bit
+  const void* ln2_w;          // norm before the feed-forward [hidden], 32-bit
   const void* qkv_bias;       // bfloat16 [(H + 2 KVH) * 128] or null
   void* k_cache;              // [pages, KVH, page, 128] bfloat16
   void* v_cache;
@@ -53,19 +54,18 @@ typedef struct {
   int table_width[TS_STEP_MAX_GROUPS];
   int group_window[TS_STEP_MAX_GROUPS];   // the window of the layers of each group (<= 0: none)
   int num_groups;
-  int pad0;
+  int l2_ahead;               // != 0: a layer's gate/up and down weights are asked into L2 when the layer begins
   const void* embedding;      // bfloat16 [vocabulary, hidden]
   const void* final_norm_w;
   // work buffers (device)
-  void* resid;                // bfloat16 [16, hidden]: the residual stream
-  void* qkv;                  // bfloat16 [16, (H + 2 KVH) * 128]
+  float* resid;               // [16, hidden]: the residual stream, 32-bit (products add their parts into it)
+  float* qkv;                 // [16, (H + 2 KVH) * 128]: sums of the q/k/v product's parts, before bias and rotation
   void* attn;                 // bfloat16 [16, H * 128]
   void* act;                  // bfloat16 [16, inter]
   float* logits;              // [T, V]
-  float* part;                // [TS_STEP_MAX_UNITS][16][128] partial sums
   float* attn_part;           // [T * H * attn_splits * (128 + 2)]
   int* ctrl;                  // [0] barrier counter, [1] abort flag: cleared by ts_decode_step
-  int* tickets;               // [TS_STEP_TICKETS], zero
+  int* tickets;               // [TS_STEP_TICKETS], zero (the attention's key splits take tickets)
   int* status;                // set by ts_decode_step
-  long long* trace;           // null, or [blocks][barriers of the step][8] clock64: arrival at and exit from every grid barrier, marks within the phase before it
+  long long* trace;           // null, or [blocks][5 L + 2][8] clock64: arrival at and exit from every grid barrier, marks within the phase before it
 } TsStepArgs;

@@ -22,6 +22,7 @@ import torch
 from turingserve_b200 import kernels
 
 MAX_TOKENS = 16
+MAX_HIDDEN = 1536          # the in-kernel norm keeps a row of this many values in registers
 MAX_GROUPS = 4
 MAX_UNITS = 1024
 MAX_PARTS = int(os.environ.get("TURINGSERVE_B200_STEP_PARTS", "16"))        # parts a product's K is cut into, at most
@@ -51,10 +52,10 @@ class StepArgs(ctypes.Structure):
                 ("ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("seq_lens", ctypes.c_void_p),
                 ("block_tables", ctypes.c_void_p * MAX_GROUPS), ("slot_mapping", ctypes.c_void_p * MAX_GROUPS),
                 ("table_width", ctypes.c_int * MAX_GROUPS), ("group_window", ctypes.c_int * MAX_GROUPS),
-                ("num_groups", ctypes.c_int), ("pad0", ctypes.c_int),
+                ("num_groups", ctypes.c_int), ("l2_ahead", ctypes.c_int),
                 ("embedding", ctypes.c_void_p), ("final_norm_w", ctypes.c_void_p),
                 ("resid", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p),
-                ("act", ctypes.c_void_p), ("logits", ctypes.c_void_p), ("part", ctypes.c_void_p),
+                ("act", ctypes.c_void_p), ("logits", ctypes.c_void_p),
                 ("attn_part", ctypes.c_void_p), ("ctrl", ctypes.c_void_p), ("tickets", ctypes.c_void_p),
                 ("status", ctypes.c_void_p), ("trace", ctypes.c_void_p)]
 
@@ -77,7 +78,7 @@ class FusedDecodeStep:
     def __init__(self, model, views, lib, blocks: int, stages: int, work_bytes: int) -> None:
         self.model, self.lib, self.blocks, self.stages, self.work_bytes = model, lib, blocks, stages, work_bytes
         self.runs = 0                                                # steps this kernel has run (graph replays not counted)
-        self.trace: torch.Tensor | None = None                       # set to an int64 [blocks, 5 L + 1, 8] tensor to record barrier times
+        self.trace: torch.Tensor | None = None                       # set to an int64 [blocks, 5 L + 2, 8] tensor to record barrier times
         cfg = model.cfg
         dev = model.device
         att0 = model.blocks[0].mixer
@@ -88,8 +89,18 @@ class FusedDecodeStep:
         self.eps = model.final_norm.eps
         self.scale = att0.scale
         self.lookahead = int(os.environ.get("TURINGSERVE_B200_STEP_LOOKAHEAD", "0"))
+        self.l2_ahead = int(os.environ.get("TURINGSERVE_B200_STEP_L2_AHEAD", "1"))
         self.cooperative = os.environ.get("TURINGSERVE_B200_STEP_COOPERATIVE", "1") != "0"
-        self.norm_w_is_f32 = int(model.final_norm.weight.dtype == torch.float32)
+        self.norm_w_is_f32 = 1
+        # the kernel reads the norms' scales as 32-bit: converted once (the conversion is exact)
+        self._scales = {}
+
+        def scale32(norm) -> torch.Tensor:
+            t = self._scales.get(id(norm))
+            if t is None:
+                t = self._scales[id(norm)] = norm.weight.float().contiguous()
+            return t
+        self._scale32 = scale32
 
         # tensor maps: per layer q/k/v, output, gate/up, down; then the head
         mats = []
@@ -110,7 +121,7 @@ class FusedDecodeStep:
             b = model.blocks[cfg.schedule[r].layer]
             att, view = b.mixer, views[r]
             ly = layers[r]
-            ly.ln1_w, ly.ln2_w = b.mixer_norm.weight.data_ptr(), b.ffn_norm.weight.data_ptr()
+            ly.ln1_w, ly.ln2_w = self._scale32(b.mixer_norm).data_ptr(), self._scale32(b.ffn_norm).data_ptr()
             ly.qkv_bias = None if att.b_qkv is None else att.b_qkv.data_ptr()
             ly.k_cache, ly.v_cache = view.k.data_ptr(), view.v.data_ptr()
             ly.cos_t = None if att.position is None else att.position.cos.data_ptr()
@@ -123,11 +134,10 @@ class FusedDecodeStep:
 
         bf = torch.bfloat16
         n_qkv = (self.H + 2 * self.KVH) * HEAD_DIM
-        self.resid = torch.zeros((MAX_TOKENS, self.hidden), dtype=bf, device=dev)
-        self.qkv = torch.zeros((MAX_TOKENS, n_qkv), dtype=bf, device=dev)
+        self.resid = torch.zeros((MAX_TOKENS, self.hidden), dtype=torch.float32, device=dev)
+        self.qkv = torch.zeros((MAX_TOKENS, n_qkv), dtype=torch.float32, device=dev)
         self.attn = torch.zeros((MAX_TOKENS, self.H * HEAD_DIM), dtype=bf, device=dev)
         self.act = torch.zeros((MAX_TOKENS, self.inter), dtype=bf, device=dev)
-        self.part = torch.empty(MAX_UNITS * MAX_TOKENS * 128, dtype=torch.float32, device=dev)
         self.attn_part = torch.empty((self.H // self.KVH) * blocks * (HEAD_DIM + 2) + 64, dtype=torch.float32, device=dev)
         self.ctrl = torch.zeros(16, dtype=torch.int32, device=dev)
         self.tickets = torch.zeros(TICKETS, dtype=torch.int32, device=dev)
@@ -184,7 +194,7 @@ class FusedDecodeStep:
             if v is None or v.k is None or not v.writable or v.k.dtype != torch.bfloat16 or v.group >= MAX_GROUPS:
                 return None
             pages.add(v.page_size)
-        if len(pages) != 1 or cfg.hidden_size % 64 or first.feed_forward.inter % 64:
+        if len(pages) != 1 or cfg.hidden_size % 64 or first.feed_forward.inter % 64 or cfg.hidden_size > MAX_HIDDEN:
             return None
         stages = int(lib.ts_decode_step_max_stages(cfg.hidden_size))
         if stages < 3:
@@ -228,10 +238,11 @@ class FusedDecodeStep:
             a.table_width[g] = grp.block_tables.shape[1]
             a.group_window[g] = self.group_window.get(g, 0)
         a.num_groups = len(step.groups)
-        a.embedding, a.final_norm_w = self.model.embedding.data_ptr(), self.model.final_norm.weight.data_ptr()
+        a.l2_ahead = self.l2_ahead
+        a.embedding, a.final_norm_w = self.model.embedding.data_ptr(), self._scale32(self.model.final_norm).data_ptr()
         logits = torch.empty((T, self.V), dtype=torch.float32, device=dev)
         a.resid, a.qkv, a.attn, a.act = (t.data_ptr() for t in (self.resid, self.qkv, self.attn, self.act))
-        a.logits, a.part, a.attn_part = logits.data_ptr(), self.part.data_ptr(), self.attn_part.data_ptr()
+        a.logits, a.attn_part = logits.data_ptr(), self.attn_part.data_ptr()
         a.ctrl, a.tickets = self.ctrl.data_ptr(), self.tickets.data_ptr()
         a.trace = None if self.trace is None else self.trace.data_ptr()
         ops = kernels.ops()
