@@ -506,8 +506,8 @@ def run_mixed(a, pk: dict) -> dict:
     runner, cache = eng.runner, eng.cache
     rcs = [cache.admit(f"d{i}") for i in range(nd)]
     for rc in rcs:
-        for at in range(0, plen, 1024):
-            runner.step([StepEntry(rc, rng.integers(0, V, size=1024).tolist(), [])])
+        for at in range(0, plen, chunk):
+            runner.step([StepEntry(rc, rng.integers(0, V, size=chunk).tolist(), [])])
 
     def prompt_round(tag: str) -> float:
         rc = cache.admit(tag)
@@ -530,7 +530,8 @@ def run_mixed(a, pk: dict) -> dict:
     for rc in rcs:
         cache.release(rc)
     # the same through the engine: 32 running requests, prompts arriving one after the other
-    params = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    # (while the later prompts arrive in portions the earlier requests already decode: a budget that lasts)
+    params = SamplingParams(temperature=0.0, max_tokens=1024, ignore_eos=True)
     for i in range(nd):
         eng.add_request(f"e{i}", rng.integers(0, V, size=plen).tolist(), params)
     while any(r.num_uncomputed > 1 for r in eng.requests.values()) or len(eng.scheduler.waiting):
@@ -546,6 +547,8 @@ def run_mixed(a, pk: dict) -> dict:
         n_tok += sum(len(o.delta_token_ids) for o in eng.step())
     torch.cuda.synchronize()
     wall_ms = 1e3 * (time.perf_counter() - t0) / 4
+    if n_tok < 4 * nd:
+        raise RuntimeError(f"the mixed run through the engine produced {n_tok} tokens in 4 steps of {nd} decoding requests")
     for rid in list(eng.requests):
         eng.abort(rid)
     eng.step()

@@ -55,14 +55,13 @@ constexpr int CW0 = 3;                     // first compute warp
 constexpr int CT = 128;                    // compute threads
 constexpr int UMMA_K = 16;
 constexpr int ATT_TILE = 64;
-constexpr int ATT_STAGES = 3;
 constexpr int D = 128;                     // head size this kernel is written for
 constexpr int PAGES_S = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int EX_BYTES = 5120;               // the gated epilogue's exchange [64][16] floats; the attention's q rows and new key/value
 constexpr int FULL_COUNT = 33;             // arrivals a stage needs: the producer's expect_tx + 32 loader lanes
 
-enum Kind : int { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_HEAD = 4 };
+enum Kind : int { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_HEAD = 4, K_ATTN = 5 };   // 0..4 index TsStepArgs::shape
 
 struct Unit {
   int kind, layer, tile, part, kb0, kb1;
@@ -72,15 +71,27 @@ struct Unit {
 // output, gate/up and down products, then the head.  Unit u of a product is (tile u / S, part u % S);
 // block c takes units (c + rot) % blocks, + blocks, ...
 struct Walker {
-  int layer, kind, u;
+  int layer, slot, u;      // slot: position in the layer's order q/k/v, attention, output, gate/up, down
   __device__ void start() {
     layer = 0;
-    kind = K_QKV;
+    slot = 0;
     u = -1;
   }
   __device__ bool next(const TsStepArgs& a, int cta, int nb, Unit& out) {
     while (true) {
       if (layer > a.L) return false;
+      const int kind = layer == a.L ? K_HEAD : (slot == 0 ? K_QKV : slot == 1 ? K_ATTN : slot == 2 ? K_O : slot == 3 ? K_GU : K_DOWN);
+      if (kind == K_ATTN) {
+        // one attention unit a block: its keys and values come through the ring like weights
+        slot = 2;
+        if (cta < a.T * a.KVH * a.attn_splits) {
+          out.kind = K_ATTN;
+          out.layer = layer;
+          out.tile = out.part = out.kb0 = out.kb1 = 0;
+          return true;
+        }
+        continue;
+      }
       const TsStepShape& sh = a.shape[kind];
       if (u < 0) u = (cta + sh.rot) % nb;
       if (u < sh.R * sh.S) {
@@ -98,9 +109,9 @@ struct Walker {
         layer = a.L + 1;
         continue;
       }
-      if (++kind == K_HEAD) {
-        kind = K_QKV;
-        if (++layer == a.L) kind = K_HEAD;
+      if (++slot == 5) {
+        slot = 0;
+        ++layer;
       }
     }
   }
@@ -164,7 +175,7 @@ __device__ __forceinline__ bool warp_wait_shared_ge(volatile int* p, int target,
   return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
 }
 
-__device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abort& ab, int code) {
+[[maybe_unused]] __device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Abort& ab, int code) {
   if (mbar_wait(bar, parity, ab.status, code, ab.flag)) return true;
   atomicExch(ab.step_abort, 1);
   return false;
@@ -182,6 +193,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, int n) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -388,77 +404,27 @@ __device__ __forceinline__ bool read_accumulator(const Smem& sm, uint32_t tmem_b
 
 // ---- decode attention for one (request, kv head, key split) -----------------------------------------
 // The four compute warps on disjoint 16-key slices of every 64-key tile (as ts_attention_decode).
-// What one attention unit (request b, kv head, key split) covers and where its tiles come from.
-struct AttentionGeometry {
-  int b, kvh, split, k_begin, k_end, n_tiles, page_first, skip_key;
-  bool staged;
-  const int* pages;
-  const int* table;
-};
-__device__ __forceinline__ AttentionGeometry attention_geometry(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit) {
-  AttentionGeometry g;
-  const KeyRange kr = key_range(a, unit, sm.seq_()[unit / (a.KVH * a.attn_splits)], ly.window);
-  g.b = kr.b; g.kvh = kr.kvh; g.split = kr.split; g.k_begin = kr.k_begin; g.k_end = kr.k_end;
-  g.n_tiles = kr.k_end > kr.k_begin ? (kr.k_end - kr.k_begin + ATT_TILE - 1) / ATT_TILE : 0;
-  g.page_first = kr.page_first;
-  g.staged = kr.n_pages <= PAGES_S;                    // then the pages were put in shared memory when the step began
-  g.pages = sm.pages_() + ly.group * PAGES_S;
-  g.table = a.block_tables[ly.group] + (size_t)kr.b * a.table_width[ly.group];
-  // the new token's row is made in this step (by the unit whose share ends there), not read
-  g.skip_key = (g.n_tiles > 0 && kr.k_end == sm.seq_()[kr.b]) ? kr.k_end - 1 : -1;
-  return g;
+// Tiles of 64 keys of this block's attention unit (windows are not taken by this kernel: the host
+// sends windowed models down the other path).
+__device__ __forceinline__ int attention_tiles(const TsStepArgs& a, const Smem& sm, int unit, KeyRange& kr) {
+  kr = key_range(a, unit, sm.seq_()[unit / (a.KVH * a.attn_splits)], 0);
+  return kr.k_end > kr.k_begin ? (kr.k_end - kr.k_begin + ATT_TILE - 1) / ATT_TILE : 0;
 }
 
-// Tile `tile` of the unit's keys and values into stage `stage` of the work area (cp.async, 16 bytes a copy).
-__device__ __noinline__ void attention_load_tile(const TsStepArgs& a, const TsStepLayer& ly, const AttentionGeometry& g,
-                                                    unsigned char* work, int tile, int stage, int ct) {
-  constexpr int CH = D / 8;
-  const int page = a.page, KVH = a.KVH;
-  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
-  const int j0 = g.k_begin + tile * ATT_TILE;
-  unsigned char* ks_ = work + stage * ATT_TILE * D * 2;
-  unsigned char* vs_ = work + (ATT_STAGES + stage) * ATT_TILE * D * 2;
-#pragma unroll 2
-  for (int idx = ct; idx < ATT_TILE * CH; idx += CT) {
-    const int key = idx / CH, c = idx % CH;
-    const int j = j0 + key;
-    if (j == g.skip_key) continue;
-    const bool ok = j < g.k_end;
-    size_t off = 0;
-    if (ok) {
-      const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
-      const int pg = g.staged ? g.pages[lp - g.page_first] : g.table[lp];
-      off = (((size_t)pg * KVH + g.kvh) * page + (size_t)(j - lp * page)) * D + c * 8;
-    }
-    cp_async_16(ks_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.k_cache) + off, ok);
-    cp_async_16(vs_ + swz<D>(key, c), reinterpret_cast<const bf16*>(ly.v_cache) + off, ok);
-  }
-}
-
-// The first tiles of the unit set out.  Called as soon as the work area is free (the q/k/v products of
-// this block have been read back), before the grid barrier that ends the q/k/v phase: keys and values
-// of earlier steps depend on nothing in this one.
-__device__ void attention_prefetch(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct) {
-  const AttentionGeometry g = attention_geometry(a, ly, sm, unit);
-#pragma unroll 1
-  for (int s = 0; s < ATT_STAGES - 1; ++s) {
-    if (s < g.n_tiles) attention_load_tile(a, ly, g, sm.work_(), s, s, ct);
-    cp_async_commit();
-  }
-}
-
-__device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct, int seq1) {
+// Keys and values arrive through the ring like weights (the producer warp copies them page by page, a
+// stage of keys and a stage of values per tile of 64, rows of 256 bytes one after the other): tile t of
+// the unit is in stages q0 + 2 t and q0 + 2 t + 1 of the block's sequence.  Returns false when a wait ran out.
+__device__ bool attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const Smem& sm, int unit, int ct, int seq1, int q0,
+                               const Abort& ab) {
   constexpr int KS = D / 16, NT = D / 8;
-  const int NS = a.attn_splits;
+  const int NS = a.attn_splits, NST = sm.nst;
   const int H = a.H, KVH = a.KVH, G = H / KVH, page = a.page;
   const int lane = ct & 31, warp = ct >> 5;
-  const AttentionGeometry geo = attention_geometry(a, ly, sm, unit);
-  const int b = geo.b, kvh = geo.kvh, split = geo.split, k_begin = geo.k_begin, k_end = geo.k_end, n_tiles = geo.n_tiles;
+  KeyRange kr;
+  const int n_tiles = attention_tiles(a, sm, unit, kr);
+  const int b = kr.b, kvh = kr.kvh, split = kr.split, k_begin = kr.k_begin, k_end = kr.k_end;
   unsigned char* work = sm.work_();
   volatile int* flag = sm.flag_();
-  unsigned char* k_s = work;
-  unsigned char* v_s = work + ATT_STAGES * ATT_TILE * D * 2;
-  // (the first ATT_STAGES - 1 tiles were asked for by attention_prefetch)
   // The q/k/v product left 32-bit sums (all its parts added up) in a.qkv: bias, rounding to bfloat16
   // and rotation happen here, where they are used.  The group's G query heads go to shared memory as
   // the A operand's rows; the block whose share ends at the new token also makes that token's key and
@@ -544,21 +510,31 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float sc = a.scale * LOG2E;
 
+  bool ok = true;
+#pragma unroll 1
   for (int t = 0; t < n_tiles; ++t) {
-    if (t + ATT_STAGES - 1 < n_tiles) attention_load_tile(a, ly, geo, work, t + ATT_STAGES - 1, (t + ATT_STAGES - 1) % ATT_STAGES, ct);
-    cp_async_commit();
-    cp_async_wait<ATT_STAGES - 1>();
-    compute_sync();
+    const int qk = q0 + 2 * t, qv = qk + 1;
+    const int sk = qk % NST, sv = qv % NST;
+    ok = mwait_now(&sm.full_()[sk], (uint32_t)(qk / NST) & 1u, ab, 61) && mwait_now(&sm.full_()[sv], (uint32_t)(qv / NST) & 1u, ab, 62);
+    ok = compute_all(ok);
+    if (!ok) return false;
+    unsigned char* ks_ = sm.ring_() + (size_t)sk * STAGE_BYTES;
+    unsigned char* vs_ = sm.ring_() + (size_t)sv * STAGE_BYTES;
     if (t == new_tile) {                               // the new token's key and value take their place in the tile
       if (ct < 2 * (D / 8)) {
         const int which = ct / (D / 8), c = ct % (D / 8);
-        unsigned char* dst = (which == 0 ? k_s : v_s) + (t % ATT_STAGES) * ATT_TILE * D * 2 + swz<D>(new_key, c);
-        *reinterpret_cast<uint4*>(dst) = reinterpret_cast<const uint4*>(kv_new + which * D)[c];
+        *reinterpret_cast<uint4*>((which == 0 ? ks_ : vs_) + new_key * (D * 2) + c * 16) = reinterpret_cast<const uint4*>(kv_new + which * D)[c];
       }
       compute_sync();
     }
-    const unsigned char* ks_ = k_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
-    const unsigned char* vs_ = v_s + (t % ATT_STAGES) * ATT_TILE * D * 2;
+    const int rows_here = min(ATT_TILE, k_end - (k_begin + t * ATT_TILE));
+    if (rows_here < ATT_TILE) {
+      // Value rows past the unit's last key were not copied: their probabilities are exactly zero, and
+      // zero times whatever the stage held before must stay zero.
+      for (int idx = ct; idx < (ATT_TILE - rows_here) * (D / 8); idx += CT)
+        *reinterpret_cast<uint4*>(vs_ + (size_t)rows_here * (D * 2) + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+      compute_sync();
+    }
     const int key0 = warp * 16;
     const int j_base = k_begin + t * ATT_TILE + key0;
     if (j_base < k_end) {
@@ -568,7 +544,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
         const int mat = lane >> 3, r = lane & 7;
         const int key = key0 + (mat >> 1) * 8 + r;
         unsigned b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, ks_ + swz<D>(key, ks * 2 + (mat & 1)));
+        ldmatrix_x4(b0, b1, b2, b3, ks_ + key * (D * 2) + (ks * 2 + (mat & 1)) * 16);
         mma_bf16(s_acc[0], qf[ks], b0, b1);
         mma_bf16(s_acc[1], qf[ks], b2, b3);
       }
@@ -623,14 +599,18 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
         const int mat = lane >> 3, r = lane & 7;
         const int key = key0 + (mat & 1) * 8 + r;
         unsigned b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + swz<D>(key, i + (mat >> 1)));
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + key * (D * 2) + (i + (mat >> 1)) * 16);
         mma_bf16(o[i], pf, b0, b1);
         mma_bf16(o[i + 1], pf, b2, b3);
       }
     }
-    compute_sync();
+    if (rows_here < ATT_TILE || t == new_tile) fence_async_smem();      // ordinary stores above, before the stage is refilled by a copy
+    compute_sync();                                    // every warp is done with the two stages
+    if (ct == 0) {
+      mbar_arrive(&sm.empty_()[sk]);
+      mbar_arrive(&sm.empty_()[sv]);
+    }
   }
-  cp_async_wait<0>();
   compute_sync();
   mark(a, seq1, 3, ct);
 
@@ -705,24 +685,26 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   }
   if (NS == 1) {
     compute_sync();
-    return;
+    return true;
   }
-  __threadfence();
-  compute_sync();
+  compute_sync();                                      // every thread's stores precede thread 0's fence
   if (ct == 0) {
+    __threadfence();
     int* counter = a.tickets + TS_STEP_TICKETS_ATTN + b * KVH + kvh;
     const int ticket = atomicAdd(counter, 1);
     const int last = ticket == NS - 1;
-    if (last) *counter = 0;
+    if (last) {
+      *counter = 0;
+      __threadfence();                                 // the other splits' states are visible from here on
+    }
     *flag = last;
   }
   compute_sync();
   mark(a, seq1, 4, ct);
   if (*flag == 0) {
     compute_sync();
-    return;
+    return true;
   }
-  __threadfence();
   float* w_s = reinterpret_cast<float*>(work);                  // [G][NS]
   float* m_all = w_s + G * NS;
   float* l_all = m_all + G * NS;
@@ -775,6 +757,7 @@ __device__ void attention_unit(const TsStepArgs& a, const TsStepLayer& ly, const
   }
   compute_sync();
   mark(a, seq1, 5, ct);
+  return true;
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------
@@ -832,7 +815,51 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
       if (a_more) a_kb = ua.kb0;
       int a_q = 0;                                    // k-blocks the look-ahead has asked L2 for
       bool ok = true;
+      bool staged = false;
       while (ok && w.next(a, cta, nb, u)) {
+        if (u.kind == K_ATTN) {
+          // This block's share of the keys and values of layer u.layer, a stage of 64 key rows and a
+          // stage of 64 value rows per tile, copied page by page (rows of one page and kv head lie one
+          // after the other in the cache).  Rows past the unit's last key are not copied.
+          if (!staged) {                               // the step's lengths and pages are in shared memory after the first barrier
+            ok = wait_shared_ge(sm.phase_open_(), 1, ab, 12);
+            staged = true;
+            if (!ok) break;
+          }
+          KeyRange kr;
+          const int n_tiles = attention_tiles(a, sm, cta, kr);
+          const TsStepLayer* ly = a.layers + u.layer;
+          const unsigned char* caches[2] = {reinterpret_cast<const unsigned char*>(ly->k_cache), reinterpret_cast<const unsigned char*>(ly->v_cache)};
+          const int group = ly->group;
+          const int page = a.page, SL = page < ATT_TILE ? page : ATT_TILE;     // key rows one copy brings
+          const bool in_smem = kr.n_pages <= PAGES_S;
+          const int* table = a.block_tables[group] + (size_t)kr.b * a.table_width[group];
+          for (int t = 0; t < n_tiles && ok; ++t)
+            for (int kv = 0; kv < 2 && ok; ++kv, ++q) {
+              const int s = q % NST;
+              if (q >= NST) ok = mwait_now(&sm.empty_()[s], (uint32_t)((q / NST) - 1) & 1u, ab, 13);
+              if (!ok) break;
+              const int j0 = kr.k_begin + t * ATT_TILE;
+              const int rows = min(ATT_TILE, kr.k_end - j0);
+              mbar_expect_tx(&sm.full_()[s], (uint32_t)rows * D * 2);
+              unsigned char* dst = sm.ring_() + (size_t)s * STAGE_BYTES;
+              for (int r0 = 0; r0 < rows; r0 += SL) {
+                const int j = j0 + r0, lp = j / page;
+                const int pg = in_smem ? sm.pages_()[group * PAGES_S + lp - kr.page_first] : table[lp];
+                const int n = min(SL, rows - r0);
+                if (pg < 0 || pg >= a.num_pages || n < 1 || n > ATT_TILE || lp < kr.page_first || (in_smem && lp - kr.page_first >= PAGES_S) ||
+                    r0 + n > ATT_TILE || j - lp * page + n > page) {          // a copy that would leave the cache or the stage: refuse, say so
+                  ab.raise(70);
+                  ok = false;
+                  break;
+                }
+                bulk_load(dst + (size_t)r0 * D * 2, caches[kv] + (((size_t)pg * a.KVH + kr.kvh) * page + (size_t)(j - lp * page)) * D * 2,
+                          (uint32_t)n * D * 2, &sm.full_()[s]);
+              }
+              mbar_arrive_n(&sm.full_()[s], 32);
+            }
+          continue;
+        }
         const CUtensorMap* map = map_of(a, u.kind, u.layer);
         const bool streamed = u.kind == K_O || u.kind == K_DOWN;
         for (int kb = u.kb0; kb < u.kb1 && ok; ++kb, ++q) {
@@ -843,7 +870,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
                            "r"(a_kb * BK), "r"(ua.tile * BM) : "memory");
             ++a_q;
             if (++a_kb >= ua.kb1) {
-              a_more = ahead.next(a, cta, nb, ua);
+              do a_more = ahead.next(a, cta, nb, ua);
+              while (a_more && ua.kind == K_ATTN);
               if (a_more) a_kb = ua.kb0;
             }
           }
@@ -872,6 +900,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
       int q = 0, v = 0, xr = 0, cur_phase = -1;
       bool ok = true;
       while (ok && w.next(a, cta, nb, u)) {
+        if (u.kind == K_ATTN) {
+          // The compute warps use these stages.  This thread still waits for each of them to fill: a
+          // parity wait tells a phase only from its neighbours, so a waiter must never fall two uses
+          // of a stage behind (with as many key/value stages as the ring is long, the next weights
+          // land in the very stage the first keys are still on their way to).
+          ok = wait_shared_ge(sm.phase_open_(), 1, ab, 24);
+          KeyRange kr;
+          const int n = ok ? 2 * attention_tiles(a, sm, cta, kr) : 0;
+          for (int i = 0; i < n && ok; ++i, ++q) ok = mwait(&sm.full_()[q % NST], (uint32_t)(q / NST) & 1u, ab, 25);
+          continue;
+        }
         const bool from_norm = u.kind == K_QKV || u.kind == K_GU || u.kind == K_HEAD;
         const int phase = u.layer * 4 + u.kind;
         if (from_norm && phase != cur_phase) {          // this phase's norm output must be in place
@@ -895,7 +934,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
                                                             : sm.ring_() + (size_t)s * STAGE_BYTES + W_BYTES));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            if (k == 0 || !(a.lookahead & 1024))
             umma(tmem_base + (uint32_t)(acc * BN), da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16),
                  idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
           umma_commit(&sm.empty_()[s]);
@@ -930,6 +968,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
           }
         }
       }
+      if (u.kind == K_ATTN) {
+        ok = warp_wait_shared_ge(sm.phase_open_(), 1, ab, 54, lane) && !ab.raised();
+        KeyRange kr;
+        if (ok) q += 2 * attention_tiles(a, sm, cta, kr);
+        continue;
+      }
       const bool stream = u.kind == K_O || u.kind == K_DOWN;
       if (!stream) {                                   // the producer arrives for this warp's lanes
         q += u.kb1 - u.kb0;
@@ -959,7 +1003,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
     const int ct = threadIdx.x - CW0 * 32;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
-    int v = 0, seq = 0;
+    int v = 0, seq = 0, q = 0;                         // q: stages of the ring this block's units have taken so far
     bool ok = true;
     if (ct < (int)sizeof(TsStepLayer) / 16)            // the first layer's table entry
       cp_async_16(reinterpret_cast<unsigned char*>(sm.layer_(0)) + 16 * ct, reinterpret_cast<const unsigned char*>(a.layers) + 16 * ct, true);
@@ -1038,12 +1082,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
         for (int i = cta * CT + ct; i < total; i += nb * CT) a.qkv[i] = 0.f;
       }
       if (kind < 0) {
-        if (cta < a.T * a.KVH * a.attn_splits) attention_unit(a, ly, sm, cta, ct, seq + 1);
+        if (cta < a.T * a.KVH * a.attn_splits) {
+          KeyRange kr;
+          const int n_tiles = attention_tiles(a, sm, cta, kr);
+          ok = attention_unit(a, ly, sm, cta, ct, seq + 1, q, ab);
+          q += 2 * n_tiles;
+        }
       } else {
         const TsStepShape& sh = a.shape[kind];
         #pragma unroll 1
         for (int un = (cta + sh.rot) % nb; ok && un < sh.R * sh.S; un += nb) {
           const Unit u{kind, layer, un / sh.S, un % sh.S, 0, 0};
+          q += min(sh.KB, (u.part + 1) * sh.per) - u.part * sh.per;
           float x[BN];
           ok = compute_all(read_accumulator(sm, tmem_base, v, quad, x, ab));
           ++v;
@@ -1090,9 +1140,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) decode_step_kernel(const __gri
           mark(a, seq + 1, 5, ct);
         }
       }
-      if (kind == K_QKV && ok && cta < a.T * a.KVH * a.attn_splits) attention_prefetch(a, ly, sm, cta, ct);
       if (!head) ok = grid_barrier(a, sm, ++seq, nb, ct, ab) && ok;
     }
+  }
+  if (*sm.abort_flag_() != 0) {
+    // A block that gives up may still have copies on their way into its shared memory, and products
+    // in flight: it stays for a millisecond (far longer than either takes) before it leaves.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {}
   }
   tc_fence_before();
   __syncthreads();
@@ -1144,13 +1199,11 @@ static size_t step_smem(int stages, int work_bytes, int hidden) {
          (size_t)(2 * BN + TS_STEP_MAX_GROUPS * (BN + PAGES_S)) * 4 + 2 * sizeof(TsStepLayer) + 2 * (size_t)hidden * 4;
 }
 
-// The work area: the norm's output for `hidden` columns, or the attention's stages and merge space.
+// The work area: the norm's output for `hidden` columns, or the attention's merge space.
 TS_API int ts_decode_step_work_bytes(int hidden) {
   const int x = (hidden / BK) * X_BYTES;
-  const int att = 2 * ATT_STAGES * ATT_TILE * D * 2;
   const int merge = 4 * (3 * 4 * 16 + 32 + 5 * 16 * D);
-  int m = x > att ? x : att;
-  m = m > merge ? m : merge;
+  int m = x > merge ? x : merge;
   return (m + 1023) / 1024 * 1024;
 }
 
@@ -1194,6 +1247,10 @@ TS_API int ts_decode_step(const void* args_host, int blocks, int cooperative, vo
   if (a.T < 1 || a.T > BN) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: %d tokens (1..%d)", a.T, BN);
   if (a.hidden > TS_STEP_MAX_HIDDEN || !a.norm_w_is_f32)
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: hidden %d (at most %d), norm scales must be 32-bit", a.hidden, TS_STEP_MAX_HIDDEN);
+  if (a.page < 1 || (ATT_TILE % a.page != 0 && a.page % ATT_TILE != 0))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: pages of %d tokens (a divisor or a multiple of %d)", a.page, ATT_TILE);
+  for (int g = 0; g < a.num_groups; ++g)
+    if (a.group_window[g] > 0) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: windowed attention is not taken by this kernel");
   if (a.hidden % BK || a.inter % BK || a.H % a.KVH || a.H / a.KVH > 16 || a.L < 1)
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_decode_step: hidden %d, inner %d, heads %d/%d are not taken by this kernel", a.hidden, a.inter, a.H, a.KVH);
   if (a.stages < 3 || a.work_bytes < ts_decode_step_work_bytes(a.hidden)) TS_REFUSE(TS_ERR_SHAPE, "ts_decode_step: stages %d, work area %d", a.stages, a.work_bytes);

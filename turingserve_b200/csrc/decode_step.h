@@ -54,6 +54,7 @@ typedef struct {
   int table_width[TS_STEP_MAX_GROUPS];
   int group_window[TS_STEP_MAX_GROUPS];   // the window of the layers of each group (<= 0: none)
   int num_groups;
+  int num_pages;              // pages of a cache pool (what a block table may name)
   int l2_ahead;               // != 0: a layer's gate/up and down weights are asked into L2 when the layer begins
   const void* embedding;      // bfloat16 [vocabulary, hidden]
   const void* final_norm_w;

@@ -52,7 +52,7 @@ class StepArgs(ctypes.Structure):
                 ("ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("seq_lens", ctypes.c_void_p),
                 ("block_tables", ctypes.c_void_p * MAX_GROUPS), ("slot_mapping", ctypes.c_void_p * MAX_GROUPS),
                 ("table_width", ctypes.c_int * MAX_GROUPS), ("group_window", ctypes.c_int * MAX_GROUPS),
-                ("num_groups", ctypes.c_int), ("l2_ahead", ctypes.c_int),
+                ("num_groups", ctypes.c_int), ("num_pages", ctypes.c_int), ("l2_ahead", ctypes.c_int), ("pad1", ctypes.c_int),
                 ("embedding", ctypes.c_void_p), ("final_norm_w", ctypes.c_void_p),
                 ("resid", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p),
                 ("act", ctypes.c_void_p), ("logits", ctypes.c_void_p),
@@ -86,6 +86,7 @@ class FusedDecodeStep:
         self.hidden, self.inter, self.V = cfg.hidden_size, model.blocks[0].feed_forward.inter, cfg.vocab_size
         self.L = len(cfg.schedule)
         self.page = views[0].page_size
+        self.num_pages = int(views[0].k.shape[0])
         self.eps = model.final_norm.eps
         self.scale = att0.scale
         self.lookahead = int(os.environ.get("TURINGSERVE_B200_STEP_LOOKAHEAD", "0"))
@@ -183,7 +184,7 @@ class FusedDecodeStep:
             a, f, a0, f0 = b.mixer, b.feed_forward, first.mixer, first.feed_forward
             if (a.H, a.KVH, a.D, a.scale) != (a0.H, a0.KVH, a0.D, a0.scale) or f.inter != f0.inter:
                 return None
-            if a.D != HEAD_DIM or a.H // a.KVH > 16 or a.b_o is not None or f.bias or f.group != 64:
+            if a.D != HEAD_DIM or a.H // a.KVH > 16 or a.b_o is not None or f.bias or f.group != 64 or a.window is not None:
                 return None
             if a.position is not None and (a.position.rotary_dim != HEAD_DIM or a.position.cos.dtype != torch.float32):
                 return None
@@ -194,7 +195,7 @@ class FusedDecodeStep:
             if v is None or v.k is None or not v.writable or v.k.dtype != torch.bfloat16 or v.group >= MAX_GROUPS:
                 return None
             pages.add(v.page_size)
-        if len(pages) != 1 or cfg.hidden_size % 64 or first.feed_forward.inter % 64 or cfg.hidden_size > MAX_HIDDEN:
+        if len(pages) != 1 or (64 % next(iter(pages)) and next(iter(pages)) % 64) or cfg.hidden_size % 64 or first.feed_forward.inter % 64 or cfg.hidden_size > MAX_HIDDEN:
             return None
         stages = int(lib.ts_decode_step_max_stages(cfg.hidden_size))
         if stages < 3:
@@ -239,6 +240,7 @@ class FusedDecodeStep:
             a.group_window[g] = self.group_window.get(g, 0)
         a.num_groups = len(step.groups)
         a.l2_ahead = self.l2_ahead
+        a.num_pages = self.num_pages
         a.embedding, a.final_norm_w = self.model.embedding.data_ptr(), self._scale32(self.model.final_norm).data_ptr()
         logits = torch.empty((T, self.V), dtype=torch.float32, device=dev)
         a.resid, a.qkv, a.attn, a.act = (t.data_ptr() for t in (self.resid, self.qkv, self.attn, self.act))
