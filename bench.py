@@ -480,8 +480,12 @@ def per_kernel(ops, kw: dict, B: int, ctx: int, page: int, prefill_tokens: int, 
     st.seq_lens = torch.tensor([T], dtype=torch.int32, device=dev)
     st.num_requests, st.max_q_len, st.max_seq_len, st.num_decode, st.streaming_decode = 1, T, T, 0, False
     po = torch.empty(T, H * D, device=dev, dtype=bf)
-    record("prefill_attention", timed_graph(lambda i: ops.attention(po, pq, kv[i % 4][0], kv[i % 4][1], table, st, H, KVH, D,
-                                                                    page, D ** -0.5, None), 4), flops=2.0 * T * T * D * H)
+    # pages shorter than a tile of 64 keys are fetched as one box where they lie one after the other
+    # in the pool (a fresh pool hands them out so) and page by page where they do not
+    in_order = torch.arange(1, table.numel() + 1, dtype=torch.int32, device=dev).view_as(table)
+    for name, tab in (("prefill_attention", in_order), ("prefill_attention_shuffled_pages", table)):
+        record(name, timed_graph(lambda i: ops.attention(po, pq, kv[i % 4][0], kv[i % 4][1], tab, st, H, KVH, D,
+                                                         page, D ** -0.5, None), 4), flops=2.0 * T * T * D * H)
     return out
 
 

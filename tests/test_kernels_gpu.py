@@ -205,14 +205,33 @@ def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, 
     assert ops.tc_status() == 0
 
 
-def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None):
-    """Random q/k/v for several requests, laid into a shuffled paged cache."""
+def _page_ids(total, order, g):
+    """Page numbers 1..total-1 in the order in which ``pop()`` hands them out: shuffled, one after
+    the other, or in runs of one to six neighbours whose order among themselves is shuffled."""
+    if order == "shuffled":
+        return (torch.randperm(total - 1, generator=g) + 1).tolist()
+    if order == "in_order":
+        return list(range(total - 1, 0, -1))
+    assert order == "runs"
+    runs, at = [], 1
+    while at < total:
+        n = min(int(torch.randint(1, 7, (1,), generator=g)), total - at)
+        runs.append(list(range(at, at + n)))
+        at += n
+    out = []
+    for r in torch.randperm(len(runs), generator=g).tolist():
+        out.extend(runs[r])
+    return out[::-1]
+
+
+def _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, order="shuffled"):
+    """Random q/k/v for several requests, laid into a paged cache."""
     g = torch.Generator().manual_seed(seed)
     B = len(q_lens)
     seq_lens = [q + p for q, p in zip(q_lens, prefixes)]
     n_pages = [-(-s // page) for s in seq_lens]
     total = sum(n_pages) + 1
-    ids = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    ids = _page_ids(total, order, g)
     W = max(n_pages + [1])
     bt = torch.zeros((B, W), dtype=torch.int32)
     kc = torch.zeros((total, KVH, page, D))
@@ -256,8 +275,8 @@ def _poison_unwritten(kc, vc, bt, sl, page):
 
 
 def _run_attention(ops, dtype, H, KVH, D, page, q_lens, prefixes, seed, window=None, needle=None, fast=True, tc=True,
-                   tma=True, poison=False):
-    qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle)
+                   tma=True, poison=False, order="shuffled"):
+    qkv, kc, vc, bt, qs, sl = _paged_case(dtype, H, KVH, D, page, q_lens, prefixes, seed, window, needle, order)
     if poison:
         _poison_unwritten(kc, vc, bt, sl, page)
     T = qkv.shape[0]
@@ -593,19 +612,23 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
 @pytest.mark.parametrize("H,KVH", [(12, 2), (28, 4), (5, 5), (40, 2)])
 @pytest.mark.parametrize("page", [16, 32, 64, 128])
 @pytest.mark.parametrize("window", [None, 70])
-def test_attention_tensor_core_portions(ops, H, KVH, page, window):
+@pytest.mark.parametrize("order", ["shuffled", "in_order", "runs"])
+def test_attention_tensor_core_portions(ops, H, KVH, page, window, order):
     """The tcgen05 prompt-portion kernel (head size 128): portions after prefixes, several requests,
-    group sizes that are no power of two, a needle far back."""
+    group sizes that are no power of two, a needle far back.  Pages smaller than a tile of keys are
+    fetched as one box where they lie one after the other in the pool and page by page where they do
+    not, so the pool is laid out shuffled, in order, and in short runs."""
     D = 128
     ops.use_tc_attention = True
     try:
         for q_lens, prefixes in (([300], [0]), ([1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129]), ([17, 40], [1000, 3])):
-            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 21, window=window)
+            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 21, window=window,
+                                         order=order)
             torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
         if window is None:
             for needle in (0, 15, 16, 63, 64, 65, 127, 500):
                 out, ref, (qkv, kc, vc, bt, qs, sl) = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [9, 130], [891, 770],
-                                                                   22, needle=needle)
+                                                                   22, needle=needle, order=order)
                 torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
         assert ops.tc_status() == 0, "a block of the tensor-core attention gave up on a wait"
     finally:

@@ -1,6 +1,8 @@
 // Paged grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor cores:
 // S = Q.K^T and O += P.V are tcgen05.mma products with their accumulators in tensor memory;
-// key/value tiles come from the paged cache by TMA (one box per page or 64 keys, and half head);
+// key/value tiles come from the paged cache by TMA (one box per page or 64 keys, and half head; with
+// pages shorter than a tile, ONE box per half head where the tile's pages happen to lie one after the
+// other in the pool, which a request's pages do until the pool has been through many requests);
 // P never leaves tensor memory (the second product reads its A operand from there).  Same
 // semantics as attention_prefill.cu (the reference's turingserve/ops/triton_prefill_attention.py:17-79
 // and turingserve/ops/reference.py:60-77,94-111, plus the optional window); bfloat16, head size 128,
@@ -21,6 +23,9 @@
 // then, O is rescaled in tensor memory, after the product before it has finished.  Two blocks
 // share an SM.  Every barrier wait is bounded; a block that gives up records where, stops, and
 // frees its tensor memory.
+#include <utility>
+#include <vector>
+
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -63,6 +68,7 @@ struct AttnArgs {
   const int* q_start;
   const int* seq_lens;
   int table_width, H, KVH, page, box;
+  int run;                 // pages per tile when a tile is several pages (then the run maps are valid), else 0
   float scale;
   int window;
   int* status;
@@ -76,6 +82,13 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
       ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// A 4-D box (64 columns, a page's rows, one kv head, `run` pages that follow one another in the pool).
+__device__ __forceinline__ void tma_load_run(void* dst, const CUtensorMap* map, int x, int kvh, int page0, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(0), "r"(kvh), "r"(page0) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -84,6 +97,7 @@ constexpr int ATT_THREADS = TQ + 64;      // warps 0-3: one query row per thread
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                            const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
                             const AttnArgs a) {
   pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -179,14 +193,49 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   if (warp == 5) {
     // ================= producer: TMA loads, one lane =================
     if ((tid & 31) == 0 && n_tiles > 0) {
-      // one TMA box per (`box` keys, 64 columns)
-      auto load = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int t) {
+      // The page ids of a tile whose pages are shorter than the tile (2 or 4 of them), kept in registers
+      // and read two tiles ahead: a table entry fetched where it is used would put a trip to memory
+      // into every tile of the one thread that issues the copies.
+      struct TilePages { int p[4]; };
+      const int run = a.run;
+      const int* tab_row = a.block_tables + (size_t)b * a.table_width;
+      auto pages_of = [&](int t) {
+        TilePages tp;
+        const int lp0 = (j_lo + t * TK) / a.page;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tp.p[i] = (i < run && t < n_tiles && lp0 + i < a.table_width) ? tab_row[lp0 + i] : -1;
+        return tp;
+      };
+      auto load = [&](const CUtensorMap* map, const CUtensorMap* run_map, unsigned char* dst, uint64_t* bar, int t,
+                      const TilePages& tp) {
         mbar_expect_tx(bar, KV_TILE_BYTES);
         const int j0 = j_lo + t * TK;
+        if (run > 1) {
+          // A TMA copy costs the unit about the same whatever it brings: where the tile's pages follow
+          // one another in the pool (page ids p, p + 1, ...), one 4-D box per half head brings them all.
+          bool in_a_row = tp.p[0] >= 0;
+#pragma unroll
+          for (int i = 1; i < 4; ++i) in_a_row = in_a_row && (i >= run || tp.p[i] == tp.p[0] + i);
+          if (in_a_row) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) tma_load_run(dst + half * HALF_K, run_map, half * 64, kvh, tp.p[0], bar);
+            return;
+          }
+          // a box is a page here: one 2-D box per page and half head
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (i >= run) break;
+            const int y = (max(tp.p[i], 0) * a.KVH + kvh) * a.page;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + i * a.page * 128, map, half * 64, y, bar);
+          }
+          return;
+        }
+        // one TMA box per (`box` keys, 64 columns)
         for (int bx = 0; bx < TK / box; ++bx) {
           const int j = j0 + bx * box;
           const int lp = j / a.page;
-          const int pg = lp < a.table_width ? a.block_tables[(size_t)b * a.table_width + lp] : 0;
+          const int pg = lp < a.table_width ? tab_row[lp] : 0;
           const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
 #pragma unroll
           for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
@@ -194,18 +243,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       };
       // keys are needed two softmax rounds before the values of the same tile: K(t+1) goes before V(t)
       bool ok = true;
-      load(&k_map, k_s, &full_k[0], 0);
+      TilePages cur = pages_of(0), nxt = pages_of(1);
+      load(&k_map, &k_run_map, k_s, &full_k[0], 0, cur);
       for (int t = 0; t < n_tiles && ok; ++t) {
+        const TilePages after = pages_of(t + 2);
         if (t + 1 < n_tiles) {
           const int sk = (t + 1) % K_STAGES;
           if (t + 1 >= K_STAGES) ok = mbar_wait(&empty_k[sk], (uint32_t)(((t + 1) / K_STAGES - 1) & 1), a.status, 4, abort_flag);
           if (!ok) break;
-          load(&k_map, k_s + sk * KV_TILE_BYTES, &full_k[sk], t + 1);
+          load(&k_map, &k_run_map, k_s + sk * KV_TILE_BYTES, &full_k[sk], t + 1, nxt);
         }
         const int sv = t % V_STAGES;
         if (t >= V_STAGES) ok = mbar_wait(&empty_v[sv], (uint32_t)((t / V_STAGES - 1) & 1), a.status, 7, abort_flag);
         if (!ok) break;
-        load(&v_map, v_s + sv * KV_TILE_BYTES, &full_v[sv], t);
+        load(&v_map, &v_run_map, v_s + sv * KV_TILE_BYTES, &full_v[sv], t, cur);
+        cur = nxt;
+        nxt = after;
       }
     }
   } else if (warp == 4) {
@@ -384,6 +437,38 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
 }
 
+// The cache [pages, KVH, page, 128] as a 4-D tensor: boxes of 64 columns x a page's rows x one kv head x
+// `run` pages (128-byte swizzle, zeros outside).  Encoded once per (cache, shape).
+bool run_map(CUtensorMap* out, const void* cache, int num_pages, int KVH, int page, int run) {
+  struct Key {
+    const void* p;
+    int n, k, g, r;
+    bool operator==(const Key& o) const { return p == o.p && n == o.n && k == o.k && g == o.g && r == o.r; }
+  };
+  static std::vector<std::pair<Key, CUtensorMap>> cache_;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{cache, num_pages, KVH, page, run};
+  for (auto& e : cache_)
+    if (e.first == key) {
+      *out = e.second;
+      return true;
+    }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)page, (cuuint64_t)KVH, (cuuint64_t)num_pages};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)page * HD * 2, (cuuint64_t)KVH * page * HD * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)page, 1, (cuuint32_t)run};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache_.size() > 1024) cache_.clear();
+  cache_.emplace_back(key, *out);
+  return true;
+}
+
 int* attn_status_word() {
   static int* p = nullptr;
   if (p == nullptr && cudaGetSymbolAddress((void**)&p, g_attn_status) != cudaSuccess) p = nullptr;
@@ -425,6 +510,11 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   const int box = page % 64 == 0 ? 64 : (page % 32 == 0 ? 32 : 16);
   if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, box) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, box))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
+  // pages shorter than a tile: the maps whose one box is a run of pages (a box may be 256 rows at most)
+  const int run = (page < TK && box == page) ? TK / page : 0;
+  CUtensorMap k_run = k_map, v_run = v_map;
+  if (run > 1 && (!run_map(&k_run, k_cache, num_pages, KVH, page, run) || !run_map(&v_run, v_cache, num_pages, KVH, page, run)))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled (runs of pages) failed");
   // Two blocks fit an SM, which is what a launch of several waves wants (8,192 tokens: 261 us against
   // 379 us with one).  A launch of about one wave is as slow as its longest block, and that block
   // runs its chain of tiles faster with an SM to itself (2,048 tokens: 41 us against 48 us): such a
@@ -452,6 +542,7 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   a.KVH = KVH;
   a.page = page;
   a.box = box;
+  a.run = run > 1 ? run : 0;
   a.scale = scale;
   a.window = window;
   a.status = status;
@@ -459,6 +550,6 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   dim3 grid(ceil_div(max_q_len * G, TQ), KVH, B);
   const long long blocks = (long long)grid.x * grid.y * grid.z;
   const size_t smem = blocks * 2 <= (long long)sms * 3 ? smem_one : smem_two;
-  ts_launch(attention_prefill_tc_kernel, grid, dim3(ATT_THREADS), smem, (cudaStream_t)stream, k_map, v_map, a);
+  ts_launch(attention_prefill_tc_kernel, grid, dim3(ATT_THREADS), smem, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
   TS_LAUNCH_CHECK();
 }
