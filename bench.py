@@ -375,6 +375,7 @@ def per_kernel(ops, kw: dict, B: int, ctx: int, page: int, prefill_tokens: int, 
     to the step; they say how far each is from its own roofline."""
     import torch
 
+    from turingserve_b200 import kernels
     from turingserve_b200.engine.batch import streaming_decode
 
     h, I, H, KVH, D, V = (kw["hidden_size"], kw["intermediate_size"], kw["num_heads"], kw["num_kv_heads"],
@@ -427,12 +428,20 @@ def per_kernel(ops, kw: dict, B: int, ctx: int, page: int, prefill_tokens: int, 
                                             slots, page), len(ws))
     record("qkv_rope", us, nqkv * h * 2)
     del ws
-    # K7, K10: output and down projections, left unreduced as the step leaves them (the norm finishes them)
+    # K7, K10: output and down projections as the step runs them: a few tokens add themselves to the residual
+    # rows (their K splits summed on chip), more leave partial sums for the norm kernel
+    resid = torch.randn(B, h, device=dev, dtype=bf)
     for name, n, k in (("o_proj", h, H * D), ("down_proj", h, I)):
         ws = weights(n, k)
-        xin = torch.randn(B, k, device=dev, dtype=bf)
+        xin = torch.randn(B, k, device=dev, dtype=bf) * 0.02
         o = torch.empty(B, n, device=dev, dtype=bf)
-        record(name, timed_graph(lambda i: ops.linear(o, xin, ws[i % len(ws)], None, may_defer=True), len(ws)), n * k * 2)
+
+        def product(i):
+            p = ops.linear(o, xin, ws[i % len(ws)], None, may_defer=True)
+            if isinstance(p, kernels.LazyProduct) and not ops._into_residual(p, resid):
+                ops._settle(p)
+
+        record(name, timed_graph(product, len(ws)), n * k * 2)
         del ws
     # K8: gate/up product with the activation in its epilogue
     ws = weights(2 * I, h)

@@ -7,6 +7,7 @@ launches), and the kernel-by-kernel timeline of one captured decode step.
     python profile_kernels.py prefill_attention [--tokens 2048] [--page 16]
     python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated] [--graph]
     python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
+    python profile_kernels.py fused_step [--batch 8] [--context 2048] [--layers 4] [--page 16]
 
 Each prints the launches it made and, timed with CUDA events, the mean time per launch.
 """
@@ -104,6 +105,8 @@ def prefill_attention(a) -> None:
     T = a.tokens
     PAGE = a.page
     caches, table = paged(1, T, 4, PAGE)
+    if a.in_order:                                                 # as a fresh pool hands its pages out
+        table = torch.arange(1, table.numel() + 1, dtype=torch.int32, device="cuda").view_as(table)
     qkv = torch.randn(T, (H + 2 * KVH) * D, device="cuda", dtype=torch.bfloat16)
     step = Step(torch.tensor([0, T], dtype=torch.int32, device="cuda"),
                 torch.tensor([T], dtype=torch.int32, device="cuda"), 1, T, T, 0)
@@ -116,7 +119,7 @@ def prefill_attention(a) -> None:
     for i in range(4):
         f(i)
     us = timed(f, 12)
-    print(f"prefill_attention {T} tokens page {PAGE}: {us:.1f} us per launch, {2.0 * T * T * D * H / us / 1e6:.1f} TFLOP/s (causal)")
+    print(f"prefill_attention {T} tokens page {PAGE}{' in order' if a.in_order else ' shuffled'}: {us:.1f} us per launch, {2.0 * T * T * D * H / us / 1e6:.1f} TFLOP/s (causal)")
 
 
 def gemm(a) -> None:
@@ -219,6 +222,60 @@ def timeline(a) -> None:
         print(f"  {r[0]:8.2f} {r[1]:8.2f}  +{r[2]:5.2f}  {r[3]}")
 
 
+def fused_step(a) -> None:
+    """The whole decode step as one persistent kernel (off by default in the engine), phase by phase:
+    the kernel stamps the clock when a block arrives at a grid barrier and when it leaves it, so a
+    phase's work (arrival minus the leave before) and its wait show per block.  Also times the same
+    step as the chain of kernels, both eagerly launched, for comparison."""
+    import numpy as np
+
+    import bench
+    from turingserve_b200.engine.batch import StepEntry
+    from turingserve_b200.parts.fused_decode import FusedDecodeStep
+
+    FusedDecodeStep.enabled = True
+    B, ctx, L = a.batch, a.context, a.layers
+    eng = bench.build_engine_on_device(a.model, L, ctx_len=2 * ctx, page=a.page, max_seqs=B, max_tokens=2048, graph_sizes=())
+    runner, cache, ops = eng.runner, eng.cache, kernels.ops()
+    fused = runner.fused
+    if fused is None:
+        raise SystemExit("the fused step does not take this model")
+    rng = np.random.default_rng(0)
+    V = SHAPE["vocab_size"]
+    rcs = [cache.admit(f"d{i}") for i in range(B)]
+    for rc in rcs:
+        runner.step([StepEntry(rc, rng.integers(0, V, size=ctx).tolist(), [])])
+
+    def step(i=0):
+        runner.step([StepEntry(rc, [int(rng.integers(0, V))], [0]) for rc in rcs])
+
+    for use in (False, True):
+        ops.use_fused_step = use
+        for _ in range(3):
+            step()
+        print(f"fused_step batch {B} context {ctx} layers {L} page {a.page}: {'one kernel' if use else 'chain of kernels'} "
+              f"{timed(step, 10):.1f} us a step (host work of an eager step included)")
+    assert ops.lib.ts_decode_step_status() == 0
+    nbar = 5 * L + 1
+    fused.trace = torch.zeros((fused.blocks, nbar + 1, 8), dtype=torch.int64, device="cuda")
+    step()
+    torch.cuda.synchronize()
+    t = fused.trace.cpu().numpy().astype(np.float64)[:, :nbar]
+    fused.trace = None
+    arrive, leave = t[:, :, 0], t[:, :, 1]
+    mhz = 1965                                                     # the clock a decode step runs at (it is far from the power cap)
+    work = arrive[:, 1:] - leave[:, :-1]
+    wait = (leave - arrive)[:, 1:]
+    length = leave[:, 1:].max(0) - leave[:, :-1].max(0)
+    print(f"phases (us at {mhz} MHz, mean over layers 1..{L - 1}): work of the slowest / median block, wait of the last / median block at the barrier, length")
+    for j, name in enumerate(("q/k/v", "attention", "output", "gate/up", "down")):
+        cols = [5 * l + j for l in range(1, L)]
+        print(f"  {name:10s} work {work[:, cols].max(0).mean() / mhz:6.2f} / {np.median(work[:, cols], 0).mean() / mhz:6.2f}   "
+              f"wait {wait[:, cols].min(0).mean() / mhz:5.2f} / {np.median(wait[:, cols], 0).mean() / mhz:5.2f}   "
+              f"length {length[cols].mean() / mhz:6.2f}")
+    print(f"  a layer: {(leave[:, 5 * L].max() - leave[:, 5].max()) / mhz / (L - 1):.2f} us")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(prog="python profile_kernels.py")
     ap.add_argument("--model", default="qwen2.5-1.5b", choices=sorted(SHAPES), help="whose layer sizes to use")
@@ -232,6 +289,7 @@ def main() -> int:
     s = sub.add_parser("prefill_attention")
     s.add_argument("--tokens", type=int, default=2048)
     s.add_argument("--page", type=int, default=PAGE)
+    s.add_argument("--in-order", action="store_true", help="page ids one after the other instead of shuffled")
     s = sub.add_parser("gemm")
     s.add_argument("--tokens", type=int, default=8)
     s.add_argument("--n", type=int, default=17920)
@@ -244,12 +302,17 @@ def main() -> int:
     s.add_argument("--context", type=int, default=2048)
     s.add_argument("--layers", type=int, default=0, help="0: as many as the model has")
     s.add_argument("--page", type=int, default=PAGE)
+    s = sub.add_parser("fused_step")
+    s.add_argument("--batch", type=int, default=8)
+    s.add_argument("--context", type=int, default=2048)
+    s.add_argument("--layers", type=int, default=4)
+    s.add_argument("--page", type=int, default=PAGE)
     a = ap.parse_args()
     global H, KVH, D, LAYERS, SHAPE
     SHAPE = SHAPES[a.model]
     H, KVH, D, LAYERS = SHAPE["num_heads"], SHAPE["num_kv_heads"], SHAPE["head_dim"], SHAPE["num_layers"]
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm": gemm,
-     "timeline": timeline}[a.workload](a)
+     "timeline": timeline, "fused_step": fused_step}[a.workload](a)
     return 0
 
 

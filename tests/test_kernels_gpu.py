@@ -508,6 +508,53 @@ def test_linear_tensor_core(ops, M, N, K):
         ops.gemm_mode = DEFAULT_GEMM
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 17, 32])
+@pytest.mark.parametrize("N,K", [(1536, 1536), (1536, 8960), (200, 72), (384, 136), (256, 4096)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_linear_into_residual(ops, M, N, K, with_bias):
+    """The few-token product that sums its K splits (a thread-block cluster, or one block) and adds
+    itself to the residual rows in place: against the formula in 32 bits, and bit for bit against the
+    path it replaces (product left unreduced, the norm kernel summing and adding) when both cut K alike."""
+    from turingserve_b200.kernels import LazyProduct
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16() if with_bias else None
+    resid = torch.randn(M, N, generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(N, generator=g))
+    h = x.float() @ w.float().t()
+    if with_bias:
+        h = h + bias.float()
+    want = (h.bfloat16().float() + resid.float()).bfloat16()
+    cu = lambda t: None if t is None else t.cuda()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    normed = torch.empty_like(out)
+    before, cap = ops.max_splits, ops.fused_link_tokens
+    try:
+        ops.max_splits = 8
+        r1 = resid.cuda()
+        p = ops.linear(out, cu(x), cu(w), cu(bias), may_defer=True)
+        assert isinstance(p, LazyProduct)
+        ops.rmsnorm(normed, p, nw.cuda(), 1e-5, r1)
+        y1 = normed.clone()
+        assert ops.tc_status() == 0
+        # a product of bfloat16 values summed in another order differs in its last bit at most
+        torch.testing.assert_close(r1.cpu().float(), want.float(), atol=2e-2, rtol=1.6e-2)
+        assert (r1.cpu() == want).float().mean() > 0.9
+        ops.fused_link_tokens = 0                    # the path it replaces
+        r2 = resid.cuda()
+        d = ops.linear(out, cu(x), cu(w), cu(bias), may_defer=True)
+        assert not isinstance(d, LazyProduct)
+        y2 = torch.empty_like(out)
+        ops.rmsnorm(y2, d, nw.cuda(), 1e-5, r2)
+        assert torch.equal(r1, r2), "same splits, same order of sums: the same bits"
+        # (two norm kernels add a row's squares up in different orders: a value may differ by one step)
+        torch.testing.assert_close(y1.float(), y2.float(), atol=3e-2, rtol=1.6e-2)
+        assert (y1 == y2).float().mean() > 0.97
+    finally:
+        ops.max_splits, ops.fused_link_tokens = before, cap
+
+
 @pytest.mark.parametrize("M", [1, 8, 16])
 @pytest.mark.parametrize("N,K", [(151936, 1536), (75800, 320)])
 def test_linear_tensor_core_output_head(ops, M, N, K):
@@ -550,7 +597,7 @@ def test_work_buffers_outlive_the_graphs_that_captured_them(ops):
         ops._outgrown.append(ops._buffers.pop("partials"))
 
     def small():
-        d = ops.linear(out, x, w, None, may_defer=True)
+        d = ops.linear(out, x, w, None, may_defer=True, lazy=False)
         assert isinstance(d, Deferred)
         ops.rmsnorm(normed, d, nw, 1e-6)
 
@@ -561,7 +608,7 @@ def test_work_buffers_outlive_the_graphs_that_captured_them(ops):
     before = ops._buffers["partials"]
     xb = _rand((128, K), torch.bfloat16, 52).cuda()       # ten splits of 128 x 1536 partial sums: twice the first buffer
     ob = torch.empty((128, N), dtype=torch.bfloat16, device="cuda")
-    d = ops.linear(ob, xb, w, None, may_defer=True)
+    d = ops.linear(ob, xb, w, None, may_defer=True, lazy=False)
     assert isinstance(d, Deferred) and d.splits * 128 * N > before.numel()
     ops.materialize(d)
     assert ops._buffers["partials"] is not before and any(b is before for b in ops._outgrown)
@@ -590,7 +637,7 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
         for bias in (None, b):
             for with_res in (True, False):
                 out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-                d = ops.linear(out, x.cuda(), w.cuda(), None if bias is None else bias.cuda(), may_defer=True)
+                d = ops.linear(out, x.cuda(), w.cuda(), None if bias is None else bias.cuda(), may_defer=True, lazy=False)
                 assert isinstance(d, Deferred) and d.shape == (M, N)
                 plain_out = ops.materialize(d).cpu()
                 ref_lin = torch.nn.functional.linear(x.float(), w.float(), None if bias is None else bias.float())

@@ -49,7 +49,15 @@ struct GemmArgs {
   bf16* k_cache;
   bf16* v_cache;
   int page, H, KVH;
+  // weights-on-rows, a few tokens, resid != null: the splits of a tile are one thread-block cluster (or a
+  // single block); the sum over them in split order, plus bias, is rounded to bfloat16 and added to
+  // `resid` [M, N] in place, rounded again: what the product's epilogue and the next norm's residual add do.
+  bf16* resid = nullptr;
 };
+
+constexpr size_t gemm_smem_bytes(int BN, int STAGES, int KSUB) {
+  return 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
+}
 
 // BN: tile columns (UMMA N).  SWAP: the tile rows are weight rows (outputs), columns are tokens.
 // KSUB: 64-column k-blocks per pipeline stage (their TMA boxes are issued back to back, so a weight
@@ -102,6 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
+  const bool fuse_resid = SWAP && args.resid != nullptr;
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -201,7 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     pdl_wait();                                    // nothing is written before the predecessor is done
     bool ok = n_kb > 0 && mbar_wait(accum, 0, args.status, 3, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    if (SWAP && args.rope == 2) {
+    if (SWAP && (args.rope == 2 || fuse_resid)) {
       // The splits of this tile are one cluster: the partial sums stay in shared memory (the stage
       // buffers are free by now) for the peers to read; see the end of the kernel.
       constexpr int CW = BN >= 32 ? 32 : 16;
@@ -431,6 +440,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     }
     __syncwarp();
     cluster_sync_all();                              // no block leaves while a peer still reads it
+  } else if (fuse_resid) {
+    // Block z of the cluster finishes tokens z, z + splits, ...: each thread sums one output out of
+    // every peer's shared memory in split order, adds the bias, rounds as a product's epilogue does
+    // and adds the result to the residual row in place (what ts_reduce_rmsnorm does, bit for bit).
+    const bool many = args.splits > 1;
+    __syncwarp();
+    if (many) cluster_sync_all();
+    else __syncthreads();
+    if (warp >= 2) {
+      const int r = (warp & 3) * 32 + lane;
+      const int n = row0 + r;
+      const float* ex = reinterpret_cast<const float*>(a_s);
+      const float bv = (args.bias != nullptr && n < args.N) ? to_f(args.bias[n]) : 0.f;
+      const int tokens = min(BN, args.M - col0);
+      for (int tok = (int)blockIdx.z; tok < tokens; tok += args.splits) {
+        float part[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) part[sp] = many ? ld_peer_f32(peer_shared(ex + tok * 128 + r, sp)) : ex[tok * 128 + r];
+        float x = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) x += part[sp];
+        if (n < args.N) {
+          bf16* dst = args.resid + (size_t)(col0 + tok) * args.N + n;
+          *dst = __float2bfloat16_rn(round_to<bf16>(x + bv) + to_f(*dst));
+        }
+      }
+    }
+    __syncwarp();
+    if (many) cluster_sync_all();
+    else __syncthreads();
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -462,15 +503,23 @@ int* status_word() {
   return p;
 }
 
+// Raises the kernel's dynamic shared memory limit to `smem` if it is lower (never lowers it).
+template <int BN, int STAGES, bool SWAP, int KSUB>
+cudaError_t allow_smem(size_t smem) {
+  static size_t allowed = 0;                        // (one device's worth: the attribute is per device, the library serves one)
+  if (smem <= allowed) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) allowed = smem;
+  return e;
+}
+
 template <int BN, int STAGES, bool SWAP, int KSUB = 1>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmArgs& args, dim3 grid, cudaStream_t s,
            dim3 cluster = dim3(1, 1, 1)) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  constexpr size_t smem = gemm_smem_bytes(BN, STAGES, KSUB);
+  {
+    cudaError_t e = allow_smem<BN, STAGES, SWAP, KSUB>(smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_linear_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    configured = true;
   }
   ts_launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, KSUB>, cluster, dim3(grid), dim3(GEMM_THREADS), smem, s, rows_map,
                     cols_map, args);
@@ -480,13 +529,13 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const GemmA
 // How many clusters of `splits` blocks of this kernel the device holds at once (asked once per count; 0: none).
 template <int BN, int STAGES, bool SWAP, int KSUB = 1>
 int cluster_fits(int splits) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 24;
+  constexpr size_t smem = gemm_smem_bytes(BN, STAGES, KSUB);
   static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
   if (splits < 2 || splits > 8) return 0;
   if (known[splits] < 0) {
     known[splits] = 0;
     auto kernel = gemm_tc_kernel<BN, STAGES, SWAP, KSUB>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+    if (allow_smem<BN, STAGES, SWAP, KSUB>(smem) == cudaSuccess) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(1, 1, splits);
       cfg.blockDim = dim3(GEMM_THREADS);
@@ -609,6 +658,7 @@ TS_API int ts_linear_tc_ex(void* out, const void* x, const void* w, const void* 
 // multiple of 128, no bias: what the fused epilogue takes (TS_ERR_UNSUPPORTED otherwise, and the
 // caller does product and activation apart).
 TS_API int ts_linear_tc_gated(void* act, const void* x, const void* w, int M, int N2, int K, void* stream) {
+
   if (M <= 0 || N2 <= 0) return 0;
   if (M > 128 || N2 % 128 != 0 || !ts_linear_tc_supported(M, N2, K))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_gated: M=%d N=%d K=%d is not taken by this kernel", M, N2, K);
@@ -652,6 +702,7 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
                                  const int* positions, const float* cos_t, const float* sin_t, const int* slots,
                                  void* k_cache, void* v_cache, int M, int H, int KVH, int page, int K, int splits,
                                  void* stream) {
+
   if (M <= 0) return 0;
   const int heads = H + 2 * KVH, N = heads * 128;
   if (M > 128 || H <= 0 || KVH <= 0 || !ts_linear_tc_supported(M, N, K))
@@ -715,4 +766,56 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
   if (bn == 64) TS_ROPE_LAUNCH(64, 4, true);
   TS_ROPE_LAUNCH(128, 4, true);
 #undef TS_ROPE_LAUNCH
+}
+
+// resid[M, N] (bf16, in place) = bf16(resid + bf16(x[M, K] . w[N, K]^T + bias)): a few-token product whose
+// K splits are one thread-block cluster that sums its partial results through shared memory and adds
+// them to the residual stream itself: the product, its reduction and the residual add of the norm that
+// follows, in one kernel, with the same roundings.  At most 128 tokens, at most 8 splits.
+// TS_ERR_UNSUPPORTED when the clusters are switched off or do not fit the device at once.
+TS_API int ts_linear_tc_resid(void* resid, const void* x, const void* w, const void* bias, int M, int N, int K, int splits,
+                              void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 128 || !ts_linear_tc_supported(M, N, K))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_resid: M=%d N=%d K=%d is not taken by this kernel", M, N, K);
+  if (resid == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_linear_tc_resid: no residual");
+  if (((uintptr_t)x | (uintptr_t)w) & 15) TS_REFUSE(TS_ERR_ALIGN, "ts_linear_tc_resid: operands must be 16-byte aligned");
+  int* status = status_word();
+  if (status == nullptr) TS_REFUSE(TS_ERR_LIMIT, "ts_linear_tc_resid: no status word");
+  const int total_kb = ceil_div(K, BK);
+  if (splits < 1) splits = 1;
+  if (splits > 8) splits = 8;
+  if (splits > total_kb) splits = total_kb;
+  const int per = ceil_div(total_kb, splits);
+  splits = ceil_div(total_kb, per);
+  if (splits > 1 && !ts_clusters_enabled()) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_resid: thread-block clusters are switched off");
+  GemmArgs a;
+  a.out = nullptr;
+  a.bias = (const bf16*)bias;
+  a.M = M; a.N = N; a.K = K;
+  a.out_is_float = 0;
+  a.gated = 0;
+  a.rope = 0;
+  a.status = status;
+  a.k_blocks_per_split = per;
+  a.splits = splits;
+  a.resid = (bf16*)resid;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap rows_map, cols_map;
+  if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_resid: cuTensorMapEncodeTiled failed");
+  dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 cl(1, 1, splits);
+#define TS_RESID_LAUNCH(...)                                          \
+  do {                                                                \
+    if (splits > 1 && (int)(grid.x * grid.y) > cluster_fits<__VA_ARGS__>(splits)) \
+      TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_resid: %d clusters of %d blocks do not fit the device at once", (int)(grid.x * grid.y), splits); \
+    return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s, cl);   \
+  } while (0)
+  if (bn == 16) TS_RESID_LAUNCH(16, 4, true, 2);
+  if (bn == 32) TS_RESID_LAUNCH(32, 4, true);
+  if (bn == 64) TS_RESID_LAUNCH(64, 4, true, 2);
+  TS_RESID_LAUNCH(128, 4, true);
+#undef TS_RESID_LAUNCH
 }
