@@ -659,14 +659,16 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
 @pytest.mark.parametrize("H,KVH", [(12, 2), (28, 4), (5, 5), (40, 2)])
 @pytest.mark.parametrize("page", [16, 32, 64, 128])
 @pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("order", ["shuffled", "in_order", "runs"])
-def test_attention_tensor_core_portions(ops, H, KVH, page, window, order):
+@pytest.mark.parametrize("order,tile", [("shuffled", 0), ("in_order", 64), ("runs", 128), ("shuffled", 128), ("in_order", 128)])
+def test_attention_tensor_core_portions(ops, H, KVH, page, window, order, tile):
     """The tcgen05 prompt-portion kernel (head size 128): portions after prefixes, several requests,
     group sizes that are no power of two, a needle far back.  Pages smaller than a tile of keys are
     fetched as one box where they lie one after the other in the pool and page by page where they do
-    not, so the pool is laid out shuffled, in order, and in short runs."""
+    not, so the pool is laid out shuffled, in order, and in short runs.  ``tile``: keys per tile, 64 or
+    128, or 0 for what the launch's size chooses."""
     D = 128
     ops.use_tc_attention = True
+    ops.lib.ts_set_prefill_tile(tile)
     try:
         for q_lens, prefixes in (([300], [0]), ([1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129]), ([17, 40], [1000, 3])):
             out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 21, window=window,
@@ -680,3 +682,4 @@ def test_attention_tensor_core_portions(ops, H, KVH, page, window, order):
         assert ops.tc_status() == 0, "a block of the tensor-core attention gave up on a wait"
     finally:
         ops.use_tc_attention = True
+        ops.lib.ts_set_prefill_tile(0)

@@ -9,14 +9,17 @@
 // pages that are a multiple of 16 tokens.
 //
 // One block = 128 query ROWS (a row is one (token, head-in-group) pair of one kv head, so a
-// group shares its key/value tiles).  Warps 0-3: thread r owns row r and tensor-memory lane r.
-// Warp 4 (one lane) issues the products, warp 5 (one lane) the TMA loads: keys into a ring of
+// group shares its key/value tiles).  Warps 0-7 are the softmax: row r = tensor-memory lane r belongs
+// to TWO threads, thread r of warps 0-3 with the first 32 keys of every tile and thread r of warps 4-7
+// with the last 32 (the chain of a tile, 64 exponentials a row, is what bounds a block, and a pair
+// walks it in half the time); the two exchange their maxima through shared memory once a tile.
+// Warp 8 (one lane) issues the products, warp 9 (one lane) the TMA loads: keys into a ring of
 // three stages, values into a ring of two.  S has two buffers in tensor memory, so the score
 // product of tile t+1 runs while the softmax warps work on tile t:
-//   warp 4   : S(t)[128x64] = Q[128x128] . K(t)[64x128]^T      (issued two tiles ahead of P)
-//   warps 0-3: read S(t) from tensor memory, mask, online softmax in 32-bit, write P(t) (bfloat16
+//   warp 8   : S(t)[128x64] = Q[128x128] . K(t)[64x128]^T      (issued two tiles ahead of P)
+//   warps 0-7: read S(t) from tensor memory, mask, online softmax in 32-bit, write P(t) (bfloat16
 //              pairs) over the first half of S(t)'s own columns; arrive on a barrier
-//   warp 4   : O[128x128] += P(t)[128x64] . V(t)[64x128]   (P from tensor memory, V MN-major as TMA
+//   warp 8   : O[128x128] += P(t)[128x64] . V(t)[64x128]   (P from tensor memory, V MN-major as TMA
 //              left it), then S(t+2) into the buffer P(t) leaves
 // The running maximum that the exponentials refer to moves only when a row's true maximum has
 // grown by more than 2^8 since (P stays below 2^8, 32-bit sums keep their scale): then, and only
@@ -34,16 +37,28 @@ namespace {
 using namespace tc;
 
 constexpr int TQ = 128;            // query rows per block = TMEM lanes
-constexpr int TK = 64;             // keys per tile
+constexpr int UNIT = 64;           // keys per unit of loading: a tile of keys is one or two of them
 constexpr int HD = 128;            // head size
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int BOX_ROWS = 16;       // keys per TMA box at least: 64, 32 or 16, the largest that divides the page
 constexpr uint32_t Q_BYTES = TQ * HD * 2;                 // 2 halves x [128 rows][128 B]
-constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;           // 2 halves x [64 keys][128 B]
-constexpr uint32_t HALF_K = TK * 128;                     // bytes between the two 64-column halves of a K/V tile
+// A tile of TK keys (64: two blocks share an SM and hide each other's waits, what a launch of many waves
+// wants; 128: one block per SM whose score products are 128 wide, what a launch of about one wave wants,
+// which is as slow as its longest block: a tcgen05.mma of 16 columns of K costs the tensor pipe about 95
+// cycles whether it is 64 or 128 wide, and the chain of a block is the chain of its products).
+template <int TK>
+struct Tile {
+  static constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;  // 2 halves x [TK keys][128 B]
+  static constexpr uint32_t HALF_K = TK * 128;            // bytes between the two 64-column halves of a K/V tile
+  static constexpr uint32_t S_BUF = TK;                   // columns of one S buffer (and, over its first half, P as bf16 pairs)
+  static constexpr uint32_t O_COL = 2 * TK;               // O behind the two S buffers
+  static constexpr uint32_t TMEM_COLS = TK == 64 ? 256 : 512;
+  static constexpr int KT = TK / 2;                       // keys of a tile per softmax thread
+  static constexpr int UNITS = TK / UNIT;
+  static constexpr size_t SMEM = Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + (2 * K_STAGES + 2 * V_STAGES + 14) * 8 + 16 + 2 * TQ * 2;
+};
 constexpr uint32_t HALF_Q = TQ * 128;
-constexpr uint32_t TMEM_COLS = 256;                       // S (and, over its first half, P as bf16 pairs): columns 0..63
-constexpr uint32_t S_COL = 0, S_BUF = 64, O_COL = 128;    // and 64..127, O: 128..255
+constexpr uint32_t S_COL = 0;
 constexpr float RESCALE_STEP = 8.f;                       // log2 of how far a maximum may run ahead of its reference
 constexpr float LOG2E_F = 1.4426950408889634f;
 
@@ -89,16 +104,36 @@ __device__ __forceinline__ void tma_load_run(void* dst, const CUtensorMap* map, 
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(0), "r"(kvh), "r"(page0) : "memory");
 }
 
+// 2^x by the special-function unit alone (2 ulp; the results are rounded to bfloat16), 0 for -inf.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int ATT_THREADS = TQ + 64;      // warps 0-3: one query row per thread; warp 4: product issue; warp 5: TMA
+constexpr int ATT_THREADS = 2 * TQ + 64;  // warps 0-7: two threads per query row; warp 8: product issue; warp 9: TMA
+constexpr int MMA_WARP = 2 * TQ / 32, TMA_WARP = MMA_WARP + 1;
 
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+
+template <int TK>
+__global__ void __launch_bounds__(ATT_THREADS, TK == 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
                             const AttnArgs a) {
+  using TL = Tile<TK>;
+  constexpr uint32_t KV_TILE_BYTES = TL::KV_TILE_BYTES, HALF_K = TL::HALF_K, S_BUF = TL::S_BUF, O_COL = TL::O_COL,
+                     TMEM_COLS = TL::TMEM_COLS;
+  constexpr int KT = TL::KT;
   pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                               // [2][128][128 B]
@@ -115,8 +150,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   uint64_t* bar_p = bar_s + 2;
   uint64_t* bar_pv = bar_p + 2;                            // an O product is complete
   uint64_t* bar_o = bar_pv + 1;                            // the last O product is complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  // the two threads of a row, per pair of warps (w, w + 4): [4] both have left their maximum of the tile
+  // in max_x, and [4] both have read the other's (so the next tile's may be written)
+  uint64_t* bar_x = bar_o + 1;
+  uint64_t* bar_r = bar_x + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_r + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  bf16* max_x = reinterpret_cast<bf16*>(const_cast<int*>(abort_flag) + 2);   // [2 halves][128 rows]
 
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = a.H / a.KVH;
@@ -145,14 +185,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
     mbar_init(&bar_s[0], 1);
     mbar_init(&bar_s[1], 1);
-    mbar_init(&bar_p[0], TQ);
-    mbar_init(&bar_p[1], TQ);
+    mbar_init(&bar_p[0], 2 * TQ);
+    mbar_init(&bar_p[1], 2 * TQ);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bar_x[i], 64);
+      mbar_init(&bar_r[i], 64);
+    }
     mbar_init(bar_pv, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -165,24 +209,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   j_lo &= ~(box - 1);
   const int n_tiles = (seq_len > 0 && j_hi >= j_lo) ? (j_hi - j_lo) / TK + 1 : 0;
 
-  // a softmax thread's row
-  const int row = row0 + tid;
-  const bool row_ok = tid < TQ && row < n_rows;
+  // a softmax thread's row and which half of a tile's keys (and of the head's columns) it takes
+  const int lane_row = tid & (TQ - 1), hh = (tid >> 7) & 1;
+  const int row = row0 + lane_row;
+  const bool row_ok = tid < 2 * TQ && row < n_rows;
   const int tok = row_ok ? row / G : 0, g = row_ok ? row % G : 0;
   const int pos = row_ok ? prefix + tok : -1;
 
   pdl_wait();                                               // q/k/v of this step are written by earlier kernels
 
   // Q rows -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7))
-  if (tid < TQ) {
-    const bf16* src = a.qkv + (size_t)(qs + tok) * (a.H + 2 * a.KVH) * HD + (size_t)(kvh * G + g) * HD;
+  if (tid < 2 * TQ) {                                         // each of a row's two threads one 64-column half
+    const bf16* src = a.qkv + (size_t)(qs + tok) * (a.H + 2 * a.KVH) * HD + (size_t)(kvh * G + g) * HD + hh * 64;
+    uint4 v[8];
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row_ok) v = *reinterpret_cast<const uint4*>(src + c * 8);
-      const int half = c >> 3, cc = c & 7;
-      *reinterpret_cast<uint4*>(q_s + half * HALF_Q + tid * 128 + ((cc ^ (tid & 7)) << 4)) = v;
-    }
+    for (int cc = 0; cc < 8; ++cc) v[cc] = row_ok ? *reinterpret_cast<const uint4*>(src + cc * 8) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc)
+      *reinterpret_cast<uint4*>(q_s + hh * HALF_Q + lane_row * 128 + ((cc ^ (lane_row & 7)) << 4)) = v[cc];
   }
   fence_async_smem();
   tc_fence_before();
@@ -190,55 +234,64 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 5) {
+  if (warp == TMA_WARP) {
     // ================= producer: TMA loads, one lane =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       // The page ids of a tile whose pages are shorter than the tile (2 or 4 of them), kept in registers
       // and read two tiles ahead: a table entry fetched where it is used would put a trip to memory
       // into every tile of the one thread that issues the copies.
-      struct TilePages { int p[4]; };
+      struct TilePages { int p[4 * TL::UNITS]; };
       const int run = a.run;
       const int* tab_row = a.block_tables + (size_t)b * a.table_width;
       auto pages_of = [&](int t) {
         TilePages tp;
-        const int lp0 = (j_lo + t * TK) / a.page;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tp.p[i] = (i < run && t < n_tiles && lp0 + i < a.table_width) ? tab_row[lp0 + i] : -1;
+        for (int u = 0; u < TL::UNITS; ++u) {
+          const int lp0 = (j_lo + t * TK + u * UNIT) / a.page;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            tp.p[4 * u + i] = (i < run && t < n_tiles && lp0 + i < a.table_width) ? tab_row[lp0 + i] : -1;
+        }
         return tp;
       };
-      auto load = [&](const CUtensorMap* map, const CUtensorMap* run_map, unsigned char* dst, uint64_t* bar, int t,
+      auto load = [&](const CUtensorMap* map, const CUtensorMap* run_map, unsigned char* tile, uint64_t* bar, int t,
                       const TilePages& tp) {
         mbar_expect_tx(bar, KV_TILE_BYTES);
-        const int j0 = j_lo + t * TK;
-        if (run > 1) {
-          // A TMA copy costs the unit about the same whatever it brings: where the tile's pages follow
-          // one another in the pool (page ids p, p + 1, ...), one 4-D box per half head brings them all.
-          bool in_a_row = tp.p[0] >= 0;
 #pragma unroll
-          for (int i = 1; i < 4; ++i) in_a_row = in_a_row && (i >= run || tp.p[i] == tp.p[0] + i);
-          if (in_a_row) {
+        for (int u = 0; u < TL::UNITS; ++u) {
+          unsigned char* dst = tile + u * UNIT * 128;          // the unit's rows within each 64-column half
+          const int j0 = j_lo + t * TK + u * UNIT;
+          if (run > 1) {
+            // A TMA copy costs the unit about the same whatever it brings: where the unit's pages follow
+            // one another in the pool (page ids p, p + 1, ...), one 4-D box per half head brings them all.
+            const int* pg = tp.p + 4 * u;
+            bool in_a_row = pg[0] >= 0;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) tma_load_run(dst + half * HALF_K, run_map, half * 64, kvh, tp.p[0], bar);
-            return;
+            for (int i = 1; i < 4; ++i) in_a_row = in_a_row && (i >= run || pg[i] == pg[0] + i);
+            if (in_a_row) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) tma_load_run(dst + half * HALF_K, run_map, half * 64, kvh, pg[0], bar);
+              continue;
+            }
+            // a box is a page here: one 2-D box per page and half head
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (i >= run) break;
+              const int y = (max(pg[i], 0) * a.KVH + kvh) * a.page;
+#pragma unroll
+              for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + i * a.page * 128, map, half * 64, y, bar);
+            }
+            continue;
           }
-          // a box is a page here: one 2-D box per page and half head
+          // one TMA box per (`box` keys, 64 columns)
+          for (int bx = 0; bx < UNIT / box; ++bx) {
+            const int j = j0 + bx * box;
+            const int lp = j / a.page;
+            const int pg = lp < a.table_width ? tab_row[lp] : 0;
+            const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (i >= run) break;
-            const int y = (max(tp.p[i], 0) * a.KVH + kvh) * a.page;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + i * a.page * 128, map, half * 64, y, bar);
+            for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
           }
-          return;
-        }
-        // one TMA box per (`box` keys, 64 columns)
-        for (int bx = 0; bx < TK / box; ++bx) {
-          const int j = j0 + bx * box;
-          const int lp = j / a.page;
-          const int pg = lp < a.table_width ? tab_row[lp] : 0;
-          const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
-#pragma unroll
-          for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
         }
       };
       // keys are needed two softmax rounds before the values of the same tile: K(t+1) goes before V(t)
@@ -261,7 +314,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         nxt = after;
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == MMA_WARP) {
     // ================= product issue, one lane =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       // S(t) = Q . K(t)^T into buffer t & 1: 8 k-steps of 16 columns, 4 per 64-column half
@@ -313,10 +366,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       }
     }
   } else {
-    // ================= softmax warps: thread = row = tensor-memory lane =================
-    float m_ref = -INFINITY, l_run = 0.f;                   // the maximum the exponentials refer to; the sum in its scale
+    // ================= softmax warps: two threads per row = tensor-memory lane =================
+    float m_ref = -INFINITY, l_run = 0.f;                   // the maximum the exponentials refer to; this half's sum in its scale
     const float sc = a.scale * LOG2E_F;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int pair = warp & 3;                              // warps `pair` and `pair + 4` share 32 rows
+    const uint32_t lane_addr = (uint32_t)(pair * 32) << 16;
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       const uint32_t s_addr = tmem + lane_addr + S_COL + (t & 1) * S_BUF;
@@ -324,17 +378,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int j0 = j_lo + t * TK;
-      uint32_t sv[2][32];
-      tmem_ld32(s_addr, sv[0]);
-      tmem_ld32(s_addr + 32, sv[1]);
+      const int j0 = j_lo + t * TK + hh * KT;               // this thread's first key of the tile
+      uint32_t sv[KT / 32][32];
+#pragma unroll
+      for (int h = 0; h < KT / 32; ++h) tmem_ld32(s_addr + hh * KT + h * 32, sv[h]);
       tmem_wait_ld();
       float mx = -INFINITY;
-      // tiles wholly before every row of the warp (the common case away from the diagonal) need no mask
-      const bool all_visible = __all_sync(0xffffffffu, (j0 + TK - 1 <= pos) && (a.window <= 0 || j0 > pos - a.window));
+      // keys wholly before every row of the warp (the common case away from the diagonal) need no mask
+      const bool all_visible = __all_sync(0xffffffffu, (j0 + KT - 1 <= pos) && (a.window <= 0 || j0 > pos - a.window));
       if (all_visible) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < KT / 32; ++h)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float v = __uint_as_float(sv[h][i]) * sc;
@@ -343,7 +397,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           }
       } else {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < KT / 32; ++h)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int j = j0 + h * 32 + i;
@@ -353,36 +407,61 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             mx = fmaxf(mx, v);
           }
       }
+      // The row's maximum over both halves, as both threads must see the same one: each leaves its own,
+      // rounded to bfloat16, and takes the larger of the two rounded values (a maximum that is a little
+      // low only lets P run a little above 1, which the 2^8 of headroom below covers).
+      if (t > 0) {
+        ok = mbar_wait_spin(&bar_r[pair], (uint32_t)((t - 1) & 1), a.status, 11, abort_flag);   // the last one has been read
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      const bf16 mine = __float2bfloat16_rn(mx);
+      max_x[hh * TQ + lane_row] = mine;
+      mbar_arrive(&bar_x[pair]);
+      // P (bfloat16 pairs), lane = row, KT / 2 words for this thread's KT keys, and their sum
+      uint32_t pw[KT / 2];
+      auto exponentials = [&](float m_use) {
+        float rs = 0.f;
+#pragma unroll
+        for (int i = 0; i < KT / 2; ++i) {
+          const int i0 = 2 * i;
+          const float p0 = ex2(__uint_as_float(sv[i0 >> 5][i0 & 31]) - m_use);
+          const float p1 = ex2(__uint_as_float(sv[(i0 + 1) >> 5][(i0 + 1) & 31]) - m_use);
+          rs += p0 + p1;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          pw[i] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        return rs;
+      };
+      // The reference maximum moves rarely once a row has one: the exponentials are taken against the
+      // present reference while the other thread's maximum is on its way, and taken again for the rows
+      // whose reference then moves after all.
+      const bool ahead = __all_sync(0xffffffffu, m_ref != -INFINITY);
+      float rs = 0.f;
+      if (ahead) rs = exponentials(m_ref);
+      ok = mbar_wait_spin(&bar_x[pair], (uint32_t)(t & 1), a.status, 12, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      mx = fmaxf(__bfloat162float(mine), __bfloat162float(max_x[(hh ^ 1) * TQ + lane_row]));
+      mbar_arrive(&bar_r[pair]);
       // the reference maximum follows the true one only in steps (and from nothing to something)
       const bool move = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
       float corr = 1.f;
       if (move) {
-        corr = exp2f(m_ref - mx);                             // 0 when there was no reference yet: O and l are 0 then
+        corr = ex2(m_ref - mx);                               // 0 when there was no reference yet: O and l are 0 then
         m_ref = mx;
       }
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float rs = 0.f;
-      // P (bfloat16 pairs), lane = row, 32 words for the 64 keys
-      uint32_t pw[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int i0 = 2 * i;
-        const float p0 = exp2f(__uint_as_float(sv[i0 >> 5][i0 & 31]) - m_use);
-        const float p1 = exp2f(__uint_as_float(sv[(i0 + 1) >> 5][(i0 + 1) & 31]) - m_use);
-        rs += p0 + p1;
-        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-        pw[i] = *reinterpret_cast<uint32_t*>(&pk);
-      }
+      if (!ahead || move) rs = exponentials((m_ref == -INFINITY) ? 0.f : m_ref);
       l_run = l_run * corr + rs;
-      // rescale O where a reference moved (skipped when no row of the warp needs it): the product of
-      // the tile before must be done with O first
+      // rescale O where a reference moved (skipped when no row of the warp needs it), each thread its half
+      // of the columns: the product of the tile before must be done with O first
       if (t > 0 && __any_sync(0xffffffffu, move)) {
         ok = mbar_wait_spin(bar_pv, (uint32_t)((t - 1) & 1), a.status, 10, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = hh * 64; c < hh * 64 + 64; c += 32) {
           uint32_t ov[32];
           tmem_ld32(tmem + lane_addr + O_COL + c, ov);
           tmem_wait_ld();
@@ -391,22 +470,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           tmem_st32(tmem + lane_addr + O_COL + c, ov);
         }
       }
-      tmem_st32(s_addr, pw);                                  // over the first half of S(t), which is in registers
+      // over the first half of S(t): the second thread's words lie over scores of the FIRST thread of the
+      // row, which has them in registers since before it left its maximum
+      if constexpr (KT == 32) tmem_st16(s_addr + hh * 16, pw);
+      else tmem_st32(s_addr + hh * 32, pw);
       tmem_wait_st();                                         // P (and a rescaled O) are in tensor memory
       tc_fence_before();
       mbar_arrive(&bar_p[t & 1]);
     }
-    // epilogue: O / l -> bfloat16 -> global, one 256-byte row per thread
+    // epilogue: O / l -> bfloat16 -> global, 128 bytes of the row per thread
     if (ok && n_tiles > 0) {
       ok = mbar_wait(bar_o, 0, a.status, 5, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
+    }
+    // the row's sum is the two halves' sums (same scale): exchanged through the shared memory Q leaves,
+    // on the pair's barrier, whose next phase is n_tiles' parity
+    if (ok && n_tiles > 0) {
+      float* l_x = reinterpret_cast<float*>(q_s);
+      l_x[hh * TQ + lane_row] = l_run;
+      mbar_arrive(&bar_x[pair]);
+      ok = mbar_wait_spin(&bar_x[pair], (uint32_t)(n_tiles & 1), a.status, 13, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) l_run += l_x[(hh ^ 1) * TQ + lane_row];
     }
     if (ok) {
       tc_fence_after();
       bf16* dst = a.out + (size_t)(qs + tok) * a.H * HD + (size_t)(kvh * G + g) * HD;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = hh * 64; c < hh * 64 + 64; c += 32) {
         uint32_t ov[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem + lane_addr + O_COL + c, ov);       // the whole warp loads; rows without a query store nothing
@@ -432,7 +524,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
 }
@@ -479,6 +571,10 @@ int* attn_status_word() {
 
 int* ts_attn_status_word() { return attn_status_word(); }
 
+static int g_tile_keys = 0;
+// Keys per tile of the prompt attention: 64, 128, or 0 for the launch's own choice (for measurements).
+TS_API void ts_set_prefill_tile(int keys) { g_tile_keys = (keys == 64 || keys == 128) ? keys : 0; }
+
 TS_API int ts_attention_prefill_tc_supported(int H, int KVH, int D, int page, int dtype) {
   return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && D == HD && page >= BOX_ROWS && page % BOX_ROWS == 0;
 }
@@ -511,21 +607,20 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   if (!tc::tensor_map(&k_map, k_cache, (int)rows, D, box) || !tc::tensor_map(&v_map, v_cache, (int)rows, D, box))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled failed");
   // pages shorter than a tile: the maps whose one box is a run of pages (a box may be 256 rows at most)
-  const int run = (page < TK && box == page) ? TK / page : 0;
+  const int run = (page < UNIT && box == page) ? UNIT / page : 0;
   CUtensorMap k_run = k_map, v_run = v_map;
   if (run > 1 && (!run_map(&k_run, k_cache, num_pages, KVH, page, run) || !run_map(&v_run, v_cache, num_pages, KVH, page, run)))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled (runs of pages) failed");
-  // Two blocks fit an SM, which is what a launch of several waves wants (8,192 tokens: 261 us against
-  // 379 us with one).  A launch of about one wave is as slow as its longest block, and that block
-  // runs its chain of tiles faster with an SM to itself (2,048 tokens: 41 us against 48 us): such a
-  // launch asks for shared memory it does not use, so that only one block fits.
-  constexpr size_t smem_two = Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + (2 * K_STAGES + 2 * V_STAGES + 6) * 8 + 16;
-  constexpr size_t smem_one = smem_two + 8192;
+  // Two blocks with tiles of 64 keys fit an SM, which is what a launch of several waves wants (8,192
+  // tokens: 261 us against 379 us with one).  A launch of about one wave is as slow as its longest block:
+  // it gets tiles of 128 keys, one block per SM.
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_one);
-    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_prefill_tc: shared memory %zu: %s", smem_one, cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<64>::SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<128>::SMEM);
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_prefill_tc: shared memory %zu: %s", Tile<128>::SMEM, cudaGetErrorString(e));
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       sms = 0;
@@ -549,7 +644,12 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   const int G = H / KVH;
   dim3 grid(ceil_div(max_q_len * G, TQ), KVH, B);
   const long long blocks = (long long)grid.x * grid.y * grid.z;
-  const size_t smem = blocks * 2 <= (long long)sms * 3 ? smem_one : smem_two;
-  ts_launch(attention_prefill_tc_kernel, grid, dim3(ATT_THREADS), smem, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
+  const bool wide = g_tile_keys == 128 || (g_tile_keys == 0 && blocks * 2 <= (long long)sms * 3);
+  if (wide)
+    ts_launch(attention_prefill_tc_kernel<128>, grid, dim3(ATT_THREADS), Tile<128>::SMEM, (cudaStream_t)stream, k_map, v_map,
+              k_run, v_run, a);
+  else
+    ts_launch(attention_prefill_tc_kernel<64>, grid, dim3(ATT_THREADS), Tile<64>::SMEM, (cudaStream_t)stream, k_map, v_map,
+              k_run, v_run, a);
   TS_LAUNCH_CHECK();
 }

@@ -148,6 +148,10 @@ class CudaOps:
         self.lib.ts_attention_prefill_tc_status.restype = c_int
         # prompt-portion attention on tcgen05 (head size 128, pages of a multiple of 16 tokens) or mma.sync
         self.use_tc_attention = os.environ.get("TURINGSERVE_B200_ATTENTION", "tc") == "tc"
+        # its tiles of keys: 64 (two blocks an SM), 128 (one), 0 = by the size of the launch
+        self.lib.ts_set_prefill_tile.argtypes = [I]
+        self.lib.ts_set_prefill_tile.restype = None
+        self.lib.ts_set_prefill_tile(int(os.environ.get("TURINGSERVE_B200_ATTENTION_TILE", "0")))
         self.lib.ts_attention_prefill_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_prefill_supported.restype = c_int
         for name, args in (("ts_decode_step_max_stages", [I]), ("ts_decode_step_blocks", [I, I]),
