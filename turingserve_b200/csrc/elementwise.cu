@@ -487,34 +487,34 @@ __device__ __forceinline__ void load_qkv8(const bf16* row, int col, const float*
                                           size_t part_row, const bf16* bias, float (&f)[8]) {
   if constexpr (!PART) {
     load_vec<bf16, 8>(row + col, f);
-    return;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = 0.f;
+    // eight splits' loads at a time (one round trip per eight), sums in ascending split order
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float4 a[8], b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < splits) {
+          a[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col));
+          b[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col + 4));
+        }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < splits) {
+          f[0] += a[u].x; f[1] += a[u].y; f[2] += a[u].z; f[3] += a[u].w;
+          f[4] += b[u].x; f[5] += b[u].y; f[6] += b[u].z; f[7] += b[u].w;
+        }
+    }
+    if (bias != nullptr) {
+      float bv[8];
+      load_vec<bf16, 8>(bias + col, bv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] += bv[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = round_to<bf16>(f[k]);
   }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) f[k] = 0.f;
-  // eight splits' loads at a time (one round trip per eight), sums in ascending split order
-  for (int s0 = 0; s0 < splits; s0 += 8) {
-    float4 a[8], b[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (s0 + u < splits) {
-        a[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col));
-        b[u] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + u) * split_stride + part_row + col + 4));
-      }
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (s0 + u < splits) {
-        f[0] += a[u].x; f[1] += a[u].y; f[2] += a[u].z; f[3] += a[u].w;
-        f[4] += b[u].x; f[5] += b[u].y; f[6] += b[u].z; f[7] += b[u].w;
-      }
-  }
-  if (bias != nullptr) {
-    float bv[8];
-    load_vec<bf16, 8>(bias + col, bv);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) f[k] += bv[k];
-  }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) f[k] = round_to<bf16>(f[k]);
 }
 
 // PART: the product arrives unreduced (`part` set).  A kernel of its own, because the partial sums
