@@ -4,7 +4,7 @@ enough for a profiler capture that ends by itself (a few hundred MB on the devic
 launches), and the kernel-by-kernel timeline of one captured decode step.
 
     python profile_kernels.py decode_attention [--model qwen2.5-1.5b] [--batch 8] [--context 2048] [--page 16] [--graph]
-    python profile_kernels.py prefill_attention [--tokens 2048] [--page 16]
+    python profile_kernels.py prefill_attention [--tokens 2048] [--prefix 0] [--page 16] [--in-order]
     python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated] [--graph]
     python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
     python profile_kernels.py fused_step [--batch 8] [--context 2048] [--layers 4] [--page 16]
@@ -102,14 +102,14 @@ def decode_attention(a) -> None:
 
 def prefill_attention(a) -> None:
     ops = kernels.ops()
-    T = a.tokens
+    T, S = a.tokens, a.prefix + a.tokens                          # a portion of T tokens after `prefix` cached ones
     PAGE = a.page
-    caches, table = paged(1, T, 4, PAGE)
+    caches, table = paged(1, S, 4, PAGE)
     if a.in_order:                                                 # as a fresh pool hands its pages out
         table = torch.arange(1, table.numel() + 1, dtype=torch.int32, device="cuda").view_as(table)
     qkv = torch.randn(T, (H + 2 * KVH) * D, device="cuda", dtype=torch.bfloat16)
     step = Step(torch.tensor([0, T], dtype=torch.int32, device="cuda"),
-                torch.tensor([T], dtype=torch.int32, device="cuda"), 1, T, T, 0)
+                torch.tensor([S], dtype=torch.int32, device="cuda"), 1, T, S, 0)
     out = torch.empty(T, H * D, device="cuda", dtype=torch.bfloat16)
 
     def f(i):
@@ -119,7 +119,9 @@ def prefill_attention(a) -> None:
     for i in range(4):
         f(i)
     us = timed(f, 12)
-    print(f"prefill_attention {T} tokens page {PAGE}{' in order' if a.in_order else ' shuffled'}: {us:.1f} us per launch, {2.0 * T * T * D * H / us / 1e6:.1f} TFLOP/s (causal)")
+    flops = 4.0 * D * H * (T * a.prefix + T * (T + 1) / 2)         # scores and values over the keys each token sees
+    print(f"prefill_attention {T} tokens after {a.prefix} page {PAGE}{' in order' if a.in_order else ' shuffled'}: "
+          f"{us:.1f} us per launch, {flops / us / 1e6:.1f} TFLOP/s")
 
 
 def gemm(a) -> None:
@@ -289,6 +291,7 @@ def main() -> int:
     s = sub.add_parser("prefill_attention")
     s.add_argument("--tokens", type=int, default=2048)
     s.add_argument("--page", type=int, default=PAGE)
+    s.add_argument("--prefix", type=int, default=0, help="tokens of the request already in the cache")
     s.add_argument("--in-order", action="store_true", help="page ids one after the other instead of shuffled")
     s = sub.add_parser("gemm")
     s.add_argument("--tokens", type=int, default=8)
