@@ -359,6 +359,30 @@ def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, s
         ops.lib.ts_set_clusters(1)
 
 
+@pytest.mark.parametrize("B,H,KVH,page", [(1, 12, 2, 16), (8, 12, 2, 16), (4, 28, 4, 64), (3, 5, 5, 32), (2, 16, 1, 48)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_attention_decode_blocks_of_eight_warps(ops, monkeypatch, B, H, KVH, page, window):
+    """Few requests whose keys the rule cuts into 16: the kernel then runs 8 splits of 8 warps, merged as
+    one cluster a (request, kv head) or, where the clusters do not all fit the chip, by the ticket (8 x 2
+    and 4 x 4 pairs here).  Contexts around the edges of its tiles of 128 keys and of its splits, a
+    window, NaN in unwritten rows; against the reference and against the blocks of 4 warps."""
+    monkeypatch.setattr(ops, "decode_splits", lambda *a: 16)
+    lens = [2049, 1, 127, 128, 129, 1023, 1024, 1025, 2500, 5000, 300, 17][:B] if B > 1 else [2049]
+    outs = []
+    try:
+        for wide in (2, 1, 0):
+            ops.lib.ts_set_decode_wide(wide)
+            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, 128, page, [1] * len(lens), [l - 1 for l in lens], 23,
+                                         window=window, tma=False, poison=True)
+            assert torch.isfinite(out).all()
+            torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+            outs.append(out)
+    finally:
+        ops.lib.ts_set_decode_wide(2)
+    torch.testing.assert_close(outs[0], outs[2], atol=4e-3, rtol=8e-3)     # one bfloat16 step
+    torch.testing.assert_close(outs[1], outs[2], atol=4e-3, rtol=8e-3)
+
+
 @pytest.mark.parametrize("H,KVH,D,page", [(12, 2, 128, 16), (14, 2, 64, 32), (16, 1, 128, 64), (9, 3, 64, 64)])
 @pytest.mark.parametrize("nsplit", [1, 2, 3, 4, 8, 16, 24])
 @pytest.mark.parametrize("window", [None, 1, 130])

@@ -25,16 +25,18 @@
 
 namespace {
 
-constexpr int DEC_WARPS = 4;
-constexpr int DEC_TILE = 64;        // keys per pipeline stage
 constexpr int DEC_STAGES = 3;
+// WARPS warps a block, 16 keys of every tile each: 4 (tiles of 64 keys, two blocks an SM), or 8 (tiles of
+// 128 keys, one block an SM) where 8 splits of 8 warps can be one cluster per (request, kv head) and all
+// clusters fit the chip: the same keys per warp as 16 splits of 4 warps, half the partial results, and
+// those merged through the cluster's shared memory instead of scratch, a fence and a ticket.
 constexpr int PAGES_S = 1024;       // block-table entries a block keeps in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Thread-block clusters: the splits of one (request, kv head) are the blocks of one cluster and read
 // each other's merged states from shared memory.
 // CLUSTER: the grid's x dimension (the splits) is one cluster; nsplit is then a power of two <= 16.
-template <int D, bool CLUSTER>
+template <int D, bool CLUSTER, int DEC_WARPS>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
@@ -45,6 +47,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
   // arrays (copied from the host before the step's first kernel) and cache rows of earlier steps.
   // The one row this step writes, the new token's at seq_len - 1, is fetched after the wait.
   pdl_launch_dependents();
+  constexpr int DEC_TILE = 16 * DEC_WARPS;        // keys per pipeline stage
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int KS = D / 16;                      // k-steps of the score product
   constexpr int NT = D / 8;                       // n-tiles of the output
@@ -405,7 +408,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_acc, fl
 
 // How many clusters of `nsplit` blocks of this kernel the device holds at once (asked once per size);
 // 0 when the splits cannot be one cluster (not 2, 4, 8 or 16 of them, or the device refuses).
-template <int D>
+template <int D, int DEC_WARPS>
 int cluster_ok(int nsplit, size_t smem) {
   static int known[5] = {-1, -1, -1, -1, -1};                      // by log2(nsplit)
   if (nsplit < 2 || nsplit > 16 || (nsplit & (nsplit - 1))) return 0;
@@ -413,9 +416,9 @@ int cluster_ok(int nsplit, size_t smem) {
   while ((1 << idx) < nsplit) ++idx;
   if (known[idx] < 0) {
     known[idx] = 0;
-    auto kernel = attention_decode_kernel<D, true>;
-    bool ok = true;
-    if (nsplit > 8)
+    auto kernel = attention_decode_kernel<D, true, DEC_WARPS>;
+    bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+    if (ok && nsplit > 8)
       ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (ok) {
       cudaLaunchConfig_t cfg = {};
@@ -437,37 +440,55 @@ int cluster_ok(int nsplit, size_t smem) {
   return known[idx];
 }
 
-template <int D>
+template <int D, int DEC_WARPS>
 int launch_decode(bf16* out, float* part_acc, float* part_ml, const bf16* qkv, const bf16* k_cache,
                   const bf16* v_cache, const int* block_tables, const int* q_start, const int* seq_lens, int B,
                   int table_width, int H, int KVH, int page, float scale, int window, int nsplit, int* counters,
                   cudaStream_t s) {
+  constexpr int DEC_TILE = 16 * DEC_WARPS;
   const size_t stage_bytes = (size_t)2 * DEC_STAGES * DEC_TILE * D * 2;
   const size_t merge_bytes = sizeof(float) * ((size_t)3 * DEC_WARPS * 16 + 32 + (size_t)(DEC_WARPS + 1) * 16 * D);
   const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false, DEC_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = cudaFuncSetAttribute(attention_decode_kernel<D, true, DEC_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   // Clusters only while all of them fit the chip at once: a launch whose clusters come in two waves
   // loses more than the merge gains (16 clusters of 16 blocks: a step a sixth slower than with the
   // ticket; they fit few places on the chip).  Clusters of 16 only while there are a handful.
-  if (ts_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && B * KVH <= cluster_ok<D>(nsplit, smem))
-    ts_launch_cluster(attention_decode_kernel<D, true>, dim3(nsplit, 1, 1), dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
+  if (ts_clusters_enabled() && (nsplit <= 8 || B * KVH <= 4) && B * KVH <= cluster_ok<D, DEC_WARPS>(nsplit, smem))
+    ts_launch_cluster(attention_decode_kernel<D, true, DEC_WARPS>, dim3(nsplit, 1, 1), dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
         out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
         scale, window, nsplit, counters);
   else
-    ts_launch(attention_decode_kernel<D, false>, dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
+    ts_launch(attention_decode_kernel<D, false, DEC_WARPS>, dim3(nsplit, KVH, B), dim3(DEC_WARPS * 32), smem, s,
         out, part_acc, part_ml, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page,
         scale, window, nsplit, counters);
   TS_LAUNCH_CHECK();
 }
 
 }  // namespace
+
+static int g_wide_blocks = 2;
+// The blocks of 8 warps: 2 = whenever they fit one per SM, 1 = only where they merge as clusters, 0 = never
+// (for measurements).
+TS_API void ts_set_decode_wide(int on) { g_wide_blocks = on; }
+static int ts_num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 1;
+  }
+  return sms;
+}
+
+// How many clusters of 8 blocks of 8 warps (head size 128) the device holds at once: the most (request,
+// kv head) pairs the wide blocks serve.
+TS_API int ts_attention_decode_wide_clusters() { return cluster_ok<128, 8>(8, (size_t)2 * DEC_STAGES * 128 * 128 * 2); }
 
 // Whether this kernel takes the shape (else the caller uses the generic kernel).
 TS_API int ts_attention_decode_supported(int H, int KVH, int D, int dtype) {
@@ -495,10 +516,21 @@ TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const vo
   float* acc = (float*)scratch;
   float* ml = acc ? acc + (size_t)B * H * nsplit * D : nullptr;
   cudaStream_t s = (cudaStream_t)stream;
+  // Few (request, kv head) pairs cut into 16: 8 splits of 8 warps instead (head size 128), one block per
+  // SM: half the partial results to merge for the same keys per warp (1.416 -> 1.394 ms a decode step at
+  // batch 8, 1.333 -> 1.272 ms at batch 4).  Merged as one cluster a pair where all clusters fit the chip
+  // at once (15 on this device), else through scratch and the ticket.
+  if (D == 128 && g_wide_blocks && nsplit == 16) {
+    constexpr size_t wide_smem = (size_t)2 * DEC_STAGES * 128 * 128 * 2;
+    const bool fits = g_wide_blocks == 2 ? B * KVH * 8 <= ts_num_sms() : (ts_clusters_enabled() && B * KVH <= cluster_ok<128, 8>(8, wide_smem));
+    if (fits)
+      return launch_decode<128, 8>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+                                   block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, 8, counters, s);
+  }
   if (D == 64)
-    return launch_decode<64>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+    return launch_decode<64, 4>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
                              block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
-  return launch_decode<128>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+  return launch_decode<128, 4>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
                             block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, nsplit, counters, s);
 }
 

@@ -123,6 +123,12 @@ class CudaOps:
         # tokens), "cp" the one built for the shortest chain, "auto" by the step's streaming_decode
         self.decode_kernel = os.environ.get("TURINGSERVE_B200_DECODE_ATTENTION", "auto")
         self.decode_stages = int(os.environ.get("TURINGSERVE_B200_DECODE_STAGES", "3"))
+        # the "cp" kernel where the rule asks for 16 splits: 8 splits of 8 warps instead.  2: whenever those
+        # blocks fit one per SM (merged as clusters where all clusters fit the chip, else by the ticket);
+        # 1: only as clusters; 0: never
+        self.lib.ts_set_decode_wide.argtypes = [I]
+        self.lib.ts_set_decode_wide.restype = None
+        self.lib.ts_set_decode_wide(int(os.environ.get("TURINGSERVE_B200_DECODE_WIDE", "2")))
         self.lib.ts_linear_tc_qkv_rope_scratch_floats.argtypes = [I, I, I]
         self.lib.ts_linear_tc_qkv_rope_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_sample_greedy_parts.argtypes = [I]
