@@ -110,6 +110,26 @@ def test_schedules_on_the_tensor_core_attention_kernels(tmp_path, monkeypatch, n
     check(got, expected_logits(folder, reqs), "bfloat16")
 
 
+@pytest.mark.parametrize("schedule", ["batched_tail", "decode_tail", "mixed"])
+@pytest.mark.parametrize("graphs", [(), (1, 2, 4)])
+def test_decode_attention_cut_into_sixteen(tmp_path, monkeypatch, schedule, graphs):
+    """What a step of few requests with long contexts runs (the split rule asks for 16 pieces, the kernel
+    then takes 8 pieces of 8 warps and tiles of 128 keys), here forced on the short contexts of the K
+    model so that most pieces hold no key at all and the others end anywhere in a tile: logits at every
+    position against the plain implementation, with and without captured graphs."""
+    from turingserve_b200 import kernels
+    folder = tiny.make_tiny_folder("K", tmp_path)
+    reqs = requests_for("K", folder)
+    steps = getattr(schedules, schedule)(reqs)
+    kernels.use(None)
+    ops = kernels.ops()
+    monkeypatch.setattr(ops, "decode_kernel", "cp")
+    monkeypatch.setattr(ops, "decode_splits", lambda *a: 16)
+    got = replay_in_process(folder, "K", steps, "bfloat16", "auto", fresh_ops=False, graphs=graphs)
+    assert ops.tc_status() == 0
+    check(got, expected_logits(folder, reqs), "bfloat16")
+
+
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16"),
                                         ("K", "bfloat16"), ("L", "bfloat16")])
 @pytest.mark.parametrize("schedule", ["batched_tail", "decode_tail", "mixed"])
