@@ -71,6 +71,15 @@ def test_toy_with_routed_feed_forward_and_its_own_position_encoding_on_cpu(tmp_p
         kernels.use(None)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 0.06)])
+def test_toy_with_routed_feed_forward_and_its_own_position_encoding_on_gpu(tmp_path, dtype, tol):
+    """The same toy through the CUDA kernels: its routed feed-forward and its position encoding are the
+    test's own code between the framework's attention, norm and step function."""
+    kernels.use(None)
+    _run_toy(_toy_folder(tmp_path, toy.TOY_ROUTED), "cuda", dtype, tol, toy.TOY_ROUTED, groups=1, states=1)
+
+
 def test_toy_with_a_third_norm_and_a_model_class_of_its_own_on_cpu(tmp_path):
     """A block arrangement that names a part in a role the built-in one does not have (a third norm,
     with its own checkpoint prefix), and a model class registered with the architecture that scales the
