@@ -35,6 +35,9 @@ sys.path.insert(0, ROOT)
 
 # BASELINE configs[2]: Qwen2.5-1.5B shape
 SHAPES = {
+    "qwen2.5-0.5b": dict(hidden_size=896, intermediate_size=4864, num_layers=24, num_heads=14, num_kv_heads=2,
+                         head_dim=64, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                         tie_word_embeddings=True, max_position_embeddings=32768),
     "qwen2.5-1.5b": dict(hidden_size=1536, intermediate_size=8960, num_layers=28, num_heads=12, num_kv_heads=2,
                          head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                          tie_word_embeddings=True, max_position_embeddings=32768),
@@ -45,7 +48,7 @@ SHAPES = {
                         head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
                         tie_word_embeddings=False, max_position_embeddings=32768),
 }
-SHAPE_NAMES = {"qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B", "qwen2.5-14b": "Qwen2.5-14B"}
+SHAPE_NAMES = {"qwen2.5-0.5b": "Qwen2.5-0.5B", "qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B", "qwen2.5-14b": "Qwen2.5-14B"}
 
 
 def metric_name(a) -> str:

@@ -681,6 +681,31 @@ def test_deferred_product_finished_by_the_norm(ops, M, N, K):
         ops.gemm_mode = DEFAULT_GEMM
 
 
+@pytest.mark.parametrize("H,KVH", [(14, 2), (3, 3), (16, 1)])
+@pytest.mark.parametrize("page,order", [(16, "in_order"), (16, "shuffled"), (32, "runs"), (64, "shuffled"), (48, "shuffled")])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("tile", [64, 128])
+def test_attention_tensor_core_portions_head_64(ops, H, KVH, page, order, window, tile):
+    """The same kernel at head size 64 (one 64-column half per row of Q, K and V; the row's two softmax
+    threads take 32 columns of the output each)."""
+    D = 64
+    ops.use_tc_attention = True
+    ops.lib.ts_set_prefill_tile(tile)
+    try:
+        for q_lens, prefixes in (([300], [0]), ([1, 1, 700, 65, 2, 130], [300, 0, 0, 1000, 77, 129]), ([17, 40], [1000, 3])):
+            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, q_lens, prefixes, 31, window=window, order=order)
+            torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+        if window is None:
+            for needle in (0, 63, 64, 127, 128, 500):
+                out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [9, 130], [891, 770], 32, needle=needle,
+                                             order=order)
+                torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+        assert ops.tc_status() == 0, "a block of the tensor-core attention gave up on a wait"
+    finally:
+        ops.use_tc_attention = True
+        ops.lib.ts_set_prefill_tile(0)
+
+
 @pytest.mark.parametrize("H,KVH", [(12, 2), (28, 4), (5, 5), (40, 2)])
 @pytest.mark.parametrize("page", [16, 32, 64, 128])
 @pytest.mark.parametrize("window", [None, 70])

@@ -38,17 +38,18 @@ using namespace tc;
 
 constexpr int TQ = 128;            // query rows per block = TMEM lanes
 constexpr int UNIT = 64;           // keys per unit of loading: a tile of keys is one or two of them
-constexpr int HD = 128;            // head size
+// HD, the head size, is 64 or 128: one or two halves of 64 columns (128 bytes, a swizzle line) per row.
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int BOX_ROWS = 16;       // keys per TMA box at least: 64, 32 or 16, the largest that divides the page
-constexpr uint32_t Q_BYTES = TQ * HD * 2;                 // 2 halves x [128 rows][128 B]
 // A tile of TK keys (64: two blocks share an SM and hide each other's waits, what a launch of many waves
 // wants; 128: one block per SM whose score products are 128 wide, what a launch of about one wave wants,
 // which is as slow as its longest block: a tcgen05.mma of 16 columns of K costs the tensor pipe about 95
 // cycles whether it is 64 or 128 wide, and the chain of a block is the chain of its products).
-template <int TK>
+template <int TK, int HD>
 struct Tile {
-  static constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;  // 2 halves x [TK keys][128 B]
+  static constexpr int HALVES = HD / 64;
+  static constexpr uint32_t Q_BYTES = TQ * HD * 2;        // halves x [128 rows][128 B]
+  static constexpr uint32_t KV_TILE_BYTES = TK * HD * 2;  // halves x [TK keys][128 B]
   static constexpr uint32_t HALF_K = TK * 128;            // bytes between the two 64-column halves of a K/V tile
   static constexpr uint32_t S_BUF = TK;                   // columns of one S buffer (and, over its first half, P as bf16 pairs)
   static constexpr uint32_t O_COL = 2 * TK;               // O behind the two S buffers
@@ -125,15 +126,16 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 
-template <int TK>
+template <int TK, int HD>
 __global__ void __launch_bounds__(ATT_THREADS, TK == 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
                             const AttnArgs a) {
-  using TL = Tile<TK>;
+  using TL = Tile<TK, HD>;
   constexpr uint32_t KV_TILE_BYTES = TL::KV_TILE_BYTES, HALF_K = TL::HALF_K, S_BUF = TL::S_BUF, O_COL = TL::O_COL,
-                     TMEM_COLS = TL::TMEM_COLS;
-  constexpr int KT = TL::KT;
+                     TMEM_COLS = TL::TMEM_COLS, Q_BYTES = TL::Q_BYTES;
+  constexpr int KT = TL::KT, HALVES = TL::HALVES;
+  constexpr int HC = HD / 2;                                // head columns of a row per softmax thread
   pdl_launch_dependents();
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                               // [2][128][128 B]
@@ -219,14 +221,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   pdl_wait();                                               // q/k/v of this step are written by earlier kernels
 
   // Q rows -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r at c ^ (r & 7))
-  if (tid < 2 * TQ) {                                         // each of a row's two threads one 64-column half
-    const bf16* src = a.qkv + (size_t)(qs + tok) * (a.H + 2 * a.KVH) * HD + (size_t)(kvh * G + g) * HD + hh * 64;
-    uint4 v[8];
+  if (tid < 2 * TQ) {                                         // each of a row's two threads half the head's columns
+    const bf16* src = a.qkv + (size_t)(qs + tok) * (a.H + 2 * a.KVH) * HD + (size_t)(kvh * G + g) * HD + hh * HC;
+    uint4 v[HC / 8];
 #pragma unroll
-    for (int cc = 0; cc < 8; ++cc) v[cc] = row_ok ? *reinterpret_cast<const uint4*>(src + cc * 8) : make_uint4(0u, 0u, 0u, 0u);
+    for (int cc = 0; cc < HC / 8; ++cc) v[cc] = row_ok ? *reinterpret_cast<const uint4*>(src + cc * 8) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int cc = 0; cc < 8; ++cc)
-      *reinterpret_cast<uint4*>(q_s + hh * HALF_Q + lane_row * 128 + ((cc ^ (lane_row & 7)) << 4)) = v[cc];
+    for (int cc = 0; cc < HC / 8; ++cc) {
+      const int c = hh * (HC / 8) + cc;                       // 16-byte piece of the row: half c / 8, piece c % 8 of it
+      *reinterpret_cast<uint4*>(q_s + (c >> 3) * HALF_Q + lane_row * 128 + (((c & 7) ^ (lane_row & 7)) << 4)) = v[cc];
+    }
   }
   fence_async_smem();
   tc_fence_before();
@@ -270,7 +274,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             for (int i = 1; i < 4; ++i) in_a_row = in_a_row && (i >= run || pg[i] == pg[0] + i);
             if (in_a_row) {
 #pragma unroll
-              for (int half = 0; half < 2; ++half) tma_load_run(dst + half * HALF_K, run_map, half * 64, kvh, pg[0], bar);
+              for (int half = 0; half < HALVES; ++half) tma_load_run(dst + half * HALF_K, run_map, half * 64, kvh, pg[0], bar);
               continue;
             }
             // a box is a page here: one 2-D box per page and half head
@@ -279,7 +283,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
               if (i >= run) break;
               const int y = (max(pg[i], 0) * a.KVH + kvh) * a.page;
 #pragma unroll
-              for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + i * a.page * 128, map, half * 64, y, bar);
+              for (int half = 0; half < HALVES; ++half) tma_load_2d(dst + half * HALF_K + i * a.page * 128, map, half * 64, y, bar);
             }
             continue;
           }
@@ -290,7 +294,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             const int pg = lp < a.table_width ? tab_row[lp] : 0;
             const int y = (pg * a.KVH + kvh) * a.page + (j - lp * a.page);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
+            for (int half = 0; half < HALVES; ++half) tma_load_2d(dst + half * HALF_K + bx * box * 128, map, half * 64, y, bar);
           }
         }
       };
@@ -317,7 +321,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   } else if (warp == MMA_WARP) {
     // ================= product issue, one lane =================
     if ((tid & 31) == 0 && n_tiles > 0) {
-      // S(t) = Q . K(t)^T into buffer t & 1: 8 k-steps of 16 columns, 4 per 64-column half
+      // S(t) = Q . K(t)^T into buffer t & 1: HD / 16 k-steps of 16 columns, 4 per 64-column half
       auto issue_s = [&](int t) {
         constexpr uint32_t idesc = instr_desc(TK);
         const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + (t % K_STAGES) * KV_TILE_BYTES);
@@ -461,7 +465,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = hh * 64; c < hh * 64 + 64; c += 32) {
+        for (int c = hh * HC; c < hh * HC + HC; c += 32) {
           uint32_t ov[32];
           tmem_ld32(tmem + lane_addr + O_COL + c, ov);
           tmem_wait_ld();
@@ -498,7 +502,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       bf16* dst = a.out + (size_t)(qs + tok) * a.H * HD + (size_t)(kvh * G + g) * HD;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
-      for (int c = hh * 64; c < hh * 64 + 64; c += 32) {
+      for (int c = hh * HC; c < hh * HC + HC; c += 32) {
         uint32_t ov[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem + lane_addr + O_COL + c, ov);       // the whole warp loads; rows without a query store nothing
@@ -531,7 +535,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 
 // The cache [pages, KVH, page, 128] as a 4-D tensor: boxes of 64 columns x a page's rows x one kv head x
 // `run` pages (128-byte swizzle, zeros outside).  Encoded once per (cache, shape).
-bool run_map(CUtensorMap* out, const void* cache, int num_pages, int KVH, int page, int run) {
+bool run_map(CUtensorMap* out, const void* cache, int num_pages, int KVH, int page, int run, int HD) {
   struct Key {
     const void* p;
     int n, k, g, r;
@@ -540,7 +544,7 @@ bool run_map(CUtensorMap* out, const void* cache, int num_pages, int KVH, int pa
   static std::vector<std::pair<Key, CUtensorMap>> cache_;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
-  const Key key{cache, num_pages, KVH, page, run};
+  const Key key{cache, num_pages, KVH, page, run + 1024 * HD};
   for (auto& e : cache_)
     if (e.first == key) {
       *out = e.second;
@@ -576,7 +580,7 @@ static int g_tile_keys = 0;
 TS_API void ts_set_prefill_tile(int keys) { g_tile_keys = (keys == 64 || keys == 128) ? keys : 0; }
 
 TS_API int ts_attention_prefill_tc_supported(int H, int KVH, int D, int page, int dtype) {
-  return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && D == HD && page >= BOX_ROWS && page % BOX_ROWS == 0;
+  return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && (D == 64 || D == 128) && page >= BOX_ROWS && page % BOX_ROWS == 0;
 }
 
 // 0 when no block ever gave up on a wait (synchronises the device).
@@ -586,6 +590,22 @@ TS_API int ts_attention_prefill_tc_status() {
   if (p != nullptr) cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
   return v;
 }
+
+namespace {
+template <int TK, int HD>
+cudaError_t launch_tiles(dim3 grid, cudaStream_t stream, const CUtensorMap& k_map, const CUtensorMap& v_map,
+                         const CUtensorMap& k_run, const CUtensorMap& v_run, const AttnArgs& a) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<TK, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Tile<TK, HD>::SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return ts_launch(attention_prefill_tc_kernel<TK, HD>, grid, dim3(ATT_THREADS), Tile<TK, HD>::SMEM, stream, k_map, v_map, k_run,
+                   v_run, a);
+}
+}  // namespace
 
 // num_pages: pages in the pool (rows of the cache = num_pages * KVH * page).
 TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cache, const void* v_cache,
@@ -609,22 +629,16 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   // pages shorter than a tile: the maps whose one box is a run of pages (a box may be 256 rows at most)
   const int run = (page < UNIT && box == page) ? UNIT / page : 0;
   CUtensorMap k_run = k_map, v_run = v_map;
-  if (run > 1 && (!run_map(&k_run, k_cache, num_pages, KVH, page, run) || !run_map(&v_run, v_cache, num_pages, KVH, page, run)))
+  if (run > 1 && (!run_map(&k_run, k_cache, num_pages, KVH, page, run, D) || !run_map(&v_run, v_cache, num_pages, KVH, page, run, D)))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_prefill_tc: cuTensorMapEncodeTiled (runs of pages) failed");
   // Two blocks with tiles of 64 keys fit an SM, which is what a launch of several waves wants (8,192
   // tokens: 261 us against 379 us with one).  A launch of about one wave is as slow as its longest block:
   // it gets tiles of 128 keys, one block per SM.
-  static bool configured = false;
   static int sms = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<64>::SMEM);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<128>::SMEM);
-    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_prefill_tc: shared memory %zu: %s", Tile<128>::SMEM, cudaGetErrorString(e));
+  if (sms == 0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      sms = 0;
-    configured = true;
+      sms = 1;
   }
   AttnArgs a;
   a.out = (bf16*)out;
@@ -645,11 +659,13 @@ TS_API int ts_attention_prefill_tc(void* out, const void* qkv, const void* k_cac
   dim3 grid(ceil_div(max_q_len * G, TQ), KVH, B);
   const long long blocks = (long long)grid.x * grid.y * grid.z;
   const bool wide = g_tile_keys == 128 || (g_tile_keys == 0 && blocks * 2 <= (long long)sms * 3);
-  if (wide)
-    ts_launch(attention_prefill_tc_kernel<128>, grid, dim3(ATT_THREADS), Tile<128>::SMEM, (cudaStream_t)stream, k_map, v_map,
-              k_run, v_run, a);
+  cudaError_t e;
+  if (D == 128)
+    e = wide ? launch_tiles<128, 128>(grid, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a)
+             : launch_tiles<64, 128>(grid, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
   else
-    ts_launch(attention_prefill_tc_kernel<64>, grid, dim3(ATT_THREADS), Tile<64>::SMEM, (cudaStream_t)stream, k_map, v_map,
-              k_run, v_run, a);
+    e = wide ? launch_tiles<128, 64>(grid, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a)
+             : launch_tiles<64, 64>(grid, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
+  if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_prefill_tc: %s", cudaGetErrorString(e));
   TS_LAUNCH_CHECK();
 }
