@@ -161,12 +161,15 @@ def test_rope_kv_write(ops, dtype, H, KVH, D, rot, T):
 
 
 @pytest.mark.parametrize("T", [1, 3, 8, 16, 40, 128])
-@pytest.mark.parametrize("H,KVH,K,bias", [(12, 2, 1536, True), (4, 2, 192, True), (5, 1, 200, False), (28, 4, 3584, True)])
-def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, T, H, KVH, K, bias):
-    """The q/k/v product of a few tokens with heads of 128 finishes itself (split sums, bias,
+@pytest.mark.parametrize("H,KVH,K,bias,D", [(12, 2, 1536, True, 128), (4, 2, 192, True, 128), (5, 1, 200, False, 128),
+                                            (28, 4, 3584, True, 128), (14, 2, 896, True, 64), (5, 1, 200, False, 64),
+                                            (3, 3, 320, True, 64)])
+def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, T, H, KVH, K, bias, D):
+    """The q/k/v product of a few tokens with heads of 128 or 64 finishes itself (split sums, bias,
     rotation, cache write in its epilogue): bit for bit what the product followed by the rotary
-    kernel gives, in the q/k/v tensor and in the cache pages."""
-    D, page, pages = 128, 16, 40
+    kernel gives, in the q/k/v tensor and in the cache pages.  With heads of 64 a tile of 128 weight
+    rows is two heads, and an odd number of heads leaves the last tile half empty."""
+    page, pages = 16, 40
     N = (H + 2 * KVH) * D
     x = _rand((T, K), torch.bfloat16, 50, 1.0).cuda()
     w = _rand((N, K), torch.bfloat16, 51, 0.05).cuda()

@@ -35,7 +35,7 @@ struct GemmArgs {
   int out_is_float;
   int gated;              // weights-on-rows only: the tile's rows are 64 gates then 64 ups; out is bf16 [M, N / 2]
   int* status;
-  // weights-on-rows q/k/v product that finishes itself (rope != 0): a tile is one head of 128; every
+  // weights-on-rows q/k/v product that finishes itself (rope != 0): a tile is one head of 128 or two of 64; every
   // block leaves its partial sums in rope_part, the block that comes last for a tile (ticket counter)
   // adds them up in split order, adds the bias, rotates q and k heads and writes q/k/v to `out` and the
   // new keys and values into the cache pages: what ts_rope_kv_write_ex does in a kernel of its own.
@@ -49,6 +49,7 @@ struct GemmArgs {
   bf16* k_cache;
   bf16* v_cache;
   int page, H, KVH;
+  int D = 128;            // head size of the product that finishes itself: 64 or 128
   // weights-on-rows, a few tokens, resid != null: the splits of a tile are one thread-block cluster (or a
   // single block); the sum over them in split order, plus bias, is rounded to bfloat16 and added to
   // `resid` [M, N] in place, rounded again: what the product's epilogue and the next norm's residual add do.
@@ -65,32 +66,51 @@ constexpr size_t gemm_smem_bytes(int BN, int STAGES, int KSUB) {
 // Columns p and p + 64 of token m of a head (q heads, then k, then v), given their sums with the
 // bias: rounded to bfloat16 as a product's epilogue rounds, rotated (q and k), written to the q/k/v
 // tensor and, for k and v, into the cache page of the token's slot.
+// (the pair is columns p and p + D/2 of the head)
 __device__ __forceinline__ void rope_finish(const GemmArgs& args, int head, int p, int m, float x1, float x2) {
+  const int D = args.D, half = D >> 1;
+  if (head >= args.H + 2 * args.KVH) return;         // the second half of a last tile that holds one head of 64
   x1 = round_to<bf16>(x1);
   x2 = round_to<bf16>(x2);
   float o1 = x1, o2 = x2;
   if (head < args.H + args.KVH) {
     const int pos = args.positions[m];
-    const float cs = round_to<bf16>(args.cos_t[(size_t)pos * 64 + p]);
-    const float sn = round_to<bf16>(args.sin_t[(size_t)pos * 64 + p]);
+    const float cs = round_to<bf16>(args.cos_t[(size_t)pos * half + p]);
+    const float sn = round_to<bf16>(args.sin_t[(size_t)pos * half + p]);
     o1 = x1 * cs - x2 * sn;
     o2 = x2 * cs + x1 * sn;
   }
   const bf16 w1 = __float2bfloat16_rn(o1), w2 = __float2bfloat16_rn(o2);
   bf16* qkv = reinterpret_cast<bf16*>(args.out);
-  qkv[(size_t)m * args.N + head * 128 + p] = w1;
-  qkv[(size_t)m * args.N + head * 128 + p + 64] = w2;
+  qkv[(size_t)m * args.N + head * D + p] = w1;
+  qkv[(size_t)m * args.N + head * D + p + half] = w2;
   if (head >= args.H && args.k_cache != nullptr) {
     const int slot = args.slots[m];
     if (slot >= 0) {
-      const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * 128;
+      const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * D;
       const bool is_k = head < args.H + args.KVH;
       bf16* dst = (is_k ? args.k_cache : args.v_cache) + cache_base +
-                  (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * 128;
+                  (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * D;
       dst[p] = w1;
-      dst[p + 64] = w2;
+      dst[p + half] = w2;
     }
   }
+}
+
+// Thread r (0..127) of the finishing stage owns pair r & 63 of its tile, of tokens r >> 6, r >> 6 + 2, ...:
+// the tile's columns c1 and c1 + D/2, which are pair p of head `head`.
+struct RopePair {
+  int head, p, c1, c2;
+};
+__device__ __forceinline__ RopePair rope_pair(const GemmArgs& args, int tile, int r) {
+  const int half = args.D >> 1, q = r & 63;
+  const int in_tile = q / half, p = q - in_tile * half;      // D = 128: head 0 of the tile, p = q
+  RopePair rp;
+  rp.head = tile * (128 / args.D) + in_tile;
+  rp.p = p;
+  rp.c1 = in_tile * args.D + p;
+  rp.c2 = rp.c1 + half;
+  return rp;
 }
 
 template <int BN, int STAGES, bool SWAP, int KSUB>
@@ -268,19 +288,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*last_flag) {
         __threadfence();
-        const int head = blockIdx.x;                           // a tile is a head: q heads, then k, then v
-        const int p = r & 63, tg = r >> 6;                     // the pair (p, p + 64) of tokens tg, tg + 2, ...
+        const RopePair rp = rope_pair(args, blockIdx.x, r);    // tiles hold the q heads, then k, then v
+        const int head = rp.head, p = rp.p, tg = r >> 6;
         const float* base = args.rope_part + (size_t)slot_id * args.splits * BN * 128;
-        const float b1 = args.bias != nullptr ? to_f(args.bias[head * 128 + p]) : 0.f;
-        const float b2 = args.bias != nullptr ? to_f(args.bias[head * 128 + p + 64]) : 0.f;
+        const bool real = head < args.H + 2 * args.KVH;
+        const float b1 = (args.bias != nullptr && real) ? to_f(args.bias[head * args.D + p]) : 0.f;
+        const float b2 = (args.bias != nullptr && real) ? to_f(args.bias[head * args.D + p + (args.D >> 1)]) : 0.f;
         const int tokens = min(BN, args.M - col0);
         for (int tok = tg; tok < tokens; tok += 2) {
           float lo[16], hi[16];
 #pragma unroll
           for (int sp = 0; sp < 16; ++sp)
             if (sp < args.splits) {
-              lo[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + p);
-              hi[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + p + 64);
+              lo[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + rp.c1);
+              hi[sp] = __ldcg(base + ((size_t)sp * BN + tok) * 128 + rp.c2);
             }
           float x1 = 0.f, x2 = 0.f;
 #pragma unroll
@@ -415,18 +436,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     cluster_sync_all();
     if (warp >= 2) {
       const int r = (warp & 3) * 32 + lane;
-      const int head = blockIdx.x, p = r & 63, tg = r >> 6;
+      const RopePair rp = rope_pair(args, blockIdx.x, r);
+      const int head = rp.head, p = rp.p, tg = r >> 6;
       const float* ex = reinterpret_cast<const float*>(a_s);
-      const float b1 = args.bias != nullptr ? to_f(args.bias[head * 128 + p]) : 0.f;
-      const float b2 = args.bias != nullptr ? to_f(args.bias[head * 128 + p + 64]) : 0.f;
+      const bool real = head < args.H + 2 * args.KVH;
+      const float b1 = (args.bias != nullptr && real) ? to_f(args.bias[head * args.D + p]) : 0.f;
+      const float b2 = (args.bias != nullptr && real) ? to_f(args.bias[head * args.D + p + (args.D >> 1)]) : 0.f;
       const int tokens = min(BN, args.M - col0);
       for (int tok = (int)blockIdx.z + tg * args.splits; tok < tokens; tok += 2 * args.splits) {
         float lo[8], hi[8];
 #pragma unroll
         for (int sp = 0; sp < 8; ++sp)
           if (sp < args.splits) {
-            lo[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + p, sp));
-            hi[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + p + 64, sp));
+            lo[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + rp.c1, sp));
+            hi[sp] = ld_peer_f32(peer_shared(ex + tok * 128 + rp.c2, sp));
           }
         float x1 = 0.f, x2 = 0.f;
 #pragma unroll
@@ -687,26 +710,25 @@ TS_API int ts_linear_tc_gated(void* act, const void* x, const void* w, int M, in
   return launch<128, 4, true>(rows_map, cols_map, a, grid, s);
 }
 
-// Floats of scratch for ts_linear_tc_qkv_rope.
-TS_API long long ts_linear_tc_qkv_rope_scratch_floats(int M, int heads, int splits) {
+// Floats of scratch for ts_linear_tc_qkv_rope; `tiles`: 128-row tiles of the product, ceil((H + 2 KVH) * D / 128).
+TS_API long long ts_linear_tc_qkv_rope_scratch_floats(int M, int tiles, int splits) {
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  return (long long)heads * ceil_div(M, bn) * splits * bn * 128;
+  return (long long)tiles * ceil_div(M, bn) * splits * bn * 128;
 }
 
-// qkv[M, (H + 2 KVH) * 128] = x[M, K] . w^T + bias with q and k heads rotated (full-width rotate-half,
-// tables [positions][64] float, rounded to bfloat16 at use) and the new keys and values written into
+// qkv[M, (H + 2 KVH) * D] = x[M, K] . w^T + bias with q and k heads rotated (full-width rotate-half,
+// tables [positions][D / 2] float, rounded to bfloat16 at use) and the new keys and values written into
 // the cache pages (slot < 0: not written; k_cache null: no cache write), all in the product's own
-// epilogue.  Head size 128, at most 128 tokens, up to 16 splits over K.  `scratch` holds
-// ts_linear_tc_qkv_rope_scratch_floats() floats, `counters` one zero int per (head, block of tokens).
+// epilogue.  Head size D = 64 or 128, at most 128 tokens, up to 16 splits over K.  `scratch` holds
+// ts_linear_tc_qkv_rope_scratch_floats() floats, `counters` one zero int per (tile, block of tokens).
 TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const void* bias, void* scratch, int* counters,
                                  const int* positions, const float* cos_t, const float* sin_t, const int* slots,
-                                 void* k_cache, void* v_cache, int M, int H, int KVH, int page, int K, int splits,
+                                 void* k_cache, void* v_cache, int M, int H, int KVH, int D, int page, int K, int splits,
                                  void* stream) {
-
   if (M <= 0) return 0;
-  const int heads = H + 2 * KVH, N = heads * 128;
-  if (M > 128 || H <= 0 || KVH <= 0 || !ts_linear_tc_supported(M, N, K))
-    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: M=%d heads=%d K=%d is not taken by this kernel", M, heads, K);
+  const int heads = H + 2 * KVH, N = heads * D;
+  if (M > 128 || H <= 0 || KVH <= 0 || (D != 64 && D != 128) || !ts_linear_tc_supported(M, N, K))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: M=%d heads=%d D=%d K=%d is not taken by this kernel", M, heads, D, K);
   if (scratch == nullptr || counters == nullptr || positions == nullptr || cos_t == nullptr || sin_t == nullptr)
     TS_REFUSE(TS_ERR_SHAPE, "ts_linear_tc_qkv_rope: scratch, counters, positions and tables are needed");
   if (k_cache != nullptr && (v_cache == nullptr || slots == nullptr || page <= 0))
@@ -741,11 +763,12 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
   a.page = page;
   a.H = H;
   a.KVH = KVH;
+  a.D = D;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap rows_map, cols_map;
   if (!tensor_map(&rows_map, w, N, K, BM) || !tensor_map(&cols_map, x, M, K, bn))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: cuTensorMapEncodeTiled failed");
-  dim3 grid(heads, ceil_div(M, bn), splits);
+  dim3 grid(ceil_div(N, BM), ceil_div(M, bn), splits);
   cudaStream_t s = (cudaStream_t)stream;
   // 2 to 8 splits of a tile as one thread-block cluster: the partial sums cross through shared
   // memory instead of scratch, a fence and a ticket.

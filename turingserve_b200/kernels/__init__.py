@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 6
+    ABI = 7
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -86,7 +86,7 @@ class CudaOps:
             "ts_silu_mul_ex": [P, P, I, I, I, I, P],
             "ts_linear_tc_gated": [P, P, P, I, I, I, P],
             "ts_linear_tc_resid": [P, P, P, P, I, I, I, I, P],
-            "ts_linear_tc_qkv_rope": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+            "ts_linear_tc_qkv_rope": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write_ex": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P, P],
             "ts_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
@@ -333,21 +333,21 @@ class CudaOps:
     def qkv_rope(self, out, x, w, bias, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                  page_size):
         """out[T, (H + 2 KVH) D] = x @ w^T + bias with q and k rotated, and the new keys and values
-        written to the cache: one kernel for a few bfloat16 tokens with heads of 128 rotated over
+        written to the cache: one kernel for a few bfloat16 tokens with heads of 64 or 128 rotated over
         their full width, otherwise the product and then ``rope_kv_write``.  Returns the q/k/v tensor."""
         T, K = x.shape[0], w.shape[1]
         use_tc = self.gemm_mode == "tc" or (self.gemm_mode == "auto" and T <= 128)
-        if (x.dtype == torch.bfloat16 and use_tc and T <= self.fused_qkv_tokens and D == 128 and rotary_dim == D
+        if (x.dtype == torch.bfloat16 and use_tc and T <= self.fused_qkv_tokens and D in (64, 128) and rotary_dim == D
                 and cos is not None and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
                 and self.lib.ts_linear_tc_supported(T, (H + 2 * KVH) * D, K)):
             splits = self.tc_splits(T, (H + 2 * KVH) * D, K)
-            need = self.lib.ts_linear_tc_qkv_rope_scratch_floats(T, H + 2 * KVH, splits)
+            need = self.lib.ts_linear_tc_qkv_rope_scratch_floats(T, -(-(H + 2 * KVH) * D // 128), splits)
             qkv_part = self._buffer("qkv_part", need, torch.float32, x.device, floor=1 << 18)
             qkv_counters = self._buffer("qkv_counters", 4096, torch.int32, x.device, zero=True)
             if (H + 2 * KVH) * -(-T // 16) <= qkv_counters.numel():
                 rc = self.lib.ts_linear_tc_qkv_rope(
                     _ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(qkv_part), _ptr(qkv_counters),
-                    _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), T, H, KVH,
+                    _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), T, H, KVH, D,
                     page_size, K, splits, self._stream())
                 if rc != self.UNSUPPORTED:
                     self._check(rc, "linear_tc_qkv_rope")
