@@ -41,14 +41,21 @@ SHAPES = {
     "qwen2.5-1.5b": dict(hidden_size=1536, intermediate_size=8960, num_layers=28, num_heads=12, num_kv_heads=2,
                          head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                          tie_word_embeddings=True, max_position_embeddings=32768),
+    "qwen2.5-3b": dict(hidden_size=2048, intermediate_size=11008, num_layers=36, num_heads=16, num_kv_heads=2,
+                       head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                       tie_word_embeddings=True, max_position_embeddings=32768),
     "qwen2.5-7b": dict(hidden_size=3584, intermediate_size=18944, num_layers=28, num_heads=28, num_kv_heads=4,
                        head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
                        tie_word_embeddings=False, max_position_embeddings=32768),
     "qwen2.5-14b": dict(hidden_size=5120, intermediate_size=13824, num_layers=48, num_heads=40, num_kv_heads=8,
                         head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
                         tie_word_embeddings=False, max_position_embeddings=32768),
+    "qwen2.5-32b": dict(hidden_size=5120, intermediate_size=27648, num_layers=64, num_heads=40, num_kv_heads=8,
+                        head_dim=128, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-5,
+                        tie_word_embeddings=False, max_position_embeddings=32768),
 }
-SHAPE_NAMES = {"qwen2.5-0.5b": "Qwen2.5-0.5B", "qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-7b": "Qwen2.5-7B", "qwen2.5-14b": "Qwen2.5-14B"}
+SHAPE_NAMES = {"qwen2.5-0.5b": "Qwen2.5-0.5B", "qwen2.5-1.5b": "Qwen2.5-1.5B", "qwen2.5-3b": "Qwen2.5-3B",
+               "qwen2.5-7b": "Qwen2.5-7B", "qwen2.5-14b": "Qwen2.5-14B", "qwen2.5-32b": "Qwen2.5-32B"}
 
 
 def metric_name(a) -> str:
