@@ -362,9 +362,10 @@ def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, s
         ops.lib.ts_set_clusters(1)
 
 
-@pytest.mark.parametrize("B,H,KVH,page", [(1, 12, 2, 16), (8, 12, 2, 16), (4, 28, 4, 64), (3, 5, 5, 32), (2, 16, 1, 48)])
+@pytest.mark.parametrize("B,H,KVH,page,D", [(1, 12, 2, 16, 128), (8, 12, 2, 16, 128), (4, 28, 4, 64, 128), (3, 5, 5, 32, 128),
+                                            (2, 16, 1, 48, 128), (8, 14, 2, 16, 64), (3, 5, 5, 32, 64)])
 @pytest.mark.parametrize("window", [None, 150])
-def test_attention_decode_blocks_of_eight_warps(ops, monkeypatch, B, H, KVH, page, window):
+def test_attention_decode_blocks_of_eight_warps(ops, monkeypatch, B, H, KVH, page, D, window):
     """Few requests whose keys the rule cuts into 16: the kernel then runs 8 splits of 8 warps, merged as
     one cluster a (request, kv head) or, where the clusters do not all fit the chip, by the ticket (8 x 2
     and 4 x 4 pairs here).  Contexts around the edges of its tiles of 128 keys and of its splits, a
@@ -375,7 +376,7 @@ def test_attention_decode_blocks_of_eight_warps(ops, monkeypatch, B, H, KVH, pag
     try:
         for wide in (2, 1, 0):
             ops.lib.ts_set_decode_wide(wide)
-            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, 128, page, [1] * len(lens), [l - 1 for l in lens], 23,
+            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens), [l - 1 for l in lens], 23,
                                          window=window, tma=False, poison=True)
             assert torch.isfinite(out).all()
             torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])

@@ -516,18 +516,21 @@ TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const vo
   float* acc = (float*)scratch;
   float* ml = acc ? acc + (size_t)B * H * nsplit * D : nullptr;
   cudaStream_t s = (cudaStream_t)stream;
-  // Few (request, kv head) pairs cut into 16: 8 splits of 8 warps instead (head size 128), one block per
+  // Few (request, kv head) pairs cut into 16: 8 splits of 8 warps instead, one block per
   // SM: half the partial results to merge for the same keys per warp (1.416 -> 1.394 ms a decode step at
   // batch 8, 1.333 -> 1.272 ms at batch 4; with more pairs and fewer splits the same change measured
   // nothing).  Merged as one cluster a pair where all clusters fit the chip at once (15 on this device),
   // else through scratch and the ticket.
-  if (D == 128 && g_wide_blocks && nsplit == 16) {
-    constexpr size_t wide_smem = (size_t)2 * DEC_STAGES * 128 * 128 * 2;
-    const bool fits = g_wide_blocks == 2 ? B * KVH * 8 <= ts_num_sms()
-                                         : (ts_clusters_enabled() && B * KVH <= cluster_ok<128, 8>(8, wide_smem));
-    if (fits)
+  if (g_wide_blocks && nsplit == 16) {
+    const size_t wide_smem = (size_t)2 * DEC_STAGES * 128 * D * 2;
+    const int clusters = D == 128 ? cluster_ok<128, 8>(8, wide_smem) : cluster_ok<64, 8>(8, wide_smem);
+    const bool fits = g_wide_blocks == 2 ? B * KVH * 8 <= ts_num_sms() : (ts_clusters_enabled() && B * KVH <= clusters);
+    if (fits && D == 128)
       return launch_decode<128, 8>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
                                    block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, 8, counters, s);
+    if (fits)
+      return launch_decode<64, 8>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
+                                  block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, 8, counters, s);
   }
   if (D == 64)
     return launch_decode<64, 4>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
