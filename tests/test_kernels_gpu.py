@@ -537,7 +537,7 @@ def test_linear_tensor_core(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 17, 32])
-@pytest.mark.parametrize("N,K", [(1536, 1536), (1536, 8960), (200, 72), (384, 136), (256, 4096)])
+@pytest.mark.parametrize("N,K", [(1536, 1536), (1536, 8960), (200, 72), (384, 136), (256, 4096), (202, 264)])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_linear_into_residual(ops, M, N, K, with_bias):
     """The few-token product that sums its K splits (a thread-block cluster, or one block) and adds
@@ -570,6 +570,8 @@ def test_linear_into_residual(ops, M, N, K, with_bias):
         # a product of bfloat16 values summed in another order differs in its last bit at most
         torch.testing.assert_close(r1.cpu().float(), want.float(), atol=2e-2, rtol=1.6e-2)
         assert (r1.cpu() == want).float().mean() > 0.9
+        if N % 8:                                    # (the path it replaces wants rows of a multiple of 8)
+            return
         ops.fused_link_tokens = 0                    # the path it replaces
         r2 = resid.cuda()
         d = ops.linear(out, cu(x), cu(w), cu(bias), may_defer=True)

@@ -12,6 +12,7 @@ reference captures the decode forward per batch size, turingserve/runner/cuda_gr
 from __future__ import annotations
 
 import dataclasses
+import gc
 
 import torch
 
@@ -162,8 +163,18 @@ class _DecodeGraph:
             torch.cuda.current_stream().wait_stream(s)
             graph = torch.cuda.CUDAGraph()
             before = getattr(ops, "launches", 0)
-            with torch.cuda.graph(graph):
-                self.logits = r.forward(step)
+            # No garbage collection while the stream captures: a finaliser that gives pinned host memory or
+            # an event back to the driver in the middle of it is a call the capture does not allow, and
+            # the capture is then lost (seen once in a long test session, never alone).
+            was_collecting = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = r.forward(step)
+            finally:
+                if was_collecting:
+                    gc.enable()
             self.kernels_per_replay = getattr(ops, "launches", 0) - before
             self.graph = graph
         self.graph.replay()

@@ -219,9 +219,9 @@ class CudaOps:
 
     # Up to this many tokens the output and down projections add themselves to the residual stream
     # (their K splits summed by a thread-block cluster) and the norm that follows reads the finished
-    # rows: 1.437 -> 1.413 ms a decode step at batch 8, 1.753 -> 1.715 ms at batch 16; at batch 32 the block
-    # that sums token after token loses (1.962 -> 1.987 ms).  0: they leave partial sums for the norm kernel.
-    fused_link_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_LINK_TOKENS", "16"))
+    # rows: 1.437 -> 1.413 ms a decode step at batch 8, 1.753 -> 1.715 ms at batch 16, 1.966 -> 1.908 ms
+    # at batch 32, 2.484 -> 2.402 ms at batch 64.  0: they leave partial sums for the norm kernel.
+    fused_link_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_LINK_TOKENS", "64"))
 
     def _settle(self, x):
         """What the kernels that finish a split-K sum take: a product not yet launched is launched now,
