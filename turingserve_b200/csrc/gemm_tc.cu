@@ -97,6 +97,50 @@ __device__ __forceinline__ void rope_finish(const GemmArgs& args, int head, int 
   }
 }
 
+// The same for four neighbouring pairs p..p+3 (p a multiple of 4) with 16- and 8-byte memory operations.
+__device__ __forceinline__ void rope_finish4(const GemmArgs& args, int head, int p, int m, const float (&x1)[4],
+                                             const float (&x2)[4]) {
+  const int D = args.D, half = D >> 1;
+  if (head >= args.H + 2 * args.KVH) return;
+  float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool rotate = head < args.H + args.KVH;
+  if (rotate) {
+    const int pos = args.positions[m];
+    const float4 c = *reinterpret_cast<const float4*>(args.cos_t + (size_t)pos * half + p);
+    const float4 s4 = *reinterpret_cast<const float4*>(args.sin_t + (size_t)pos * half + p);
+    cs[0] = c.x; cs[1] = c.y; cs[2] = c.z; cs[3] = c.w;
+    sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+  }
+  bf16 w1[4], w2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = round_to<bf16>(x1[i]), b = round_to<bf16>(x2[i]);
+    float o1 = a, o2 = b;
+    if (rotate) {
+      const float c = round_to<bf16>(cs[i]), s1 = round_to<bf16>(sn[i]);
+      o1 = a * c - b * s1;
+      o2 = b * c + a * s1;
+    }
+    w1[i] = __float2bfloat16_rn(o1);
+    w2[i] = __float2bfloat16_rn(o2);
+  }
+  const uint2 v1 = *reinterpret_cast<const uint2*>(w1), v2 = *reinterpret_cast<const uint2*>(w2);
+  bf16* qkv = reinterpret_cast<bf16*>(args.out);
+  *reinterpret_cast<uint2*>(qkv + (size_t)m * args.N + head * D + p) = v1;
+  *reinterpret_cast<uint2*>(qkv + (size_t)m * args.N + head * D + p + half) = v2;
+  if (head >= args.H && args.k_cache != nullptr) {
+    const int slot = args.slots[m];
+    if (slot >= 0) {
+      const size_t cache_base = ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * D;
+      const bool is_k = head < args.H + args.KVH;
+      bf16* dst = (is_k ? args.k_cache : args.v_cache) + cache_base +
+                  (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * D;
+      *reinterpret_cast<uint2*>(dst + p) = v1;
+      *reinterpret_cast<uint2*>(dst + p + half) = v2;
+    }
+  }
+}
+
 // Thread r (0..127) of the finishing stage owns pair r & 63 of its tile, of tokens r >> 6, r >> 6 + 2, ...:
 // the tile's columns c1 and c1 + D/2, which are pair p of head `head`.
 struct RopePair {
@@ -434,7 +478,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     // out of every peer's shared memory, in split order (the sums of the ticket path, bit for bit).
     __syncwarp();
     cluster_sync_all();
-    if (warp >= 2) {
+    if (BN >= 32 && warp >= 2) {
+      // more than 16 tokens: four neighbouring pairs a thread (16 bytes from every peer), eight tokens a pass
+      const int r = (warp & 3) * 32 + lane;
+      const int q4 = (r & 15) * 4, tsub = r >> 4;
+      const int half = args.D >> 1, in_tile = q4 / half, p = q4 - in_tile * half;
+      const int head = (int)blockIdx.x * (128 / args.D) + in_tile;
+      const int c1 = in_tile * args.D + p, c2 = c1 + half;
+      const float* ex = reinterpret_cast<const float*>(a_s);
+      float b1[4] = {0.f, 0.f, 0.f, 0.f}, b2[4] = {0.f, 0.f, 0.f, 0.f};
+      if (args.bias != nullptr && head < args.H + 2 * args.KVH) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          b1[i] = to_f(args.bias[head * args.D + p + i]);
+          b2[i] = to_f(args.bias[head * args.D + p + half + i]);
+        }
+      }
+      const int tokens = min(BN, args.M - col0);
+      for (int tok = (int)blockIdx.z + tsub * args.splits; tok < tokens; tok += 8 * args.splits) {
+        float4 lo[8], hi[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) {
+            lo[sp] = ld_peer_v4(peer_shared(ex + tok * 128 + c1, sp));
+            hi[sp] = ld_peer_v4(peer_shared(ex + tok * 128 + c2, sp));
+          }
+        float x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < args.splits) {
+            x1[0] += lo[sp].x; x1[1] += lo[sp].y; x1[2] += lo[sp].z; x1[3] += lo[sp].w;
+            x2[0] += hi[sp].x; x2[1] += hi[sp].y; x2[2] += hi[sp].z; x2[3] += hi[sp].w;
+          }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          x1[i] += b1[i];
+          x2[i] += b2[i];
+        }
+        rope_finish4(args, head, p, col0 + tok, x1, x2);
+      }
+    } else if (warp >= 2) {
       const int r = (warp & 3) * 32 + lane;
       const RopePair rp = rope_pair(args, blockIdx.x, r);
       const int head = rp.head, p = rp.p, tg = r >> 6;

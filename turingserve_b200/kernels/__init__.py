@@ -327,8 +327,9 @@ class CudaOps:
 
     # up to this many tokens the q/k/v product finishes itself (sum over its splits, bias, rotation,
     # cache write in its own epilogue) instead of leaving that to the rotary kernel (batch 24: 1.93
-    # against 2.09 ms a step, batch 32: 2.01 against 2.15 ms; batch 64: 2.50 against 2.47 ms)
-    fused_qkv_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_QKV_TOKENS", "32"))
+    # against 2.09 ms a step; batch 48: 2.12 against 2.27 ms, batch 64: 2.32 against 2.39 ms since the
+    # block that finishes a token takes four pairs a thread)
+    fused_qkv_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_QKV_TOKENS", "64"))
 
     def qkv_rope(self, out, x, w, bias, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots,
                  page_size):
