@@ -365,6 +365,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
       float* ex = reinterpret_cast<float*>(a_s);               // [64][BN]
       constexpr int CW = BN >= 32 ? 32 : 16;
       if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if constexpr (BN >= 32) {
+        // More than 16 tokens: all four warps leave their rows in shared memory, gates and ups, token-major
+        // ([2][BN][64 rows]: a warp's 32 rows side by side), and then every thread takes one output column
+        // for half of the tokens, so that the activation is spread over 128 threads instead of 64.
+        if (ok) {
+          float* mine = ex + (size_t)(r >> 6) * BN * 64 + (r & 63);
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mine[(c + i) * 64] = __uint_as_float(v[i]);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok) {
+          const int I = args.N / 2;
+          const int row = r & 63, c0 = (r >> 6) * (BN / 2);
+          const int n = (int)blockIdx.x * 64 + row;              // output column
+          bf16* outb = reinterpret_cast<bf16*>(args.out);
+          if (n < I) {
+#pragma unroll 4
+            for (int c = c0; c < c0 + BN / 2; ++c) {
+              const int m = col0 + c;                            // token
+              if (m >= args.M) break;
+              const float g = round_to<bf16>(ex[c * 64 + row]);
+              const float u = round_to<bf16>(ex[(BN + c) * 64 + row]);
+              const float sl = round_to<bf16>(silu_for<bf16>(g));
+              outb[(size_t)m * I + n] = __float2bfloat16_rn(sl * u);
+            }
+          }
+        }
+      } else {
       if (ok && q >= 2) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += CW) {
@@ -412,6 +446,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
             }
           }
         }
+      }
       }
     } else if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -283,8 +283,8 @@ class CudaOps:
 
     GATE_GROUP = 64      # rows of gates, then of ups, in one 128-row tile of the few-token product
     # up to this many tokens the activation goes into the product's epilogue (the kernel takes 128; above
-    # 32 its epilogue, two of four warps doing the activation, costs more than the kernel it saves:
-    # 2.69 against 2.47 ms a step at batch 64, 2.001 against 2.012 ms at batch 32)
+    # 16 tokens all four warps of its epilogue share the activation: 1.739 -> 1.688 ms a step at batch 24,
+    # 1.857 -> 1.805 ms at batch 32; at batch 48 and 64 it is within half a percent of the kernel of its own)
     fused_gate_tokens = int(os.environ.get("TURINGSERVE_B200_FUSED_GATE_TOKENS", "32"))
 
     def gated_linear(self, out, x, w, bias, group: int) -> None:
