@@ -228,8 +228,9 @@ def run_ours(a) -> dict:
     V = kw["vocab_size"]
 
     max_b = max(B, 64)
+    ctx_len = max(ctx_len, a.prefill_tokens + 64, prompt_len + a.steps + max(3, a.warmup) + 64)
     eng = build_engine_on_device(a.model, layers, ctx_len=ctx_len, page=a.kv_block, max_seqs=max_b,
-                                 max_tokens=max(2048, max_b), graph_sizes=(1, 8, 64, B))
+                                 max_tokens=max(2048, max_b, a.prefill_tokens), graph_sizes=(1, 8, 64, B))
     runner, cache = eng.runner, eng.cache
 
     def ev():
