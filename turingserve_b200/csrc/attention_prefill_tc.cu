@@ -13,8 +13,8 @@
 // to TWO threads, thread r of warps 0-3 with the first 32 keys of every tile and thread r of warps 4-7
 // with the last 32 (the chain of a tile, 64 exponentials a row, is what bounds a block, and a pair
 // walks it in half the time); the two exchange their maxima through shared memory once a tile.
-// Warp 8 (one lane) issues the products, warp 9 (one lane) the TMA loads: keys into a ring of
-// three stages, values into a ring of two.  S has two buffers in tensor memory, so the score
+// Warp 8 (one lane) issues the products, warps 9 and 10 (one lane each) the TMA loads: keys into a
+// ring of three stages, values into a ring of two.  S has two buffers in tensor memory, so the score
 // product of tile t+1 runs while the softmax warps work on tile t:
 //   warp 8   : S(t)[128x64] = Q[128x128] . K(t)[64x128]^T      (issued two tiles ahead of P)
 //   warps 0-7: read S(t) from tensor memory, mask, online softmax in 32-bit, write P(t) (bfloat16
@@ -116,8 +116,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int ATT_THREADS = 2 * TQ + 64;  // warps 0-7: two threads per query row; warp 8: product issue; warp 9: TMA
-constexpr int MMA_WARP = 2 * TQ / 32, TMA_WARP = MMA_WARP + 1;
+// warps 0-7: two threads per query row; warp 8: product issue; warp 9: TMA loads of keys; warp 10: of values
+// (one thread each: with pages shorter than a tile in a shuffled pool a tile is up to 16 copies of keys and
+// 16 of values at about 100 cycles of issue each, more than one thread gets through in a tile's time)
+constexpr int ATT_THREADS = 2 * TQ + 96;
+constexpr int MMA_WARP = 2 * TQ / 32, TMA_WARP = MMA_WARP + 1, TMA_V_WARP = MMA_WARP + 2;
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
   asm volatile(
@@ -238,8 +241,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == TMA_WARP) {
-    // ================= producer: TMA loads, one lane =================
+  if (warp == TMA_WARP || warp == TMA_V_WARP) {
+    // ================= producers: TMA loads of keys (one warp) and of values (another), one lane each =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       // The page ids of a tile whose pages are shorter than the tile (2 or 4 of them), kept in registers
       // and read two tiles ahead: a table entry fetched where it is used would put a trip to memory
@@ -298,22 +301,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           }
         }
       };
-      // keys are needed two softmax rounds before the values of the same tile: K(t+1) goes before V(t)
+      // each ring fills as far ahead as its stages allow
       bool ok = true;
+      const bool keys = warp == TMA_WARP;
+      const CUtensorMap* map = keys ? &k_map : &v_map;
+      const CUtensorMap* rmap = keys ? &k_run_map : &v_run_map;
+      unsigned char* ring = keys ? k_s : v_s;
+      uint64_t* full = keys ? full_k : full_v;
+      uint64_t* empty = keys ? empty_k : empty_v;
+      const int stages = keys ? K_STAGES : V_STAGES;
       TilePages cur = pages_of(0), nxt = pages_of(1);
-      load(&k_map, &k_run_map, k_s, &full_k[0], 0, cur);
       for (int t = 0; t < n_tiles && ok; ++t) {
         const TilePages after = pages_of(t + 2);
-        if (t + 1 < n_tiles) {
-          const int sk = (t + 1) % K_STAGES;
-          if (t + 1 >= K_STAGES) ok = mbar_wait(&empty_k[sk], (uint32_t)(((t + 1) / K_STAGES - 1) & 1), a.status, 4, abort_flag);
-          if (!ok) break;
-          load(&k_map, &k_run_map, k_s + sk * KV_TILE_BYTES, &full_k[sk], t + 1, nxt);
-        }
-        const int sv = t % V_STAGES;
-        if (t >= V_STAGES) ok = mbar_wait(&empty_v[sv], (uint32_t)((t / V_STAGES - 1) & 1), a.status, 7, abort_flag);
+        const int st = t % stages;
+        if (t >= stages) ok = mbar_wait(&empty[st], (uint32_t)((t / stages - 1) & 1), a.status, keys ? 4 : 7, abort_flag);
         if (!ok) break;
-        load(&v_map, &v_run_map, v_s + sv * KV_TILE_BYTES, &full_v[sv], t, cur);
+        load(map, rmap, ring + st * KV_TILE_BYTES, &full[st], t, cur);
         cur = nxt;
         nxt = after;
       }
