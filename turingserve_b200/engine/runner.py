@@ -87,7 +87,8 @@ class ModelRunner:
         hidden = self.model.forward(step, self.views, self.cache.states)
         if step.sample_rows.shape[0] == 0:
             return None
-        return self.model.logits(hidden, step.sample_rows)
+        # a captured decode step samples every row in order: no rows to pick out
+        return self.model.logits(hidden, None if step.all_rows_sampled else step.sample_rows)
 
     def _check(self, entries: list[StepEntry]) -> None:
         seen = set()

@@ -77,9 +77,11 @@ class DecoderModel:
         kernels.ops().embedding(h, self.embedding, step.input_ids)
         return h
 
-    def logits(self, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-        """fp32 logits [S, V] of the hidden rows named by ``rows`` (int32 indices on the device)."""
-        out = torch.empty((rows.shape[0], self.cfg.vocab_size), dtype=torch.float32, device=self.device)
+    def logits(self, hidden: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
+        """fp32 logits [S, V] of the hidden rows named by ``rows`` (int32 indices on the device; None: of
+        every row, in order)."""
+        count = hidden.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((count, self.cfg.vocab_size), dtype=torch.float32, device=self.device)
         kernels.ops().linear(out, hidden, self.lm_head, None, rows)
         return self.finish_logits(out)
 
