@@ -110,6 +110,28 @@ def test_schedules_on_the_tensor_core_attention_kernels(tmp_path, monkeypatch, n
     check(got, expected_logits(folder, reqs), "bfloat16")
 
 
+@pytest.mark.parametrize("graphs", [(), (1,)])
+def test_long_context_on_the_kernels_a_long_context_picks(tmp_path, graphs):
+    """One request of 3,900 tokens and a second of 700 on the K model: the prompt attention with several
+    waves of blocks, then decoding where the split rule by itself asks for sixteen pieces (the blocks of
+    8 warps) and, under a captured graph, launch geometry for the longest context; logits of the last 32
+    positions one by one against the plain implementation."""
+    from turingserve_b200 import kernels
+    from turingserve_b200.models.qwen2 import make_config
+    from turingserve_b200.weights import write_random_model
+    folder = str(tmp_path / "long")
+    write_random_model(folder, make_config(hidden_size=192, intermediate_size=320, num_layers=2, num_heads=4, num_kv_heads=2,
+                                           head_dim=128, vocab_size=300, rope_theta=1e6, rms_norm_eps=1e-6,
+                                           tie_word_embeddings=True, max_position_embeddings=4096), seed=9, std=0.03)
+    cfg, _ = plain.read_folder(folder)
+    reqs = {"long": tiny.random_ids(3900, cfg["vocab_size"], 7), "short": tiny.random_ids(700, cfg["vocab_size"], 8)}
+    steps = schedules.decode_tail(reqs)
+    kernels.use(None)
+    got = replay_in_process(folder, "K", steps, "bfloat16", "auto", graphs=graphs)
+    assert kernels.ops().tc_status() == 0
+    check(got, expected_logits(folder, reqs), "bfloat16")
+
+
 @pytest.mark.parametrize("schedule", ["batched_tail", "decode_tail", "mixed"])
 @pytest.mark.parametrize("graphs", [(), (1, 2, 4)])
 def test_decode_attention_cut_into_sixteen(tmp_path, monkeypatch, schedule, graphs):
