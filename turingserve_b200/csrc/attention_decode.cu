@@ -516,21 +516,23 @@ TS_API int ts_attention_decode(void* out, void* scratch, int* counters, const vo
   float* acc = (float*)scratch;
   float* ml = acc ? acc + (size_t)B * H * nsplit * D : nullptr;
   cudaStream_t s = (cudaStream_t)stream;
-  // Few (request, kv head) pairs cut into 16: 8 splits of 8 warps instead, one block per
-  // SM: half the partial results to merge for the same keys per warp (1.416 -> 1.394 ms a decode step at
-  // batch 8, 1.333 -> 1.272 ms at batch 4; with more pairs and fewer splits the same change measured
-  // nothing).  Merged as one cluster a pair where all clusters fit the chip at once (15 on this device),
-  // else through scratch and the ticket.
-  if (g_wide_blocks && nsplit == 16) {
+  // Few (request, kv head) pairs cut into 16 or more: half as many splits of 8 warps instead (as many as
+  // fit one block per SM, at least 8), tiles of 128 keys: half the partial results to merge for the same
+  // keys per warp (1.416 -> 1.394 ms a decode step at batch 8, 1.333 -> 1.272 ms at batch 4).  Merged as
+  // one cluster a pair where the count is 8 and all clusters fit the chip at once (15 on this device), else
+  // through scratch and the ticket.
+  if (g_wide_blocks && nsplit >= 16) {
     const size_t wide_smem = (size_t)2 * DEC_STAGES * 128 * D * 2;
+    int ws = (nsplit + 1) / 2;
+    if (ws > ts_num_sms() / (B * KVH)) ws = ts_num_sms() / (B * KVH);
     const int clusters = D == 128 ? cluster_ok<128, 8>(8, wide_smem) : cluster_ok<64, 8>(8, wide_smem);
-    const bool fits = g_wide_blocks == 2 ? B * KVH * 8 <= ts_num_sms() : (ts_clusters_enabled() && B * KVH <= clusters);
+    const bool fits = ws >= 8 && (g_wide_blocks == 2 || (ws == 8 && ts_clusters_enabled() && B * KVH <= clusters));
     if (fits && D == 128)
       return launch_decode<128, 8>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
-                                   block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, 8, counters, s);
+                                   block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, ws, counters, s);
     if (fits)
       return launch_decode<64, 8>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,
-                                  block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, 8, counters, s);
+                                  block_tables, q_start, seq_lens, B, table_width, H, KVH, page, scale, window, ws, counters, s);
   }
   if (D == 64)
     return launch_decode<64, 4>((bf16*)out, acc, ml, (const bf16*)qkv, (const bf16*)k_cache, (const bf16*)v_cache,

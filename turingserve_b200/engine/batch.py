@@ -70,8 +70,10 @@ class StepInputs:
 
 
 # From about this many keys under the decode rows of a step (requests x longest context), reading them
-# takes longer than the fixed chain of a decode-attention launch.
-STREAMING_DECODE_KEYS = 32768
+# takes longer than the fixed chain of a decode-attention launch, and the kernel built for streaming wins
+# (measured at 12 heads over 2 kv heads of 128: 4 x 16,384 keys 23 against 26 us for the short-chain kernel,
+# 8 x 16,384 keys 38 against 32 us).  The kernels' front adds its own rule for many requests.
+STREAMING_DECODE_KEYS = 98304
 
 
 def streaming_decode(num_decode: int, longest_context: int) -> bool:
