@@ -873,7 +873,9 @@ TS_API long long ts_linear_tc_qkv_rope_scratch_floats(int M, int tiles, int spli
 // qkv[M, (H + 2 KVH) * D] = x[M, K] . w^T + bias with q and k heads rotated (full-width rotate-half,
 // tables [positions][D / 2] float, rounded to bfloat16 at use) and the new keys and values written into
 // the cache pages (slot < 0: not written; k_cache null: no cache write), all in the product's own
-// epilogue.  Head size D = 64 or 128, at most 128 tokens, up to 16 splits over K.  `scratch` holds
+// epilogue.  Head size D = 64 or 128, at most 128 tokens (more than 32 only where the splits of a tile can be
+// one cluster and all clusters fit the chip: the block that comes last for a tile would otherwise sum token
+// after token, which a kernel of its own does faster), up to 16 splits over K.  `scratch` holds
 // ts_linear_tc_qkv_rope_scratch_floats() floats, `counters` one zero int per (tile, block of tokens).
 TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const void* bias, void* scratch, int* counters,
                                  const int* positions, const float* cos_t, const float* sin_t, const int* slots,
@@ -936,6 +938,8 @@ TS_API int ts_linear_tc_qkv_rope(void* qkv, const void* x, const void* w, const 
       a.rope = 2;                                                     \
       return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s, cl); \
     }                                                                 \
+    if (M > 32)                                                       \
+      TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_linear_tc_qkv_rope: %d tokens only with the splits as clusters", M); \
     return launch<__VA_ARGS__>(rows_map, cols_map, a, grid, s);       \
   } while (0)
   if (bn == 16) TS_ROPE_LAUNCH(16, 4, true, 2);
