@@ -255,6 +255,10 @@ class CudaOps:
         if not (residual.dtype == torch.bfloat16 and residual.is_contiguous() and tuple(residual.shape) == (M, N)):
             return False
         splits = min(self.tc_splits(M, N, K), 8)
+        if M <= 16 and M > 4 * splits:
+            # up to 16 tokens a block of the cluster sums its tokens one after the other: with few splits that
+            # are many (0.5B shape, 16 tokens over 3 splits: 1.201 against 1.162 ms a step with the norm kernel)
+            return False
         rc = self.lib.ts_linear_tc_resid(_ptr(residual), _ptr(p.x), _ptr(p.w), _ptr(p.bias), M, N, K, splits, self._stream())
         if rc == self.UNSUPPORTED:
             return False
