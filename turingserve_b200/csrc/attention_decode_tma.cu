@@ -410,6 +410,8 @@ int* dec_status_word() {
   return p;
 }
 
+int g_cluster_max = 8;
+
 template <int D>
 int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t s) {
   const size_t smem = (size_t)a.stages * 2 * TILE * D * 2;
@@ -423,13 +425,18 @@ int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t 
   // Up to 8 splits can be one thread-block cluster per (request, kv head), but only while all clusters
   // fit the chip at once: clusters that come in two waves lose more than the merge gains (batch 24 x
   // 2 kv heads: clusters of 6 25 us, 6 splits with the ticket 21 us, clusters of 4 17 us).  So: the
-  // largest count from the wanted one down to 0.6 of it whose clusters all fit; none: the ticket.
+  // largest count from the wanted one down to 0.6 of it whose clusters all fit (from 0.8 of it down where
+  // more than 8 are wanted); none: the ticket.
   DecArgs b = a;
   b.cluster = 0;
   if (ts_clusters_enabled() && a.nsplit >= 2) {
     static int known[MAX_STAGES + 1][9];                           // 0: not asked, -1: no cluster, else how many fit at once
     const int pairs = B * a.KVH;
-    for (int n = a.nsplit < 8 ? a.nsplit : 8; n >= 2 && 10 * n >= 6 * a.nsplit; --n) {
+    for (int n = a.nsplit < g_cluster_max ? a.nsplit : g_cluster_max; n >= 2 && 10 * n >= 6 * a.nsplit; --n) {
+      // (9 or 10 wanted and clusters of 8 instead lose inside a step: 32 (request, kv head) pairs, 9 wanted:
+      // 1.711 against 1.511 ms a decode step with the ticket; while 12 wanted, clusters of 8: 1.436 against
+      // 1.480 ms, and 6 wanted, clusters of 5: 1.686 against 1.806 ms)
+      if (a.nsplit > 8 && 10 * n > 8 * a.nsplit) continue;
       int& k = known[a.stages][n];
       if (k == 0) {
         k = -1;
@@ -461,6 +468,9 @@ int launch_tma(const CUtensorMap& kv_map, const DecArgs& a, int B, cudaStream_t 
 }
 
 }  // namespace
+
+// The largest cluster the splits of a (request, kv head) may form (2..8; for measurements).
+TS_API void ts_set_decode_tma_cluster_max(int n) { g_cluster_max = n < 1 ? 1 : (n > 8 ? 8 : n); }
 
 // Whether this kernel takes the shape (else the caller uses ts_attention_decode or the generic kernel).
 int* ts_dec_status_word() { return dec_status_word(); }

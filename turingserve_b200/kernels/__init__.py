@@ -123,6 +123,10 @@ class CudaOps:
         # tokens), "cp" the one built for the shortest chain, "auto" by the step's streaming_decode
         self.decode_kernel = os.environ.get("TURINGSERVE_B200_DECODE_ATTENTION", "auto")
         self.decode_stages = int(os.environ.get("TURINGSERVE_B200_DECODE_STAGES", "3"))
+        self.lib.ts_set_decode_tma_cluster_max.argtypes = [I]
+        self.lib.ts_set_decode_tma_cluster_max.restype = None
+        if "TURINGSERVE_B200_DECODE_TMA_CLUSTER" in os.environ:
+            self.lib.ts_set_decode_tma_cluster_max(int(os.environ["TURINGSERVE_B200_DECODE_TMA_CLUSTER"]))
         # the "cp" kernel where the rule asks for 16 splits: 8 splits of 8 warps instead.  2: whenever those
         # blocks fit one per SM (merged as clusters where all clusters fit the chip, else by the ticket);
         # 1: only as clusters; 0: never
