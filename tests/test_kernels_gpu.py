@@ -587,6 +587,99 @@ def test_linear_into_residual(ops, M, N, K, with_bias):
         ops.max_splits, ops.fused_link_tokens = before, cap
 
 
+@pytest.mark.parametrize("width", [0, 256, 192, 128])
+@pytest.mark.parametrize("M,N,K,with_bias", [(256, 256, 64, False), (300, 520, 200, True), (129, 1000, 1536, True),
+                                             (1100, 1536, 904, False), (2048, 2048, 1536, True)])
+def test_linear_on_pairs_of_sms(ops, M, N, K, with_bias, width):
+    """The many-row product whose tiles are computed by two SMs together, at every tile width, with ragged
+    edges in all three sizes: against the formula in 32 bits.  More tiles than pairs of SMs (the last
+    shape at width 128) makes blocks take several tiles, with both accumulators in use."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16() if with_bias else None
+    want = x.float() @ w.float().t()
+    if with_bias:
+        want = want + bias.float()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.lib.ts_set_pair_tile_width(width)
+    try:
+        assert ops.linear_pair(out, x.cuda(), w.cuda(), None if bias is None else bias.cuda(), ops.PAIR_PLAIN)
+    finally:
+        ops.lib.ts_set_pair_tile_width(0)
+    assert ops.tc_status() == 0
+    torch.testing.assert_close(out.cpu().float(), want, atol=3e-2, rtol=1.6e-2)
+    assert (out.cpu() == want.bfloat16()).float().mean() > 0.9, "another order of sums moves the last bit at most"
+
+
+@pytest.mark.parametrize("T,inter,K", [(129, 128, 64), (300, 320, 200), (700, 1280, 1536), (2048, 8960, 1536)])
+def test_gated_linear_on_pairs_of_sms(ops, monkeypatch, T, inter, K):
+    """Gate/up product of many rows with the activation in its epilogue: no product tensor, no activation
+    kernel, and the result of the two steps with the product rounded to bfloat16 in between."""
+    x, w = _rand((T, K), torch.bfloat16, 30, 1.0).cuda(), _rand((2 * inter, K), torch.bfloat16, 31, 0.1).cuda()
+    two = torch.empty((T, inter), dtype=torch.bfloat16, device="cuda")
+    monkeypatch.setattr(ops, "pair_wins", lambda *a: False)
+    ops.gated_linear(two, x, w, None, 64)
+    separate = []
+    monkeypatch.setattr(ops, "pair_wins", lambda *a: True)
+    monkeypatch.setattr(ops, "silu_mul", lambda *a, _f=ops.silu_mul: (separate.append(1), _f(*a))[1])
+    out = torch.full((T, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gated_linear(out, x, w, None, 64)
+    assert not separate
+    assert ops.tc_status() == 0
+    ref = torch.empty((T, inter), dtype=torch.bfloat16)
+    TwinOps().gated_linear(ref, x.cpu(), w.cpu(), None, 64)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=3e-2, rtol=3e-2)
+    # against the library product and the activation kernel: the sums differ in their order only
+    torch.testing.assert_close(out.float(), two.float(), atol=3e-2, rtol=3e-2)
+    assert (out == two).float().mean() > 0.9
+
+
+@pytest.mark.parametrize("T", [65, 300, 1500])
+@pytest.mark.parametrize("H,KVH,K,bias,D", [(12, 2, 1536, True, 128), (5, 1, 200, False, 128), (14, 2, 896, True, 64),
+                                            (3, 3, 320, True, 64), (5, 1, 200, False, 64)])
+def test_qkv_product_on_pairs_of_sms_rotates_and_writes_the_cache(ops, monkeypatch, T, H, KVH, K, bias, D):
+    """The q/k/v product of many rows with bias, rotation and cache write in its epilogue: what the library
+    product followed by the rotary kernel gives, in the q/k/v tensor and in the cache pages (slots of -1 are
+    not written); tiles of 256 columns are two heads of 128 or four of 64, the last tile partly empty."""
+    page, pages = 16, 120
+    N = (H + 2 * KVH) * D
+    x = _rand((T, K), torch.bfloat16, 50, 1.0).cuda()
+    w = _rand((N, K), torch.bfloat16, 51, 0.05).cuda()
+    b = _rand((N,), torch.bfloat16, 52, 0.5).cuda() if bias else None
+    pos = torch.randint(0, 600, (T,), dtype=torch.int32).cuda()
+    cos, sin = (t.cuda() for t in plain.rope_tables(D, 1e6, 600))
+    slots = (torch.randperm(page * (pages - 1))[:T].to(torch.int32) + page)
+    slots[1] = -1
+    slots[T - 1] = -1
+    slots = slots.cuda()
+    kc0, vc0 = _rand((pages, KVH, page, D), torch.bfloat16, 53), _rand((pages, KVH, page, D), torch.bfloat16, 54)
+    got = {}
+    for pairs in (True, False):
+        monkeypatch.setattr(ops, "pair_wins", lambda *a, _p=pairs: _p)
+        kc, vc = kc0.clone().cuda(), vc0.clone().cuda()
+        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        launches = ops.launches
+        q = ops.qkv_rope(out, x, w, b, pos, cos, sin, H, KVH, D, D, kc, vc, slots, page)
+        if pairs:
+            assert ops.launches - launches == 1
+        got[pairs] = (q.clone(), kc, vc)
+    assert ops.tc_status() == 0
+    for a, c in zip(got[True], got[False]):
+        torch.testing.assert_close(a.float(), c.float(), atol=3e-2, rtol=2e-2)
+        assert (a == c).float().mean() > 0.9
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots[slots >= 0].long().cpu()] = False
+    for cache, before in ((got[True][1], kc0), (got[True][2], vc0)):
+        rows = cache.cpu().permute(0, 2, 1, 3).reshape(pages * page, KVH, D)
+        assert torch.equal(rows[untouched], before.permute(0, 2, 1, 3).reshape(pages * page, KVH, D)[untouched])
+    # rotate only (a run that reads another run's cache): no cache write
+    monkeypatch.setattr(ops, "pair_wins", lambda *a: True)
+    out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    q = ops.qkv_rope(out, x, w, b, pos, cos, sin, H, KVH, D, D, None, None, slots, page)
+    assert torch.equal(q, got[True][0])
+
+
 @pytest.mark.parametrize("M", [1, 8, 16])
 @pytest.mark.parametrize("N,K", [(151936, 1536), (75800, 320)])
 def test_linear_tensor_core_output_head(ops, M, N, K):

@@ -16,7 +16,7 @@ void ts_set_error(const char* fmt, ...) {
 TS_API const char* ts_last_error() { return g_error; }
 
 // Compiled-for architecture and ABI version, so the Python side can refuse a stale library.
-TS_API int ts_abi_version() { return 7; }
+TS_API int ts_abi_version() { return 8; }
 
 // Programmatic dependent launch for this library's kernels (on by default).
 static bool g_pdl = true;

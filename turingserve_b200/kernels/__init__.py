@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 7
+    ABI = 8
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -86,6 +86,8 @@ class CudaOps:
             "ts_silu_mul_ex": [P, P, I, I, I, I, P],
             "ts_linear_tc_gated": [P, P, P, I, I, I, P],
             "ts_linear_tc_resid": [P, P, P, P, I, I, I, I, P],
+            "ts_linear_pair": [P, P, P, P, I, I, I, I, P],
+            "ts_linear_pair_qkv": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
             "ts_linear_tc_qkv_rope": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rope_kv_write_ex": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, I, P, P],
@@ -130,6 +132,8 @@ class CudaOps:
         # the "cp" kernel where the rule asks for 16 splits: 8 splits of 8 warps instead.  2: whenever those
         # blocks fit one per SM (merged as clusters where all clusters fit the chip, else by the ticket);
         # 1: only as clusters; 0: never
+        self.lib.ts_set_pair_tile_width.argtypes = [I]
+        self.lib.ts_set_pair_tile_width.restype = None
         self.lib.ts_set_decode_wide.argtypes = [I]
         self.lib.ts_set_decode_wide.restype = None
         self.lib.ts_set_decode_wide(int(os.environ.get("TURINGSERVE_B200_DECODE_WIDE", "2")))
@@ -308,6 +312,10 @@ class CudaOps:
             if rc != self.UNSUPPORTED:
                 self._check(rc, "linear_tc_gated")
                 return
+        if (x.dtype == torch.bfloat16 and bias is None and group == self.GATE_GROUP and T > self.fused_gate_tokens
+                and x.is_contiguous() and self.pair_wins(T, 2 * inter, K, 6.0 * T * inter)
+                and self.linear_pair(out, x, w, None, self.PAIR_GATED)):
+            return
         gu = torch.empty((T, 2 * inter), dtype=x.dtype, device=x.device)
         self.linear(gu, x, w, bias)
         self.silu_mul(out, gu, group)
@@ -361,6 +369,16 @@ class CudaOps:
                 if rc != self.UNSUPPORTED:
                     self._check(rc, "linear_tc_qkv_rope")
                     return out
+        if (T > self.fused_qkv_tokens and x.dtype == torch.bfloat16 and D in (64, 128) and rotary_dim == D
+                and cos is not None and cos.dtype == torch.float32 and x.is_contiguous()
+                and self.pair_wins(T, (H + 2 * KVH) * D, K, 4.0 * T * (H + 2 * KVH) * D)):
+            x = self.materialize(x)
+            rc = self.lib.ts_linear_pair_qkv(
+                _ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(positions), _ptr(cos), _ptr(sin), _ptr(slots),
+                _ptr(k_cache), _ptr(v_cache), T, H, KVH, D, page_size, K, self._stream())
+            if rc != self.UNSUPPORTED:
+                self._check(rc, "linear_pair_qkv")
+                return out
         qkv = self.linear(out, x, w, bias, may_defer=True)
         return self.rope_kv_write(qkv, positions, cos, sin, H, KVH, D, rotary_dim, k_cache, v_cache, slots, page_size)
 
@@ -498,6 +516,36 @@ class CudaOps:
         self._check(self.lib.ts_linear_simt(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows), M, N, K,
                                             _code(x.dtype), _code(out.dtype), self._stream()), "linear")
         return out
+
+    PAIR_PLAIN, PAIR_GATED = 0, 1
+    # The many-row products whose epilogue saves a kernel (gate/up with the activation, q/k/v with rotation and
+    # cache write) run on this library's kernel for pairs of SMs where its schedule is the shorter one; 0: never.
+    pair_gemm = os.environ.get("TURINGSERVE_B200_PAIR_GEMM", "1") != "0"
+
+    def pair_wins(self, M: int, N: int, K: int, saved_bytes: float) -> bool:
+        """Whether the pair kernel's schedule (rounds of 256 x 256 tiles over the pairs of SMs, 0.42 us a
+        64-wide k-block: 79 us measured for 2,048 x 17,920 x 1,536, 353 us for 2,048 x 37,888 x 3,584) is shorter
+        than the library product at 1.35 PFLOP/s followed by a kernel that moves ``saved_bytes`` at 5.5 TB/s
+        (2,048 tokens of the 1.5B shape: 80 + 19 us; 544 tokens of the 14B shape: 113 + 9 us against 147)."""
+        if not (self.pair_gemm and self.gemm_mode in ("auto", "tc")):
+            return False
+        tiles = -(-M // 256) * -(-N // 256)
+        rounds = -(-tiles // max(1, self.num_sms // 2))
+        pair_us = rounds * -(-K // 64) * 0.42 + 3.0
+        library_us = 2.0 * M * N * K / 1.35e9 + 3.0 + saved_bytes / 5.5e6 + 2.0
+        return pair_us < library_us
+
+    def linear_pair(self, out, x, w, bias, epilogue: int) -> bool:
+        """The many-row bfloat16 product on pairs of SMs.  ``epilogue`` PAIR_PLAIN: out[M, N] = x @ w^T + bias;
+        PAIR_GATED: out[M, N / 2] = silu(g) * u, the rows of ``w`` in blocks of 64 gates and their 64 ups.
+        False when the kernel does not take the shape."""
+        M, K = x.shape
+        N = w.shape[0]
+        rc = self.lib.ts_linear_pair(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K, epilogue, self._stream())
+        if rc == self.UNSUPPORTED:
+            return False
+        self._check(rc, "linear_pair")
+        return True
 
     def partial_scratch(self, floats: int, device) -> torch.Tensor:
         """The buffer deferred products leave their partial sums in (one deferred product at a time)."""
