@@ -84,6 +84,11 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Two floats rounded to bfloat16: `lo` in the low half of the word, `hi` in the high half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+}
+
 template <int EPI, int BN>
 __global__ void __launch_bounds__(PAIR_THREADS)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const PairArgs args) {
@@ -133,6 +138,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weights do not depend on the kernel before this one: those of the first stages are on their
+      // way before this block waits for its predecessor; the activations follow after the wait.
+      const int early = pair < tiles ? min(n_kb, PAIR_STAGES) : 0;
+      {
+        const int row_w = (pair / args.tiles_m) * PN + (int)rank * HALF_N;
+        for (int kb = 0; kb < early; ++kb) {
+          if (rank == 0) mbar_expect_tx(&full[kb], 2 * PSTAGE_BYTES);
+          tma_load_2d_pair(b_s + kb * PB_BYTES, &map_w, kb * BK, row_w, peer_shared(&full[kb], 0));
+        }
+      }
       pdl_wait();
       int it = 0;
       bool ok = true;
@@ -146,10 +161,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             ok = false;
             break;
           }
-          if (rank == 0) mbar_expect_tx(&full[s], 2 * PSTAGE_BYTES);
           const uint32_t bar = peer_shared(&full[s], 0);
+          if (it >= early) {
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * PSTAGE_BYTES);
+            tma_load_2d_pair(b_s + s * PB_BYTES, &map_w, kb * BK, row_w, bar);
+          }
           tma_load_2d_pair(a_s + s * PA_BYTES, &map_x, kb * BK, row_x, bar);
-          tma_load_2d_pair(b_s + s * PB_BYTES, &map_w, kb * BK, row_w, bar);
         }
       }
     }
@@ -191,11 +208,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int tile = pair; tile < tiles && ok; tile += pairs, ++t) {
       const int tm = tile % args.tiles_m, tn = tile / args.tiles_m;
       const int b = t & 1;
+      const int row = tm * 2 * PM + (int)rank * PM + q * 32 + lane;
+      // QKV: what the rotation needs of this thread's token is fetched while the products run: position, slot,
+      // and the 32 cosines and sines of this warp's pairs (the same in every head), rounded to bfloat16 as
+      // they are used and packed two to a register.
+      int slot = -1;
+      uint32_t cs_sn[EPI == EPI_QKV ? 32 : 1];
+      if constexpr (EPI == EPI_QKV) {
+        const int half = args.D >> 1, p0 = args.D == 128 ? part * 32 : 0;
+        const int pos = row < args.M ? args.positions[row] : 0;
+        if (row < args.M && args.k_cache != nullptr) slot = args.slots[row];
+        const float4* cs = reinterpret_cast<const float4*>(args.cos_t + (size_t)pos * half + p0);
+        const float4* sn = reinterpret_cast<const float4*>(args.sin_t + (size_t)pos * half + p0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 c = cs[i], n = sn[i];
+          cs_sn[4 * i + 0] = pack_bf16x2(c.x, n.x);
+          cs_sn[4 * i + 1] = pack_bf16x2(c.y, n.y);
+          cs_sn[4 * i + 2] = pack_bf16x2(c.z, n.z);
+          cs_sn[4 * i + 3] = pack_bf16x2(c.w, n.w);
+        }
+      }
       ok = mbar_wait(&acc_full[b], (t >> 1) & 1, args.status, 14, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * 2 * PM + (int)rank * PM + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACC_STRIDE);
       if constexpr (EPI == EPI_GATED) {
         // columns of the pair tile: 64 gates, their 64 ups, the next 64 gates, their 64 ups
@@ -231,8 +268,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // Columns p and p + D/2 of a head are a rotation pair (turingserve/ops/reference.py:31-42); the tile
         // holds 256 / D whole heads, a thread one token's row of them, 32 pairs at a time.
         const int D = args.D, half = D >> 1, heads = args.H + 2 * args.KVH;
-        const int pos = row < args.M ? args.positions[row] : 0;
-        const int slot = (row < args.M && args.k_cache != nullptr) ? args.slots[row] : -1;
 #pragma unroll 1
         for (int j = part; j < 4; j += 2) {
           const int hl = D == 128 ? (j >> 1) : j, p0 = D == 128 ? (j & 1) * 32 : 0;
@@ -252,8 +287,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                    ((size_t)(slot / args.page) * args.KVH * args.page + (size_t)(slot % args.page)) * D +
                    (size_t)(head - args.H - (is_k ? 0 : args.KVH)) * args.page * D + p0;
           }
-          const float* cs = args.cos_t + (size_t)pos * half + p0;
-          const float* sn = args.sin_t + (size_t)pos * half + p0;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             float x1[8], x2[8];
@@ -277,15 +310,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             bf16* w1 = reinterpret_cast<bf16*>(&o1);
             bf16* w2 = reinterpret_cast<bf16*>(&o2);
             if (rotate) {
-              float c[8], n[8];
-              *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs + v * 8);
-              *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + v * 8 + 4);
-              *reinterpret_cast<float4*>(n) = *reinterpret_cast<const float4*>(sn + v * 8);
-              *reinterpret_cast<float4*>(n + 4) = *reinterpret_cast<const float4*>(sn + v * 8 + 4);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float y1 = round_to<bf16>(x1[i]), y2 = round_to<bf16>(x2[i]);
-                const float cc = round_to<bf16>(c[i]), ss = round_to<bf16>(n[i]);
+                const float cc = __uint_as_float(cs_sn[v * 8 + i] << 16), ss = __uint_as_float(cs_sn[v * 8 + i] & 0xffff0000u);
                 w1[i] = from_f<bf16>(y1 * cc - y2 * ss);
                 w2[i] = from_f<bf16>(y2 * cc + y1 * ss);
               }

@@ -369,7 +369,7 @@ class CudaOps:
                 if rc != self.UNSUPPORTED:
                     self._check(rc, "linear_tc_qkv_rope")
                     return out
-        if (T > self.fused_qkv_tokens and x.dtype == torch.bfloat16 and D in (64, 128) and rotary_dim == D
+        if (self.pair_qkv and T > self.fused_qkv_tokens and x.dtype == torch.bfloat16 and D in (64, 128) and rotary_dim == D
                 and cos is not None and cos.dtype == torch.float32 and x.is_contiguous()
                 and self.pair_wins(T, (H + 2 * KVH) * D, K, 4.0 * T * (H + 2 * KVH) * D)):
             x = self.materialize(x)
@@ -520,7 +520,9 @@ class CudaOps:
     PAIR_PLAIN, PAIR_GATED = 0, 1
     # The many-row products whose epilogue saves a kernel (gate/up with the activation, q/k/v with rotation and
     # cache write) run on this library's kernel for pairs of SMs where its schedule is the shorter one; 0: never.
+    # ("gated": the gate/up product only)
     pair_gemm = os.environ.get("TURINGSERVE_B200_PAIR_GEMM", "1") != "0"
+    pair_qkv = os.environ.get("TURINGSERVE_B200_PAIR_GEMM", "1") not in ("0", "gated")
 
     def pair_wins(self, M: int, N: int, K: int, saved_bytes: float) -> bool:
         """Whether the pair kernel's schedule (rounds of 256 x 256 tiles over the pairs of SMs, 0.42 us a
