@@ -5,7 +5,7 @@ launches), and the kernel-by-kernel timeline of one captured decode step.
 
     python profile_kernels.py decode_attention [--model qwen2.5-1.5b] [--batch 8] [--context 2048] [--page 16] [--graph]
     python profile_kernels.py prefill_attention [--tokens 2048] [--prefix 0] [--page 16] [--in-order]
-    python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated|--resid] [--graph]
+    python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated|--resid] [--pair] [--graph]
     python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
     python profile_kernels.py fused_step [--batch 8] [--context 2048] [--layers 4] [--page 16]
 
@@ -137,7 +137,10 @@ def gemm(a) -> None:
     resid = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
 
     def f(i):
-        if a.gated:                                               # block-interleaved gate/up rows, SiLU*mul in the epilogue
+        if a.pair:                                                # the many-row kernel on pairs of SMs, whatever the cost rule says
+            if not ops.linear_pair(act if a.gated else out, x, ws[i % copies], None, ops.PAIR_GATED if a.gated else ops.PAIR_PLAIN):
+                raise SystemExit("the pair kernel does not take this shape")
+        elif a.gated:                                             # block-interleaved gate/up rows, SiLU*mul in the epilogue
             ops.gated_linear(act, x, ws[i % copies], None, 64)
         elif a.resid:                                             # the product adds itself to the residual rows
             p = ops.linear(out, x, ws[i % copies], None, may_defer=True)
@@ -157,7 +160,7 @@ def gemm(a) -> None:
         us = timed(lambda i: g.replay(), 5) / copies
     else:
         us = timed(f, 3 * copies)
-    print(f"gemm {M}x{N}x{K} mode {a.mode}{' gated' if a.gated else ''}{' into the residual' if a.resid else ''}{' (graph)' if a.graph else ''}: {us:.2f} us per launch, "
+    print(f"gemm {M}x{N}x{K} mode {a.mode}{' on pairs of SMs' if a.pair else ''}{' gated' if a.gated else ''}{' into the residual' if a.resid else ''}{' (graph)' if a.graph else ''}: {us:.2f} us per launch, "
           f"{N * K * 2 / us / 1e6:.2f} TB/s of weights, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
 
 
@@ -304,6 +307,7 @@ def main() -> int:
     s.add_argument("--k", type=int, default=1536)
     s.add_argument("--mode", default="auto", choices=["auto", "tc", "library"])
     s.add_argument("--gated", action="store_true", help="gate/up product with the activation in its epilogue")
+    s.add_argument("--pair", action="store_true", help="the many-row kernel whose tiles are computed by two SMs together")
     s.add_argument("--resid", action="store_true", help="the product that sums its splits on chip and adds itself to residual rows")
     s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
     s = sub.add_parser("timeline")
