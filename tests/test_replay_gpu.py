@@ -110,6 +110,32 @@ def test_schedules_on_the_tensor_core_attention_kernels(tmp_path, monkeypatch, n
     check(got, expected_logits(folder, reqs), "bfloat16")
 
 
+@pytest.mark.parametrize("name", ["K", "L"])
+@pytest.mark.parametrize("schedule", ["whole", "portions", "mixed"])
+def test_schedules_with_the_many_row_products_on_pairs_of_sms(tmp_path, monkeypatch, name, schedule):
+    """Steps of more than four tokens with the q/k/v product (bias, rotation and cache write in
+    its epilogue) and the gate/up product (activation in its epilogue) on the kernel for pairs of SMs,
+    which the cost rule would not pick for models this small: heads of 128 and of 64, steps in which
+    single decoded tokens of other requests sit in front of the portion's rows."""
+    from turingserve_b200 import kernels
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = getattr(schedules, schedule)(reqs)
+    kernels.use(None)
+    ops = kernels.ops()
+    monkeypatch.setattr(ops, "pair_wins", lambda *a: True)
+    monkeypatch.setattr(ops, "fused_qkv_tokens", 4)            # every step of more than four tokens takes them
+    monkeypatch.setattr(ops, "fused_gate_tokens", 4)
+    used = []
+    monkeypatch.setattr(ops, "linear_pair", lambda *a, _f=ops.linear_pair: (used.append("gated"), _f(*a))[1])
+    qkv = ops.lib.ts_linear_pair_qkv
+    monkeypatch.setattr(ops.lib, "ts_linear_pair_qkv", lambda *a: (used.append("qkv"), qkv(*a))[1])
+    got = replay_in_process(folder, name, steps, "bfloat16", "auto", fresh_ops=False)
+    assert "qkv" in used and ("gated" in used) == (name == "K"), "a feed-forward width of 272 has no blocks of 64 gates"
+    assert ops.tc_status() == 0
+    check(got, expected_logits(folder, reqs), "bfloat16")
+
+
 @pytest.mark.parametrize("graphs", [(), (1,)])
 def test_long_context_on_the_kernels_a_long_context_picks(tmp_path, graphs):
     """One request of 3,900 tokens and a second of 700 on the K model: the prompt attention with several
