@@ -145,7 +145,7 @@ def make_model(shape: str, layers: int, tmp: str) -> str:
 
 
 def build_engine_on_device(shape: str, layers: int, *, ctx_len: int, page: int, max_seqs: int, max_tokens: int,
-                           graph_sizes: tuple[int, ...], model=None):
+                           graph_sizes: tuple[int, ...], model=None, portion_budget: int | None = None):
     """An engine around a model whose N(0, 0.02) weights are drawn on the device (no checkpoint file:
     the 14B shape would be 30 GB of it); everything else as ``LLMEngine.from_config`` builds it."""
     import torch
@@ -170,10 +170,13 @@ def build_engine_on_device(shape: str, layers: int, *, ctx_len: int, page: int, 
     cfg = EngineConfig(model=f"<random {shape}>", dtype="bfloat16", max_model_len=ctx_len, block_size=page,
                        num_blocks=max_seqs * (-(-ctx_len // page)) + 8, max_num_seqs=max_seqs,
                        max_num_batched_tokens=max_tokens, graph_batch_sizes=graph_sizes, watermark=0.0)
+    if portion_budget is not None:
+        cfg.graph_portion_budget = portion_budget
     cfg.validate(mcfg.max_position_embeddings)
     cache = CacheManager(run_needs(model), page, cfg.num_blocks, max_seqs, torch.bfloat16, device)
-    runner = ModelRunner(model, cache, max(max_tokens, max_seqs), max_seqs, ctx_len, cfg.graph_batch_sizes)
-    sched = Scheduler(cache, max_tokens, max_seqs, 0.0)
+    portions = cfg.graph_portion_sizes() if graph_sizes else ()
+    runner = ModelRunner(model, cache, max(max_tokens, max_seqs), max_seqs, ctx_len, cfg.graph_batch_sizes, portions)
+    sched = Scheduler(cache, max_tokens, max_seqs, 0.0, runner.padded_decodes if portions else None)
     return LLMEngine(cfg, runner, cache, sched, Sampler(device), mcfg.eos_token_ids, ctx_len, mcfg.vocab_size)
 
 
@@ -525,8 +528,9 @@ def run_mixed(a, pk: dict) -> dict:
     layers = kw["num_layers"]
     V = kw["vocab_size"]
     rng = np.random.default_rng(1)
+    # (steps of 32 decoding requests beside a 512-token portion are one captured graph, as in serving)
     eng = build_engine_on_device(shape, layers, ctx_len=ctx_len, page=a.kv_block, max_seqs=nd + 2, max_tokens=nd + chunk,
-                                 graph_sizes=())
+                                 graph_sizes=(nd,))
     runner, cache = eng.runner, eng.cache
     rcs = [cache.admit(f"d{i}") for i in range(nd)]
     for rc in rcs:

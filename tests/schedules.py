@@ -120,6 +120,41 @@ def batched_tail(requests: dict[str, list[int]], tail: int = 24, seed: int = 0, 
     return steps
 
 
+def served(requests: dict[str, list[int]], portion: int = 16, tail: int = 20, max_live: int = 4) -> list[dict]:
+    """As a serving engine cuts its steps: every live request that is past its prompt (all but its last
+    ``tail`` tokens) brings one token and wants its logits; beside them ONE request still in its prompt
+    brings a portion of exactly ``portion`` tokens (its last portion: what is left) and wants the logits
+    of the prompt's last token only.  These are the steps a captured graph of (decoding rows, portion
+    length) serves."""
+    waiting = list(requests.items())
+    live: dict[str, dict] = {}
+    steps = []
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = {"toks": toks, "at": 0, "prompt": max(1, len(toks) - tail)}
+        entries, end = [], []
+        in_prompt = [rid for rid, st in live.items() if st["at"] < st["prompt"]]
+        for rid, st in live.items():
+            if st["at"] >= st["prompt"]:
+                entries.append({"id": rid, "tokens": [st["toks"][st["at"]]], "want": [0]})
+                st["at"] += 1
+        if in_prompt:
+            rid = in_prompt[0]
+            st = live[rid]
+            n = min(portion, st["prompt"] - st["at"])
+            last = st["at"] + n == st["prompt"]
+            entries.append({"id": rid, "tokens": st["toks"][st["at"]:st["at"] + n], "want": [n - 1] if last else []})
+            st["at"] += n
+        for rid, st in live.items():
+            if st["at"] == len(st["toks"]):
+                end.append(rid)
+        for rid in end:
+            del live[rid]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+    return steps
+
+
 def peak_tokens(steps: list[dict], round_to: int = 64) -> int:
     """The most tokens live requests hold at any time, each rounded up to ``round_to``."""
     held: dict[str, int] = {}

@@ -104,6 +104,39 @@ def test_cuda_graphs_and_look_ahead_do_not_change_tokens(tmp_path):
     assert stopped[True][2][0] == base[2][:base[2].index(stop) + 1]
 
 
+@pytest.mark.parametrize("name", ["B", "K"])
+def test_captured_steps_with_a_prompt_portion_do_not_change_tokens(tmp_path, name):
+    """Long prompts arrive while three requests decode: under a budget of 32 tokens the decoding rows are
+    filled up to 4 and the portion beside them is 28 tokens, a step shape that is captured once and
+    replayed (the scheduler counts the padding row against the budget).  The tokens are those of an
+    engine that captures pure-decode steps only, and of one that captures nothing."""
+    from turingserve_b200 import SamplingParams
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    cfg, _ = plain.read_folder(folder)
+    short = [tiny.random_ids(n, cfg["vocab_size"], 70 + n) for n in (5, 9, 3)]
+    long_ = [tiny.random_ids(n, cfg["vocab_size"], 90 + n) for n in (150, 97)]
+    runs = {}
+    for mode in ("portions", "decodes", "none"):
+        eng = engine(folder, "bfloat16", cuda_graphs=mode != "none", graph_batch_sizes=(1, 2, 4), max_num_seqs=6,
+                     max_num_batched_tokens=32, block_size=tiny.page_size(name), max_model_len=250,
+                     graph_portion_budget=1024 if mode == "portions" else 0)
+        for i, p in enumerate(short):
+            eng.add_request(f"s{i}", p, SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True))
+        got, steps = {}, 0
+        while eng.has_unfinished():
+            if steps in (3, 9):
+                eng.add_request(f"l{steps}", long_[steps // 9], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+            for o in eng.step():
+                got.setdefault(o.request_id, []).extend(o.delta_token_ids)
+            steps += 1
+        assert not eng.cache.live
+        shapes = {(size, portion) for size, portion, _ in eng.runner._graphs}
+        assert ((4, 28) in shapes) == (mode == "portions"), shapes
+        runs[mode] = got
+    assert runs["portions"] == runs["decodes"] == runs["none"]
+    assert sorted(len(v) for v in runs["none"].values()) == [8, 8, 60, 60, 60]
+
+
 def test_decode_kernel_choice_switches_inside_a_generation(tmp_path, monkeypatch):
     """The keys under the decode rows grow past the point where the streaming (TMA) decode-attention
     kernel takes over from the short-chain one, in the middle of a generation and with captured
@@ -117,12 +150,13 @@ def test_decode_kernel_choice_switches_inside_a_generation(tmp_path, monkeypatch
     # 4 requests: below the threshold while the longest context is under 150 keys, above from there on
     monkeypatch.setattr(batch, "STREAMING_DECODE_KEYS", 600)
     seen = set()
-    real = runner._DecodeGraph.__init__
+    real = runner._StepGraph.__init__
 
-    def spy(self, r, size, streaming):
-        seen.add((size, streaming))
-        real(self, r, size, streaming)
-    monkeypatch.setattr(runner._DecodeGraph, "__init__", spy)
+    def spy(self, r, size, portion, streaming):
+        if portion == 0:
+            seen.add((size, streaming))
+        real(self, r, size, portion, streaming)
+    monkeypatch.setattr(runner._StepGraph, "__init__", spy)
     kernels.use(None)
     eng = engine(folder, "bfloat16", cuda_graphs=True, graph_batch_sizes=(1, 2, 4), max_num_seqs=4)
     outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)] * 4)

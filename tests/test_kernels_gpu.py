@@ -112,14 +112,15 @@ def test_gated_linear(ops, monkeypatch, dtype, T, inter, K, group):
     monkeypatch.setattr(ops, "silu_mul", lambda *a, _f=ops.silu_mul: (separate.append(1), _f(*a))[1])
     monkeypatch.setattr(ops, "fused_gate_tokens", 128)            # everything the fused kernel takes
     ops.gated_linear(out, x.cuda(), w.cuda(), None, group)
-    fused = dtype == torch.bfloat16 and T <= 128 and group == 64
-    assert (not separate) == fused, "no activation kernel of its own exactly when the fused epilogue applies"
+    # (more tokens than the few-token kernel takes: the kernel for pairs of SMs, where its schedule is the shorter)
+    fused = dtype == torch.bfloat16 and group == 64 and (T <= 128 or ops.pair_wins(T, 2 * inter, K, 6.0 * T * inter))
+    assert (not separate) == fused, "no activation kernel of its own exactly when a fused epilogue applies"
     monkeypatch.undo()
     ref = torch.empty((T, inter), dtype=dtype)
     twin.gated_linear(ref, x, w, None, group)
     tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)       # as test_linear
     torch.testing.assert_close(out.cpu().float(), ref.float(), **tol)
-    if fused and ops.tc_splits(T, 2 * inter, K) == 1:       # same sums, same roundings: the same bits
+    if fused and T <= 128 and ops.tc_splits(T, 2 * inter, K) == 1:       # same sums, same roundings: the same bits
         two = torch.empty((T, inter), dtype=dtype, device="cuda")
         gu = torch.empty((T, 2 * inter), dtype=dtype, device="cuda")
         ops.linear(gu, x.cuda(), w.cuda(), None)
@@ -181,6 +182,7 @@ def test_qkv_product_that_rotates_and_writes_the_cache_itself(ops, monkeypatch, 
         slots[1] = -1
     kc0, vc0 = _rand((pages, KVH, page, D), torch.bfloat16, 53), _rand((pages, KVH, page, D), torch.bfloat16, 54)
     got = {}
+    monkeypatch.setattr(ops, "pair_wins", lambda *a: False)       # (the many-row kernel has a test of its own)
     # fused with its splits as one thread-block cluster (where the split count allows), fused with
     # scratch and a ticket counter, and product and rotary kernel apart
     for fused, clusters in ((True, 1), ("ticket", 0), (False, 1)):

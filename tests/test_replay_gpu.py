@@ -50,14 +50,14 @@ def check(got, expected, dtype):
             assert bad is None, f"first wrong place (request, position, error): {bad}, bound {tol}"
 
 
-def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True, graphs=(), replayer=None):
+def replay_in_process(folder, name, steps, dtype, gemm="library", fresh_ops=True, graphs=(), replayer=None, portions=()):
     from turingserve_b200 import kernels
     from turingserve_b200.engine.replay import Replayer
     if fresh_ops:
         kernels.use(None)
     kernels.ops().gemm_mode = gemm
     rp = Replayer(folder, getattr(torch, dtype), schedules.peak_tokens(steps), "cuda", page_size=tiny.page_size(name),
-                  graph_batch_sizes=graphs)
+                  graph_batch_sizes=graphs, graph_portion_sizes=portions)
     if replayer is not None:
         replayer.append(rp)
     outs = {}
@@ -197,12 +197,36 @@ def test_captured_decode_graphs_give_the_same_logits(tmp_path, monkeypatch, name
     got = replay_in_process(folder, name, steps, dtype, "auto", graphs=(1, 2, 4), replayer=held)
     captured = set(held[0].runner._graphs)
     sizes = {len(s["entries"]) for s in steps if all(len(e["tokens"]) == 1 for e in s["entries"])}
-    assert {sz for sz, _ in captured} >= {1 if 1 in sizes else min(sizes)}, captured
+    assert {sz for sz, _, _ in captured} >= {1 if 1 in sizes else min(sizes)}, captured
     if schedule == "batched_tail":
-        assert 3 in sizes and {sz for sz, _ in captured} >= {1, 2, 4}, (sizes, captured)
-        assert {st for _, st in captured} == {False, True}, captured
+        assert 3 in sizes and {sz for sz, _, _ in captured} >= {1, 2, 4}, (sizes, captured)
+        assert {st for _, _, st in captured} == {False, True}, captured
     assert sum(len(v) for v in got.values()) == sum(len(t) for t in reqs.values())
     check(got, expected_logits(folder, reqs), dtype)
+    assert kernels.ops().tc_status() == 0
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("K", "bfloat16"), ("L", "bfloat16")])
+def test_captured_steps_of_decodes_beside_a_prompt_portion(tmp_path, monkeypatch, name, dtype):
+    """Steps as a serving engine cuts them (decoding requests, filled up to 1, 2 or 4 rows, beside one prompt
+    portion of 16 tokens) replayed from captured graphs, one per (rows, portion length, decode-attention
+    choice); the last, shorter portion of a prompt and the first steps run kernel by kernel.  The logits of
+    every decoded token and of every prompt's last token against the plain implementation: the portions'
+    keys and values, written by replayed graphs, are what the decoded tokens read."""
+    from turingserve_b200 import kernels
+    from turingserve_b200.engine import batch
+    folder = tiny.make_tiny_folder(name, tmp_path)
+    reqs = requests_for(name, folder)
+    steps = schedules.served(reqs, portion=16)
+    monkeypatch.setattr(batch, "STREAMING_DECODE_KEYS", 150)
+    held = []
+    got = replay_in_process(folder, name, steps, dtype, "auto", graphs=(1, 2, 4), replayer=held, portions=(16,))
+    captured = set(held[0].runner._graphs)
+    beside = {sz for sz, p, _ in captured if p == 16}
+    assert len(beside) >= 2 and 4 in beside and any(p == 0 for _, p, _ in captured), captured
+    expected = expected_logits(folder, reqs)
+    assert sum(len(v) for v in got.values()) > sum(min(20, len(t) - 1) for t in reqs.values())
+    check(got, expected, dtype)
     assert kernels.ops().tc_status() == 0
 
 

@@ -266,3 +266,31 @@ def test_a_kernel_fault_ends_the_steps_requests_and_switches_the_kernel_off():
         assert reasons == {"d": "length"} and out["d"] == expected_output([7, 8, 9], 4)
     finally:
         kernels.use(None)
+
+
+@pytest.mark.parametrize("padded", [True, False])
+def test_padding_rows_of_captured_steps_count_against_the_budget(padded):
+    """Where the runner fills decoding requests up to a captured number of rows, those rows come out of the
+    token budget, so that the prompt portion beside them has the budget less a captured size: 3 decoding
+    requests are 4 rows, a budget of 32 leaves 28 for the portion (29 without).  The tokens are the same."""
+    eng = make_fake_engine(num_pages=256, budget=32, max_seqs=8)
+    if padded:
+        eng.scheduler.padded_decodes = lambda n: next((s for s in (1, 2, 4, 8) if s >= n), None)
+    for i in range(3):
+        eng.add_request(f"d{i}", [i + 1, i + 2, i + 3], greedy(40))
+    eng.step()
+    long_prompt = list(range(100))
+    eng.add_request("long", long_prompt, greedy(5))
+    plan = eng.scheduler.schedule()
+    assert plan.num_decode == 3
+    assert [p.num_tokens for p in plan.items] == [1, 1, 1, 28 if padded else 29]
+    out = {}
+    for o in eng._run(plan):
+        out.setdefault(o.request_id, []).extend(o.delta_token_ids)
+    while eng.has_unfinished():
+        for o in eng.step():
+            out.setdefault(o.request_id, []).extend(o.delta_token_ids)
+        check_invariants(eng)
+    assert out["long"] == expected_output(long_prompt, 5)
+    for i in range(3):
+        assert out[f"d{i}"][-1] == expected_output([i + 1, i + 2, i + 3], 40)[-1]

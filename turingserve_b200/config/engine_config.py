@@ -30,6 +30,11 @@ class EngineConfig:
     watermark: float = 0.01
     cuda_graphs: bool = True
     graph_batch_sizes: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128)
+    # Steps of decoding requests beside one prompt portion are captured too where the token budget is
+    # at most this: launched kernel by kernel such a step costs the host about 3 ms whatever its size, more
+    # than the GPU needs for a few hundred tokens.  The portion then has the budget less the (padded)
+    # decoding rows.  0: never.
+    graph_portion_budget: int = 1024
     # launch the next decode step before the host has read the current step's tokens (they are fed
     # back on the device); a request that stops on a token then runs one step in vain
     async_decode: bool = True
@@ -40,6 +45,14 @@ class EngineConfig:
         import torch
 
         return {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.dtype]
+
+    def graph_portion_sizes(self) -> tuple[int, ...]:
+        """Lengths of the prompt portions whose steps are captured: the token budget less each captured
+        number of decoding rows (and less none)."""
+        budget = self.max_num_batched_tokens
+        if not self.cuda_graphs or budget > self.graph_portion_budget:
+            return ()
+        return tuple(sorted({budget - s for s in (0, *self.graph_batch_sizes) if budget - s >= 16}))
 
     def resolve_max_model_len(self, max_position_embeddings: int) -> int:
         if self.max_model_len is None:
@@ -99,6 +112,8 @@ def add_engine_arguments(s: argparse.ArgumentParser) -> None:
     g.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false")
     s.set_defaults(cuda_graphs=d.cuda_graphs)
     s.add_argument("--graph-batch-sizes", default=",".join(map(str, d.graph_batch_sizes)))
+    s.add_argument("--graph-portion-budget", type=int, default=d.graph_portion_budget,
+                   help="token budgets up to this also capture steps of decoding requests beside one prompt portion")
     g2 = s.add_mutually_exclusive_group()
     g2.add_argument("--async-decode", dest="async_decode", action="store_true",
                     help="launch the next decode step before reading this step's tokens")

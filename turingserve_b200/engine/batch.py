@@ -111,13 +111,17 @@ class StepInputBuilder:
 
     def build(self, entries: list[StepEntry], *, fixed_width: int | None = None,
               pad_requests: int = 0, arena: torch.Tensor | None = None) -> StepInputs:
-        """Lay out the step.  ``pad_requests`` appends that many empty decode rows (context 0,
-        slot -1, null pages): used to fill a captured batch size.  ``fixed_width`` forces the
+        """Lay out the step.  ``pad_requests`` puts that many empty decode rows (context 0, slot -1,
+        null pages) behind the single-token requests: used to fill a captured batch size.  ``fixed_width`` forces the
         block-table width; ``arena`` is an alternative device buffer (static addresses)."""
         order = self.order(entries)
-        ents = [entries[i] for i in order]
-        B = len(ents) + pad_requests
-        q_lens = [len(e.tokens) for e in ents] + [1] * pad_requests
+        n_dec = sum(1 for e in entries if len(e.tokens) == 1)
+        # batch order: single-token requests, the padding rows, then the rest
+        order = order[:n_dec] + [None] * pad_requests + order[n_dec:]
+        rows_e = [None if i is None else entries[i] for i in order]
+        ents = [e for e in rows_e if e is not None]
+        B = len(rows_e)
+        q_lens = [1 if e is None else len(e.tokens) for e in rows_e]
         T = sum(q_lens)
         if B > self.max_requests:
             raise ValueError(f"step has {B} requests, the engine was sized for {self.max_requests}")
@@ -125,13 +129,8 @@ class StepInputBuilder:
             raise ValueError(f"step has {T} tokens, the engine was sized for {self.max_tokens}")
         if T == 0:
             raise ValueError("empty step")
-        starts = [e.cache.num_tokens for e in ents] + [0] * pad_requests
-        num_decode = 0
-        for e in ents:
-            if len(e.tokens) == 1:
-                num_decode += 1
-        if len(ents) == num_decode:
-            num_decode += pad_requests
+        starts = [0 if e is None else e.cache.num_tokens for e in rows_e]
+        num_decode = n_dec + pad_requests
         ps = self.cache.page_size
         widths = []
         for gi in range(len(self.cache.groups)):
@@ -145,9 +144,10 @@ class StepInputBuilder:
         # caller-order sample rows
         row_of = {}
         off = 0
-        for i, e in zip(order, ents):
-            row_of[i] = off
-            off += len(e.tokens)
+        for i, n in zip(order, q_lens):
+            if i is not None:
+                row_of[i] = off
+            off += n
         sample = []
         for i, e in enumerate(entries):
             for w_ in e.want:
@@ -174,7 +174,7 @@ class StepInputBuilder:
         static = arena is not None
         o_ids, o_pos, o_req = take(T), take(T), take(T)
         o_qs, o_sl, o_ss, o_sr = take(B + 1), take(B), take(B), take(T if static else max(S, 1))
-        fb = [(b, e.feedback) for b, e in enumerate(ents) if e.feedback is not None]
+        fb = [(b, e.feedback) for b, e in enumerate(rows_e) if e is not None and e.feedback is not None]
         F = len(fb)
         o_fr, o_fs = take(B if static else max(F, 1)), take(B if static else max(F, 1))
         o_slot = [take(T) for _ in widths]
@@ -191,7 +191,16 @@ class StepInputBuilder:
         ss = host[o_ss:o_ss + B]
         qs[0] = 0
         t = 0
-        for b, e in enumerate(ents):
+        for b, e in enumerate(rows_e):
+            if e is None:                           # a padding row: no context, nothing written
+                ids[t] = 0
+                pos[t] = 0
+                req[t] = b
+                t += 1
+                qs[b + 1] = t
+                sl[b] = 0
+                ss[b] = self.cache.null_slot
+                continue
             n = len(e.tokens)
             ids[t:t + n] = e.tokens
             pos[t:t + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
@@ -200,14 +209,6 @@ class StepInputBuilder:
             qs[b + 1] = t
             sl[b] = starts[b] + n
             ss[b] = e.cache.slot
-        for b in range(len(ents), B):
-            ids[t] = 0
-            pos[t] = 0
-            req[t] = b
-            t += 1
-            qs[b + 1] = t
-            sl[b] = 0
-            ss[b] = self.cache.null_slot
         host[o_sr:o_sr + S] = sample
         for i, (b, src) in enumerate(fb):
             if q_lens[b] != 1:
@@ -220,7 +221,11 @@ class StepInputBuilder:
             bt[:] = 0
             sm = host[o_slot[gi]:o_slot[gi] + T]
             t = 0
-            for b, e in enumerate(ents):
+            for b, e in enumerate(rows_e):
+                if e is None:
+                    sm[t] = -1
+                    t += 1
+                    continue
                 table = e.cache.tables[gi]
                 bt[b, :len(table)] = table
                 n = len(e.tokens)
@@ -228,7 +233,6 @@ class StepInputBuilder:
                 tab = np.asarray(table, dtype=np.int32)
                 sm[t:t + n] = tab[p // ps] * ps + p % ps
                 t += n
-            sm[t:T] = -1
 
         dev = self._dev if arena is None else arena
         dev[:used].copy_(host_t[:used], non_blocking=True)

@@ -112,8 +112,9 @@ class LLMEngine:
         cache = CacheManager(needs, cfg.block_size, num_pages, cfg.max_num_seqs, cfg.torch_dtype, device)
         runner = ModelRunner(model, cache, max(cfg.max_num_batched_tokens, cfg.max_num_seqs),
                              cfg.max_num_seqs, max_len,
-                             cfg.graph_batch_sizes if cfg.cuda_graphs else ())
-        scheduler = Scheduler(cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, cfg.watermark)
+                             cfg.graph_batch_sizes if cfg.cuda_graphs else (), cfg.graph_portion_sizes())
+        scheduler = Scheduler(cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, cfg.watermark,
+                              runner.padded_decodes if cfg.graph_portion_sizes() else None)
         return cls(cfg, runner, cache, scheduler, Sampler(device), mcfg.eos_token_ids, max_len, mcfg.vocab_size)
 
     # -- requests -----------------------------------------------------------------------------------

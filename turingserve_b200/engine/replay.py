@@ -32,9 +32,11 @@ ROUND_TO = 64
 class Replayer:
     def __init__(self, model_dir: str, dtype: torch.dtype, max_tokens: int, device,
                  page_size: int = 64, max_step_tokens: int | None = None,
-                 graph_batch_sizes: tuple[int, ...] = ()) -> None:
+                 graph_batch_sizes: tuple[int, ...] = (), graph_portion_sizes: tuple[int, ...] = ()) -> None:
         """``graph_batch_sizes``: steps made of single tokens whose logits are wanted replay a captured
-        CUDA graph of the smallest of these sizes that holds them, as generation does; empty: none."""
+        CUDA graph of the smallest of these sizes that holds them, as generation does; empty: none.
+        ``graph_portion_sizes``: so do steps of such tokens beside one prompt portion of one of these lengths
+        of which the last logits, or none, are wanted."""
         if ROUND_TO % page_size:
             raise ValueError(f"page size {page_size} must divide {ROUND_TO}")
         self.model, self.cfg = load_model(model_dir, dtype, device)
@@ -44,7 +46,7 @@ class Replayer:
         self.cache = CacheManager(needs, page_size, num_pages, MAX_LIVE, dtype, device)
         max_len = min(self.cfg.max_position_embeddings, max_tokens)
         self.runner = ModelRunner(self.model, self.cache, max_step_tokens or max_tokens, MAX_LIVE, max_len,
-                                  tuple(s for s in graph_batch_sizes if s <= MAX_LIVE))
+                                  tuple(s for s in graph_batch_sizes if s <= MAX_LIVE), tuple(graph_portion_sizes))
         self.live: dict[str, object] = {}
 
     def step(self, record: dict) -> np.ndarray | None:

@@ -6,7 +6,9 @@ decoded tokens (turingserve/runner/model_runner.py:20-32; design in docs/ARCHITE
 the reference).  It runs only the tokens it is given; everything earlier comes from the cache.
 
 Pure-decode steps whose request count fits a captured size are replayed from a CUDA graph (the
-reference captures the decode forward per batch size, turingserve/runner/cuda_graphs.py:44-78).
+reference captures the decode forward per batch size, turingserve/runner/cuda_graphs.py:44-78).  So
+are steps of decoding requests beside ONE prompt portion of a captured length (``graph_portion_sizes``):
+launched kernel by kernel, a step of a few hundred tokens costs the host more time than the GPU.
 """
 
 from __future__ import annotations
@@ -35,17 +37,21 @@ class ModelRunner:
     supports_feedback = True            # entries may take their token id from the previous sampler output
 
     def __init__(self, model: DecoderModel, cache: CacheManager, max_tokens: int, max_requests: int,
-                 max_model_len: int, graph_batch_sizes: tuple[int, ...] = ()) -> None:
+                 max_model_len: int, graph_batch_sizes: tuple[int, ...] = (),
+                 graph_portion_sizes: tuple[int, ...] = ()) -> None:
         self.model, self.cache = model, cache
         self.max_model_len = max_model_len
         self.max_pages = -(-max_model_len // cache.page_size)
-        self.builder = StepInputBuilder(cache, max_tokens, max_requests, self.max_pages, model.device)
+        # (rows of a captured step: the decoding requests filled up to a captured size, and the portion's)
+        rows = max_requests + (1 if graph_portion_sizes else 0)
+        self.builder = StepInputBuilder(cache, max_tokens, rows, self.max_pages, model.device)
         self.views = cache.views()
         self.graph_batch_sizes = tuple(sorted(graph_batch_sizes))
+        self.graph_portion_sizes = frozenset(graph_portion_sizes)
         # a step of a few single tokens as ONE kernel, where the model's parts are the ones it is written for
         from turingserve_b200.parts.fused_decode import FusedDecodeStep
         self.fused = FusedDecodeStep.try_build(model, self.views) if hasattr(model, "blocks") else None
-        self._graphs: dict[tuple[int, bool], _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int, bool], _StepGraph] = {}
 
     # -- the step ---------------------------------------------------------------------------------
     def step(self, entries: list[StepEntry], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
@@ -58,9 +64,9 @@ class ModelRunner:
             raise ValueError("entries with device feedback need the previous step's tokens")
         for e in entries:
             self.cache.grow(e.cache, len(e.tokens))
-        graph_size = self._graph_size(entries)
-        if graph_size is not None:
-            logits = self._replay(graph_size, entries, prev_tokens)
+        shape = self._graph_shape(entries)
+        if shape is not None:
+            logits = self._replay(shape, entries, prev_tokens)
         else:
             step = self.builder.build(entries)
             self._feed(step, prev_tokens)
@@ -107,50 +113,90 @@ class ModelRunner:
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.cache.request_id!r}: token id outside [0, {vocab})")
 
-    # -- CUDA graphs for pure-decode steps ----------------------------------------------------------
-    def _graph_size(self, entries: list[StepEntry]) -> int | None:
-        if not self.graph_batch_sizes:
-            return None
-        n = len(entries)
-        if any(len(e.tokens) != 1 or e.want != [0] for e in entries):
-            return None
+    # -- CUDA graphs -------------------------------------------------------------------------------
+    def padded_decodes(self, n: int) -> int | None:
+        """The captured batch size that ``n`` decoding requests are filled up to (None: none takes them)."""
+        if n == 0:
+            return 0
         for s in self.graph_batch_sizes:
             if s >= n:
                 return s
         return None
 
-    def _replay(self, size: int, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
+    def _graph_shape(self, entries: list[StepEntry]) -> tuple[int, int] | None:
+        """(decode rows after padding, tokens of the one prompt portion or 0) when the step is one that
+        graphs are kept for: single tokens whose logits are wanted, and at most one portion of a captured
+        length whose last logits, or none, are wanted."""
+        if not self.graph_batch_sizes:
+            return None
+        n_dec, portion = 0, 0
+        for e in entries:
+            n = len(e.tokens)
+            if n == 1 and e.want == [0]:
+                n_dec += 1
+            elif (n > 1 and portion == 0 and n in self.graph_portion_sizes and e.feedback is None
+                    and (not e.want or e.want == [n - 1])):
+                portion = n
+            else:
+                return None
+        size = self.padded_decodes(n_dec)
+        if size is None or size + (1 if portion else 0) > self.builder.max_requests or size + portion > self.builder.max_tokens:
+            return None
+        return size, portion
+
+    def _replay(self, shape: tuple[int, int], entries: list[StepEntry], prev_tokens=None) -> torch.Tensor | None:
         # which attention kernel the decode rows get is part of what a graph captures
-        streaming = streaming_decode(len(entries), max(e.cache.num_tokens for e in entries) + 1)
-        g = self._graphs.get((size, streaming))
+        decodes = [e for e in entries if len(e.tokens) == 1]
+        streaming = bool(decodes) and streaming_decode(len(decodes), max(e.cache.num_tokens for e in decodes) + 1)
+        key = (*shape, streaming)
+        g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[(size, streaming)] = _DecodeGraph(self, size, streaming)
+            g = self._graphs[key] = _StepGraph(self, shape[0], shape[1], streaming)
         return g.run(entries, prev_tokens)
 
 
-class _DecodeGraph:
-    """One captured decode step for ``size`` requests and one choice of decode-attention kernel:
-    static input arena, static logits."""
+class _StepGraph:
+    """One captured step for ``size`` single-token requests (fewer are filled up with empty rows) and, when
+    ``portion`` is not 0, one prompt portion of that many tokens behind them, with one choice of
+    decode-attention kernel: static input arena, static logits (a row per single-token request in batch
+    order, then the portion's last row)."""
 
-    def __init__(self, runner: ModelRunner, size: int, streaming: bool) -> None:
-        self.runner, self.size, self.streaming = runner, size, streaming
+    def __init__(self, runner: ModelRunner, size: int, portion: int, streaming: bool) -> None:
+        self.runner, self.size, self.portion, self.streaming = runner, size, portion, streaming
         b = runner.builder
-        self.arena = torch.zeros(b.capacity, dtype=torch.int32, device=runner.model.device)
+        dev = runner.model.device
+        self.arena = torch.zeros(b.capacity, dtype=torch.int32, device=dev)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         # in a captured decode step every row is sampled: row b of the logits is request b
-        self.rows = torch.arange(size, dtype=torch.int32, device=runner.model.device)
+        rows = list(range(size)) + ([size + portion - 1] if portion else [])
+        self.rows = torch.tensor(rows, dtype=torch.int32, device=dev)
         self.kernels_per_replay = 0
 
     def _build(self, entries: list[StepEntry]) -> StepInputs:
         r = self.runner
-        step = r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - len(entries),
-                               arena=self.arena)
+        n_dec = sum(1 for e in entries if len(e.tokens) == 1)
+        step = r.builder.build(entries, fixed_width=r.max_pages, pad_requests=self.size - n_dec, arena=self.arena)
         # launch geometry must not depend on this step's lengths: size it for the longest context
         return dataclasses.replace(step, sample_rows=self.rows, max_seq_len=r.max_model_len,
-                                   streaming_decode=self.streaming, all_rows_sampled=True)
+                                   streaming_decode=self.streaming, all_rows_sampled=self.portion == 0)
 
-    def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor:
+    def _wanted(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """The caller's rows (order of ``entries`` and of their ``want``) out of the static logits."""
+        idx, n_dec = [], 0
+        for e in entries:
+            if len(e.tokens) == 1:
+                idx.append(n_dec)                   # single-token requests keep the caller's order among themselves
+                n_dec += 1
+            elif e.want:
+                idx.append(self.size)
+        if not idx:
+            return None
+        if idx == list(range(len(idx))):
+            return self.logits[:len(idx)]
+        return self.logits[torch.tensor(idx, dtype=torch.long, device=self.logits.device)]
+
+    def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor | None:
         step = self._build(entries)
         self.runner._feed(step, prev_tokens)
         ops = kernels.ops()
@@ -181,5 +227,4 @@ class _DecodeGraph:
         self.graph.replay()
         if hasattr(ops, "launches"):
             ops.launches += self.kernels_per_replay
-        # rows are in batch order (decodes first = caller order for pure decode)
-        return self.logits[:len(entries)]
+        return self._wanted(entries)

@@ -77,8 +77,12 @@ class _Draft:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_num_batched_tokens: int, max_num_seqs: int,
-                 watermark: float = 0.01) -> None:
+                 watermark: float = 0.01, padded_decodes=None) -> None:
+        """``padded_decodes``: n -> the number of rows the runner fills n decoding requests up to (None: it
+        does not); those rows count against the token budget, so that a prompt portion beside them has one
+        of a few lengths and the step one of a few captured shapes."""
         self.cache = cache
+        self.padded_decodes = padded_decodes
         self.max_num_batched_tokens = max_num_batched_tokens
         self.max_num_seqs = min(max_num_seqs, cache.max_requests)
         smallest_pool = min((g.allocator.num_usable for g in cache.groups), default=0)
@@ -136,6 +140,10 @@ class Scheduler:
     def schedule(self) -> StepPlan:
         draft = _Draft(self.max_num_batched_tokens)
         self._take_decodes(draft)
+        if self.padded_decodes is not None and draft.decodes:
+            rows = self.padded_decodes(len(draft.decodes))
+            if rows is not None:
+                draft.budget = max(0, draft.budget - (rows - len(draft.decodes)))
         self._take_running_prompts(draft)
         if not draft.evicted:
             self._admit(draft)
