@@ -194,6 +194,10 @@ class _StepGraph:
             return None
         if idx == list(range(len(idx))):
             return self.logits[:len(idx)]
+        if idx[:-1] == list(range(len(idx) - 1)) and idx[-1] == self.size:
+            # the single tokens first, then the portion, as a scheduler orders them: two slices, no index
+            # tensor (made on the host, it would be a copy from pageable memory, which waits for the stream)
+            return torch.cat([self.logits[:len(idx) - 1], self.logits[self.size:self.size + 1]])
         return self.logits[torch.tensor(idx, dtype=torch.long, device=self.logits.device)]
 
     def run(self, entries: list[StepEntry], prev_tokens=None) -> torch.Tensor | None:
