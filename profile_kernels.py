@@ -5,6 +5,7 @@ launches), and the kernel-by-kernel timeline of one captured decode step.
 
     python profile_kernels.py decode_attention [--model qwen2.5-1.5b] [--batch 8] [--context 2048] [--page 16] [--graph]
     python profile_kernels.py prefill_attention [--tokens 2048] [--prefix 0] [--page 16] [--in-order]
+    python profile_kernels.py timeline --prefill 2048
     python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated|--resid] [--pair] [--graph]
     python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
     python profile_kernels.py fused_step [--batch 8] [--context 2048] [--layers 4] [--page 16]
@@ -180,6 +181,8 @@ def timeline(a) -> None:
     from turingserve_b200.models.qwen2 import make_config
     from turingserve_b200.weights.random_init import write_random_model
 
+    if a.prefill:
+        return prefill_timeline(a)
     B, ctx = a.batch, a.context
     with tempfile.TemporaryDirectory() as tmp:
         kw = dict(SHAPE)
@@ -230,6 +233,55 @@ def timeline(a) -> None:
     per_layer = (len(step) - 10) // max(a.layers or LAYERS, 1)
     for r in rows[3 + per_layer: 3 + 2 * per_layer]:
         print(f"  {r[0]:8.2f} {r[1]:8.2f}  +{r[2]:5.2f}  {r[3]}")
+
+
+def prefill_timeline(a) -> None:
+    """One prompt of ``--prefill`` tokens in one step, launched kernel by kernel: the duration of every
+    kernel (CUPTI through torch.profiler), summed per kernel, and the layers' share of the step.  The
+    profiler slows the host, so the step's own time comes from CUDA events without it."""
+    import collections
+    import re
+
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+
+    import bench
+    from turingserve_b200.engine.batch import StepEntry
+
+    T, L = a.prefill, a.layers or LAYERS
+    eng = bench.build_engine_on_device(a.model, L, ctx_len=T + 64, page=a.page, max_seqs=8, max_tokens=T, graph_sizes=())
+    runner, cache = eng.runner, eng.cache
+    toks = np.random.default_rng(0).integers(0, SHAPE["vocab_size"], size=T).tolist()
+
+    def once(i=0):
+        rc = cache.admit("p")
+        runner.step([StepEntry(rc, toks, [T - 1])])
+        cache.release(rc)
+
+    for _ in range(4):
+        once()
+    us = timed(once, 5)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        once()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+
+    def short(name: str) -> str:
+        m = re.search(r"(gemm_pair_kernel<[^>]*>|gemm_tc_kernel<[^>]*>|attention_\w+_kernel|rope_kv_write\w*|rmsnorm\w*|"
+                      r"silu_mul\w*|embedding_kernel|gather_rows_kernel|Memcpy \w+|nvjet\w*)", name)
+        return m.group(1) if m else name[:50]
+
+    share = collections.OrderedDict()
+    for e in evs:
+        d = e.time_range.end - e.time_range.start
+        share.setdefault(short(e.name), [0, 0.0])
+        share[short(e.name)][0] += 1
+        share[short(e.name)][1] += d
+    total = sum(d for _, d in share.values())
+    print(f"prefill timeline {T} tokens layers {L} page {a.page}: one step = {us:.1f} us (CUDA events), "
+          f"kernel durations add up to {total:.1f} us, {len(evs)} kernels and copies")
+    for n, (c, d) in sorted(share.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {d:8.1f} us  {c:4d} x {d / c:7.2f}  {n}")
 
 
 def fused_step(a) -> None:
@@ -315,6 +367,7 @@ def main() -> int:
     s.add_argument("--context", type=int, default=2048)
     s.add_argument("--layers", type=int, default=0, help="0: as many as the model has")
     s.add_argument("--page", type=int, default=PAGE)
+    s.add_argument("--prefill", type=int, default=0, help="instead: one prompt of this many tokens in one step")
     s = sub.add_parser("fused_step")
     s.add_argument("--batch", type=int, default=8)
     s.add_argument("--context", type=int, default=2048)
