@@ -340,13 +340,15 @@ def test_attention_decode_split_counts(ops, B, ctx, window):
 
 
 @pytest.mark.parametrize("H,KVH,D,page", [(12, 2, 128, 16), (14, 2, 64, 32), (16, 1, 128, 48), (9, 3, 64, 64), (7, 1, 128, 128)])
-@pytest.mark.parametrize("nsplit,stages", [(1, 2), (1, 6), (3, 3), (7, 8), (128, 6)])
+@pytest.mark.parametrize("nsplit,stages", [(1, 2), (1, 6), (3, 3), (7, 8), (20, 4), (40, 3), (128, 6)])
 @pytest.mark.parametrize("window", [None, 1, 130])
 def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, stages, window):
     """The TMA decode kernel with every way its ring of stages and its split count can fall: more
     tiles than stages (stages reused several times), more splits than tiles (blocks that leave at
     once), contexts that end on and around tile and page edges, a window whose low edge cuts a
-    tile, and a cache whose unwritten rows hold NaN."""
+    tile, and a cache whose unwritten rows hold NaN.  More than 16 splits with a tile each merge in two
+    levels (groups of 8, the last group smaller: 17 tiles are 8 + 8 + 1), and the launch is made twice:
+    every ticket counter is back at zero."""
     if stages * 2 * 64 * D * 2 > 220 * 1024:
         pytest.skip("more stages than shared memory holds at this head size")
     lens = [1, 63, 64, 65, 128, 129, 1000, 1024, 1025, 2500, 16, 17]
@@ -357,10 +359,11 @@ def test_attention_decode_tma_rings(ops, monkeypatch, H, KVH, D, page, nsplit, s
     try:
         for clusters in ((1, 0) if 2 <= nsplit <= 8 else (1,)):
             ops.lib.ts_set_clusters(clusters)
-            out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens), [l - 1 for l in lens],
-                                         17, window=window, poison=True)
-            assert torch.isfinite(out).all()
-            torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
+            for _ in range(2):
+                out, ref, _ = _run_attention(ops, torch.bfloat16, H, KVH, D, page, [1] * len(lens), [l - 1 for l in lens],
+                                             17, window=window, poison=True)
+                assert torch.isfinite(out).all()
+                torch.testing.assert_close(out, ref, **ATT_TOL[torch.bfloat16])
     finally:
         ops.lib.ts_set_clusters(1)
 

@@ -37,6 +37,8 @@ using namespace dec;
 constexpr int CWARPS = 4;            // consumer warps at most: min(4, stages) of them, then the producer warp
 constexpr int MAX_THREADS = (CWARPS + 1) * 32;
 constexpr int MAX_STAGES = 8;
+// The ticket's merge: up to MERGE_FLAT splits by one block; more in groups of MERGE_GROUP, then the groups.
+constexpr int MERGE_FLAT = 32, MERGE_GROUP = 8, MERGE_GROUPS_MAX = 16;
 
 __device__ int g_dec_status = 0;     // 0 = fine; otherwise the wait that ran out
 
@@ -318,52 +320,92 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const De
 
   // The block that finishes last for this (request, kv head) merges all splits, in split order:
   //   out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int ticket = atomicAdd(&a.counters[b * a.KVH + kvh], 1);
-    is_last = (ticket == eff - 1);
-    if (is_last) a.counters[b * a.KVH + kvh] = 0;                  // ready for the next launch
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  float* w_s = reinterpret_cast<float*>(smem);                     // [G][eff]
-  float* m_all = w_s + G * eff;                                    // [G][eff]
-  float* l_all = m_all + G * eff;                                  // [G][eff]
-  for (int idx = threadIdx.x; idx < G * eff; idx += THREADS) {
-    const int g = idx / eff, s2 = idx % eff;
-    const size_t pi = ((size_t)b * a.H + kvh * G + g) * a.nsplit + s2;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + pi * 2));
-    m_all[idx] = ml.x;
-    l_all[idx] = ml.y;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * eff; idx += THREADS) {
-    const int g = idx / eff;
-    float M = -INFINITY, L = 0.f;
-    for (int s2 = 0; s2 < eff; ++s2) M = fmaxf(M, m_all[g * eff + s2]);
-    if (M > -INFINITY)
-      for (int s2 = 0; s2 < eff; ++s2) L += l_all[g * eff + s2] * exp2f(m_all[g * eff + s2] - M);
-    w_s[idx] = (L > 0.f) ? exp2f(m_all[idx] - M) / L : 0.f;
-  }
-  __syncthreads();
-  // out[g, d..d+3] = sum_s w[g, s] * acc[g, s, d..d+3]: independent 16-byte loads, split order
-  for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {
-    const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
-    const int h = kvh * G + g;
-    const float* src = a.part_acc + (((size_t)b * a.H + h) * a.nsplit) * D + d;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int s2 = 0; s2 < eff; ++s2) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s2 * D));
-      const float w = w_s[g * eff + s2];
-      acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+  // More than 32 splits (one or two requests with a very long context) merge in two levels, or the one
+  // block that merges would fetch hundreds of kilobytes alone (128 splits: 22 us of a 53 us launch): the
+  // last block of every 8 neighbouring splits folds them into the first one's place (same form: sums
+  // against the group's maximum), the last of those blocks merges the groups.
+  float* w_s = reinterpret_cast<float*>(smem);                     // [G][count]
+  auto merge = [&](int first, int stride, int count, bool final) {
+    float* m_all = w_s + G * count;                                // [G][count]
+    float* l_all = m_all + G * count;                              // [G][count]
+    float* ML = l_all + G * count;                                 // [G][2]: what a fold leaves as (m, l)
+    for (int idx = threadIdx.x; idx < G * count; idx += THREADS) {
+      const int g = idx / count, s2 = idx % count;
+      const size_t pi = ((size_t)b * a.H + kvh * G + g) * a.nsplit + first + s2 * stride;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + pi * 2));
+      m_all[idx] = ml.x;
+      l_all[idx] = ml.y;
     }
-    bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)h * D + d;
-    *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x, acc.y);
-    *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * count; idx += THREADS) {
+      const int g = idx / count;
+      float M = -INFINITY, L = 0.f;
+      for (int s2 = 0; s2 < count; ++s2) M = fmaxf(M, m_all[g * count + s2]);
+      if (M > -INFINITY)
+        for (int s2 = 0; s2 < count; ++s2) L += l_all[g * count + s2] * exp2f(m_all[g * count + s2] - M);
+      if (final) {
+        w_s[idx] = (L > 0.f) ? exp2f(m_all[idx] - M) / L : 0.f;
+      } else {
+        w_s[idx] = (M > -INFINITY) ? exp2f(m_all[idx] - M) : 0.f;
+        if (idx % count == 0) {
+          ML[2 * g] = M;
+          ML[2 * g + 1] = L;
+        }
+      }
+    }
+    __syncthreads();
+    // sum_s w[g, s] * acc[g, s, d..d+3]: independent 16-byte loads, split order
+    for (int idx = threadIdx.x; idx < G * (D / 4); idx += THREADS) {
+      const int g = idx / (D / 4), d = (idx % (D / 4)) * 4;
+      const int h = kvh * G + g;
+      float* src = a.part_acc + (((size_t)b * a.H + h) * a.nsplit + first) * D + d;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int s2 = 0; s2 < count; ++s2) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s2 * stride * D));
+        const float w = w_s[g * count + s2];
+        acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+      }
+      if (final) {
+        bf16* op = a.out + (size_t)row_q * a.H * D + (size_t)h * D + d;
+        *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x, acc.y);
+        *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z, acc.w);
+      } else {
+        *reinterpret_cast<float4*>(src) = acc;                     // (this thread alone reads and writes this piece)
+        if (d == 0) {
+          const size_t pi = ((size_t)b * a.H + h) * a.nsplit + first;
+          *reinterpret_cast<float2*>(a.part_ml + pi * 2) = make_float2(ML[2 * g], ML[2 * g + 1]);
+        }
+      }
+    }
+  };
+  // true for the block that arrives last of `of` at `counter`, which it leaves at zero for the next launch
+  auto last_of = [&](int* counter, int of) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int ticket = atomicAdd(counter, 1);
+      is_last = (ticket == of - 1);
+      if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    const bool last = is_last;
+    __syncthreads();                                               // (is_last is written again at the second level)
+    if (last) __threadfence();
+    return last;
+  };
+  const int pair = b * a.KVH + kvh;
+  if (eff <= MERGE_FLAT) {
+    if (!last_of(&a.counters[pair], eff)) return;
+    merge(0, 1, eff, true);
+    return;
   }
+  const int group = split / MERGE_GROUP, first = group * MERGE_GROUP;
+  const int groups = (eff + MERGE_GROUP - 1) / MERGE_GROUP;
+  if (!last_of(&a.counters[(int)gridDim.z * a.KVH + pair * MERGE_GROUPS_MAX + group], min(MERGE_GROUP, eff - first))) return;
+  merge(first, 1, min(MERGE_GROUP, eff - first), false);
+  if (!last_of(&a.counters[pair], groups)) return;
+  merge(0, MERGE_GROUP, groups, true);
 }
 
 // K and V caches ([rows, D] bfloat16 each, `gap` bytes apart) as one tensor of
@@ -511,7 +553,8 @@ TS_API int ts_attention_decode_tma_blocks_per_sm(int D, int stages) {
 
 // One query token per request (rows q_start[b]).  `scratch` holds
 // ts_attention_decode_scratch_floats(B, H, D, nsplit) floats when nsplit > 1, and `counters`
-// B * KVH ints that are zero on entry (the kernel leaves them zero).  num_pages: pages in the pool
+// B * KVH ints, 17 times as many when nsplit > 16 (one per group of 8 splits besides), that are zero on
+// entry (the kernel leaves them zero).  num_pages: pages in the pool
 // (rows of the cache = num_pages * KVH * page).  window <= 0: none.  stages: 2..8 tiles of
 // 64 keys in flight per block.
 TS_API int ts_attention_decode_tma(void* out, void* scratch, int* counters, const void* qkv, const void* k_cache,

@@ -408,7 +408,9 @@ class CudaOps:
         if nsplit <= 1:
             return None, None
         scratch = self.scratch(self.lib.ts_attention_decode_scratch_floats(nd, H, D, nsplit), device)
-        return scratch, self._buffer("counters", nd * KVH, torch.int32, device, floor=1 << 16, zero=True)
+        # (one ticket counter per (request, kv head); the streaming kernel's two-level merge of more than 16
+        # splits takes 16 more for each)
+        return scratch, self._buffer("counters", nd * KVH * 17, torch.int32, device, floor=1 << 16, zero=True)
 
     def attention(self, out, qkv, k_cache, v_cache, block_tables, step, H, KVH, D, page_size, scale,
                   window) -> None:
