@@ -394,7 +394,7 @@ def test_attention_decode_blocks_of_eight_warps(ops, monkeypatch, B, H, KVH, pag
 
 
 @pytest.mark.parametrize("H,KVH,D,page", [(12, 2, 128, 16), (14, 2, 64, 32), (16, 1, 128, 64), (9, 3, 64, 64)])
-@pytest.mark.parametrize("nsplit", [1, 2, 3, 4, 8, 16, 24])
+@pytest.mark.parametrize("nsplit", [1, 2, 3, 4, 8, 16, 24, 40, 128])
 @pytest.mark.parametrize("window", [None, 1, 130])
 def test_attention_decode_merge_of_splits(ops, monkeypatch, H, KVH, D, page, nsplit, window):
     """The cp.async decode kernel's two ways of merging its key splits: 2, 4, 8 or 16 splits as one
