@@ -294,3 +294,16 @@ def test_padding_rows_of_captured_steps_count_against_the_budget(padded):
     assert out["long"] == expected_output(long_prompt, 5)
     for i in range(3):
         assert out[f"d{i}"][-1] == expected_output([i + 1, i + 2, i + 3], 40)[-1]
+
+
+def test_padding_rows_never_starve_a_prompt():
+    """5 decoding requests would be filled up to 8 rows: under a budget of 20 that would leave a prompt 12
+    tokens, fewer than any captured portion, so the padding is not charged and the prompt gets all 15."""
+    eng = make_fake_engine(num_pages=256, budget=20, max_seqs=8)
+    eng.scheduler.padded_decodes = lambda n: next((s for s in (1, 2, 4, 8) if s >= n), None)
+    for i in range(5):
+        eng.add_request(f"d{i}", [i + 1, i + 2], greedy(30))
+    eng.step()
+    eng.add_request("long", list(range(60)), greedy(2))
+    plan = eng.scheduler.schedule()
+    assert [p.num_tokens for p in plan.items] == [1, 1, 1, 1, 1, 15]

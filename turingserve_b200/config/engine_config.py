@@ -52,7 +52,9 @@ class EngineConfig:
         budget = self.max_num_batched_tokens
         if not self.cuda_graphs or budget > self.graph_portion_budget:
             return ()
-        return tuple(sorted({budget - s for s in (0, *self.graph_batch_sizes) if budget - s >= 16}))
+        from turingserve_b200.engine.scheduler import Scheduler
+        least = Scheduler.SMALLEST_CAPTURED_PORTION
+        return tuple(sorted({budget - s for s in (0, *self.graph_batch_sizes) if budget - s >= least}))
 
     def resolve_max_model_len(self, max_position_embeddings: int) -> int:
         if self.max_model_len is None:

@@ -76,6 +76,8 @@ class _Draft:
 
 
 class Scheduler:
+    SMALLEST_CAPTURED_PORTION = 16      # shorter prompt portions than this get no captured step shape
+
     def __init__(self, cache: CacheManager, max_num_batched_tokens: int, max_num_seqs: int,
                  watermark: float = 0.01, padded_decodes=None) -> None:
         """``padded_decodes``: n -> the number of rows the runner fills n decoding requests up to (None: it
@@ -142,8 +144,10 @@ class Scheduler:
         self._take_decodes(draft)
         if self.padded_decodes is not None and draft.decodes:
             rows = self.padded_decodes(len(draft.decodes))
-            if rows is not None:
-                draft.budget = max(0, draft.budget - (rows - len(draft.decodes)))
+            # (not where the padding would leave a prompt next to nothing: that step is launched kernel by
+            # kernel, with all of the budget)
+            if rows is not None and draft.budget - (rows - len(draft.decodes)) >= self.SMALLEST_CAPTURED_PORTION:
+                draft.budget -= rows - len(draft.decodes)
         self._take_running_prompts(draft)
         if not draft.evicted:
             self._admit(draft)
