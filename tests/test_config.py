@@ -127,3 +127,17 @@ def test_a_head_size_no_attention_kernel_takes_is_refused_when_the_model_is_buil
     with pytest.raises(ValueError, match="head sizes up to 256"):
         DecoderModel(cfg, torch.float32, "cpu", 16)
     DecoderModel(qwen2.parse_config({**BASE, "head_dim": 256}), torch.float32, "cpu", 16)
+
+
+def test_captured_portion_lengths_follow_the_token_budget():
+    """Token budgets up to `graph_portion_budget` capture steps of decoding requests beside one prompt
+    portion: the portion lengths are the budget less each captured batch size (and less none), down to 16
+    tokens; larger budgets, or no graphs, capture none."""
+    from turingserve_b200 import EngineConfig
+    c = EngineConfig(model="m", max_num_batched_tokens=512, graph_batch_sizes=(1, 2, 4, 8, 16, 32, 64, 128))
+    assert c.graph_portion_sizes() == (384, 448, 480, 496, 504, 508, 510, 511, 512)
+    assert EngineConfig(model="m", max_num_batched_tokens=40, graph_batch_sizes=(1, 8, 32)).graph_portion_sizes() == (32, 39, 40)
+    assert EngineConfig(model="m", max_num_batched_tokens=2048).graph_portion_sizes() == ()
+    assert EngineConfig(model="m", max_num_batched_tokens=2048, graph_portion_budget=4096).graph_portion_sizes()[-1] == 2048
+    assert EngineConfig(model="m", max_num_batched_tokens=512, cuda_graphs=False).graph_portion_sizes() == ()
+    assert EngineConfig(model="m", max_num_batched_tokens=512, graph_portion_budget=0).graph_portion_sizes() == ()
