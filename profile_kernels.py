@@ -6,7 +6,7 @@ launches), and the kernel-by-kernel timeline of one captured decode step.
     python profile_kernels.py decode_attention [--model qwen2.5-1.5b] [--batch 8] [--context 2048] [--page 16] [--graph]
     python profile_kernels.py prefill_attention [--tokens 2048] [--prefix 0] [--page 16] [--in-order]
     python profile_kernels.py timeline --prefill 2048
-    python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated|--resid] [--pair] [--graph]
+    python profile_kernels.py gemm [--tokens 8] [--n 17920] [--k 1536] [--mode auto|tc|library] [--gated|--resid] [--pair] [--qkv] [--graph]
     python profile_kernels.py timeline [--batch 8] [--context 2048] [--layers 0] [--page 16]
     python profile_kernels.py fused_step [--batch 8] [--context 2048] [--layers 4] [--page 16]
 
@@ -137,8 +137,26 @@ def gemm(a) -> None:
     act = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
     resid = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
 
+    if a.qkv:        # the q/k/v product of the model's heads with bias, rotation and cache write in its epilogue (pairs of SMs)
+        N = (H + 2 * KVH) * D
+        ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        bias = torch.randn(N, device="cuda", dtype=torch.bfloat16) * 0.1
+        freqs = torch.outer(torch.arange(M + 1).float(), 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D)))
+        cos, sin = freqs.cos().cuda().contiguous(), freqs.sin().cuda().contiguous()
+        pos = torch.arange(M, dtype=torch.int32, device="cuda")
+        slots = pos + PAGE
+        kc = torch.zeros((M // PAGE + 2, KVH, PAGE, D), device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+
     def f(i):
-        if a.pair:                                                # the many-row kernel on pairs of SMs, whatever the cost rule says
+        if a.qkv:
+            rc = ops.lib.ts_linear_pair_qkv(out.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), bias.data_ptr(), pos.data_ptr(),
+                                            cos.data_ptr(), sin.data_ptr(), slots.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                            M, H, KVH, D, PAGE, K, None)
+            if rc:
+                raise SystemExit(f"ts_linear_pair_qkv refused: {rc}")
+        elif a.pair:                                              # the many-row kernel on pairs of SMs, whatever the cost rule says
             if not ops.linear_pair(act if a.gated else out, x, ws[i % copies], None, ops.PAIR_GATED if a.gated else ops.PAIR_PLAIN):
                 raise SystemExit("the pair kernel does not take this shape")
         elif a.gated:                                             # block-interleaved gate/up rows, SiLU*mul in the epilogue
@@ -360,6 +378,7 @@ def main() -> int:
     s.add_argument("--mode", default="auto", choices=["auto", "tc", "library"])
     s.add_argument("--gated", action="store_true", help="gate/up product with the activation in its epilogue")
     s.add_argument("--pair", action="store_true", help="the many-row kernel whose tiles are computed by two SMs together")
+    s.add_argument("--qkv", action="store_true", help="that kernel as the q/k/v product of the model's heads: bias, rotation, cache write (--n is ignored)")
     s.add_argument("--resid", action="store_true", help="the product that sums its splits on chip and adds itself to residual rows")
     s.add_argument("--graph", action="store_true", help="time the launches inside one CUDA graph")
     s = sub.add_parser("timeline")
